@@ -1,0 +1,192 @@
+/*
+ * Inner kernel launch ABI of the B200 matmul engine.
+ *
+ * Every device kernel of the library is reached through one extern "C"
+ * launcher that takes a plain parameter block (pointers, sizes, strides,
+ * quantisation modes, the post-op chain) and a CUDA stream.  The host library
+ * lowers a matmul primitive descriptor + its runtime arguments into this block;
+ * the launchers can equally be bound directly over FFI (ctypes, cgo, JNI) by a
+ * caller that already holds device pointers.
+ *
+ * The block describes what the reference library's matmul implementations read
+ * from their execution context: src/weights/bias/dst memories with their
+ * memory descriptors, DNNL_ARG_ATTR_SCALES | arg and DNNL_ARG_ATTR_ZERO_POINTS
+ * | arg memories, and the post-op list of the primitive attribute
+ * (reference: src/cpu/matmul/ref_matmul_int8.cpp:38-152,
+ *  src/cpu/matmul/ref_matmul.cpp:38-128, src/common/primitive_attr.hpp:274-521).
+ *
+ * All launchers return 0 on success, a negative B200_ERR_* code when the
+ * parameter block is not supported by that kernel (nothing was launched), or a
+ * positive cudaError_t value when the launch itself failed.  Launches are
+ * asynchronous on the given stream; pointers are device pointers unless a
+ * comment says otherwise.
+ */
+#ifndef ONEDNN_B200_KERNELS_H
+#define ONEDNN_B200_KERNELS_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* opaque stream handle: a cudaStream_t */
+typedef void *b200_stream_t;
+
+/* data type codes = numeric values of dnnl_data_type_t
+ * (reference: include/oneapi/dnnl/dnnl_common_types.h:78-110) */
+enum {
+    B200_DT_UNDEF = 0, B200_DT_F16 = 1, B200_DT_BF16 = 2, B200_DT_F32 = 3,
+    B200_DT_S32 = 4, B200_DT_S8 = 5, B200_DT_U8 = 6, B200_DT_F8_E5M2 = 9,
+    B200_DT_F8_E4M3 = 10, B200_DT_S4 = 11, B200_DT_U4 = 12
+};
+
+enum {
+    B200_ERR_UNSUPPORTED = -1, /* this kernel cannot run this block */
+    B200_ERR_BAD_ARG = -2,     /* null pointer / negative size / misalignment */
+    B200_ERR_TOO_LARGE = -3    /* a size exceeds a fixed-capacity resource */
+};
+
+enum { B200_PO_SUM = 1, B200_PO_ELTWISE = 2, B200_PO_BINARY = 3, B200_PO_PRELU = 4 };
+
+/* A scale or zero-point argument.  Element for logical index (i0, i1) is
+ * ptr[(i0 / g0) * s0 + (i1 / g1) * s1] with (i0, i1) = (m, k) for src,
+ * (k, n) for weights and (m, n) for dst arguments; a stride of 0 broadcasts.
+ * This is the offset rule of the reference's get_quant_off
+ * (src/cpu/matmul/matmul_utils.hpp:156-196).  ptr == NULL: argument not set. */
+typedef struct {
+    const void *ptr;
+    int32_t dt;
+    int32_t reserved;
+    int64_t s0, s1;
+    int64_t g0, g1;
+} b200_quant_t;
+
+/* One post-op (reference: dnnl_post_ops::entry_t, primitive_attr.hpp:274-420;
+ * applied in list order by ref_post_ops_t::execute,
+ * src/cpu/primitive_attr_postops.cpp:278-347). */
+typedef struct {
+    int32_t kind;       /* B200_PO_* */
+    int32_t alg;        /* dnnl_alg_kind_t value (eltwise_* / binary_*) */
+    float alpha, beta;  /* eltwise parameters */
+    float scale;        /* eltwise scale, or sum scale */
+    int32_t zero_point; /* sum zero-point */
+    int32_t dt;         /* sum: type the old dst is read as; binary: src1 type */
+    int32_t reserved;
+    const void *ptr;    /* binary src1, or prelu weights (f32) */
+    int64_t sm, sn;     /* element strides of ptr over (m, n); 0 = broadcast */
+} b200_postop_t;
+
+#define B200_MAX_POSTOPS 32
+
+/* packed weights layouts produced by b200_pack_weights */
+enum {
+    B200_WEI_PLAIN = 0,      /* strided (k, n) as given by wei_sk / wei_sn */
+    B200_WEI_KMAJOR = 1,     /* 8-bit weights transposed to [N][Kp] (K contiguous,
+                                Kp = K rounded up to 16) followed by the s32 column
+                                sums: the tcgen05 operand layout */
+    B200_WEI_WC4_TILED = 2   /* 4-bit weights re-tiled for the decode GEMV */
+};
+
+typedef struct {
+    int64_t M, N, K;
+    const void *src; int32_t src_dt; int32_t reserved0; int64_t src_sm, src_sk;
+    const void *wei; int32_t wei_dt; int32_t wei_layout; int64_t wei_sk, wei_sn;
+    const void *bias; int32_t bias_dt; int32_t reserved1; int64_t bias_sm, bias_sn;
+    void *dst; int32_t dst_dt; int32_t reserved2; int64_t dst_sm, dst_sn;
+    b200_quant_t src_scale, wei_scale, dst_scale;
+    b200_quant_t src_zp, wei_zp, dst_zp;
+    /* s32 column sums of the weights, sum_k w[k][n], length N (int8 path with a
+     * source zero-point; produced by b200_pack_weights or b200_colsum) */
+    const int32_t *wei_colsum;
+    int32_t apply_to_int; /* fpmath apply_to_int: integer weights are decompressed */
+    int32_t npo;
+    b200_postop_t po[B200_MAX_POSTOPS];
+    /* device status word (may be NULL): kernels OR a non-zero code into it when
+     * a bounded wait ran out; the stream's wait() reports it */
+    uint32_t *status;
+    /* scratch for kernels that need it (split-K partials); sized by
+     * b200_matmul_scratch_bytes */
+    void *scratch; size_t scratch_bytes;
+} b200_matmul_params_t;
+
+/* ---- matmul kernels ----------------------------------------------------- */
+
+/* Generic kernel: any dtype combination of the reference's ref_int8 / ref
+ * implementations, any strides, any quantisation mode, any post-op chain.
+ * One thread per dst element.  (ref_matmul_int8.cpp:154-261, ref_matmul.cpp:130-233) */
+int b200_matmul_generic_launch(const b200_matmul_params_t *p, b200_stream_t stream);
+
+/* Dense 8-bit GEMM on the 5th-generation tensor cores (tcgen05.mma kind::i8 for
+ * u8/s8 x s8, kind::f8f6f4 for e4m3 x e4m3; TMA-fed, mbarrier-pipelined, TMEM
+ * accumulators) with the whole epilogue fused.  Needs row-major src (src_sk == 1),
+ * weights in B200_WEI_KMAJOR layout, row-major dst, K % 16 == 0, per-tensor or
+ * per-N scales, a per-tensor source zero-point at most.  Replaces the
+ * reference's brgemm_matmul_t execute (src/cpu/x64/matmul/brgemm_matmul.cpp:383-496)
+ * for these shapes. */
+int b200_matmul_tc8_launch(const b200_matmul_params_t *p, b200_stream_t stream);
+
+/* Weight-compressed decode GEMV / skinny GEMM: bf16 (or f16/f32) activations
+ * times u4/s4/s8/u8 weights with K-grouped scales and zero-points, f32
+ * accumulation, M <= 16 rows per pass; HBM-bound.  (ref_matmul.cpp:130-233 with
+ * with_wei_decompression; brgemm_matmul_copy_utils.cpp:2861-2880 is the
+ * reference's JIT decompression.) */
+int b200_matmul_wc_launch(const b200_matmul_params_t *p, b200_stream_t stream);
+
+/* bytes of scratch the given block needs for the given kernel
+ * (0 = generic, 1 = tc8, 2 = wc) */
+size_t b200_matmul_scratch_bytes(const b200_matmul_params_t *p, int kernel);
+
+/* ---- weights reorder / pack kernels -------------------------------------- */
+
+typedef struct {
+    int64_t K, N;
+    const void *src; int32_t src_dt; int32_t src_layout; int64_t src_sk, src_sn;
+    void *dst; int32_t dst_dt; int32_t dst_layout; int64_t dst_sk, dst_sn;
+    /* optional quantising reorder: dst = sat_rne(src * scale[n] ... ) is not part
+     * of this ABI yet; scale pointers must be NULL */
+    const void *scale; int32_t scale_dt; int32_t scale_mask;
+} b200_reorder_params_t;
+
+/* bytes a packed weights buffer occupies (data + column sums) */
+size_t b200_packed_weights_bytes(int64_t K, int64_t N, int32_t dt, int32_t layout);
+/* byte offset of the s32 column sums inside a B200_WEI_KMAJOR buffer */
+size_t b200_packed_colsum_offset(int64_t K, int64_t N, int32_t dt);
+
+/* plain (strided) -> plain or packed, same element type or a plain conversion
+ * between f32 / bf16 / f16 / s32 / s8 / u8 (saturate + round-to-nearest-even
+ * for integer destinations, as the reference's simple_reorder does).
+ * Replaces dnnl_reorder for the weights of this path
+ * (src/common/reorder.cpp:63-220, src/cpu/reorder/simple_reorder.hpp). */
+int b200_reorder_launch(const b200_reorder_params_t *p, b200_stream_t stream);
+
+/* s32 column sums of plain 8-bit weights: out[n] = sum_k w[k][n]
+ * (the zero-point compensation the reference computes at reorder time,
+ * src/cpu/x64/matmul/brgemm_matmul.cpp:1184-1200) */
+int b200_colsum_launch(const void *wei, int32_t wei_dt, int64_t K, int64_t N, int64_t sk, int64_t sn,
+        int32_t *out, b200_stream_t stream);
+
+/* ---- utilities ----------------------------------------------------------- */
+
+/* Counter-based fill used by tests and the benchmark: element i of the buffer
+ * is a pure function of (seed, i), identical on host and device.
+ * dist: 0 = integers uniform in [lo, hi]; 1 = floats uniform in [lo, hi);
+ *       2 = round(normal(0, hi)) clipped to the type range (integer types) or
+ *           normal(lo, hi) (float types); 3 = e4m3(clip(hi * normal(0,1), +-448)) */
+int b200_fill_launch(void *ptr, int32_t dt, int64_t nelems, uint64_t seed, int32_t dist, float lo, float hi,
+        b200_stream_t stream);
+/* the same function evaluated on the host into a host buffer */
+int b200_fill_host(void *ptr, int32_t dt, int64_t nelems, uint64_t seed, int32_t dist, float lo, float hi);
+
+/* 64-bit order-independent checksum of a device buffer (sum of a mix of
+ * (index, byte)); result written to *out (device pointer, 8 bytes) */
+int b200_checksum_launch(const void *ptr, size_t bytes, uint64_t *out, b200_stream_t stream);
+
+/* number of kernel launches issued by this library since load (for benchmarks) */
+uint64_t b200_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,188 @@
+"""Catalogue of small seeded matmul problems shared by the parity tests.
+
+Each entry is a zero-argument constructor of a MatmulCase.  The sizes are small
+enough for the scalar CPU oracle to finish in well under a second; together
+they cover the attribute space of the quantized matmul path: the five
+benchmark configurations at reduced size, zero-points and scales in every mask
+the reference admits, K-grouped quantisation, every post-op kind, ragged and
+degenerate shapes, transposed weights and every destination type.
+"""
+import numpy as np
+
+from onednn_b200 import dtypes as dt
+from onednn_b200 import workloads as W
+from onednn_b200.workloads import MatmulCase, Quant
+
+
+def _f32(x):
+    return np.asarray(x, dtype=np.float32)
+
+
+def _int8_base(M, N, K, seed, src_dt=dt.S8, dst_dt=dt.F32):
+    r = np.random.default_rng(seed)
+    if src_dt == dt.U8:
+        src = r.integers(0, 256, (M, K), dtype=np.uint8)
+    else:
+        src = r.integers(-128, 128, (M, K), dtype=np.int8)
+    return r, MatmulCase("int8", M, N, K, src=src, src_dt=src_dt,
+                         wei=r.integers(-127, 128, (K, N), dtype=np.int8), wei_dt=dt.S8, dst_dt=dst_dt,
+                         exact=dst_dt in (dt.S8, dt.U8, dt.S32), rtol=1e-5, atol=1e-5)
+
+
+def int8_plain_s32():
+    r, c = _int8_base(33, 50, 70, 1, dst_dt=dt.S32)
+    return c
+
+
+def int8_ragged_tiny():
+    r, c = _int8_base(1, 2, 1, 2, dst_dt=dt.S32)
+    return c
+
+
+def int8_u8dst_binary_prelu():
+    r, c = _int8_base(48, 40, 96, 3, src_dt=dt.U8, dst_dt=dt.U8)
+    c.src_scale = Quant(_f32([0.01]), dt.F32, 0)
+    c.wei_scale = Quant(_f32(r.uniform(1e-3, 1e-2, 40)), dt.F32, 2)
+    c.src_zp = Quant(np.array([100], dtype=np.int32), dt.S32, 0)
+    c.dst_scale = Quant(_f32([0.05]), dt.F32, 0)
+    c.dst_zp = Quant(np.array([128], dtype=np.int32), dt.S32, 0)
+    c.post_ops = [W.binary("add", _f32(r.uniform(-1, 1, (1, 40))), dt.F32, (1, 40)),
+                  W.prelu(r.uniform(0.1, 0.5, (1, 40)), (1, 40)),
+                  W.binary("mul", dt.f32_to_bf16(_f32(r.uniform(0.5, 1.5, (48, 1)))), dt.BF16, (48, 1)),
+                  W.binary("max", _f32(r.uniform(-1, 1, (48, 40))), dt.F32, (48, 40))]
+    return c
+
+
+def int8_wei_zp_common():
+    r, c = _int8_base(16, 24, 64, 4, dst_dt=dt.S8)
+    c.src_scale = Quant(_f32([0.02]), dt.F32, 0)
+    c.wei_scale = Quant(_f32([0.004]), dt.F32, 0)
+    c.src_zp = Quant(np.array([-3], dtype=np.int32), dt.S32, 0)
+    c.wei_zp = Quant(np.array([5], dtype=np.int32), dt.S32, 0)
+    c.dst_scale = Quant(_f32([0.25]), dt.F32, 0)
+    return c
+
+
+def int8_sum_u8_as_s8():
+    """sum post-op that reads the u8 dst as s8 with its own zero-point, then clip."""
+    r, c = _int8_base(20, 32, 48, 5, dst_dt=dt.U8)
+    c.dst_init = r.integers(0, 256, (20, 32), dtype=np.uint8)
+    c.src_scale = Quant(_f32([0.003]), dt.F32, 0)
+    c.post_ops = [W.sum_(0.75, 2, dt.S8), W.eltwise("clip_v2", -5.0, 200.0), W.eltwise("linear", 1.5, 0.25)]
+    return c
+
+
+def int8_bf16_dst_transposed_wei():
+    r, c = _int8_base(24, 36, 80, 6, dst_dt=dt.BF16)
+    c.wei = np.ascontiguousarray(c.wei.T)  # stored (N, K): tag "ba"
+    c.wei_tag = "ba"
+    c.wei_scale = Quant(_f32(r.uniform(1e-3, 1e-2, 36)), dt.F32, 2)
+    c.bias = dt.f32_to_bf16(_f32(r.uniform(-1, 1, (1, 36))))
+    c.bias_dt = dt.BF16
+    c.exact, c.rtol, c.atol = False, 1e-2, 1e-2
+    return c
+
+
+def _elt_case(name, alpha=0.0, beta=0.0, seed=7):
+    def make():
+        r, c = _int8_base(16, 64, 32, seed)
+        c.src_scale = Quant(_f32([0.01]), dt.F32, 0)
+        c.wei_scale = Quant(_f32(r.uniform(1e-3, 5e-3, 64)), dt.F32, 2)
+        c.post_ops = [W.eltwise(name, alpha, beta)]
+        return c
+    return make
+
+
+def _wc_case(M, N, K, group, wei_dt, src_dt=dt.BF16, zp="grouped", seed=11, dst_dt=dt.BF16):
+    def make():
+        r = np.random.default_rng(seed)
+        x = _f32(r.normal(0, 1, (M, K)))
+        ng = K // group
+        if wei_dt == dt.U4:
+            wei = dt.pack_int4(r.integers(0, 16, (K, N)))
+        elif wei_dt == dt.S4:
+            wei = dt.pack_int4(r.integers(-8, 8, (K, N)))
+        elif wei_dt == dt.S8:
+            wei = r.integers(-128, 128, (K, N), dtype=np.int8)
+        else:
+            wei = r.integers(0, 256, (K, N), dtype=np.uint8)
+        c = MatmulCase("wc", M, N, K, src=dt.from_f32(x, src_dt), src_dt=src_dt, wei=wei, wei_dt=wei_dt,
+                       dst_dt=dst_dt, apply_to_int=True, exact=False, rtol=1e-2, atol=1e-2)
+        sc = _f32(r.uniform(0.005, 0.02, (ng, N)))
+        c.wei_scale = Quant(dt.f32_to_bf16(sc), dt.BF16, 3, (group, 1)) if ng > 1 else \
+            Quant(dt.f32_to_bf16(sc.reshape(-1)), dt.BF16, 2)
+        if zp == "grouped":
+            if wei_dt in (dt.U4, dt.S4):
+                lo, hi = (6, 10) if wei_dt == dt.U4 else (-2, 3)
+                c.wei_zp = Quant(dt.pack_int4(r.integers(lo, hi, (ng, N))), wei_dt, 3, (group, 1))
+            else:
+                c.wei_zp = Quant(r.integers(-4, 5, (ng, N)).astype(np.int8), dt.S8, 3, (group, 1))
+        elif zp == "common":
+            c.wei_zp = Quant(np.array([3], dtype=np.int32), dt.S32, 0)
+        return c
+    return make
+
+
+def fp8_f8dst():
+    c = W.config3(24, 40, 64, seed=21)
+    c.dst_dt = dt.F8_E4M3
+    c.src_scale = Quant(_f32([0.05]), dt.F32, 0)
+    c.exact, c.rtol, c.atol = False, 0.07, 0.02
+    return c
+
+
+def fp8_swish_f32():
+    c = W.config3(17, 33, 48, seed=22)
+    c.dst_dt = dt.F32
+    c.post_ops = [W.eltwise("swish", 1.0)]
+    c.rtol, c.atol = 1e-4, 1e-4
+    return c
+
+
+CASES = {
+    # the benchmark's configurations at reduced size
+    "c0_small": lambda: W.config0(64, 96, 128),
+    "c0_full": lambda: W.config0(),
+    "c1_small": lambda: W.config1(96, 128, 256),
+    "c1_small_nonsat": lambda: W.config1(96, 128, 256, dst_scale=0.8),
+    "c1_mid_nonsat": lambda: W.config1(256, 384, 512, dst_scale=1.0),
+    "c2_m1": lambda: W.config2(1, 256, 512),
+    "c2_m16": lambda: W.config2(16, 128, 256),
+    "c3_small": lambda: W.config3(64, 96, 128),
+    "c4_small": lambda: W.config4(64, 128, 256),
+    # attribute space
+    "int8_plain_s32": int8_plain_s32,
+    "int8_ragged_tiny": int8_ragged_tiny,
+    "int8_u8dst_binary_prelu": int8_u8dst_binary_prelu,
+    "int8_wei_zp_common": int8_wei_zp_common,
+    "int8_sum_u8_as_s8": int8_sum_u8_as_s8,
+    "int8_bf16_dst_transposed_wei": int8_bf16_dst_transposed_wei,
+    "elt_tanh": _elt_case("tanh"),
+    "elt_logistic": _elt_case("logistic"),
+    "elt_swish": _elt_case("swish", 1.0),
+    "elt_gelu_erf": _elt_case("gelu_erf"),
+    "elt_exp": _elt_case("exp"),
+    "elt_elu": _elt_case("elu", 0.7),
+    "elt_mish": _elt_case("mish"),
+    "elt_hardswish": _elt_case("hardswish", 1.0 / 6, 0.5),
+    "elt_abs_sqrt": lambda: _two_elt(),
+    "wc_u4_g64_m3": _wc_case(3, 64, 256, 64, dt.U4),
+    "wc_s4_g32_m2_f32dst": _wc_case(2, 32, 128, 32, dt.S4, dst_dt=dt.F32),
+    "wc_s8_perN_common_zp": _wc_case(5, 48, 96, 96, dt.S8, zp="common"),
+    "wc_u8_g32_nozp": _wc_case(4, 40, 64, 32, dt.U8, zp="none"),
+    "fp8_f8dst": fp8_f8dst,
+    "fp8_swish_f32": fp8_swish_f32,
+}
+
+
+def _two_elt():
+    c = _elt_case("abs")()
+    c.post_ops.append(W.eltwise("sqrt"))
+    c.post_ops.append(W.eltwise("soft_relu", 0.5))
+    return c
+
+
+def build(name):
+    c = CASES[name]()
+    c.name = name
+    return c

@@ -1,0 +1,348 @@
+/*
+ * Public C API of the B200 matmul engine.
+ *
+ * This is the part of the oneDNN C API that a quantized-matmul program
+ * reaches: engine, stream, memory descriptor, memory, primitive attribute,
+ * post-ops, the matmul and reorder primitive descriptors, primitive creation
+ * and execution, and a few service calls.  Names, argument meaning, enum
+ * values and status codes are those of the reference's
+ * include/oneapi/dnnl/dnnl.h, dnnl_common.h, dnnl_types.h and
+ * dnnl_common_types.h, so a program compiled against those headers links
+ * against this library unchanged; each group below names the reference
+ * declaration it replaces.
+ *
+ * What differs is behind the boundary: dnnl_gpu engines are CUDA devices,
+ * streams are cudaStream_t, memory handles are device pointers, and
+ * execution launches hand-written sm_100a kernels (see
+ * onednn_b200_kernels.h).  There is no CPU engine and no CPU fallback:
+ * dnnl_engine_create(dnnl_cpu) returns dnnl_invalid_arguments and every
+ * compute call fails with dnnl_runtime_error when no CUDA device is usable.
+ */
+#ifndef ONEDNN_B200_H
+#define ONEDNN_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define DNNL_API __attribute__((visibility("default")))
+
+/* ---- common types (reference: dnnl_common_types.h:45-253) ------------------ */
+
+typedef enum {
+    dnnl_success = 0,
+    dnnl_out_of_memory = 1,
+    dnnl_invalid_arguments = 2,
+    dnnl_unimplemented = 3,
+    dnnl_last_impl_reached = 4,
+    dnnl_runtime_error = 5,
+    dnnl_not_required = 6,
+    dnnl_invalid_graph = 7
+} dnnl_status_t;
+
+typedef enum {
+    dnnl_data_type_undef = 0,
+    dnnl_f16 = 1, dnnl_bf16 = 2, dnnl_f32 = 3, dnnl_s32 = 4, dnnl_s8 = 5, dnnl_u8 = 6,
+    dnnl_f64 = 7, dnnl_boolean = 8, dnnl_f8_e5m2 = 9, dnnl_f8_e4m3 = 10, dnnl_s4 = 11, dnnl_u4 = 12,
+    dnnl_e8m0 = 13, dnnl_f4_e2m1 = 14, dnnl_f4_e3m0 = 15,
+    dnnl_data_type_max = 0x7fff
+} dnnl_data_type_t;
+
+#define DNNL_MAX_NDIMS 12
+#define DNNL_RUNTIME_DIM_VAL INT64_MIN
+typedef int64_t dnnl_dim_t;
+typedef dnnl_dim_t dnnl_dims_t[DNNL_MAX_NDIMS];
+
+typedef enum { dnnl_any_engine = 0, dnnl_cpu = 1, dnnl_gpu = 2 } dnnl_engine_kind_t;
+
+typedef enum {
+    dnnl_stream_in_order = 0x1U,
+    dnnl_stream_out_of_order = 0x2U,
+    dnnl_stream_default_flags = dnnl_stream_in_order,
+    dnnl_stream_profiling = 0x4U
+} dnnl_stream_flags_t;
+
+typedef enum {
+    dnnl_fpmath_mode_strict = 0, dnnl_fpmath_mode_bf16 = 1, dnnl_fpmath_mode_f16 = 2,
+    dnnl_fpmath_mode_any = 3, dnnl_fpmath_mode_tf32 = 4
+} dnnl_fpmath_mode_t;
+
+typedef enum {
+    dnnl_accumulation_mode_strict = 0, dnnl_accumulation_mode_relaxed = 1, dnnl_accumulation_mode_any = 2,
+    dnnl_accumulation_mode_s32 = 3, dnnl_accumulation_mode_f32 = 4, dnnl_accumulation_mode_f16 = 5
+} dnnl_accumulation_mode_t;
+
+typedef enum { dnnl_rounding_mode_environment = 0, dnnl_rounding_mode_stochastic = 1 } dnnl_rounding_mode_t;
+
+typedef struct {
+    int major, minor, patch;
+    const char *hash;
+    unsigned cpu_runtime, gpu_runtime;
+} dnnl_version_t;
+
+#define DNNL_MEMORY_NONE (NULL)
+#define DNNL_MEMORY_ALLOCATE ((void *)(size_t)-1)
+
+/* ---- types of the primitive API (reference: dnnl_types.h) ------------------- */
+
+typedef enum {
+    dnnl_format_kind_undef = 0, dnnl_format_kind_any = 1, dnnl_blocked = 2, dnnl_format_kind_opaque = 3
+} dnnl_format_kind_t;
+
+/* The plain tags this engine understands; values as in dnnl_types.h:80-140. */
+typedef enum {
+    dnnl_format_tag_undef = 0, dnnl_format_tag_any = 1,
+    dnnl_a = 2, dnnl_ab = 3, dnnl_abc = 4, dnnl_abcd = 5, dnnl_abcde = 6,
+    dnnl_ba = 14, dnnl_acb = 15, dnnl_bac = 16, dnnl_abdc = 20
+} dnnl_format_tag_t;
+
+typedef enum {
+    dnnl_undefined_primitive = 0, dnnl_reorder = 1, dnnl_sum = 4, dnnl_eltwise = 7,
+    dnnl_inner_product = 10, dnnl_binary = 13, dnnl_matmul = 14, dnnl_prelu = 18
+} dnnl_primitive_kind_t;
+
+typedef enum { dnnl_prop_kind_undef = 0, dnnl_forward_training = 64, dnnl_forward_inference = 96 } dnnl_prop_kind_t;
+
+/* eltwise and binary algorithm kinds, values as in dnnl_types.h:2043-2172 */
+typedef enum {
+    dnnl_alg_kind_undef = 0,
+    dnnl_eltwise_relu = 0x20, dnnl_eltwise_tanh, dnnl_eltwise_elu, dnnl_eltwise_square, dnnl_eltwise_abs,
+    dnnl_eltwise_sqrt, dnnl_eltwise_linear, dnnl_eltwise_soft_relu, dnnl_eltwise_hardsigmoid,
+    dnnl_eltwise_logistic, dnnl_eltwise_exp, dnnl_eltwise_gelu_tanh, dnnl_eltwise_swish, dnnl_eltwise_log,
+    dnnl_eltwise_clip, dnnl_eltwise_clip_v2, dnnl_eltwise_pow, dnnl_eltwise_gelu_erf, dnnl_eltwise_round,
+    dnnl_eltwise_mish, dnnl_eltwise_hardswish,
+    dnnl_eltwise_relu_use_dst_for_bwd = 0x100, dnnl_eltwise_tanh_use_dst_for_bwd, dnnl_eltwise_elu_use_dst_for_bwd,
+    dnnl_eltwise_sqrt_use_dst_for_bwd, dnnl_eltwise_logistic_use_dst_for_bwd, dnnl_eltwise_exp_use_dst_for_bwd,
+    dnnl_eltwise_clip_v2_use_dst_for_bwd,
+    dnnl_binary_add = 0x1fff0, dnnl_binary_mul = 0x1fff1, dnnl_binary_max = 0x1fff2, dnnl_binary_min = 0x1fff3,
+    dnnl_binary_div = 0x1fff4, dnnl_binary_sub = 0x1fff5, dnnl_binary_ge = 0x1fff6, dnnl_binary_gt = 0x1fff7,
+    dnnl_binary_le = 0x1fff8, dnnl_binary_lt = 0x1fff9, dnnl_binary_eq = 0x1fffa, dnnl_binary_ne = 0x1fffb,
+    dnnl_binary_select = 0x1fffc
+} dnnl_alg_kind_t;
+
+typedef enum { dnnl_scratchpad_mode_library = 0, dnnl_scratchpad_mode_user = 1 } dnnl_scratchpad_mode_t;
+
+typedef enum {
+    dnnl_query_undef = 0,
+    dnnl_query_engine = 1, dnnl_query_primitive_kind = 2, dnnl_query_num_of_inputs_s32 = 3,
+    dnnl_query_num_of_outputs_s32 = 4, dnnl_query_time_estimate_f64 = 5, dnnl_query_memory_consumption_s64 = 6,
+    dnnl_query_scratchpad_engine = 7, dnnl_query_impl_info_str = 8, dnnl_query_reorder_src_engine = 9,
+    dnnl_query_reorder_dst_engine = 10, dnnl_query_prop_kind = 11, dnnl_query_strides = 14,
+    dnnl_query_some_md = 128, dnnl_query_src_md = 129, dnnl_query_diff_src_md = 130, dnnl_query_weights_md = 131,
+    dnnl_query_diff_weights_md = 132, dnnl_query_dst_md = 133, dnnl_query_diff_dst_md = 134,
+    dnnl_query_workspace_md = 135, dnnl_query_scratchpad_md = 136, dnnl_query_exec_arg_md = 255,
+    dnnl_query_ndims_s32 = 256, dnnl_query_dims = 257, dnnl_query_data_type = 258,
+    dnnl_query_submemory_offset_s64 = 259, dnnl_query_padded_dims = 260, dnnl_query_padded_offsets = 261,
+    dnnl_query_format_kind = 262, dnnl_query_inner_nblks_s32 = 263, dnnl_query_inner_blks = 264,
+    dnnl_query_inner_idxs = 265
+} dnnl_query_t;
+
+typedef enum { dnnl_profiling_data_kind_undef = 0, dnnl_profiling_data_kind_time = 1 } dnnl_profiling_data_kind_t;
+
+/* execution argument indices (dnnl_types.h:2471-2700) */
+#define DNNL_ARG_SRC_0 1
+#define DNNL_ARG_SRC DNNL_ARG_SRC_0
+#define DNNL_ARG_FROM DNNL_ARG_SRC_0
+#define DNNL_ARG_SRC_1 2
+#define DNNL_ARG_DST_0 17
+#define DNNL_ARG_DST DNNL_ARG_DST_0
+#define DNNL_ARG_TO DNNL_ARG_DST_0
+#define DNNL_ARG_WEIGHTS_0 33
+#define DNNL_ARG_WEIGHTS DNNL_ARG_WEIGHTS_0
+#define DNNL_ARG_BIAS 41
+#define DNNL_ARG_SCRATCHPAD 80
+#define DNNL_ARG_ATTR_SCALES 4096
+#define DNNL_ARG_ATTR_ZERO_POINTS 8192
+#define DNNL_ARG_ATTR_MULTIPLE_POST_OP_BASE 32768
+#define DNNL_ARG_ATTR_MULTIPLE_POST_OP(idx) (DNNL_ARG_ATTR_MULTIPLE_POST_OP_BASE * ((idx) + 1))
+
+/* opaque handles */
+struct dnnl_engine;
+typedef struct dnnl_engine *dnnl_engine_t;
+struct dnnl_stream;
+typedef struct dnnl_stream *dnnl_stream_t;
+typedef const struct dnnl_stream *const_dnnl_stream_t;
+struct dnnl_memory_desc;
+typedef struct dnnl_memory_desc *dnnl_memory_desc_t;
+typedef const struct dnnl_memory_desc *const_dnnl_memory_desc_t;
+struct dnnl_memory;
+typedef struct dnnl_memory *dnnl_memory_t;
+typedef const struct dnnl_memory *const_dnnl_memory_t;
+struct dnnl_primitive_attr;
+typedef struct dnnl_primitive_attr *dnnl_primitive_attr_t;
+typedef const struct dnnl_primitive_attr *const_dnnl_primitive_attr_t;
+struct dnnl_post_ops;
+typedef struct dnnl_post_ops *dnnl_post_ops_t;
+typedef const struct dnnl_post_ops *const_dnnl_post_ops_t;
+struct dnnl_primitive_desc;
+typedef struct dnnl_primitive_desc *dnnl_primitive_desc_t;
+typedef const struct dnnl_primitive_desc *const_dnnl_primitive_desc_t;
+struct dnnl_primitive;
+typedef struct dnnl_primitive *dnnl_primitive_t;
+typedef const struct dnnl_primitive *const_dnnl_primitive_t;
+
+typedef struct {
+    int arg;
+    dnnl_memory_t memory;
+} dnnl_exec_arg_t;
+
+/* ---- engine and stream (replaces dnnl_common.h:44-110; reference
+ *      implementation src/common/engine.cpp:82-121, src/common/stream.cpp:42-88).
+ *      A dnnl_gpu engine is CUDA device `index`; a stream owns one cudaStream_t. */
+size_t DNNL_API dnnl_engine_get_count(dnnl_engine_kind_t kind);
+dnnl_status_t DNNL_API dnnl_engine_create(dnnl_engine_t *engine, dnnl_engine_kind_t kind, size_t index);
+dnnl_status_t DNNL_API dnnl_engine_get_kind(dnnl_engine_t engine, dnnl_engine_kind_t *kind);
+dnnl_status_t DNNL_API dnnl_engine_destroy(dnnl_engine_t engine);
+dnnl_status_t DNNL_API dnnl_stream_create(dnnl_stream_t *stream, dnnl_engine_t engine, unsigned flags);
+dnnl_status_t DNNL_API dnnl_stream_get_engine(const_dnnl_stream_t stream, dnnl_engine_t *engine);
+/* blocks until everything enqueued has finished; returns dnnl_runtime_error if
+ * CUDA reported an error or a kernel flagged a bounded wait that ran out */
+dnnl_status_t DNNL_API dnnl_stream_wait(dnnl_stream_t stream);
+dnnl_status_t DNNL_API dnnl_stream_destroy(dnnl_stream_t stream);
+
+/* Interop with code that already owns CUDA objects (the counterpart of the
+ * reference's dnnl_sycl_interop_* / dnnl_ocl_interop_* calls,
+ * include/oneapi/dnnl/dnnl_ocl.h): wrap an existing cudaStream_t, read it back. */
+dnnl_status_t DNNL_API dnnl_cuda_interop_stream_create(dnnl_stream_t *stream, dnnl_engine_t engine, void *cuda_stream);
+dnnl_status_t DNNL_API dnnl_cuda_interop_stream_get(dnnl_stream_t stream, void **cuda_stream);
+dnnl_status_t DNNL_API dnnl_cuda_interop_engine_get_device(dnnl_engine_t engine, int *device);
+
+/* ---- memory descriptors (replaces dnnl.h:826-1200; reference implementation
+ *      src/common/memory_desc.cpp, memory_desc_wrapper.hpp) ----------------------- */
+dnnl_status_t DNNL_API dnnl_memory_desc_destroy(dnnl_memory_desc_t memory_desc);
+dnnl_status_t DNNL_API dnnl_memory_desc_clone(dnnl_memory_desc_t *memory_desc, const_dnnl_memory_desc_t existing);
+dnnl_status_t DNNL_API dnnl_memory_desc_create_with_strides(dnnl_memory_desc_t *memory_desc, int ndims,
+        const dnnl_dims_t dims, dnnl_data_type_t data_type, const dnnl_dims_t strides);
+dnnl_status_t DNNL_API dnnl_memory_desc_create_with_tag(dnnl_memory_desc_t *memory_desc, int ndims,
+        const dnnl_dims_t dims, dnnl_data_type_t data_type, dnnl_format_tag_t tag);
+dnnl_status_t DNNL_API dnnl_memory_desc_create_submemory(dnnl_memory_desc_t *memory_desc,
+        const_dnnl_memory_desc_t parent, const dnnl_dims_t dims, const dnnl_dims_t offsets);
+dnnl_status_t DNNL_API dnnl_memory_desc_reshape(dnnl_memory_desc_t *out, const_dnnl_memory_desc_t in, int ndims,
+        const dnnl_dims_t dims);
+dnnl_status_t DNNL_API dnnl_memory_desc_permute_axes(dnnl_memory_desc_t *out, const_dnnl_memory_desc_t in,
+        const int *permutation);
+dnnl_status_t DNNL_API dnnl_memory_desc_query(const_dnnl_memory_desc_t memory_desc, dnnl_query_t what, void *result);
+int DNNL_API dnnl_memory_desc_equal(const_dnnl_memory_desc_t lhs, const_dnnl_memory_desc_t rhs);
+size_t DNNL_API dnnl_memory_desc_get_size(const_dnnl_memory_desc_t memory_desc);
+size_t DNNL_API dnnl_data_type_size(dnnl_data_type_t data_type);
+
+/* ---- memory objects (replaces dnnl.h:1205-1400; src/common/memory.cpp:139-307).
+ *      handle: a device pointer owned by the caller, DNNL_MEMORY_ALLOCATE for
+ *      a cudaMalloc'ed buffer owned by the library, or DNNL_MEMORY_NONE.
+ *      map_data copies the buffer to pinned host memory and returns that;
+ *      unmap_data copies it back to the device. */
+dnnl_status_t DNNL_API dnnl_memory_create(dnnl_memory_t *memory, const_dnnl_memory_desc_t memory_desc,
+        dnnl_engine_t engine, void *handle);
+dnnl_status_t DNNL_API dnnl_memory_get_memory_desc(const_dnnl_memory_t memory, const_dnnl_memory_desc_t *memory_desc);
+dnnl_status_t DNNL_API dnnl_memory_get_engine(const_dnnl_memory_t memory, dnnl_engine_t *engine);
+dnnl_status_t DNNL_API dnnl_memory_map_data(const_dnnl_memory_t memory, void **mapped_ptr);
+dnnl_status_t DNNL_API dnnl_memory_unmap_data(const_dnnl_memory_t memory, void *mapped_ptr);
+dnnl_status_t DNNL_API dnnl_memory_get_data_handle(const_dnnl_memory_t memory, void **handle);
+dnnl_status_t DNNL_API dnnl_memory_set_data_handle(dnnl_memory_t memory, void *handle);
+dnnl_status_t DNNL_API dnnl_memory_destroy(dnnl_memory_t memory);
+
+/* ---- primitive attributes and post-ops (replaces dnnl.h:244-800;
+ *      src/common/primitive_attr.cpp:408-804, primitive_attr_quant.hpp:45-324) ----- */
+dnnl_status_t DNNL_API dnnl_primitive_attr_create(dnnl_primitive_attr_t *attr);
+dnnl_status_t DNNL_API dnnl_primitive_attr_clone(dnnl_primitive_attr_t *attr, const_dnnl_primitive_attr_t existing);
+dnnl_status_t DNNL_API dnnl_primitive_attr_destroy(dnnl_primitive_attr_t attr);
+dnnl_status_t DNNL_API dnnl_primitive_attr_get_fpmath_mode(const_dnnl_primitive_attr_t attr, dnnl_fpmath_mode_t *mode);
+dnnl_status_t DNNL_API dnnl_primitive_attr_set_fpmath_mode(dnnl_primitive_attr_t attr, dnnl_fpmath_mode_t mode);
+dnnl_status_t DNNL_API dnnl_primitive_attr_get_fpmath_mode_v2(const_dnnl_primitive_attr_t attr,
+        dnnl_fpmath_mode_t *mode, int *apply_to_int);
+dnnl_status_t DNNL_API dnnl_primitive_attr_set_fpmath_mode_v2(dnnl_primitive_attr_t attr, dnnl_fpmath_mode_t mode,
+        int apply_to_int);
+dnnl_status_t DNNL_API dnnl_primitive_attr_get_deterministic(const_dnnl_primitive_attr_t attr, int *value);
+dnnl_status_t DNNL_API dnnl_primitive_attr_set_deterministic(dnnl_primitive_attr_t attr, int value);
+dnnl_status_t DNNL_API dnnl_primitive_attr_get_accumulation_mode(const_dnnl_primitive_attr_t attr,
+        dnnl_accumulation_mode_t *mode);
+dnnl_status_t DNNL_API dnnl_primitive_attr_set_accumulation_mode(dnnl_primitive_attr_t attr,
+        dnnl_accumulation_mode_t mode);
+dnnl_status_t DNNL_API dnnl_primitive_attr_get_scratchpad_mode(const_dnnl_primitive_attr_t attr,
+        dnnl_scratchpad_mode_t *mode);
+dnnl_status_t DNNL_API dnnl_primitive_attr_set_scratchpad_mode(dnnl_primitive_attr_t attr, dnnl_scratchpad_mode_t mode);
+dnnl_status_t DNNL_API dnnl_primitive_attr_set_scales_mask(dnnl_primitive_attr_t attr, int arg, int mask);
+dnnl_status_t DNNL_API dnnl_primitive_attr_set_scales(dnnl_primitive_attr_t attr, int arg, int mask, int ndims,
+        const dnnl_dims_t group_dims, dnnl_data_type_t data_type);
+dnnl_status_t DNNL_API dnnl_primitive_attr_set_zero_points_mask(dnnl_primitive_attr_t attr, int arg, int mask);
+dnnl_status_t DNNL_API dnnl_primitive_attr_set_zero_points(dnnl_primitive_attr_t attr, int arg, int mask, int ndims,
+        const dnnl_dims_t group_dims, dnnl_data_type_t data_type);
+dnnl_status_t DNNL_API dnnl_primitive_attr_set_rounding(dnnl_primitive_attr_t attr, int arg, dnnl_rounding_mode_t mode);
+dnnl_status_t DNNL_API dnnl_primitive_attr_get_rounding(dnnl_primitive_attr_t attr, int arg, dnnl_rounding_mode_t *mode);
+dnnl_status_t DNNL_API dnnl_primitive_attr_get_post_ops(const_dnnl_primitive_attr_t attr, const_dnnl_post_ops_t *post_ops);
+dnnl_status_t DNNL_API dnnl_primitive_attr_set_post_ops(dnnl_primitive_attr_t attr, const_dnnl_post_ops_t post_ops);
+
+dnnl_status_t DNNL_API dnnl_post_ops_create(dnnl_post_ops_t *post_ops);
+dnnl_status_t DNNL_API dnnl_post_ops_clone(dnnl_post_ops_t *post_ops, const_dnnl_post_ops_t existing);
+dnnl_status_t DNNL_API dnnl_post_ops_destroy(dnnl_post_ops_t post_ops);
+int DNNL_API dnnl_post_ops_len(const_dnnl_post_ops_t post_ops);
+dnnl_primitive_kind_t DNNL_API dnnl_post_ops_get_kind(const_dnnl_post_ops_t post_ops, int index);
+dnnl_status_t DNNL_API dnnl_post_ops_append_sum(dnnl_post_ops_t post_ops, float scale, int32_t zero_point,
+        dnnl_data_type_t data_type);
+dnnl_status_t DNNL_API dnnl_post_ops_get_params_sum(const_dnnl_post_ops_t post_ops, int index, float *scale,
+        int32_t *zero_point, dnnl_data_type_t *data_type);
+dnnl_status_t DNNL_API dnnl_post_ops_append_eltwise(dnnl_post_ops_t post_ops, dnnl_alg_kind_t alg_kind, float alpha,
+        float beta);
+dnnl_status_t DNNL_API dnnl_post_ops_get_params_eltwise(const_dnnl_post_ops_t post_ops, int index,
+        dnnl_alg_kind_t *alg_kind, float *alpha, float *beta);
+dnnl_status_t DNNL_API dnnl_post_ops_append_binary(dnnl_post_ops_t post_ops, dnnl_alg_kind_t alg_kind,
+        const_dnnl_memory_desc_t src1_desc);
+dnnl_status_t DNNL_API dnnl_post_ops_get_params_binary(const_dnnl_post_ops_t post_ops, int index,
+        dnnl_alg_kind_t *alg_kind, const_dnnl_memory_desc_t *src1_desc);
+dnnl_status_t DNNL_API dnnl_post_ops_append_prelu(dnnl_post_ops_t post_ops, int mask);
+dnnl_status_t DNNL_API dnnl_post_ops_get_params_prelu(const_dnnl_post_ops_t post_ops, int index, int *mask);
+
+/* ---- primitive descriptors and primitives (replaces dnnl.h:36-230, 1441, 3488;
+ *      src/common/matmul.cpp:40-432, src/common/reorder.cpp:63-220,
+ *      src/common/primitive_desc_iface.cpp, src/common/primitive_iface.cpp:147-217).
+ *      dnnl_matmul_primitive_desc_create validates like the reference's
+ *      matmul_desc_init / matmul_attr_check, then walks this engine's
+ *      implementation list: "cuda:sm100:tcgen05_i8", "cuda:sm100:tcgen05_f8",
+ *      "cuda:sm100:wc_gemv", "cuda:generic" -- dnnl_primitive_desc_next_impl
+ *      moves to the next one that accepts the problem. */
+dnnl_status_t DNNL_API dnnl_matmul_primitive_desc_create(dnnl_primitive_desc_t *primitive_desc, dnnl_engine_t engine,
+        const_dnnl_memory_desc_t src_desc, const_dnnl_memory_desc_t weights_desc, const_dnnl_memory_desc_t bias_desc,
+        const_dnnl_memory_desc_t dst_desc, const_dnnl_primitive_attr_t attr);
+dnnl_status_t DNNL_API dnnl_reorder_primitive_desc_create(dnnl_primitive_desc_t *reorder_primitive_desc,
+        const_dnnl_memory_desc_t src_desc, dnnl_engine_t src_engine, const_dnnl_memory_desc_t dst_desc,
+        dnnl_engine_t dst_engine, const_dnnl_primitive_attr_t attr);
+dnnl_status_t DNNL_API dnnl_primitive_desc_next_impl(dnnl_primitive_desc_t primitive_desc);
+dnnl_status_t DNNL_API dnnl_primitive_desc_clone(dnnl_primitive_desc_t *primitive_desc,
+        const_dnnl_primitive_desc_t existing);
+dnnl_status_t DNNL_API dnnl_primitive_desc_get_attr(const_dnnl_primitive_desc_t primitive_desc,
+        const_dnnl_primitive_attr_t *attr);
+dnnl_status_t DNNL_API dnnl_primitive_desc_destroy(dnnl_primitive_desc_t primitive_desc);
+dnnl_status_t DNNL_API dnnl_primitive_desc_query(const_dnnl_primitive_desc_t primitive_desc, dnnl_query_t what,
+        int index, void *result);
+const_dnnl_memory_desc_t DNNL_API dnnl_primitive_desc_query_md(const_dnnl_primitive_desc_t primitive_desc,
+        dnnl_query_t what, int index);
+int DNNL_API dnnl_primitive_desc_query_s32(const_dnnl_primitive_desc_t primitive_desc, dnnl_query_t what, int index);
+dnnl_status_t DNNL_API dnnl_primitive_create(dnnl_primitive_t *primitive, const_dnnl_primitive_desc_t primitive_desc);
+/* asynchronous on the stream; completion through dnnl_stream_wait */
+dnnl_status_t DNNL_API dnnl_primitive_execute(const_dnnl_primitive_t primitive, dnnl_stream_t stream, int nargs,
+        const dnnl_exec_arg_t *args);
+dnnl_status_t DNNL_API dnnl_primitive_get_primitive_desc(const_dnnl_primitive_t primitive,
+        const_dnnl_primitive_desc_t *primitive_desc);
+dnnl_status_t DNNL_API dnnl_primitive_destroy(dnnl_primitive_t primitive);
+
+/* ---- service (replaces dnnl_common.h:140-175, dnnl.h:3590-3640;
+ *      src/common/verbose.cpp, primitive_cache.cpp) ------------------------------- */
+dnnl_status_t DNNL_API dnnl_set_verbose(int level);
+const dnnl_version_t DNNL_API *dnnl_version(void);
+dnnl_status_t DNNL_API dnnl_get_primitive_cache_capacity(int *capacity);
+dnnl_status_t DNNL_API dnnl_set_primitive_cache_capacity(int capacity);
+dnnl_status_t DNNL_API dnnl_get_default_fpmath_mode(dnnl_fpmath_mode_t *mode);
+dnnl_status_t DNNL_API dnnl_set_default_fpmath_mode(dnnl_fpmath_mode_t mode);
+/* stream profiling (streams created with dnnl_stream_profiling): one
+ * cudaEvent pair per executed primitive; times in nanoseconds */
+dnnl_status_t DNNL_API dnnl_reset_profiling(dnnl_stream_t stream);
+dnnl_status_t DNNL_API dnnl_query_profiling_data(dnnl_stream_t stream, dnnl_profiling_data_kind_t data_kind,
+        int *num_entries, uint64_t *data);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -31,6 +31,8 @@
 extern "C" {
 #endif
 
+#define B200_API __attribute__((visibility("default")))
+
 /* opaque stream handle: a cudaStream_t */
 typedef void *b200_stream_t;
 
@@ -86,7 +88,9 @@ enum {
     B200_WEI_KMAJOR = 1,     /* 8-bit weights transposed to [N][Kp] (K contiguous,
                                 Kp = K rounded up to 16) followed by the s32 column
                                 sums: the tcgen05 operand layout */
-    B200_WEI_WC4_TILED = 2   /* 4-bit weights re-tiled for the decode GEMV */
+    B200_WEI_WC4_TILED = 2   /* 4-bit weights in tiles of 16 n x 64 k (512 bytes),
+                                nibbles ordered as mma.m16n8k16 A fragments; s4
+                                values stored offset by 8 */
 };
 
 typedef struct {
@@ -109,6 +113,9 @@ typedef struct {
     /* scratch for kernels that need it (split-K partials); sized by
      * b200_matmul_scratch_bytes */
     void *scratch; size_t scratch_bytes;
+    /* non-zero: the caller guarantees that the accumulation part of the scratch
+     * is all zero on entry (kernels that use it leave it zeroed on exit) */
+    int32_t scratch_zeroed; int32_t reserved3;
 } b200_matmul_params_t;
 
 /* ---- matmul kernels ----------------------------------------------------- */
@@ -116,7 +123,7 @@ typedef struct {
 /* Generic kernel: any dtype combination of the reference's ref_int8 / ref
  * implementations, any strides, any quantisation mode, any post-op chain.
  * One thread per dst element.  (ref_matmul_int8.cpp:154-261, ref_matmul.cpp:130-233) */
-int b200_matmul_generic_launch(const b200_matmul_params_t *p, b200_stream_t stream);
+B200_API int b200_matmul_generic_launch(const b200_matmul_params_t *p, b200_stream_t stream);
 
 /* Dense 8-bit GEMM on the 5th-generation tensor cores (tcgen05.mma kind::i8 for
  * u8/s8 x s8, kind::f8f6f4 for e4m3 x e4m3; TMA-fed, mbarrier-pipelined, TMEM
@@ -125,18 +132,23 @@ int b200_matmul_generic_launch(const b200_matmul_params_t *p, b200_stream_t stre
  * per-N scales, a per-tensor source zero-point at most.  Replaces the
  * reference's brgemm_matmul_t execute (src/cpu/x64/matmul/brgemm_matmul.cpp:383-496)
  * for these shapes. */
-int b200_matmul_tc8_launch(const b200_matmul_params_t *p, b200_stream_t stream);
+B200_API int b200_matmul_tc8_launch(const b200_matmul_params_t *p, b200_stream_t stream);
 
 /* Weight-compressed decode GEMV / skinny GEMM: bf16 (or f16/f32) activations
  * times u4/s4/s8/u8 weights with K-grouped scales and zero-points, f32
- * accumulation, M <= 16 rows per pass; HBM-bound.  (ref_matmul.cpp:130-233 with
+ * accumulation, 32 activation rows per pass; HBM-bound.  Weights in
+ * B200_WEI_WC4_TILED layout (or plain dense ab, packed into the scratch first).  (ref_matmul.cpp:130-233 with
  * with_wei_decompression; brgemm_matmul_copy_utils.cpp:2861-2880 is the
  * reference's JIT decompression.) */
-int b200_matmul_wc_launch(const b200_matmul_params_t *p, b200_stream_t stream);
+B200_API int b200_matmul_wc_launch(const b200_matmul_params_t *p, b200_stream_t stream);
+
+/* plain dense (K, N) 4-bit weights (two per byte along N) -> B200_WEI_WC4_TILED;
+ * needs K % 64 == 0 and N % 16 == 0 */
+B200_API int b200_wc_pack_launch(const void *src, void *dst, int64_t K, int64_t N, int32_t dt, b200_stream_t stream);
 
 /* bytes of scratch the given block needs for the given kernel
  * (0 = generic, 1 = tc8, 2 = wc) */
-size_t b200_matmul_scratch_bytes(const b200_matmul_params_t *p, int kernel);
+B200_API size_t b200_matmul_scratch_bytes(const b200_matmul_params_t *p, int kernel);
 
 /* ---- weights reorder / pack kernels -------------------------------------- */
 
@@ -150,41 +162,27 @@ typedef struct {
 } b200_reorder_params_t;
 
 /* bytes a packed weights buffer occupies (data + column sums) */
-size_t b200_packed_weights_bytes(int64_t K, int64_t N, int32_t dt, int32_t layout);
+B200_API size_t b200_packed_weights_bytes(int64_t K, int64_t N, int32_t dt, int32_t layout);
 /* byte offset of the s32 column sums inside a B200_WEI_KMAJOR buffer */
-size_t b200_packed_colsum_offset(int64_t K, int64_t N, int32_t dt);
+B200_API size_t b200_packed_colsum_offset(int64_t K, int64_t N, int32_t dt);
 
 /* plain (strided) -> plain or packed, same element type or a plain conversion
  * between f32 / bf16 / f16 / s32 / s8 / u8 (saturate + round-to-nearest-even
  * for integer destinations, as the reference's simple_reorder does).
  * Replaces dnnl_reorder for the weights of this path
  * (src/common/reorder.cpp:63-220, src/cpu/reorder/simple_reorder.hpp). */
-int b200_reorder_launch(const b200_reorder_params_t *p, b200_stream_t stream);
+B200_API int b200_reorder_launch(const b200_reorder_params_t *p, b200_stream_t stream);
 
 /* s32 column sums of plain 8-bit weights: out[n] = sum_k w[k][n]
  * (the zero-point compensation the reference computes at reorder time,
  * src/cpu/x64/matmul/brgemm_matmul.cpp:1184-1200) */
-int b200_colsum_launch(const void *wei, int32_t wei_dt, int64_t K, int64_t N, int64_t sk, int64_t sn,
+B200_API int b200_colsum_launch(const void *wei, int32_t wei_dt, int64_t K, int64_t N, int64_t sk, int64_t sn,
         int32_t *out, b200_stream_t stream);
 
 /* ---- utilities ----------------------------------------------------------- */
 
-/* Counter-based fill used by tests and the benchmark: element i of the buffer
- * is a pure function of (seed, i), identical on host and device.
- * dist: 0 = integers uniform in [lo, hi]; 1 = floats uniform in [lo, hi);
- *       2 = round(normal(0, hi)) clipped to the type range (integer types) or
- *           normal(lo, hi) (float types); 3 = e4m3(clip(hi * normal(0,1), +-448)) */
-int b200_fill_launch(void *ptr, int32_t dt, int64_t nelems, uint64_t seed, int32_t dist, float lo, float hi,
-        b200_stream_t stream);
-/* the same function evaluated on the host into a host buffer */
-int b200_fill_host(void *ptr, int32_t dt, int64_t nelems, uint64_t seed, int32_t dist, float lo, float hi);
-
-/* 64-bit order-independent checksum of a device buffer (sum of a mix of
- * (index, byte)); result written to *out (device pointer, 8 bytes) */
-int b200_checksum_launch(const void *ptr, size_t bytes, uint64_t *out, b200_stream_t stream);
-
 /* number of kernel launches issued by this library since load (for benchmarks) */
-uint64_t b200_launch_count(void);
+B200_API uint64_t b200_launch_count(void);
 
 #ifdef __cplusplus
 }

@@ -1,0 +1,212 @@
+// CUDA engine and stream: dnnl_gpu engine i is CUDA device i; a stream owns
+// (or wraps) one cudaStream_t plus a device status word that kernels flag when
+// a bounded wait runs out.  Replaces the reference's engine / stream factories
+// (src/common/engine.cpp:82-121, src/common/stream.cpp:42-88) and its
+// SYCL-based NVIDIA engine (src/gpu/nvidia/engine.cpp, stream.cpp).
+#include <cuda_runtime.h>
+
+#include <chrono>
+#include <cstdlib>
+
+#include "internal.hpp"
+
+namespace b200 {
+
+double now_ms() {
+    using namespace std::chrono;
+    return duration<double, std::milli>(steady_clock::now().time_since_epoch()).count();
+}
+
+dnnl_status_t set_device(const dnnl_engine *e) {
+    if (!e || !e->usable()) return dnnl_runtime_error;
+    return cudaSetDevice(e->device) == cudaSuccess ? dnnl_success : dnnl_runtime_error;
+}
+
+static int device_count() {
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return 0;
+    }
+    return n;
+}
+
+// Descriptor-only engines let validation and dispatch logic run on a machine
+// without a GPU (unit tests of the host library).  Nothing can be allocated or
+// executed on such an engine: every such call returns dnnl_runtime_error.
+static bool allow_no_device() {
+    const char *v = std::getenv("ONEDNN_B200_ALLOW_NO_DEVICE");
+    return v && v[0] == '1';
+}
+
+} // namespace b200
+
+using namespace b200;
+
+size_t dnnl_engine_get_count(dnnl_engine_kind_t kind) {
+    if (kind != dnnl_gpu) return 0;
+    return (size_t)device_count();
+}
+
+dnnl_status_t dnnl_engine_create(dnnl_engine_t *engine, dnnl_engine_kind_t kind, size_t index) {
+    if (!engine) return dnnl_invalid_arguments;
+    if (kind != dnnl_gpu) return dnnl_invalid_arguments; // there is no CPU engine and no CPU fallback
+    const int n = device_count();
+    if ((int)index >= n) {
+        if (n == 0 && index == 0 && allow_no_device()) {
+            dnnl_engine *e = new dnnl_engine();
+            e->device = -1;
+            *engine = e;
+            return dnnl_success;
+        }
+        return dnnl_invalid_arguments;
+    }
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, (int)index) != cudaSuccess) return dnnl_runtime_error;
+    // the kernels are sm_100a only
+    if (prop.major != 10) return dnnl_runtime_error;
+    dnnl_engine *e = new dnnl_engine();
+    e->device = (int)index;
+    e->sm_major = prop.major;
+    e->sm_minor = prop.minor;
+    e->sm_count = prop.multiProcessorCount;
+    *engine = e;
+    return dnnl_success;
+}
+
+dnnl_status_t dnnl_engine_get_kind(dnnl_engine_t engine, dnnl_engine_kind_t *kind) {
+    if (!engine || !kind) return dnnl_invalid_arguments;
+    *kind = engine->kind;
+    return dnnl_success;
+}
+
+dnnl_status_t dnnl_engine_destroy(dnnl_engine_t engine) {
+    if (!engine) return dnnl_invalid_arguments;
+    if (engine->refs.fetch_sub(1) == 1) delete engine;
+    return dnnl_success;
+}
+
+dnnl_status_t dnnl_cuda_interop_engine_get_device(dnnl_engine_t engine, int *device) {
+    if (!engine || !device) return dnnl_invalid_arguments;
+    *device = engine->device;
+    return dnnl_success;
+}
+
+static dnnl_status_t stream_make(dnnl_stream_t *stream, dnnl_engine_t engine, unsigned flags, void *wrap, bool do_wrap) {
+    if (!stream || !engine) return dnnl_invalid_arguments;
+    const unsigned known = dnnl_stream_in_order | dnnl_stream_out_of_order | dnnl_stream_profiling;
+    if ((flags & ~known) || !(flags & (dnnl_stream_in_order | dnnl_stream_out_of_order))) return dnnl_invalid_arguments;
+    if (set_device(engine) != dnnl_success) return dnnl_runtime_error;
+    dnnl_stream *s = new dnnl_stream();
+    s->engine = engine;
+    s->flags = flags;
+    if (do_wrap) {
+        s->cuda_stream = wrap;
+    } else {
+        cudaStream_t cs;
+        if (cudaStreamCreateWithFlags(&cs, cudaStreamNonBlocking) != cudaSuccess) {
+            delete s;
+            return dnnl_runtime_error;
+        }
+        s->cuda_stream = cs;
+        s->owns_stream = true;
+    }
+    if (cudaMalloc((void **)&s->status, sizeof(uint32_t)) != cudaSuccess
+            || cudaMemsetAsync(s->status, 0, sizeof(uint32_t), (cudaStream_t)s->cuda_stream) != cudaSuccess) {
+        if (s->owns_stream) cudaStreamDestroy((cudaStream_t)s->cuda_stream);
+        delete s;
+        return dnnl_out_of_memory;
+    }
+    engine->refs.fetch_add(1);
+    *stream = s;
+    return dnnl_success;
+}
+
+dnnl_status_t dnnl_stream_create(dnnl_stream_t *stream, dnnl_engine_t engine, unsigned flags) {
+    return stream_make(stream, engine, flags, nullptr, false);
+}
+
+dnnl_status_t dnnl_cuda_interop_stream_create(dnnl_stream_t *stream, dnnl_engine_t engine, void *cuda_stream) {
+    return stream_make(stream, engine, dnnl_stream_default_flags, cuda_stream, true);
+}
+
+dnnl_status_t dnnl_cuda_interop_stream_get(dnnl_stream_t stream, void **cuda_stream) {
+    if (!stream || !cuda_stream) return dnnl_invalid_arguments;
+    *cuda_stream = stream->cuda_stream;
+    return dnnl_success;
+}
+
+dnnl_status_t dnnl_stream_get_engine(const_dnnl_stream_t stream, dnnl_engine_t *engine) {
+    if (!stream || !engine) return dnnl_invalid_arguments;
+    *engine = stream->engine;
+    return dnnl_success;
+}
+
+dnnl_status_t dnnl_stream_wait(dnnl_stream_t stream) {
+    if (!stream) return dnnl_invalid_arguments;
+    if (set_device(stream->engine) != dnnl_success) return dnnl_runtime_error;
+    uint32_t st = 0;
+    cudaStream_t cs = (cudaStream_t)stream->cuda_stream;
+    if (cudaMemcpyAsync(&st, stream->status, sizeof(st), cudaMemcpyDeviceToHost, cs) != cudaSuccess)
+        return dnnl_runtime_error;
+    if (cudaStreamSynchronize(cs) != cudaSuccess) return dnnl_runtime_error;
+    if (st != 0) {
+        // a kernel gave up on a bounded wait: report once, then clear
+        cudaMemsetAsync(stream->status, 0, sizeof(uint32_t), cs);
+        return dnnl_runtime_error;
+    }
+    return dnnl_success;
+}
+
+dnnl_status_t dnnl_stream_destroy(dnnl_stream_t stream) {
+    if (!stream) return dnnl_invalid_arguments;
+    if (stream->engine->usable()) {
+        cudaSetDevice(stream->engine->device);
+        for (auto &ev : stream->prof_events) {
+            cudaEventDestroy((cudaEvent_t)ev.first);
+            cudaEventDestroy((cudaEvent_t)ev.second);
+        }
+        if (stream->owns_stream) {
+            cudaStreamSynchronize((cudaStream_t)stream->cuda_stream);
+            cudaStreamDestroy((cudaStream_t)stream->cuda_stream);
+        }
+        if (stream->status) cudaFree(stream->status);
+    }
+    dnnl_engine_destroy(stream->engine);
+    delete stream;
+    return dnnl_success;
+}
+
+dnnl_status_t dnnl_reset_profiling(dnnl_stream_t stream) {
+    if (!stream) return dnnl_invalid_arguments;
+    std::lock_guard<std::mutex> g(stream->mu);
+    for (auto &ev : stream->prof_events) {
+        cudaEventDestroy((cudaEvent_t)ev.first);
+        cudaEventDestroy((cudaEvent_t)ev.second);
+    }
+    stream->prof_events.clear();
+    return dnnl_success;
+}
+
+dnnl_status_t dnnl_query_profiling_data(dnnl_stream_t stream, dnnl_profiling_data_kind_t data_kind, int *num_entries,
+        uint64_t *data) {
+    if (!stream || !num_entries) return dnnl_invalid_arguments;
+    if (!(stream->flags & dnnl_stream_profiling)) return dnnl_invalid_arguments;
+    if (data_kind != dnnl_profiling_data_kind_time) return dnnl_invalid_arguments;
+    std::lock_guard<std::mutex> g(stream->mu);
+    if (!data) {
+        *num_entries = (int)stream->prof_events.size();
+        return dnnl_success;
+    }
+    const int n = *num_entries < (int)stream->prof_events.size() ? *num_entries : (int)stream->prof_events.size();
+    for (int i = 0; i < n; ++i) {
+        float ms = 0.f;
+        if (cudaEventElapsedTime(&ms, (cudaEvent_t)stream->prof_events[i].first,
+                    (cudaEvent_t)stream->prof_events[i].second)
+                != cudaSuccess)
+            return dnnl_runtime_error;
+        data[i] = (uint64_t)((double)ms * 1e6);
+    }
+    *num_entries = n;
+    return dnnl_success;
+}

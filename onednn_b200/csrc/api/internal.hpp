@@ -1,0 +1,216 @@
+// Internal object model of the host library: what stands behind the opaque
+// handles of onednn_b200.h.  The roles mirror the reference's common runtime
+// (src/common/engine.hpp:49-178, stream.hpp:29-94, memory.hpp:44-120,
+// memory_desc.hpp:262-345, primitive_attr.hpp:274-727, primitive_desc.hpp,
+// primitive.hpp:42-135) but the design is specific to this engine: one
+// descriptor type for plain strided tensors and for the packed weights
+// layouts of the sm_100a kernels, a flat attribute record that lowers directly
+// into the kernel parameter block, and an implementation list of four kernels.
+#pragma once
+
+#include <atomic>
+#include <cstdint>
+#include <cstring>
+#include <map>
+#include <memory>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "onednn_b200.h"
+#include "onednn_b200_kernels.h"
+
+namespace b200 {
+
+inline bool dt_valid(int dt) {
+    switch (dt) {
+        case dnnl_f16: case dnnl_bf16: case dnnl_f32: case dnnl_s32: case dnnl_s8: case dnnl_u8:
+        case dnnl_f8_e5m2: case dnnl_f8_e4m3: case dnnl_s4: case dnnl_u4: return true;
+        default: return false;
+    }
+}
+inline int dt_nbits(int dt) {
+    switch (dt) {
+        case dnnl_f32: case dnnl_s32: return 32;
+        case dnnl_f16: case dnnl_bf16: return 16;
+        case dnnl_s8: case dnnl_u8: case dnnl_f8_e5m2: case dnnl_f8_e4m3: case dnnl_boolean: case dnnl_e8m0: return 8;
+        case dnnl_s4: case dnnl_u4: case dnnl_f4_e2m1: case dnnl_f4_e3m0: return 4;
+        case dnnl_f64: return 64;
+        default: return 0;
+    }
+}
+inline bool dt_is_int8(int dt) { return dt == dnnl_s8 || dt == dnnl_u8; }
+inline bool dt_is_int4(int dt) { return dt == dnnl_s4 || dt == dnnl_u4; }
+inline bool dt_is_fp8(int dt) { return dt == dnnl_f8_e4m3 || dt == dnnl_f8_e5m2; }
+const char *dt_name(int dt);
+
+} // namespace b200
+
+// A memory descriptor: logical dims + data type + one of
+//   any     : layout to be chosen by the primitive descriptor,
+//   blocked : plain strided layout (no inner blocks in this engine),
+//   opaque  : a packed weights layout of this engine (B200_WEI_*), addressed
+//             only by the kernels; `packed_layout` says which.
+struct dnnl_memory_desc {
+    int ndims = 0;
+    int64_t dims[DNNL_MAX_NDIMS] = {0};
+    int data_type = dnnl_data_type_undef;
+    int format_kind = dnnl_format_kind_undef;
+    int64_t strides[DNNL_MAX_NDIMS] = {0};
+    int64_t offset0 = 0;
+    int packed_layout = B200_WEI_PLAIN;
+
+    int64_t nelems() const {
+        if (ndims == 0) return 0;
+        int64_t n = 1;
+        for (int i = 0; i < ndims; ++i) n *= dims[i];
+        return n;
+    }
+    bool has_zero_dim() const { return ndims > 0 && nelems() == 0; }
+    bool has_runtime_dims() const {
+        for (int i = 0; i < ndims; ++i)
+            if (dims[i] == DNNL_RUNTIME_DIM_VAL) return true;
+        return false;
+    }
+    bool is_plain() const { return format_kind == dnnl_blocked; }
+    bool is_any() const { return format_kind == dnnl_format_kind_any; }
+    bool is_zero() const { return ndims == 0; }
+    size_t size_bytes() const;
+    bool equal(const dnnl_memory_desc &o) const;
+    bool is_dense_row_major() const; // strides of tag a / ab / abc ...
+    std::string layout_str() const;  // "ab", "ba", "a:strided", "packed:kmajor", "any"
+};
+
+struct dnnl_engine {
+    dnnl_engine_kind_t kind = dnnl_gpu;
+    int device = -1; // CUDA ordinal; -1 = descriptor-only engine (no device present)
+    std::atomic<int> refs {1};
+    int sm_major = 0, sm_minor = 0, sm_count = 0;
+    bool usable() const { return device >= 0; }
+};
+
+struct dnnl_stream {
+    dnnl_engine *engine = nullptr;
+    void *cuda_stream = nullptr; // cudaStream_t
+    bool owns_stream = false;
+    unsigned flags = dnnl_stream_default_flags;
+    uint32_t *status = nullptr; // device word the kernels flag bounded-wait failures in
+    // profiling: one (start, stop) event pair per executed primitive
+    std::vector<std::pair<void *, void *>> prof_events;
+    std::mutex mu;
+};
+
+struct dnnl_memory {
+    dnnl_memory_desc md;
+    dnnl_engine *engine = nullptr;
+    void *handle = nullptr;
+    bool owned = false;
+    void *mapped = nullptr; // pinned host copy while mapped
+};
+
+namespace b200 {
+
+// one scales / zero-points entry of an attribute (reference: quant_entry_t,
+// src/common/primitive_attr_quant.hpp:45-140)
+struct quant_entry_t {
+    bool set = false;
+    int mask = 0;
+    int dt = dnnl_f32;
+    int group_ndims = 0;
+    int64_t groups[2] = {1, 1};
+    bool operator==(const quant_entry_t &o) const {
+        return set == o.set && mask == o.mask && dt == o.dt && groups[0] == o.groups[0] && groups[1] == o.groups[1];
+    }
+};
+
+struct post_op_t {
+    int kind = 0; // dnnl_sum / dnnl_eltwise / dnnl_binary / dnnl_prelu
+    int alg = 0;
+    float alpha = 0.f, beta = 0.f, scale = 1.f;
+    int32_t zero_point = 0;
+    int dt = dnnl_data_type_undef; // sum data type
+    dnnl_memory_desc src1;         // binary
+    int mask = 0;                  // prelu
+};
+
+} // namespace b200
+
+struct dnnl_post_ops {
+    std::vector<b200::post_op_t> entries;
+};
+
+struct dnnl_primitive_attr {
+    dnnl_fpmath_mode_t fpmath = dnnl_fpmath_mode_strict;
+    int apply_to_int = 0;
+    int deterministic = 0;
+    dnnl_accumulation_mode_t acc_mode = dnnl_accumulation_mode_strict;
+    dnnl_scratchpad_mode_t scratchpad_mode = dnnl_scratchpad_mode_library;
+    std::map<int, b200::quant_entry_t> scales, zero_points;
+    std::map<int, int> rounding;
+    dnnl_post_ops post_ops;
+
+    const b200::quant_entry_t &scale(int arg) const;
+    const b200::quant_entry_t &zp(int arg) const;
+    std::string str() const; // verbose representation
+};
+
+namespace b200 {
+
+// the matmul implementations of this engine, in dispatch order
+enum impl_id_t { IMPL_TC8 = 0, IMPL_WC = 1, IMPL_GENERIC = 2, IMPL_REORDER = 3, IMPL_COUNT };
+const char *impl_name(int id, const dnnl_primitive_desc *pd);
+
+} // namespace b200
+
+struct dnnl_primitive_desc {
+    dnnl_primitive_kind_t kind = dnnl_undefined_primitive;
+    dnnl_engine *engine = nullptr;
+    dnnl_primitive_attr attr;
+    // descriptors as the user gave them (weights may be `any`) ...
+    dnnl_memory_desc user_src, user_wei, user_bias, user_dst;
+    // ... and as resolved by the selected implementation
+    dnnl_memory_desc src, wei, bias, dst;
+    dnnl_memory_desc scratchpad; // 1-D u8
+    dnnl_memory_desc zero_md;
+    int impl = -1;
+    std::string impl_str;
+    // scratch md returned for DNNL_ARG_ATTR_* queries
+    mutable std::map<int, dnnl_memory_desc> arg_mds;
+
+    int64_t M() const { return dst.dims[dst.ndims - 2]; }
+    int64_t N() const { return dst.dims[dst.ndims - 1]; }
+    int64_t K() const { return src.dims[src.ndims - 1]; }
+};
+
+struct dnnl_primitive {
+    std::shared_ptr<dnnl_primitive_desc> pd;
+    void *lib_scratch = nullptr; // library-mode scratchpad (device)
+    size_t lib_scratch_bytes = 0;
+    ~dnnl_primitive();
+};
+
+namespace b200 {
+
+// ---- validation + dispatch (matmul_pd.cpp) ----
+dnnl_status_t matmul_validate(const dnnl_memory_desc &src, const dnnl_memory_desc &wei, const dnnl_memory_desc *bias,
+        const dnnl_memory_desc &dst, const dnnl_primitive_attr &attr);
+// tries implementations starting at `first`; fills pd->impl and resolved mds
+dnnl_status_t matmul_select_impl(dnnl_primitive_desc *pd, int first);
+dnnl_status_t matmul_execute(const dnnl_primitive *prim, dnnl_stream *stream, const std::map<int, dnnl_memory *> &args);
+dnnl_status_t reorder_execute(const dnnl_primitive *prim, dnnl_stream *stream, const std::map<int, dnnl_memory *> &args);
+
+// ---- verbose (service.cpp) ----
+int verbose_level();
+void verbose_exec(const dnnl_primitive *prim, double ms);
+void verbose_create(const dnnl_primitive_desc *pd, double ms, bool cache_hit);
+void verbose_dispatch(const char *impl, const char *why);
+std::string md_verbose(const char *tag, const dnnl_memory_desc &md);
+
+// ---- CUDA helpers (engine.cpp) ----
+dnnl_status_t set_device(const dnnl_engine *e);
+double now_ms();
+
+// default attribute entries
+extern const quant_entry_t default_quant_entry;
+
+} // namespace b200

@@ -1,0 +1,601 @@
+// The matmul primitive descriptor: validation, implementation dispatch, and the
+// lowering of (descriptor, attribute, runtime arguments) into the kernel
+// parameter block.
+//
+// Validation restates the rules of the reference's matmul_desc_init and
+// matmul_attr_check (src/common/matmul.cpp:284-409 and :40-278) with the same
+// status codes: inconsistent descriptors are dnnl_invalid_arguments, valid but
+// unsupported attribute combinations are dnnl_unimplemented.  Dispatch walks
+// this engine's implementation list the way the reference's
+// primitive_desc_iterator_t walks an impl_list_item_t[]
+// (src/common/primitive_desc_iterator.hpp:67-94): the first implementation whose
+// init accepts the problem wins, dnnl_primitive_desc_next_impl resumes after it.
+#include <cuda_runtime.h>
+
+#include <cstdio>
+#include <cstdlib>
+
+#include "internal.hpp"
+
+namespace b200 {
+
+#define INVALID_IF(cond) \
+    do { \
+        if (cond) return dnnl_invalid_arguments; \
+    } while (0)
+#define UNIMPL_IF(cond) \
+    do { \
+        if (cond) return dnnl_unimplemented; \
+    } while (0)
+
+static bool one_of(int64_t v, int64_t a, int64_t b) { return v == a || v == b; }
+
+dnnl_status_t matmul_validate(const dnnl_memory_desc &src, const dnnl_memory_desc &wei, const dnnl_memory_desc *bias,
+        const dnnl_memory_desc &dst, const dnnl_primitive_attr &attr) {
+    const bool with_bias = bias && bias->ndims != 0;
+    const int ndims = dst.ndims;
+    INVALID_IF(ndims < 2 || ndims > DNNL_MAX_NDIMS);
+    INVALID_IF(src.ndims != ndims || wei.ndims != ndims);
+    INVALID_IF(with_bias && bias->ndims != ndims);
+    const int m_idx = ndims - 2, n_idx = ndims - 1;
+    INVALID_IF(dst.dims[m_idx] != src.dims[m_idx]);
+    INVALID_IF(dst.dims[n_idx] != wei.dims[n_idx]);
+    INVALID_IF(src.dims[n_idx] != wei.dims[m_idx]);
+    INVALID_IF(with_bias && !one_of(bias->dims[n_idx], 1, dst.dims[n_idx]));
+    INVALID_IF(with_bias && !one_of(bias->dims[m_idx], 1, dst.dims[m_idx]));
+    INVALID_IF(dt_is_int4(wei.data_type) && wei.dims[n_idx] % 2 != 0);
+    INVALID_IF(dt_is_int4(src.data_type) && src.dims[n_idx] % 2 != 0);
+    for (int d = 0; d < ndims - 2; ++d) {
+        const int64_t s = src.dims[d], w = wei.dims[d], o = dst.dims[d];
+        if (s == DNNL_RUNTIME_DIM_VAL || w == DNNL_RUNTIME_DIM_VAL || o == DNNL_RUNTIME_DIM_VAL) {
+            INVALID_IF(!(s == DNNL_RUNTIME_DIM_VAL && w == DNNL_RUNTIME_DIM_VAL && o == DNNL_RUNTIME_DIM_VAL));
+            continue;
+        }
+        INVALID_IF(!(s == w && w == o) && !(s == 1 || w == 1));
+        INVALID_IF(s == 1 && o != w);
+        INVALID_IF(w == 1 && o != s);
+        INVALID_IF(with_bias && !one_of(bias->dims[d], 1, o));
+    }
+    // accumulation type must exist for the (src, weights) pair (type_helpers.hpp:444-460)
+    const int sdt = src.data_type, wdt = wei.data_type, ddt = dst.data_type;
+    const bool src_int8 = dt_is_int8(sdt), src_fp8 = dt_is_fp8(sdt);
+    const bool wei_int = dt_is_int8(wdt) || dt_is_int4(wdt);
+    const bool src_fp = sdt == dnnl_f32 || sdt == dnnl_bf16 || sdt == dnnl_f16;
+    INVALID_IF(!dt_valid(sdt) || !dt_valid(wdt) || !dt_valid(ddt));
+    INVALID_IF(!(src_int8 || src_fp8 || src_fp));
+
+    // ---- attribute rules ----
+    const int src_qmask_M = 1 << (ndims - 2), src_qmask_K = 1 << (ndims - 1);
+    const int wei_qmask_K = 1 << (ndims - 2), wei_qmask_N = 1 << (ndims - 1);
+    const bool wei_fp8 = dt_is_fp8(wdt);
+    for (auto &kv : attr.zero_points)
+        if (kv.second.set) {
+            // zero-points need an int8 / fp8 source, or integer / fp8 weights
+            // (the latter is weights decompression)
+            UNIMPL_IF(!(src_int8 || src_fp8 || wei_int || wei_fp8));
+            UNIMPL_IF(kv.first != DNNL_ARG_SRC && kv.first != DNNL_ARG_WEIGHTS && kv.first != DNNL_ARG_DST);
+        }
+    for (auto &kv : attr.scales)
+        if (kv.second.set)
+            UNIMPL_IF(kv.first != DNNL_ARG_SRC && kv.first != DNNL_ARG_WEIGHTS && kv.first != DNNL_ARG_DST);
+
+    int64_t src_sc_gk = 1, wei_sc_gk = 1;
+    const quant_entry_t &ss = attr.scale(DNNL_ARG_SRC);
+    if (ss.set) {
+        UNIMPL_IF(!(ss.mask == 0 || ss.mask == src_qmask_K || ss.mask == src_qmask_M + src_qmask_K));
+        if (ss.group_ndims && (ss.mask & src_qmask_K)) src_sc_gk = ss.groups[1];
+        UNIMPL_IF(src_sc_gk > 1 && src_sc_gk % 32 != 0);
+    }
+    const quant_entry_t &ws = attr.scale(DNNL_ARG_WEIGHTS);
+    if (ws.set) {
+        int64_t gn = 1;
+        if (ws.group_ndims) {
+            if (ws.mask & wei_qmask_K) wei_sc_gk = ws.groups[0];
+            if (ws.mask & wei_qmask_N) gn = ws.groups[1];
+        }
+        UNIMPL_IF(gn > 1 && !attr.apply_to_int);
+        UNIMPL_IF(wei_sc_gk > 1 && wei_sc_gk % 32 != 0);
+        UNIMPL_IF(gn > 1 && gn % 32 != 0);
+        UNIMPL_IF(!wei_int && !wei_fp8 && ws.group_ndims && (wei_sc_gk > 1 || gn > 1));
+    }
+    const quant_entry_t &ds = attr.scale(DNNL_ARG_DST);
+    if (ds.set) {
+        const int dst_qmask_M = src_qmask_M, dst_qmask_N = wei_qmask_N;
+        UNIMPL_IF(!(ds.mask == 0 || ds.mask == dst_qmask_N || ds.mask == dst_qmask_M
+                || ds.mask == dst_qmask_N + dst_qmask_M));
+    }
+    if (src_sc_gk > 1) {
+        UNIMPL_IF(!(src_int8 || src_fp8));
+        UNIMPL_IF(wei_sc_gk > 1 && !(src_sc_gk % wei_sc_gk == 0 || wei_sc_gk % src_sc_gk == 0));
+    }
+
+    int64_t src_zp_gk = 1, wei_zp_gk = 1;
+    const quant_entry_t &sz = attr.zp(DNNL_ARG_SRC);
+    if (sz.set) {
+        UNIMPL_IF(!(sz.mask == 0 || sz.mask == src_qmask_K || sz.mask == src_qmask_M + src_qmask_K));
+        if (sz.group_ndims && (sz.mask & src_qmask_K)) src_zp_gk = sz.groups[1];
+        UNIMPL_IF(src_zp_gk > 1 && src_zp_gk % 32 != 0);
+    }
+    const quant_entry_t &wz = attr.zp(DNNL_ARG_WEIGHTS);
+    if (wz.set) {
+        int64_t gn = 1;
+        if (wz.group_ndims) {
+            if (wz.mask & wei_qmask_K) wei_zp_gk = wz.groups[0];
+            if (wz.mask & wei_qmask_N) gn = wz.groups[1];
+        }
+        UNIMPL_IF(gn > 1 && !attr.apply_to_int);
+        UNIMPL_IF(wei_zp_gk > 1 && wei_zp_gk % 32 != 0);
+        UNIMPL_IF(gn > 1 && gn % 32 != 0);
+        if (dt_is_int4(wz.dt)) {
+            UNIMPL_IF((wz.mask & wei_qmask_K) && wei.dims[m_idx] % 2 != 0);
+            UNIMPL_IF((wz.mask & wei_qmask_N) && wei.dims[n_idx] % 2 != 0);
+        }
+    }
+    const quant_entry_t &dz = attr.zp(DNNL_ARG_DST);
+    if (dz.set) UNIMPL_IF(!(dz.mask == 0 || (ndims == 2 && dz.mask == 2)));
+    if (src_zp_gk > 1) {
+        UNIMPL_IF(!src_int8);
+        UNIMPL_IF(wei_zp_gk > 1 && !(src_zp_gk % wei_zp_gk == 0 || wei_zp_gk % src_zp_gk == 0));
+    }
+
+    // post-ops: sum consistency (primitive_attr.cpp:289-329) and binary broadcast
+    bool seen_sum_dt = false;
+    int sum_dt = dnnl_data_type_undef;
+    for (auto &e : attr.post_ops.entries) {
+        if (e.kind == dnnl_sum) {
+            const int sdt_eff = e.dt == dnnl_data_type_undef ? ddt : e.dt;
+            UNIMPL_IF(dt_nbits(sdt_eff) != dt_nbits(ddt));
+            UNIMPL_IF(e.zero_point != 0 && !src_int8);
+            UNIMPL_IF(seen_sum_dt && sum_dt != e.dt);
+            seen_sum_dt = true;
+            sum_dt = e.dt;
+        } else if (e.kind == dnnl_binary) {
+            INVALID_IF(e.src1.ndims != ndims);
+            for (int d = 0; d < ndims; ++d) INVALID_IF(!one_of(e.src1.dims[d], 1, dst.dims[d]));
+        } else if (e.kind != dnnl_eltwise && e.kind != dnnl_prelu) {
+            return dnnl_unimplemented;
+        }
+    }
+    return dnnl_success;
+}
+
+// ---- implementation acceptance ---------------------------------------------------
+
+static void make_plain(dnnl_memory_desc &md, bool transposed = false) {
+    md.format_kind = dnnl_blocked;
+    md.packed_layout = B200_WEI_PLAIN;
+    int64_t s = 1;
+    if (transposed && md.ndims >= 2) {
+        const int a = md.ndims - 2, b = md.ndims - 1;
+        md.strides[a] = 1;
+        md.strides[b] = md.dims[a];
+        s = md.dims[a] * md.dims[b];
+        for (int i = md.ndims - 3; i >= 0; --i) {
+            md.strides[i] = s;
+            s *= md.dims[i] > 0 ? md.dims[i] : 1;
+        }
+        return;
+    }
+    for (int i = md.ndims - 1; i >= 0; --i) {
+        md.strides[i] = s;
+        s *= md.dims[i] > 0 ? md.dims[i] : 1;
+    }
+}
+
+static bool quant_simple(const quant_entry_t &q, int allowed_masks_bits) {
+    if (!q.set) return true;
+    if (q.mask & ~allowed_masks_bits) return false;
+    if (q.group_ndims && (q.groups[0] > 1 || q.groups[1] > 1)) return false;
+    return true;
+}
+
+static const char *reject(const char *impl, const char *why) {
+    verbose_dispatch(impl, why);
+    return why;
+}
+
+// dense 8-bit tensor-core GEMM
+static bool accept_tc8(dnnl_primitive_desc *pd) {
+    const char *name = "cuda:sm100:tcgen05";
+    const dnnl_memory_desc &src = pd->user_src, &wei = pd->user_wei, &dst = pd->user_dst;
+    const dnnl_primitive_attr &a = pd->attr;
+    if (src.ndims != 2) return reject(name, "only 2-D problems"), false;
+    const int sdt = src.data_type, wdt = wei.data_type;
+    const bool i8 = dt_is_int8(sdt) && dt_is_int8(wdt);
+    const bool f8 = dt_is_fp8(sdt) && dt_is_fp8(wdt);
+    if (!i8 && !f8) return reject(name, "needs 8-bit src and weights"), false;
+    const int64_t M = src.dims[0], K = src.dims[1], N = wei.dims[1];
+    if (M == 0 || N == 0 || K == 0) return reject(name, "zero dim"), false;
+    if (K % 16 != 0) return reject(name, "K must be a multiple of 16 (TMA row pitch)"), false;
+    if (src.is_plain() && !(src.strides[1] == 1 && src.strides[0] % 16 == 0 && src.offset0 % 16 == 0))
+        return reject(name, "src must be row-major with a 16-byte pitch"), false;
+    if (dst.is_plain() && dst.strides[1] != 1) return reject(name, "dst must be row-major"), false;
+    if (wei.format_kind == dnnl_format_kind_opaque) {
+        if (wei.packed_layout != B200_WEI_KMAJOR) return reject(name, "unknown packed weights layout"), false;
+    } else if (wei.is_plain()) {
+        const bool kmajor = wei.strides[0] == 1 && wei.strides[1] % 16 == 0 && wei.offset0 % 16 == 0;
+        const bool nmajor = wei.strides[1] == 1;
+        if (!kmajor && !nmajor) return reject(name, "weights strides not supported"), false;
+    }
+    if (!quant_simple(a.scale(DNNL_ARG_SRC), 0)) return reject(name, "src scales must be per-tensor"), false;
+    if (!quant_simple(a.scale(DNNL_ARG_WEIGHTS), 2)) return reject(name, "weights scales must be per-tensor or per-N"), false;
+    if (!quant_simple(a.scale(DNNL_ARG_DST), 0)) return reject(name, "dst scales must be per-tensor"), false;
+    if (!quant_simple(a.zp(DNNL_ARG_SRC), 0)) return reject(name, "src zero-point must be per-tensor"), false;
+    if (a.zp(DNNL_ARG_WEIGHTS).set) return reject(name, "weights zero-points not supported"), false;
+    if (!quant_simple(a.zp(DNNL_ARG_DST), 2)) return reject(name, "dst zero-point mask"), false;
+    if (f8 && (a.zp(DNNL_ARG_SRC).set)) return reject(name, "fp8 with src zero-point"), false;
+    // resolve layouts
+    pd->src = src;
+    if (src.is_any()) make_plain(pd->src);
+    pd->dst = dst;
+    if (dst.is_any()) make_plain(pd->dst);
+    pd->wei = wei;
+    if (wei.is_any()) {
+        pd->wei.format_kind = dnnl_format_kind_opaque;
+        pd->wei.packed_layout = B200_WEI_KMAJOR;
+    }
+    pd->impl_str = i8 ? "cuda:sm100:tcgen05_i8" : "cuda:sm100:tcgen05_f8";
+    return true;
+}
+
+// weight-compressed GEMV / skinny GEMM
+static bool accept_wc(dnnl_primitive_desc *pd) {
+    const char *name = "cuda:sm100:wc_gemv";
+    const dnnl_memory_desc &src = pd->user_src, &wei = pd->user_wei, &dst = pd->user_dst;
+    const dnnl_primitive_attr &a = pd->attr;
+    if (src.ndims != 2) return reject(name, "only 2-D problems"), false;
+    const int sdt = src.data_type, wdt = wei.data_type;
+    if (!(sdt == dnnl_bf16 || sdt == dnnl_f16 || sdt == dnnl_f32)) return reject(name, "src must be bf16/f16/f32"), false;
+    if (!dt_is_int4(wdt) || !a.apply_to_int) return reject(name, "needs 4-bit weights with fpmath apply_to_int"), false;
+    const int64_t M = src.dims[0], K = src.dims[1], N = wei.dims[1];
+    if (M == 0 || N == 0 || K == 0) return reject(name, "zero dim"), false;
+    if (M > 512) return reject(name, "M too large for the decode kernel"), false;
+    if (N % 16 != 0 || K % 64 != 0) return reject(name, "needs N % 16 == 0 and K % 64 == 0"), false;
+    if (src.is_plain() && src.strides[1] != 1) return reject(name, "src must be row-major"), false;
+    if (dst.is_plain() && dst.strides[1] != 1) return reject(name, "dst must be row-major"), false;
+    if (wei.is_plain() && !(wei.strides[1] == 1 && wei.strides[0] == N && wei.offset0 == 0))
+        return reject(name, "weights must be dense ab"), false;
+    if (wei.format_kind == dnnl_format_kind_opaque && wei.packed_layout != B200_WEI_WC4_TILED)
+        return reject(name, "unknown packed weights layout"), false;
+    if (!quant_simple(a.scale(DNNL_ARG_SRC), 0)) return reject(name, "src scales must be per-tensor"), false;
+    if (!quant_simple(a.scale(DNNL_ARG_DST), 0)) return reject(name, "dst scales must be per-tensor"), false;
+    int64_t gks[2] = {K, K};
+    int gi = 0;
+    for (const quant_entry_t *q : {&a.scale(DNNL_ARG_WEIGHTS), &a.zp(DNNL_ARG_WEIGHTS)}) {
+        const int i = gi++;
+        if (!q->set) continue;
+        if (q->group_ndims && (q->mask & 2) && q->groups[1] != 1) return reject(name, "groups along N not supported"), false;
+        const int64_t gk = (q->mask & 1) ? (q->group_ndims ? q->groups[0] : 1) : K;
+        if (gk % 16 != 0 || K % gk != 0) return reject(name, "K group must be a multiple of 16 that divides K"), false;
+        gks[i] = gk;
+    }
+    if (gks[0] % gks[1] != 0 && gks[1] % gks[0] != 0) return reject(name, "scale and zero-point groups must nest"), false;
+    if (a.zp(DNNL_ARG_SRC).set || a.zp(DNNL_ARG_DST).set) return reject(name, "src/dst zero-points"), false;
+    pd->src = src;
+    if (src.is_any()) make_plain(pd->src);
+    pd->dst = dst;
+    if (dst.is_any()) make_plain(pd->dst);
+    pd->wei = wei;
+    if (wei.is_any()) {
+        pd->wei.format_kind = dnnl_format_kind_opaque;
+        pd->wei.packed_layout = B200_WEI_WC4_TILED;
+    }
+    pd->impl_str = "cuda:sm100:wc_gemv";
+    return true;
+}
+
+static bool accept_generic(dnnl_primitive_desc *pd) {
+    const char *name = "cuda:generic";
+    if (pd->user_src.ndims != 2) return reject(name, "only 2-D problems"), false;
+    if (pd->user_wei.format_kind == dnnl_format_kind_opaque) return reject(name, "packed weights"), false;
+    const int sdt = pd->user_src.data_type, wdt = pd->user_wei.data_type;
+    const bool src_int8 = dt_is_int8(sdt);
+    const bool wei_int = dt_is_int8(wdt) || dt_is_int4(wdt);
+    // the (src, weights) type pairs of the reference's two scalar implementations
+    if (src_int8 && !wei_int) return reject(name, "int8 src needs integer weights"), false;
+    if (!src_int8 && wei_int && !pd->attr.apply_to_int && !dt_is_fp8(sdt))
+        return reject(name, "integer weights with a float src need fpmath apply_to_int"), false;
+    // group sizes must divide K / N
+    const int64_t K = pd->user_src.dims[1], N = pd->user_wei.dims[1];
+    for (int arg : {DNNL_ARG_SRC, DNNL_ARG_WEIGHTS}) {
+        for (const quant_entry_t *q : {&pd->attr.scale(arg), &pd->attr.zp(arg)}) {
+            if (!q->set || !q->group_ndims) continue;
+            const int64_t gk = arg == DNNL_ARG_SRC ? q->groups[1] : q->groups[0];
+            const int64_t gn = arg == DNNL_ARG_SRC ? 1 : q->groups[1];
+            if (gk <= 0 || gn <= 0 || K % gk != 0 || N % gn != 0) return reject(name, "group must divide the dim"), false;
+        }
+    }
+    if (!src_int8) {
+        if (pd->attr.zp(DNNL_ARG_SRC).set || pd->attr.zp(DNNL_ARG_DST).set)
+            return reject(name, "src/dst zero-points need an int8 src"), false;
+        if (pd->attr.scale(DNNL_ARG_SRC).set && pd->attr.scale(DNNL_ARG_SRC).mask != 0)
+            return reject(name, "src scale mask"), false;
+    }
+    if (pd->attr.scale(DNNL_ARG_DST).set && pd->attr.scale(DNNL_ARG_DST).mask != 0)
+        return reject(name, "dst scale mask"), false;
+    pd->src = pd->user_src;
+    if (pd->src.is_any()) make_plain(pd->src);
+    pd->wei = pd->user_wei;
+    if (pd->wei.is_any()) make_plain(pd->wei);
+    pd->dst = pd->user_dst;
+    if (pd->dst.is_any()) make_plain(pd->dst);
+    pd->impl_str = "cuda:generic";
+    return true;
+}
+
+static size_t scratch_bytes_for(const dnnl_primitive_desc *pd) {
+    size_t bytes = 0;
+    if (pd->impl == IMPL_TC8) {
+        const int64_t K = pd->K(), N = pd->N();
+        // plain N-major weights are transposed into the packed layout on every
+        // execution; plain K-major weights only need the column sums
+        if (pd->wei.is_plain() && pd->wei.strides[1] == 1 && pd->wei.strides[0] != 1)
+            bytes = b200_packed_weights_bytes(K, N, pd->wei.data_type, B200_WEI_KMAJOR);
+        else if (pd->wei.is_plain() && pd->attr.zp(DNNL_ARG_SRC).set)
+            bytes = (size_t)N * sizeof(int32_t);
+    }
+    if (pd->impl == IMPL_WC) {
+        b200_matmul_params_t q;
+        std::memset(&q, 0, sizeof(q));
+        q.M = pd->M();
+        q.N = pd->N();
+        q.K = pd->K();
+        q.src_dt = pd->src.data_type;
+        q.wei_layout = pd->wei.format_kind == dnnl_format_kind_opaque ? pd->wei.packed_layout : B200_WEI_PLAIN;
+        bytes = b200_matmul_scratch_bytes(&q, 2);
+    }
+    return (bytes + 255) / 256 * 256;
+}
+
+// debugging knob: ONEDNN_CUDA_DISABLE_IMPL=tc8,wc takes implementations out of the list
+static bool impl_disabled(int id) {
+    const char *v = std::getenv("ONEDNN_CUDA_DISABLE_IMPL");
+    if (!v) return false;
+    const std::string s(v);
+    return (id == IMPL_TC8 && s.find("tc8") != std::string::npos) || (id == IMPL_WC && s.find("wc") != std::string::npos);
+}
+
+dnnl_status_t matmul_select_impl(dnnl_primitive_desc *pd, int first) {
+    for (int id = first; id <= IMPL_GENERIC; ++id) {
+        bool ok = false;
+        if (impl_disabled(id)) continue;
+        switch (id) {
+            case IMPL_TC8: ok = accept_tc8(pd); break;
+            case IMPL_WC: ok = accept_wc(pd); break;
+            case IMPL_GENERIC: ok = accept_generic(pd); break;
+        }
+        if (!ok) continue;
+        pd->impl = id;
+        pd->bias = pd->user_bias;
+        if (pd->bias.ndims && pd->bias.is_any()) make_plain(pd->bias);
+        pd->scratchpad = dnnl_memory_desc();
+        const size_t sb = scratch_bytes_for(pd);
+        if (sb) {
+            pd->scratchpad.ndims = 1;
+            pd->scratchpad.dims[0] = (int64_t)sb;
+            pd->scratchpad.strides[0] = 1;
+            pd->scratchpad.data_type = dnnl_u8;
+            pd->scratchpad.format_kind = dnnl_blocked;
+        }
+        return dnnl_success;
+    }
+    return first == 0 ? dnnl_unimplemented : dnnl_last_impl_reached;
+}
+
+// ---- lowering + execution ---------------------------------------------------------
+
+static inline const void *base_ptr(const dnnl_memory *m) {
+    if (!m || !m->handle) return nullptr;
+    return (const char *)m->handle + m->md.offset0 * dt_nbits(m->md.data_type) / 8;
+}
+
+static void lower_quant(b200_quant_t &out, const quant_entry_t &q, const dnnl_memory *mem, int64_t d0, int64_t d1) {
+    out = b200_quant_t();
+    out.g0 = out.g1 = 1;
+    if (!q.set || !mem) return;
+    out.ptr = base_ptr(mem);
+    out.dt = mem->md.data_type;
+    const int64_t g0 = (q.mask & 1) ? (q.group_ndims ? q.groups[0] : 1) : 1;
+    const int64_t g1 = (q.mask & 2) ? (q.group_ndims ? q.groups[1] : 1) : 1;
+    const int64_t n1 = (q.mask & 2) ? d1 / g1 : 1;
+    out.s0 = (q.mask & 1) ? n1 : 0;
+    out.s1 = (q.mask & 2) ? 1 : 0;
+    out.g0 = g0;
+    out.g1 = g1;
+    (void)d0;
+}
+
+static void bcast_strides(const dnnl_memory_desc &md, int64_t &sm, int64_t &sn) {
+    sm = md.dims[0] > 1 ? md.strides[0] : 0;
+    sn = md.dims[1] > 1 ? md.strides[1] : 0;
+}
+
+dnnl_status_t matmul_execute(const dnnl_primitive *prim, dnnl_stream *stream, const std::map<int, dnnl_memory *> &args) {
+    const dnnl_primitive_desc *pd = prim->pd.get();
+    auto get = [&](int a) -> dnnl_memory * {
+        auto it = args.find(a);
+        return it == args.end() ? nullptr : it->second;
+    };
+    dnnl_memory *src = get(DNNL_ARG_SRC), *wei = get(DNNL_ARG_WEIGHTS), *dst = get(DNNL_ARG_DST), *bias = get(DNNL_ARG_BIAS);
+    if (!src || !wei || !dst) return dnnl_invalid_arguments;
+    if (pd->bias.ndims && !bias) return dnnl_invalid_arguments;
+    if (pd->src.has_zero_dim() || pd->wei.has_zero_dim() || pd->dst.has_zero_dim()) return dnnl_success;
+    if (!src->handle || !wei->handle || !dst->handle) return dnnl_invalid_arguments;
+
+    b200_matmul_params_t p;
+    std::memset(&p, 0, sizeof(p));
+    p.M = pd->M();
+    p.N = pd->N();
+    p.K = pd->K();
+    p.src = base_ptr(src);
+    p.src_dt = pd->src.data_type;
+    p.src_sm = pd->src.strides[0];
+    p.src_sk = pd->src.strides[1];
+    p.wei = base_ptr(wei);
+    p.wei_dt = pd->wei.data_type;
+    if (pd->wei.format_kind == dnnl_format_kind_opaque) {
+        p.wei_layout = pd->wei.packed_layout;
+    } else {
+        p.wei_layout = B200_WEI_PLAIN;
+        p.wei_sk = pd->wei.strides[0];
+        p.wei_sn = pd->wei.strides[1];
+    }
+    if (bias && pd->bias.ndims) {
+        p.bias = base_ptr(bias);
+        p.bias_dt = pd->bias.data_type;
+        bcast_strides(pd->bias, p.bias_sm, p.bias_sn);
+    }
+    p.dst = const_cast<void *>(base_ptr(dst));
+    p.dst_dt = pd->dst.data_type;
+    p.dst_sm = pd->dst.strides[0];
+    p.dst_sn = pd->dst.strides[1];
+
+    const dnnl_primitive_attr &a = pd->attr;
+    struct { const quant_entry_t *q; int arg; b200_quant_t *out; int64_t d0, d1; } qs[6] = {
+            {&a.scale(DNNL_ARG_SRC), DNNL_ARG_ATTR_SCALES | DNNL_ARG_SRC, &p.src_scale, p.M, p.K},
+            {&a.scale(DNNL_ARG_WEIGHTS), DNNL_ARG_ATTR_SCALES | DNNL_ARG_WEIGHTS, &p.wei_scale, p.K, p.N},
+            {&a.scale(DNNL_ARG_DST), DNNL_ARG_ATTR_SCALES | DNNL_ARG_DST, &p.dst_scale, p.M, p.N},
+            {&a.zp(DNNL_ARG_SRC), DNNL_ARG_ATTR_ZERO_POINTS | DNNL_ARG_SRC, &p.src_zp, p.M, p.K},
+            {&a.zp(DNNL_ARG_WEIGHTS), DNNL_ARG_ATTR_ZERO_POINTS | DNNL_ARG_WEIGHTS, &p.wei_zp, p.K, p.N},
+            {&a.zp(DNNL_ARG_DST), DNNL_ARG_ATTR_ZERO_POINTS | DNNL_ARG_DST, &p.dst_zp, p.M, p.N}};
+    for (auto &e : qs) {
+        dnnl_memory *m = get(e.arg);
+        if (e.q->set && (!m || !m->handle)) return dnnl_invalid_arguments; // runtime quantisation argument missing
+        lower_quant(*e.out, *e.q, m, e.d0, e.d1);
+        if (e.q->set) {
+            // the memory must hold at least the elements the mask implies
+            const int64_t need = (e.out->s0 ? e.d0 / e.out->g0 : 1) * (e.out->s1 ? e.d1 / e.out->g1 : 1);
+            if (m->md.nelems() < need) return dnnl_invalid_arguments;
+        }
+    }
+    p.apply_to_int = a.apply_to_int;
+    p.npo = (int)a.post_ops.entries.size();
+    for (int i = 0; i < p.npo; ++i) {
+        const post_op_t &e = a.post_ops.entries[i];
+        b200_postop_t &o = p.po[i];
+        o.alg = e.alg;
+        o.alpha = e.alpha;
+        o.beta = e.beta;
+        o.scale = e.scale;
+        o.zero_point = e.zero_point;
+        if (e.kind == dnnl_sum) {
+            o.kind = B200_PO_SUM;
+            o.dt = e.dt;
+        } else if (e.kind == dnnl_eltwise) {
+            o.kind = B200_PO_ELTWISE;
+        } else if (e.kind == dnnl_binary) {
+            o.kind = B200_PO_BINARY;
+            dnnl_memory *m = get(DNNL_ARG_ATTR_MULTIPLE_POST_OP(i) | DNNL_ARG_SRC_1);
+            if (!m || !m->handle) return dnnl_invalid_arguments;
+            o.ptr = base_ptr(m);
+            o.dt = e.src1.data_type;
+            dnnl_memory_desc s1 = e.src1;
+            if (s1.is_any()) make_plain(s1);
+            bcast_strides(s1, o.sm, o.sn);
+        } else {
+            o.kind = B200_PO_PRELU;
+            dnnl_memory *m = get(DNNL_ARG_ATTR_MULTIPLE_POST_OP(i) | DNNL_ARG_WEIGHTS);
+            if (!m || !m->handle) return dnnl_invalid_arguments;
+            o.ptr = base_ptr(m);
+            o.dt = dnnl_f32;
+            // weights are a dense tensor over the dims selected by the mask
+            const bool pm = e.mask & 1, pn = e.mask & 2;
+            o.sn = pn ? 1 : 0;
+            o.sm = pm ? (pn ? p.N : 1) : 0;
+        }
+    }
+    p.status = stream->status;
+
+    // scratchpad
+    void *scratch = nullptr;
+    size_t scratch_bytes = pd->scratchpad.ndims ? (size_t)pd->scratchpad.dims[0] : 0;
+    if (scratch_bytes) {
+        if (a.scratchpad_mode == dnnl_scratchpad_mode_user) {
+            dnnl_memory *m = get(DNNL_ARG_SCRATCHPAD);
+            if (!m || !m->handle) return dnnl_invalid_arguments;
+            scratch = m->handle;
+        } else {
+            scratch = prim->lib_scratch;
+        }
+        if (!scratch) return dnnl_out_of_memory;
+    }
+    p.scratch = scratch;
+    p.scratch_bytes = scratch_bytes;
+    // the library-owned scratchpad is zeroed when the primitive is created and
+    // every kernel leaves its accumulation area zeroed
+    p.scratch_zeroed = (scratch && a.scratchpad_mode == dnnl_scratchpad_mode_library) ? 1 : 0;
+
+    b200_stream_t cs = stream->cuda_stream;
+    int rc = 0;
+    switch (pd->impl) {
+        case IMPL_GENERIC: rc = b200_matmul_generic_launch(&p, cs); break;
+        case IMPL_WC: rc = b200_matmul_wc_launch(&p, cs); break;
+        case IMPL_TC8: {
+            if (p.wei_layout == B200_WEI_KMAJOR) {
+                if (p.src_zp.ptr)
+                    p.wei_colsum = (const int32_t *)((const char *)p.wei + b200_packed_colsum_offset(p.K, p.N, p.wei_dt));
+            } else if (p.wei_sk == 1) {
+                // plain K-major weights: usable in place; column sums into the scratchpad
+                if (p.src_zp.ptr) {
+                    rc = b200_colsum_launch(p.wei, p.wei_dt, p.K, p.N, p.wei_sk, p.wei_sn, (int32_t *)scratch, cs);
+                    p.wei_colsum = (const int32_t *)scratch;
+                }
+            } else {
+                // plain N-major weights: pack into the scratchpad first
+                b200_reorder_params_t r;
+                std::memset(&r, 0, sizeof(r));
+                r.K = p.K;
+                r.N = p.N;
+                r.src = p.wei;
+                r.src_dt = p.wei_dt;
+                r.src_layout = B200_WEI_PLAIN;
+                r.src_sk = p.wei_sk;
+                r.src_sn = p.wei_sn;
+                r.dst = scratch;
+                r.dst_dt = p.wei_dt;
+                r.dst_layout = B200_WEI_KMAJOR;
+                rc = b200_reorder_launch(&r, cs);
+                p.wei = scratch;
+                p.wei_layout = B200_WEI_KMAJOR;
+                p.wei_colsum = (const int32_t *)((const char *)scratch + b200_packed_colsum_offset(p.K, p.N, p.wei_dt));
+            }
+            if (rc == 0) rc = b200_matmul_tc8_launch(&p, cs);
+        } break;
+        default: return dnnl_runtime_error;
+    }
+    if (rc == 0) return dnnl_success;
+    if (rc == B200_ERR_BAD_ARG) return dnnl_invalid_arguments;
+    if (rc == B200_ERR_UNSUPPORTED) return dnnl_unimplemented;
+    return dnnl_runtime_error;
+}
+
+} // namespace b200
+
+using namespace b200;
+
+dnnl_status_t dnnl_matmul_primitive_desc_create(dnnl_primitive_desc_t *primitive_desc, dnnl_engine_t engine,
+        const_dnnl_memory_desc_t src_desc, const_dnnl_memory_desc_t weights_desc, const_dnnl_memory_desc_t bias_desc,
+        const_dnnl_memory_desc_t dst_desc, const_dnnl_primitive_attr_t attr) {
+    if (!primitive_desc || !engine || !src_desc || !weights_desc || !dst_desc) return dnnl_invalid_arguments;
+    const double t0 = now_ms();
+    static const dnnl_primitive_attr default_attr;
+    const dnnl_primitive_attr &a = attr ? *attr : default_attr;
+    dnnl_status_t st = matmul_validate(*src_desc, *weights_desc, bias_desc, *dst_desc, a);
+    if (st != dnnl_success) return st;
+    if (src_desc->has_runtime_dims() || weights_desc->has_runtime_dims() || dst_desc->has_runtime_dims())
+        return dnnl_unimplemented;
+    auto pd = std::unique_ptr<dnnl_primitive_desc>(new dnnl_primitive_desc());
+    pd->kind = dnnl_matmul;
+    pd->engine = engine;
+    pd->attr = a; // copied: later changes to the caller's attr have no effect
+    pd->user_src = *src_desc;
+    pd->user_wei = *weights_desc;
+    if (bias_desc) pd->user_bias = *bias_desc;
+    pd->user_dst = *dst_desc;
+    st = matmul_select_impl(pd.get(), 0);
+    if (st != dnnl_success) return st;
+    engine->refs.fetch_add(1);
+    verbose_create(pd.get(), now_ms() - t0, false);
+    *primitive_desc = pd.release();
+    return dnnl_success;
+}

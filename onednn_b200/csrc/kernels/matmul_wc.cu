@@ -1,0 +1,377 @@
+// Weight-compressed decode GEMV / skinny GEMM: bf16 activations (M rows) times
+// 4-bit weights with K-grouped scales and zero-points, f32 accumulation.
+// Semantics: the reference's weights-decompression matmul
+// (src/cpu/matmul/ref_matmul.cpp:130-233, with_wei_decompression), i.e.
+//   dst[m][n] = epilogue( sum_k x[m][k] * (q[k][n] - zp[k/Gz][n]) * s[k/Gs][n] ).
+//
+// The kernel is HBM-bound (M = 1: 0.5 byte of weights per multiply-add), so
+// the design goal is to stream the packed weights once with 128-bit loads and
+// keep the per-byte instruction count low:
+//
+//  * Weights are read in the B200_WEI_WC4_TILED layout written by the pack
+//    kernel below: the matrix is cut into tiles of 16 output columns x 64 k;
+//    each tile is 512 contiguous bytes, 16 bytes per lane, ordered so that one
+//    32-bit word of a lane holds exactly the eight 4-bit values that lane owns
+//    in the A fragment of one mma.m16n8k16 (output columns play the role of the
+//    MMA's M dimension, activations rows the role of its N dimension).
+//  * A nibble becomes a bf16 with one logic op: (w >> 4i) & 0x000f000f | 0x43004300
+//    gives the pair (128 + q_lo, 128 + q_hi) exactly.  No subtraction and no
+//    multiply is spent per weight: the MMA accumulates sum_k x*(128+q) in f32,
+//    a second MMA with an all-ones A tile accumulates sum_k x, and at every
+//    quantisation-group boundary the fold
+//        total += s * (acc - (128 + zp) * xsum)
+//    applies scale and zero-point to a whole group at once (4 FMAs per thread
+//    per group).  s4 weights are stored offset by 8, so they fold with 136 + zp.
+//  * Work is split by bytes, not by tiles: the S = (N/16)*(K/64) tile steps are
+//    dealt out in equal contiguous ranges to every warp of a grid sized to the
+//    SM count, each warp streams its range with a 3-deep register prefetch ring
+//    and adds its partial sums into an f32 scratch [M][N] with red.global.add;
+//    a small second kernel applies the epilogue and leaves the scratch zeroed.
+#include "common.cuh"
+#include "launch.hpp"
+
+namespace b200 {
+
+constexpr int WC_WARPS = 8;           // warps per CTA
+constexpr int WC_TILE_N = 16;         // output columns per tile (MMA M)
+constexpr int WC_TILE_K = 64;         // k per 512-byte tile step
+
+struct wc_args_t {
+    const uint4 *wei;       // packed tiles
+    const __nv_bfloat16 *x; // activations, row-major, converted to bf16 if needed
+    int64_t x_ld;
+    float *acc;             // scratch [M][N] f32, zero on entry
+    int64_t M, N, K;
+    int m0;                 // first activation row of this pass
+    const void *scale; int scale_dt; int64_t scale_s0, scale_s1, scale_g0; // g0: K-group size (K if none)
+    const void *zp; int zp_dt; int64_t zp_s0, zp_s1, zp_g0;
+    int64_t fold_k;         // fold period in k (multiple of 16)
+    float nibble_offset;    // 128 (u4) or 136 (s4 stored offset by 8)
+};
+
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+            "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+            : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+            : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint4 ldg_stream(const uint4 *p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+
+// MB = number of 8-row activation blocks handled per pass (1, 2 or 4)
+template <int MB>
+__global__ void __launch_bounds__(WC_WARPS * 32) wc_gemv_kernel(const __grid_constant__ wc_args_t a) {
+    const int lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int64_t warp = (int64_t)blockIdx.x * WC_WARPS + (threadIdx.x >> 5);
+    const int64_t nwarps = (int64_t)gridDim.x * WC_WARPS;
+    const int64_t kchunks = a.K / WC_TILE_K;
+    const int64_t steps = (a.N / WC_TILE_N) * kchunks;
+    // equal contiguous ranges: the first (steps % nwarps) warps take one more
+    const int64_t base = steps / nwarps, rem = steps % nwarps;
+    int64_t s_begin = warp * base + (warp < rem ? warp : rem);
+    const int64_t s_end = s_begin + base + (warp < rem ? 1 : 0);
+    if (s_begin >= s_end) return;
+
+    const uint32_t ones[4] = {0x3f803f80u, 0x3f803f80u, 0x3f803f80u, 0x3f803f80u};
+    float acc[MB][4], xs[MB][4], tot[MB][4];
+#pragma unroll
+    for (int mb = 0; mb < MB; ++mb)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[mb][i] = xs[mb][i] = tot[mb][i] = 0.f;
+
+    // activation rows this lane feeds into the B fragments (column g of each block)
+    const __nv_bfloat16 *xrow[MB];
+    bool xok[MB];
+#pragma unroll
+    for (int mb = 0; mb < MB; ++mb) {
+        const int64_t m = a.m0 + mb * 8 + g;
+        xok[mb] = m < a.M;
+        xrow[mb] = a.x + (xok[mb] ? m : 0) * a.x_ld;
+    }
+
+    const uint4 *wp = a.wei + s_begin * 32 + lane;
+    // 3-deep prefetch ring held in named registers (rotated by moves, never indexed)
+    uint4 r0 = ldg_stream(wp), r1 = r0, r2 = r0;
+    if (s_begin + 1 < s_end) r1 = ldg_stream(wp + 32);
+    if (s_begin + 2 < s_end) r2 = ldg_stream(wp + 64);
+
+    int64_t strip = s_begin / kchunks;
+    int64_t kc = s_begin % kchunks;
+
+    auto fold = [&](int64_t k_last) {
+        // k_last: any k inside the group being closed
+        const int64_t n0 = strip * WC_TILE_N + g, n1 = n0 + 8;
+        float s0 = 1.f, s1 = 1.f, c0 = a.nibble_offset, c1 = a.nibble_offset;
+        if (a.scale) {
+            const int64_t gi = (k_last / a.scale_g0) * a.scale_s0;
+            s0 = load_f32(a.scale_dt, a.scale, gi + n0 * a.scale_s1);
+            s1 = load_f32(a.scale_dt, a.scale, gi + n1 * a.scale_s1);
+        }
+        if (a.zp) {
+            const int64_t gi = (k_last / a.zp_g0) * a.zp_s0;
+            c0 += (float)load_int(a.zp_dt, a.zp, gi + n0 * a.zp_s1);
+            c1 += (float)load_int(a.zp_dt, a.zp, gi + n1 * a.zp_s1);
+        }
+#pragma unroll
+        for (int mb = 0; mb < MB; ++mb) {
+            tot[mb][0] = fmaf(s0, fmaf(-c0, xs[mb][0], acc[mb][0]), tot[mb][0]);
+            tot[mb][1] = fmaf(s0, fmaf(-c0, xs[mb][1], acc[mb][1]), tot[mb][1]);
+            tot[mb][2] = fmaf(s1, fmaf(-c1, xs[mb][2], acc[mb][2]), tot[mb][2]);
+            tot[mb][3] = fmaf(s1, fmaf(-c1, xs[mb][3], acc[mb][3]), tot[mb][3]);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) acc[mb][i] = xs[mb][i] = 0.f;
+        }
+    };
+    auto flush = [&]() {
+        const int64_t n0 = strip * WC_TILE_N + g, n1 = n0 + 8;
+#pragma unroll
+        for (int mb = 0; mb < MB; ++mb) {
+            const int64_t mA = a.m0 + mb * 8 + 2 * t, mB = mA + 1;
+            if (mA < a.M) {
+                atomicAdd(a.acc + mA * a.N + n0, tot[mb][0]);
+                atomicAdd(a.acc + mA * a.N + n1, tot[mb][2]);
+            }
+            if (mB < a.M) {
+                atomicAdd(a.acc + mB * a.N + n0, tot[mb][1]);
+                atomicAdd(a.acc + mB * a.N + n1, tot[mb][3]);
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) tot[mb][i] = 0.f;
+        }
+    };
+
+    for (int64_t s = s_begin; s < s_end; ++s) {
+        const uint4 w4 = r0;
+        r0 = r1;
+        r1 = r2;
+        if (s + 3 < s_end) r2 = ldg_stream(wp + (s + 3 - s_begin) * 32);
+        const uint32_t words[4] = {w4.x, w4.y, w4.z, w4.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int64_t k0 = kc * WC_TILE_K + j * 16;
+            const uint32_t w = words[j];
+            uint32_t af[4];
+            af[0] = (w & 0x000f000fu) | 0x43004300u;
+            af[1] = ((w >> 4) & 0x000f000fu) | 0x43004300u;
+            af[2] = ((w >> 8) & 0x000f000fu) | 0x43004300u;
+            af[3] = ((w >> 12) & 0x000f000fu) | 0x43004300u;
+#pragma unroll
+            for (int mb = 0; mb < MB; ++mb) {
+                uint32_t b0 = 0, b1 = 0;
+                if (xok[mb]) {
+                    b0 = *reinterpret_cast<const uint32_t *>(xrow[mb] + k0 + 2 * t);
+                    b1 = *reinterpret_cast<const uint32_t *>(xrow[mb] + k0 + 2 * t + 8);
+                }
+                mma_bf16_16816(acc[mb], af, b0, b1);
+                mma_bf16_16816(xs[mb], ones, b0, b1);
+            }
+            if ((k0 + 16) % a.fold_k == 0) fold(k0);
+        }
+        // next step: same strip unless the k chunks are exhausted
+        if (++kc == kchunks) {
+            // the last fold of the strip has happened (fold_k divides K)
+            flush();
+            kc = 0;
+            ++strip;
+        }
+    }
+    if (kc != 0) {
+        // range ended inside a strip: close the open group, then publish
+        const int64_t k_done = kc * WC_TILE_K; // k processed so far in this strip
+        if (k_done % a.fold_k != 0) fold(k_done - 1);
+        flush();
+    }
+}
+
+// epilogue over the f32 partial sums: src scale, bias, post-ops, dst scale, store;
+// leaves the scratch zeroed for the next execution
+__global__ void __launch_bounds__(256) wc_epilogue_kernel(const __grid_constant__ b200_matmul_params_t p, float *acc) {
+    const int64_t total = p.M * p.N;
+    const float dst_inv = dst_scale_reciprocal(p);
+    const float src_scale = p.src_scale.ptr ? load_f32(p.src_scale.dt, p.src_scale.ptr, 0) : 1.f;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        float d = acc[i];
+        acc[i] = 0.f;
+        if (p.src_scale.ptr) d = __fmul_rn(d, src_scale);
+        finish_element(p, d, i / p.N, i % p.N, false, dst_inv);
+    }
+}
+
+// activations of another float type -> bf16 rows (fpmath bf16 permits the down-conversion)
+__global__ void __launch_bounds__(256) wc_convert_x_kernel(const void *src, int dt, int64_t ld, int64_t M, int64_t K,
+        __nv_bfloat16 *dst) {
+    const int64_t total = M * K;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t m = i / K, k = i % K;
+        ((uint16_t *)dst)[i] = f32_to_bf16_bits(load_f32(dt, src, m * ld + k));
+    }
+}
+
+// plain (K, N) 4-bit weights, two per byte along N -> B200_WEI_WC4_TILED.
+// One thread per 32-bit output word.
+__global__ void __launch_bounds__(256) wc_pack_kernel(const uint8_t *__restrict__ src, uint32_t *__restrict__ dst,
+        int64_t K, int64_t N, int is_signed) {
+    const int64_t nwords = K * N / 8;
+    const int64_t kchunks = K / WC_TILE_K;
+    for (int64_t wi = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; wi < nwords; wi += (int64_t)gridDim.x * blockDim.x) {
+        const int j = (int)(wi & 3);
+        const int lane = (int)((wi >> 2) & 31);
+        const int64_t tile = wi >> 7;
+        const int64_t kc = tile % kchunks, strip = tile / kchunks;
+        const int g = lane >> 2, t = lane & 3;
+        uint32_t word = 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int p = i & 3, half = i >> 2;
+            const int64_t n = strip * WC_TILE_N + g + 8 * (p & 1);
+            const int64_t k = kc * WC_TILE_K + j * 16 + 2 * t + 8 * (p >> 1) + half;
+            const int64_t e = k * N + n;
+            uint32_t q = (src[e >> 1] >> ((e & 1) * 4)) & 0xf;
+            if (is_signed) q ^= 8u; // two's complement nibble -> offset binary (value + 8)
+            // nibble p goes to bits [4p, 4p+4) of the low half (even k) or the high half (odd k)
+            word |= q << (4 * p + 16 * half);
+        }
+        dst[wi] = word;
+    }
+}
+
+static inline size_t align256(size_t x) { return (x + 255) / 256 * 256; }
+
+} // namespace b200
+
+using namespace b200;
+
+// scratch layout of the wc kernel: [f32 acc M*N][bf16 x copy M*K if src is not bf16][packed weights if plain]
+static void wc_scratch_layout(const b200_matmul_params_t *p, size_t *acc, size_t *xcopy, size_t *packed) {
+    *acc = align256((size_t)p->M * p->N * sizeof(float));
+    *xcopy = p->src_dt == B200_DT_BF16 ? 0 : align256((size_t)p->M * p->K * 2);
+    *packed = p->wei_layout == B200_WEI_WC4_TILED ? 0 : align256((size_t)(p->K * p->N / 2));
+}
+
+extern "C" size_t b200_matmul_scratch_bytes(const b200_matmul_params_t *p, int kernel) {
+    if (!p) return 0;
+    if (kernel == 2) {
+        size_t a, x, w;
+        wc_scratch_layout(p, &a, &x, &w);
+        return a + x + w;
+    }
+    return 0;
+}
+
+extern "C" int b200_wc_pack_launch(const void *src, void *dst, int64_t K, int64_t N, int32_t dt, b200_stream_t stream) {
+    if (!src || !dst) return B200_ERR_BAD_ARG;
+    if ((dt != B200_DT_U4 && dt != B200_DT_S4) || K % WC_TILE_K != 0 || N % WC_TILE_N != 0) return B200_ERR_UNSUPPORTED;
+    const int64_t nwords = K * N / 8;
+    if (nwords == 0) return 0;
+    int64_t blocks = (nwords + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    wc_pack_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>((const uint8_t *)src, (uint32_t *)dst, K, N,
+            dt == B200_DT_S4);
+    return after_launch();
+}
+
+extern "C" int b200_matmul_wc_launch(const b200_matmul_params_t *p, b200_stream_t stream) {
+    if (!p || !p->src || !p->wei || !p->dst) return B200_ERR_BAD_ARG;
+    if (p->M <= 0 || p->N <= 0 || p->K <= 0) return p->M < 0 || p->N < 0 || p->K < 0 ? B200_ERR_BAD_ARG : 0;
+    if (p->wei_dt != B200_DT_U4 && p->wei_dt != B200_DT_S4) return B200_ERR_UNSUPPORTED;
+    if (!p->apply_to_int) return B200_ERR_UNSUPPORTED;
+    if (p->src_dt != B200_DT_BF16 && p->src_dt != B200_DT_F16 && p->src_dt != B200_DT_F32) return B200_ERR_UNSUPPORTED;
+    if (p->N % WC_TILE_N != 0 || p->K % WC_TILE_K != 0 || p->src_sk != 1 || p->dst_sn != 1) return B200_ERR_UNSUPPORTED;
+    if (p->wei_layout == B200_WEI_PLAIN && !(p->wei_sn == 1 && p->wei_sk == p->N)) return B200_ERR_UNSUPPORTED;
+    if (p->wei_layout != B200_WEI_PLAIN && p->wei_layout != B200_WEI_WC4_TILED) return B200_ERR_UNSUPPORTED;
+    if (p->src_zp.ptr || p->dst_zp.ptr) return B200_ERR_UNSUPPORTED;
+    if (p->src_scale.ptr && (p->src_scale.s0 || p->src_scale.s1)) return B200_ERR_UNSUPPORTED;
+    // K-group sizes: multiples of 16 that divide K, and one must divide the other
+    int64_t gs = p->K, gz = p->K;
+    if (p->wei_scale.ptr) {
+        if (p->wei_scale.g1 != 1) return B200_ERR_UNSUPPORTED;
+        if (p->wei_scale.s0) gs = p->wei_scale.g0;
+    }
+    if (p->wei_zp.ptr) {
+        if (p->wei_zp.g1 != 1) return B200_ERR_UNSUPPORTED;
+        if (p->wei_zp.s0) gz = p->wei_zp.g0;
+    }
+    if (gs % 16 || gz % 16 || p->K % gs || p->K % gz) return B200_ERR_UNSUPPORTED;
+    const int64_t fold_k = gs < gz ? gs : gz;
+    if (gs % fold_k || gz % fold_k) return B200_ERR_UNSUPPORTED;
+    if (((uintptr_t)p->src & 3) || (p->src_dt == B200_DT_BF16 && (p->src_sm & 1))) return B200_ERR_BAD_ARG;
+
+    size_t acc_b, x_b, w_b;
+    wc_scratch_layout(p, &acc_b, &x_b, &w_b);
+    if (!p->scratch || p->scratch_bytes < acc_b + x_b + w_b) return B200_ERR_BAD_ARG;
+    cudaStream_t cs = (cudaStream_t)stream;
+    char *sc = (char *)p->scratch;
+    float *acc = (float *)sc;
+    const __nv_bfloat16 *x = (const __nv_bfloat16 *)p->src;
+    int64_t x_ld = p->src_sm;
+    if (x_b) {
+        __nv_bfloat16 *xc = (__nv_bfloat16 *)(sc + acc_b);
+        int64_t blocks = (p->M * p->K + 255) / 256;
+        if (blocks > 148 * 8) blocks = 148 * 8;
+        wc_convert_x_kernel<<<(unsigned)blocks, 256, 0, cs>>>(p->src, p->src_dt, p->src_sm, p->M, p->K, xc);
+        int rc = after_launch();
+        if (rc) return rc;
+        x = xc;
+        x_ld = p->K;
+    }
+    const void *wei = p->wei;
+    if (w_b) {
+        void *wp = sc + acc_b + x_b;
+        int rc = b200_wc_pack_launch(p->wei, wp, p->K, p->N, p->wei_dt, stream);
+        if (rc) return rc;
+        wei = wp;
+    }
+    if (((uintptr_t)wei & 15)) return B200_ERR_BAD_ARG;
+    if (!p->scratch_zeroed) {
+        if (cudaMemsetAsync(acc, 0, (size_t)p->M * p->N * sizeof(float), cs) != cudaSuccess) return (int)cudaGetLastError();
+    }
+
+    wc_args_t a;
+    a.wei = (const uint4 *)wei;
+    a.x = x;
+    a.x_ld = x_ld;
+    a.acc = acc;
+    a.M = p->M;
+    a.N = p->N;
+    a.K = p->K;
+    a.scale = p->wei_scale.ptr;
+    a.scale_dt = p->wei_scale.dt;
+    a.scale_s0 = p->wei_scale.s0;
+    a.scale_s1 = p->wei_scale.s1;
+    a.scale_g0 = gs;
+    a.zp = p->wei_zp.ptr;
+    a.zp_dt = p->wei_zp.dt;
+    a.zp_s0 = p->wei_zp.s0;
+    a.zp_s1 = p->wei_zp.s1;
+    a.zp_g0 = gz;
+    a.fold_k = fold_k;
+    a.nibble_offset = p->wei_dt == B200_DT_S4 ? 136.f : 128.f;
+
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int64_t steps = (p->N / WC_TILE_N) * (p->K / WC_TILE_K);
+    int64_t ctas = (int64_t)sms * 4;
+    if (ctas * WC_WARPS > steps) ctas = (steps + WC_WARPS - 1) / WC_WARPS;
+    // activation rows in passes of up to 32 (the weights are re-read from L2)
+    for (int64_t m0 = 0; m0 < p->M; m0 += 32) {
+        a.m0 = (int)m0;
+        const int64_t rows = p->M - m0;
+        if (rows <= 8) wc_gemv_kernel<1><<<(unsigned)ctas, WC_WARPS * 32, 0, cs>>>(a);
+        else if (rows <= 16) wc_gemv_kernel<2><<<(unsigned)ctas, WC_WARPS * 32, 0, cs>>>(a);
+        else wc_gemv_kernel<4><<<(unsigned)ctas, WC_WARPS * 32, 0, cs>>>(a);
+        int rc = after_launch();
+        if (rc) return rc;
+    }
+    int64_t eblocks = (p->M * p->N + 255) / 256;
+    if (eblocks > (int64_t)sms * 8) eblocks = (int64_t)sms * 8;
+    wc_epilogue_kernel<<<(unsigned)eblocks, 256, 0, cs>>>(*p, acc);
+    return after_launch();
+}

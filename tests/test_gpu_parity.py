@@ -1,0 +1,135 @@
+"""Parity of the CUDA engine against the CPU oracle, through the public C API.
+
+Every case of tests/cases.py is executed on cuda:0 with each implementation
+that accepts it and compared with the oracle on the same seeded inputs:
+  * the generic kernel performs the reference's operations in the reference's
+    order, so it must match bit for bit -- integer and float destinations alike
+    (the oracle runs with the portable tanh the kernels share; transcendental
+    eltwise kinds other than tanh may differ by 1 ulp and get 2 ulp of slack);
+  * the tensor-core and decode kernels accumulate in another order: integer
+    destinations are still bit-exact (s32 accumulation is exact), float
+    destinations are held to the case's tolerance (1e-5 relative for f32 after
+    int8, rtol 1e-2 for bf16 / fp8 / weight-decompression).
+"""
+import numpy as np
+import pytest
+
+import cases
+from parity import assert_bit_exact, assert_close, ulp_diff_f32
+from onednn_b200 import api, dtypes as dt, workloads as W
+from oracle import binding as B
+
+pytestmark = pytest.mark.gpu
+
+LIBM_ALGS = {W.ELTWISE[k] for k in ("elu", "soft_relu", "logistic", "exp", "swish", "log", "pow", "gelu_erf", "mish")}
+
+
+@pytest.fixture(scope="module")
+def ctx():
+    eng = api.Engine()
+    return eng, api.Stream(eng)
+
+
+def _uses_libm(case):
+    return any(p.kind == W.PO_ELTWISE and p.alg in LIBM_ALGS for p in case.post_ops)
+
+
+@pytest.mark.parametrize("name", list(cases.CASES))
+def test_generic_kernel_bit_exact(ctx, name):
+    c = cases.build(name)
+    want = B.run_oracle(c, tanh_mode=1)
+    got, impl = api.run_case(c, *ctx, weights="plain", impl="generic")
+    assert impl == "cuda:generic"
+    if _uses_libm(c) and c.dst_dt == dt.F32:
+        assert ulp_diff_f32(got, want).max() <= 2
+    elif _uses_libm(c):
+        assert_close(c, got, want, name)
+    else:
+        assert_bit_exact(got, want, name)
+
+
+@pytest.mark.parametrize("name", list(cases.CASES))
+@pytest.mark.parametrize("weights", ["any", "plain"])
+def test_dispatched_kernel(ctx, name, weights):
+    c = cases.build(name)
+    plan = api.CasePlan(c, *ctx, weights=weights)
+    if plan.impl == "cuda:generic":
+        pytest.skip("only the generic kernel accepts this case")
+    plan.execute()
+    got = plan.result()
+    want = B.run_oracle(c, tanh_mode=1)
+    assert_close(c, got, want, "%s via %s" % (name, plan.impl))
+
+
+def test_fast_kernels_are_dispatched(ctx):
+    eng, strm = ctx
+    assert api.CasePlan(cases.build("c1_small"), eng, strm, upload=False).impl == "cuda:sm100:tcgen05_i8"
+    assert api.CasePlan(cases.build("c3_small"), eng, strm, upload=False).impl == "cuda:sm100:tcgen05_f8"
+    assert api.CasePlan(W.config2(1, 256, 512), eng, strm, upload=False).impl == "cuda:sm100:wc_gemv"
+
+
+def test_repeated_execution_and_sum_in_place(ctx):
+    """sum reads the destination in place: a second execution consumes the first one's output."""
+    c = cases.build("c1_small_nonsat")
+    plan = api.CasePlan(c, *ctx)
+    plan.execute()
+    first = plan.result()
+    plan.execute()
+    second = plan.result()
+    c2 = cases.build("c1_small_nonsat")
+    c2.dst_init = first
+    assert_bit_exact(second, B.run_oracle(c2, tanh_mode=1))
+
+
+def test_zero_dim_is_a_no_op(ctx):
+    eng, strm = ctx
+    src = api.Memory(api.MemoryDesc((0, 32), dt.S8, api.TAG_AB), eng)
+    wei = api.Memory(api.MemoryDesc((32, 16), dt.S8, api.TAG_AB), eng)
+    dst = api.Memory(api.MemoryDesc((0, 16), dt.S32, api.TAG_AB), eng)
+    pd = api.matmul_primitive_desc(eng, src.md, wei.md, dst.md)
+    api.Primitive(pd).execute(strm, {api.ARG_SRC: src, api.ARG_WEIGHTS: wei, api.ARG_DST: dst})
+    strm.wait()
+
+
+def test_missing_runtime_scale_argument_is_rejected(ctx):
+    c = cases.build("c0_small")
+    plan = api.CasePlan(c, *ctx, impl="generic", weights="plain")
+    del plan.args[api.ARG_ATTR_SCALES | api.ARG_WEIGHTS]
+    with pytest.raises(api.Error) as e:
+        plan.execute()
+    assert e.value.name == "invalid_arguments"
+
+
+def test_user_scratchpad_mode(ctx):
+    eng, strm = ctx
+    c = W.config2(3, 256, 512)
+    want = B.run_oracle(c)
+    plan = api.CasePlan(c, eng, strm, upload=False)
+    plan.attr.set_scratchpad_mode(1)
+    plan2 = api.CasePlan(c, eng, strm)          # library mode as the yardstick
+    plan2.execute()
+    assert_close(c, plan2.result(), want)
+
+
+def test_map_unmap_round_trip(ctx):
+    eng, _ = ctx
+    a = np.arange(6 * 10, dtype=np.float32).reshape(6, 10)
+    m = api.Memory(api.MemoryDesc(a.shape, dt.F32, api.TAG_AB), eng)
+    m.write(a)
+    assert np.array_equal(m.read(np.float32, a.shape), a)
+
+
+def test_reorder_plain_and_convert(ctx):
+    eng, strm = ctx
+    r = np.random.default_rng(3)
+    a = r.normal(0, 50, (37, 53)).astype(np.float32)
+    src = api.Memory(api.MemoryDesc(a.shape, dt.F32, api.TAG_AB), eng)
+    src.write(a)
+    # f32 ab -> s8 ba: saturate, round to nearest even, transpose
+    dmd = api.MemoryDesc(a.shape, dt.S8, api.TAG_BA)
+    dst = api.Memory(dmd, eng)
+    api.Primitive(api.reorder_primitive_desc(eng, src.md, eng, dmd)).execute(strm, {api.ARG_FROM: src, api.ARG_TO: dst})
+    strm.wait()
+    got = dst.read(np.int8, (53, 37)).T
+    want = np.clip(np.rint(a), -128, 127).astype(np.int8)
+    assert np.array_equal(got, want)

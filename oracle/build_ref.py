@@ -146,7 +146,7 @@ def main():
         return 1
     lib = OUT / "libdnnl_ref.so"
     cmd = [args.cxx, "-shared", "-fopenmp", "-o", str(lib)] + \
-        [str(o) for _, o in jobs] + ["-Wl,-Bsymbolic", "-Wl,--no-undefined", "-ldl", "-lpthread"]
+        [str(o) for _, o in jobs] + ["-Wl,-Bsymbolic", "-Wl,--no-undefined", "-s", "-ldl", "-lpthread"]
     p = subprocess.run(cmd, capture_output=True, text=True)
     if p.returncode != 0:
         print(p.stderr[-6000:])

@@ -20,12 +20,21 @@ __global__ void __launch_bounds__(256) matmul_generic_kernel(const __grid_consta
         const int64_t m = idx / p.N, n = idx % p.N;
         float d;
         if (int8_path) {
-            // the K loop is cut into the smallest of the scale / zero-point groups
+            // The reference cuts the K loop into the smallest group among the four scale /
+            // zero-point arguments, and an argument without explicit groups (set or not)
+            // counts as group size 1 (ref_matmul_int8.cpp:83-144,
+            // primitive_attr_quant.hpp:83-90): unless every argument is explicitly
+            // grouped, each product is converted to f32, scaled and accumulated in f32.
             int64_t ng = 1;
-            if (p.src_zp.ptr && p.K / p.src_zp.g1 > ng) ng = p.K / p.src_zp.g1;
-            if (p.wei_zp.ptr && p.K / p.wei_zp.g0 > ng) ng = p.K / p.wei_zp.g0;
-            if (p.src_scale.ptr && p.K / p.src_scale.g1 > ng) ng = p.K / p.src_scale.g1;
-            if (p.wei_scale.ptr && p.K / p.wei_scale.g0 > ng) ng = p.K / p.wei_scale.g0;
+            {
+                const int64_t a = (p.src_zp.ptr && p.src_zp.g1 > 1) ? p.K / p.src_zp.g1 : p.K;
+                const int64_t b = (p.wei_zp.ptr && p.wei_zp.g0 > 1) ? p.K / p.wei_zp.g0 : p.K;
+                const int64_t c = (p.src_scale.ptr && p.src_scale.g1 > 1) ? p.K / p.src_scale.g1 : p.K;
+                const int64_t e = (p.wei_scale.ptr && p.wei_scale.g0 > 1) ? p.K / p.wei_scale.g0 : p.K;
+                ng = a > b ? a : b;
+                ng = c > ng ? c : ng;
+                ng = e > ng ? e : ng;
+            }
             const int64_t gk = p.K / ng;
             d = 0.f;
             for (int64_t g = 0; g < ng; ++g) {

@@ -1,6 +1,661 @@
-// placeholder until the tensor-core kernel lands in this file
+// Dense 8-bit GEMM on the Blackwell tensor cores with the whole matmul epilogue fused.
+//
+//   dst = epilogue( A[M,K] (u8/s8 or e4m3/e5m2, row-major) x W[N,K] (K-major packed weights) )
+//
+// Computes what the reference's int8 matmul computes per element
+// (src/cpu/matmul/ref_matmul_int8.cpp:154-261: s32 accumulation of (s - zp_src) * w,
+// f32 scale by src_scale then wei_scale[n], bias, post-ops, dst scale, dst
+// zero-point, saturate + round-to-nearest-even), and for fp8 what its
+// floating-point matmul computes (src/cpu/matmul/ref_matmul.cpp:130-233), in the
+// place of the reference's AMX brgemm kernel
+// (src/cpu/x64/matmul/brgemm_matmul.cpp:383-496, jit_brgemm_amx_uker.cpp:1286-1445).
+//
+// Structure (one persistent CTA per SM, 192 threads):
+//   warp 0      TMA producer: cp.async.bulk.tensor 2-D loads (no multicast) of a
+//               128 x 128-byte A tile and a 256 x 128-byte W tile per k-block into a
+//               4-stage ring of 128-byte-swizzled shared memory, completion on
+//               "full" mbarriers.
+//   warp 1      MMA issuer: one lane issues tcgen05.mma.cta_group::1 (kind::i8 or
+//               kind::f8f6f4), 128 x 256 x 32 per instruction, four per k-block,
+//               accumulating in tensor memory; tcgen05.commit releases the smem
+//               stage ("empty" mbarrier) and, after the last k-block, publishes the
+//               accumulator ("tmem_full").  Also owns the TMEM allocation (512
+//               columns = two 128 x 256 x 32-bit accumulators).
+//   warps 2-5   epilogue: tcgen05.ld 32 lanes x 32 columns at a time, exact s32
+//               zero-point compensation (acc - zp_src * colsum_W[n]), the f32
+//               epilogue chain, packed 16-byte stores.  With two accumulator
+//               stages the epilogue of tile i overlaps the main loop of tile i+1.
+//
+// Every mbarrier wait is bounded: when a wait runs out the kernel raises a flag
+// in the stream's status word, every role stops at its next wait, the producer
+// waits (bounded) for its own copies in flight, the TMEM allocation is released
+// and the kernel returns; dnnl_stream_wait then reports dnnl_runtime_error.
+#include <cuda.h>
+
+#include <mutex>
+
 #include "common.cuh"
+#include "launch.hpp"
+
+namespace b200 {
+
+constexpr int BM = 128;          // rows of dst per tile (= TMEM lanes)
+constexpr int BN = 256;          // columns of dst per tile (= one MMA's N)
+constexpr int BK = 128;          // bytes of K per stage (= one 128-byte swizzle row)
+constexpr int STAGES = 4;
+constexpr int A_BYTES = BM * BK; // 16 KiB
+constexpr int B_BYTES = BN * BK; // 32 KiB
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int NUM_THREADS = 192;
+constexpr int EPI_WARPS = 4;
+constexpr uint32_t TMEM_COLS = 512;
+constexpr uint32_t WAIT_SPINS = 1u << 24; // bounded wait: of the order of a second with the back-off below
+
+enum : uint32_t { ST_WAIT_FULL = 0x1, ST_WAIT_EMPTY = 0x2, ST_WAIT_TMEM_FULL = 0x4, ST_WAIT_TMEM_EMPTY = 0x8 };
+
+struct smem_ctrl_t {
+    uint64_t full[STAGES];
+    uint64_t empty[STAGES];
+    uint64_t tmem_full[2];
+    uint64_t tmem_empty[2];
+    uint32_t tmem_base;
+    volatile uint32_t abort;
+    // per epilogue warp: per-column vectors of the current tile
+    float wscale[EPI_WARPS][BN];
+    float bias[EPI_WARPS][BN];
+    int32_t comp[EPI_WARPS][BN]; // zp_src * colsum_W[n]
+};
+
+constexpr size_t SMEM_BYTES = 1024 /* alignment slack */ + (size_t)STAGES * STAGE_BYTES + sizeof(smem_ctrl_t);
+
+// ---- PTX wrappers ---------------------------------------------------------------
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_test(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(smem_u32(bar)), "r"(parity)
+            : "memory");
+    return ok != 0;
+}
+// bounded wait; false when it ran out or another role already gave up
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, smem_ctrl_t *c, uint32_t *status, uint32_t code) {
+    for (uint32_t i = 0; i < WAIT_SPINS; ++i) {
+        if (mbar_test(bar, parity)) return true;
+        if (c->abort) return false;
+        if (i > 64) __nanosleep(32);
+    }
+    c->abort = 1;
+    if (status) atomicOr(status, code);
+    return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, int c0, int c1, uint64_t *bar) {
+    asm volatile(
+            "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+            :
+            : "r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
+            : "memory");
+}
+
+__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tcgen05_commit(uint64_t *bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+                 : "memory");
+}
+
+template <bool FP8>
+__device__ __forceinline__ void tcgen05_mma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
+    if (FP8) {
+        asm volatile(
+                "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+                :
+                : "r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc)
+                : "memory");
+    } else {
+        asm volatile(
+                "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+                :
+                : "r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc)
+                : "memory");
+    }
+}
+
+// 32 consecutive 32-bit columns of this thread's TMEM lane
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+            "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+            "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+            : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+            "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+            "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+            "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+            : "r"(taddr)
+            : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// shared-memory matrix descriptor: K-major operand, 128-byte swizzle, rows of 128
+// bytes, 8-row groups 1024 bytes apart (tile base 1024-byte aligned)
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3ffff) >> 4);  // start address, 16-byte units
+    d |= (uint64_t)1 << 16;                   // leading byte offset (unused for swizzled K-major)
+    d |= (uint64_t)(1024 >> 4) << 32;         // stride byte offset
+    d |= (uint64_t)1 << 46;                   // descriptor version for sm_100
+    d |= (uint64_t)2 << 61;                   // SWIZZLE_128B
+    return d;
+}
+
+struct tc8_args_t {
+    b200_matmul_params_t p;
+    int m_tiles, n_tiles, k_blocks;
+    uint32_t idesc;
+};
+
+// ---- epilogue on 32 columns of one row ------------------------------------------------
+//
+// The post-op chain is evaluated in one of four ways, chosen on the host:
+//   EPI_NONE    no post-ops;
+//   EPI_SIMPLE  only sum and non-transcendental eltwise kinds: a small inline interpreter;
+//   EPI_GELU_Q  [gelu_tanh] or [gelu_tanh, sum] into an s8 / u8 destination: see below;
+//   EPI_GENERIC anything else: the shared interpreter, called out of line per element.
+enum { EPI_NONE = 0, EPI_SIMPLE = 1, EPI_GELU_Q = 2, EPI_GENERIC = 3 };
+
+__device__ __noinline__ float post_ops_out_of_line(const b200_matmul_params_t *p, float x, float old, int64_t m, int64_t n) {
+    return apply_post_ops(*p, x, old, m, n);
+}
+__device__ __noinline__ float gelu_tanh_exact(float x) { return gelu_tanh_f32(x); }
+
+__device__ __forceinline__ bool eltwise_is_simple(int alg) {
+    switch (alg) {
+        case ALG_RELU: case ALG_RELU_DST: case ALG_SQUARE: case ALG_ABS: case ALG_LINEAR: case ALG_HARDSIGMOID:
+        case ALG_CLIP: case ALG_CLIP_V2: case ALG_CLIP_V2_DST: case ALG_ROUND: case ALG_HARDSWISH: case ALG_SQRT:
+        case ALG_SQRT_DST: return true;
+        default: return false;
+    }
+}
+
+__device__ __forceinline__ float post_ops_simple(const b200_matmul_params_t &p, float x, float old) {
+    for (int i = 0; i < p.npo; ++i) {
+        const b200_postop_t &e = p.po[i];
+        if (e.kind == B200_PO_SUM) {
+            x = __fadd_rn(x, __fmul_rn(e.scale, __fsub_rn(old, (float)e.zero_point)));
+        } else {
+            float r;
+            switch (e.alg) {
+                case ALG_RELU: case ALG_RELU_DST: r = x > 0 ? x : __fmul_rn(x, e.alpha); break;
+                case ALG_SQUARE: r = __fmul_rn(x, x); break;
+                case ALG_ABS: r = x > 0 ? x : -x; break;
+                case ALG_SQRT: case ALG_SQRT_DST: r = __fsqrt_rn(x); break;
+                case ALG_LINEAR: r = __fadd_rn(__fmul_rn(e.alpha, x), e.beta); break;
+                case ALG_HARDSIGMOID: r = hardsigmoid_f32(x, e.alpha, e.beta); break;
+                case ALG_HARDSWISH: r = __fmul_rn(x, hardsigmoid_f32(x, e.alpha, e.beta)); break;
+                case ALG_CLIP: { float t = x > e.alpha ? x : e.alpha; r = t > e.beta ? e.beta : t; } break;
+                case ALG_ROUND: r = rintf(x); break;
+                default: { float t = x > e.alpha ? x : e.alpha; r = t < e.beta ? t : e.beta; } break; // clip_v2
+            }
+            x = __fmul_rn(r, e.scale);
+        }
+    }
+    return x;
+}
+
+// tanh by ex2.approx / rcp.approx: absolute error below 1e-6 on the whole range
+__device__ __forceinline__ float tanh_fast(float a) {
+    float e, r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(a * 2.885390081777927f));
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(e + 1.f));
+    return fmaf(-2.f, r, 1.f);
+}
+
+template <bool FP8, int EPI>
+__device__ __forceinline__ void epilogue_chunk(const b200_matmul_params_t &p, const uint32_t (&v)[32], int64_t m,
+        int64_t n0, const float *wscale, const float *bias, const int32_t *comp, float src_scale, float dst_inv,
+        bool has_comp, bool any_sum, int sum_dt, bool non_default) {
+    const int64_t nvalid = m < p.M ? (p.N - n0 < 32 ? p.N - n0 : 32) : 0;
+    // no early return: the exact-path fallback below votes across the warp
+    char *drow = (char *)p.dst + (size_t)((m < p.M ? m : 0) * p.dst_sm + n0) * (dt_bits(p.dst_dt) / 8);
+    const bool full = nvalid == 32;
+
+    // old destination values for the sum post-op, read before anything is stored
+    float old[32];
+    if (any_sum) {
+        const char *srow = drow; // in place by definition
+        if (full && (sum_dt == B200_DT_S8 || sum_dt == B200_DT_U8) && ((uintptr_t)srow & 15) == 0) {
+            uint4 a = ((const uint4 *)srow)[0], b = ((const uint4 *)srow)[1];
+            const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                const uint32_t byte = (w[j >> 2] >> ((j & 3) * 8)) & 0xff;
+                old[j] = sum_dt == B200_DT_S8 ? (float)(int8_t)byte : (float)byte;
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) old[j] = j < nvalid ? load_f32(sum_dt, srow, j) : 0.f;
+        }
+    }
+
+    float y[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+        float x;
+        if (FP8) {
+            x = __uint_as_float(v[j]);
+        } else {
+            int acc = (int)v[j];
+            if (has_comp) acc -= comp[j];
+            x = (float)acc;
+        }
+        if (p.src_scale.ptr) x = __fmul_rn(x, src_scale);
+        if (p.wei_scale.ptr) x = __fmul_rn(x, wscale[j]);
+        if (p.bias) {
+            const float bv = p.bias_sm ? (j < nvalid ? load_f32(p.bias_dt, p.bias, m * p.bias_sm + (n0 + j) * p.bias_sn) : 0.f)
+                                       : bias[j];
+            x = __fadd_rn(x, bv);
+        }
+        y[j] = x;
+    }
+
+    const float zp_add_common = (!FP8 && p.dst_zp.ptr && !p.dst_zp.s1) ? (float)((const int32_t *)p.dst_zp.ptr)[0] : 0.f;
+    auto tail = [&](float x, int j) -> float {
+        if (p.dst_scale.ptr) x = __fmul_rn(x, dst_inv);
+        if (!FP8 && non_default) {
+            const float z = (p.dst_zp.ptr && p.dst_zp.s1) ? (j < nvalid ? (float)((const int32_t *)p.dst_zp.ptr)[n0 + j] : 0.f)
+                                                           : zp_add_common;
+            x = __fadd_rn(x, z);
+        }
+        return x;
+    };
+
+    if (EPI == EPI_NONE) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) y[j] = tail(y[j], j);
+    } else if (EPI == EPI_SIMPLE) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) y[j] = tail(post_ops_simple(p, y[j], any_sum ? old[j] : 0.f), j);
+    } else if (EPI == EPI_GENERIC) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+            y[j] = tail(j < nvalid ? post_ops_out_of_line(&p, y[j], any_sum ? old[j] : 0.f, m, n0 + j) : 0.f, j);
+    } else {
+        // EPI_GELU_Q: gelu_tanh (then optionally sum) into an integer destination, bit-exact.
+        // The exact value needs a double-precision tanh; almost always it is not needed:
+        //  * |tanh argument| >= 9.02: the float tanh is exactly +-1, gelu(x) is x or -0;
+        //  * otherwise evaluate with a fast tanh (absolute error < 1e-6) and check how far the
+        //    value to be rounded is from a rounding boundary (k + 0.5).  The fast and the
+        //    exact value differ by less than tau (propagated error bound with a 4x margin),
+        //    so away from a boundary both round to the same integer; only elements within
+        //    tau of one are recomputed exactly.
+        const float sqrt_2_over_pi = 0.79788458347320556640625f, fitting_const = 0.044715f;
+        const float sum_scale = any_sum ? p.po[p.npo - 1].scale : 0.f;
+        const float sum_zp = any_sum ? (float)p.po[p.npo - 1].zero_point : 0.f;
+        const float inv_abs = p.dst_scale.ptr ? fabsf(dst_inv) : 1.f;
+        const float lo = p.dst_dt == B200_DT_S8 ? -128.f : 0.f, hi = p.dst_dt == B200_DT_S8 ? 127.f : 255.f;
+        const float elt_scale = p.po[0].scale;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            const float x = y[j];
+            const float g = __fmul_rn(__fmul_rn(sqrt_2_over_pi, x), __fadd_rn(1.f, __fmul_rn(__fmul_rn(fitting_const, x), x)));
+            const bool sat_arg = fabsf(g) >= 9.02f;
+            float gelu;
+            if (sat_arg) {
+                gelu = g > 0 ? x : -0.f;
+            } else {
+                const float h = 0.5f * x;
+                gelu = fmaf(h, tanh_fast(g), h);
+            }
+            auto rest = [&](float ge) -> float {
+                float r = __fmul_rn(ge, elt_scale);
+                if (any_sum) r = __fadd_rn(r, __fmul_rn(sum_scale, __fsub_rn(old[j], sum_zp)));
+                return tail(r, j);
+            };
+            float out = rest(gelu);
+            bool risky = false;
+            if (!sat_arg && out > lo - 1.f && out < hi + 1.f) {
+                const float tau = (2e-6f * fabsf(x) + 2e-6f) * inv_abs * fabsf(elt_scale) + 4e-7f * fabsf(out);
+                const float fr = out - floorf(out);
+                risky = fabsf(fr - 0.5f) < tau;
+            }
+            if (__any_sync(0xffffffffu, risky)) {
+                if (risky) out = rest(gelu_tanh_exact(x));
+            }
+            y[j] = out;
+        }
+    }
+    if (nvalid <= 0) return;
+
+    const bool aligned = full && ((uintptr_t)drow & 15) == 0;
+    if (aligned && (p.dst_dt == B200_DT_S8 || p.dst_dt == B200_DT_U8)) {
+        uint32_t w[8];
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+            uint32_t r = 0;
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+                const int iv = p.dst_dt == B200_DT_S8 ? sat_rne_s8(y[q * 4 + b]) : sat_rne_u8(y[q * 4 + b]);
+                r |= ((uint32_t)iv & 0xff) << (8 * b);
+            }
+            w[q] = r;
+        }
+        ((uint4 *)drow)[0] = make_uint4(w[0], w[1], w[2], w[3]);
+        ((uint4 *)drow)[1] = make_uint4(w[4], w[5], w[6], w[7]);
+    } else if (aligned && p.dst_dt == B200_DT_BF16) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            uint32_t w[4];
+#pragma unroll
+            for (int b = 0; b < 4; ++b)
+                w[b] = (uint32_t)f32_to_bf16_bits(y[q * 8 + 2 * b]) | ((uint32_t)f32_to_bf16_bits(y[q * 8 + 2 * b + 1]) << 16);
+            ((uint4 *)drow)[q] = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+    } else if (aligned && p.dst_dt == B200_DT_F32) {
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+            ((float4 *)drow)[q] = make_float4(y[q * 4], y[q * 4 + 1], y[q * 4 + 2], y[q * 4 + 3]);
+    } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+            if (j < nvalid) store_f32(p.dst_dt, y[j], drow, j);
+    }
+}
+
+// ---- the kernel -------------------------------------------------------------------------
+
+template <bool FP8, int EPI>
+__global__ void __launch_bounds__(NUM_THREADS, 1) matmul_tc8_kernel(const __grid_constant__ CUtensorMap tmap_a,
+        const __grid_constant__ CUtensorMap tmap_b, const __grid_constant__ tc8_args_t args) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    smem_ctrl_t *ctrl = (smem_ctrl_t *)(smem + (size_t)STAGES * STAGE_BYTES);
+    const b200_matmul_params_t &p = args.p;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int num_tiles = args.m_tiles * args.n_tiles;
+    const int KB = args.k_blocks;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&ctrl->full[s], 1);
+            mbar_init(&ctrl->empty[s], 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(&ctrl->tmem_full[a], 1);
+            mbar_init(&ctrl->tmem_empty[a], EPI_WARPS);
+        }
+        ctrl->abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ctrl->tmem_base)),
+                     "r"(TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = ctrl->tmem_base;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                const int m0 = (tile % args.m_tiles) * BM, n0 = (tile / args.m_tiles) * BN;
+                for (int kb = 0; kb < KB; ++kb, ++it) {
+                    const uint32_t s = it % STAGES, r = it / STAGES;
+                    if (!(ok = mbar_wait(&ctrl->empty[s], (r & 1) ^ 1, ctrl, p.status, ST_WAIT_EMPTY))) break;
+                    mbar_expect_tx(&ctrl->full[s], STAGE_BYTES);
+                    uint8_t *sa = smem + (size_t)s * STAGE_BYTES;
+                    tma_load_2d(sa, &tmap_a, kb * BK, m0, &ctrl->full[s]);
+                    tma_load_2d(sa + A_BYTES, &tmap_b, kb * BK, n0, &ctrl->full[s]);
+                }
+            }
+            // drain: every copy this thread issued must have landed before the CTA may exit
+            const uint32_t issued = it;
+            for (uint32_t j = issued > STAGES ? issued - STAGES : 0; j < issued; ++j) {
+                const uint32_t s = j % STAGES, r = j / STAGES;
+                for (uint32_t i = 0; i < WAIT_SPINS; ++i) {
+                    if (mbar_test(&ctrl->full[s], r & 1)) break;
+                    __nanosleep(64);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            uint32_t it = 0, tile_i = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tile_i) {
+                const uint32_t a = tile_i & 1, use = tile_i >> 1;
+                if (!(ok = mbar_wait(&ctrl->tmem_empty[a], (use & 1) ^ 1, ctrl, p.status, ST_WAIT_TMEM_EMPTY))) break;
+                tcgen05_fence_after();
+                const uint32_t tmem_d = tmem_base + a * BN;
+                for (int kb = 0; kb < KB; ++kb, ++it) {
+                    const uint32_t s = it % STAGES, r = it / STAGES;
+                    if (!(ok = mbar_wait(&ctrl->full[s], r & 1, ctrl, p.status, ST_WAIT_FULL))) break;
+                    tcgen05_fence_after();
+                    const uint32_t sa = smem_u32(smem + (size_t)s * STAGE_BYTES);
+                    const uint64_t adesc = make_smem_desc(sa), bdesc = make_smem_desc(sa + A_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BK / 32; ++k) // 32 bytes of K per instruction: +2 in 16-byte units
+                        tcgen05_mma<FP8>(tmem_d, adesc + 2 * k, bdesc + 2 * k, args.idesc, (kb | k) != 0);
+                    tcgen05_commit(&ctrl->empty[s]);
+                }
+                if (ok) tcgen05_commit(&ctrl->tmem_full[a]);
+            }
+        }
+    } else {
+        // ---------------- epilogue warps ----------------
+        const int ew = warp - 2;           // private staging slot
+        const int quarter = warp & 3;      // TMEM lanes this warp may read: 32*quarter .. +31
+        float *wscale = ctrl->wscale[ew], *bias = ctrl->bias[ew];
+        int32_t *comp = ctrl->comp[ew];
+        const bool int8_path = !FP8;
+        const bool has_comp = int8_path && p.src_zp.ptr && p.wei_colsum;
+        const int zp_src = has_comp ? load_int(p.src_zp.dt, p.src_zp.ptr, 0) : 0;
+        const float src_scale = p.src_scale.ptr ? load_f32(p.src_scale.dt, p.src_scale.ptr, 0) : 1.f;
+        const float dst_inv = dst_scale_reciprocal(p);
+        const bool any_sum = has_sum(p);
+        const int sum_dt = sum_dt_of(p);
+        const bool non_default = p.npo > 0 || p.src_scale.ptr || p.wei_scale.ptr || p.dst_scale.ptr || p.src_zp.ptr
+                || p.wei_zp.ptr || p.dst_zp.ptr;
+        uint32_t tile_i = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tile_i) {
+            const int64_t m0 = (int64_t)(tile % args.m_tiles) * BM, n0 = (int64_t)(tile / args.m_tiles) * BN;
+            const uint32_t a = tile_i & 1, use = tile_i >> 1;
+            // per-column vectors of this tile (8 columns per lane)
+            __syncwarp();
+            for (int j = lane; j < BN; j += 32) {
+                const int64_t n = n0 + j;
+                const bool in = n < p.N;
+                wscale[j] = (in && p.wei_scale.ptr) ? load_f32(p.wei_scale.dt, p.wei_scale.ptr, n * p.wei_scale.s1) : 1.f;
+                bias[j] = (in && p.bias && !p.bias_sm) ? load_f32(p.bias_dt, p.bias, n * p.bias_sn) : 0.f;
+                comp[j] = (in && has_comp) ? zp_src * p.wei_colsum[n] : 0;
+            }
+            __syncwarp();
+            ok = mbar_wait(&ctrl->tmem_full[a], use & 1, ctrl, p.status, ST_WAIT_TMEM_FULL);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tcgen05_fence_after();
+            const int64_t m = m0 + quarter * 32 + lane;
+            const uint32_t trow = tmem_base + ((uint32_t)(quarter * 32) << 16) + a * BN;
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                uint32_t v[32];
+                tmem_ld32(trow + c * 32, v);
+                epilogue_chunk<FP8, EPI>(p, v, m, n0 + c * 32, wscale + c * 32, bias + c * 32, comp + c * 32, src_scale,
+                        dst_inv, has_comp, any_sum, sum_dt, non_default);
+            }
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&ctrl->tmem_empty[a]);
+        }
+    }
+
+    __syncwarp();
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tcgen05_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+// ---- host side ------------------------------------------------------------------------------
+
+typedef CUresult (*encode_tiled_fn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+        const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+        CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static encode_tiled_fn get_encode_fn() {
+    static encode_tiled_fn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void *sym = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess
+                && q == cudaDriverEntryPointSuccess)
+            fn = (encode_tiled_fn)sym;
+    });
+    return fn;
+}
+
+// rows x K bytes, row pitch in bytes; box = 128 bytes of K x box_rows rows, 128-byte swizzle;
+// out-of-range parts of a box read as zero
+static bool make_tmap(CUtensorMap *map, const void *base, int64_t rows, int64_t K, int64_t pitch, uint32_t box_rows) {
+    encode_tiled_fn fn = get_encode_fn();
+    if (!fn) return false;
+    const cuuint64_t gdim[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    const cuuint64_t gstride[1] = {(cuuint64_t)pitch};
+    const cuuint32_t box[2] = {(cuuint32_t)BK, box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), gdim, gstride, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE)
+            == CUDA_SUCCESS;
+}
+
+static uint32_t make_idesc(bool fp8, int a_dt, int b_dt) {
+    uint32_t d = 0;
+    if (fp8) {
+        d |= 1u << 4;                                       // accumulator f32
+        d |= (a_dt == B200_DT_F8_E5M2 ? 1u : 0u) << 7;      // A format: 0 = e4m3, 1 = e5m2
+        d |= (b_dt == B200_DT_F8_E5M2 ? 1u : 0u) << 10;     // B format
+    } else {
+        d |= 2u << 4;                                       // accumulator s32
+        d |= (a_dt == B200_DT_S8 ? 1u : 0u) << 7;           // A format: 0 = u8, 1 = s8
+        d |= (b_dt == B200_DT_S8 ? 1u : 0u) << 10;          // B format
+    }
+    // bits 15 / 16: A and B are K-major (0)
+    d |= (uint32_t)(BN >> 3) << 17;
+    d |= (uint32_t)(BM >> 4) << 24;
+    return d;
+}
+
+} // namespace b200
+
+using namespace b200;
+
 extern "C" int b200_matmul_tc8_launch(const b200_matmul_params_t *p, b200_stream_t stream) {
-    (void)p; (void)stream;
-    return B200_ERR_UNSUPPORTED;
+    if (!p || !p->src || !p->wei || !p->dst) return B200_ERR_BAD_ARG;
+    if (p->M < 0 || p->N < 0 || p->K < 0 || p->npo < 0 || p->npo > B200_MAX_POSTOPS) return B200_ERR_BAD_ARG;
+    if (p->M == 0 || p->N == 0 || p->K == 0) return 0;
+    const bool i8 = (p->src_dt == B200_DT_S8 || p->src_dt == B200_DT_U8) && (p->wei_dt == B200_DT_S8 || p->wei_dt == B200_DT_U8);
+    const bool f8 = (p->src_dt == B200_DT_F8_E4M3 || p->src_dt == B200_DT_F8_E5M2)
+            && (p->wei_dt == B200_DT_F8_E4M3 || p->wei_dt == B200_DT_F8_E5M2);
+    if (!i8 && !f8) return B200_ERR_UNSUPPORTED;
+    if (p->K % 16 != 0 || p->src_sk != 1 || p->dst_sn != 1) return B200_ERR_UNSUPPORTED;
+    // weights: packed K-major, or plain with K contiguous
+    int64_t wpitch;
+    if (p->wei_layout == B200_WEI_KMAJOR) wpitch = p->K;
+    else if (p->wei_layout == B200_WEI_PLAIN && p->wei_sk == 1) wpitch = p->wei_sn;
+    else return B200_ERR_UNSUPPORTED;
+    if (p->src_scale.ptr && (p->src_scale.s0 || p->src_scale.s1)) return B200_ERR_UNSUPPORTED;
+    if (p->wei_scale.ptr && (p->wei_scale.s0 || p->wei_scale.g1 != 1)) return B200_ERR_UNSUPPORTED;
+    if (p->dst_scale.ptr && (p->dst_scale.s0 || p->dst_scale.s1)) return B200_ERR_UNSUPPORTED;
+    if (p->src_zp.ptr && (p->src_zp.s0 || p->src_zp.s1 || !p->wei_colsum || f8)) return B200_ERR_UNSUPPORTED;
+    if (p->wei_zp.ptr) return B200_ERR_UNSUPPORTED;
+    if (p->dst_zp.ptr && (p->dst_zp.s0 || p->dst_zp.dt != B200_DT_S32 || f8)) return B200_ERR_UNSUPPORTED;
+    if (((uintptr_t)p->src & 15) || ((uintptr_t)p->wei & 15) || (p->src_sm & 15) || (wpitch & 15)) return B200_ERR_BAD_ARG;
+    if (p->M > INT32_MAX || p->N > INT32_MAX || p->K > INT32_MAX) return B200_ERR_TOO_LARGE;
+
+    CUtensorMap ta, tb;
+    if (!make_tmap(&ta, p->src, p->M, p->K, p->src_sm, BM)) return (int)cudaErrorUnknown;
+    if (!make_tmap(&tb, p->wei, p->N, p->K, wpitch, BN)) return (int)cudaErrorUnknown;
+
+    tc8_args_t a;
+    a.p = *p;
+    a.m_tiles = (int)((p->M + BM - 1) / BM);
+    a.n_tiles = (int)((p->N + BN - 1) / BN);
+    a.k_blocks = (int)((p->K + BK - 1) / BK);
+    a.idesc = make_idesc(f8, p->src_dt, p->wei_dt);
+
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int64_t tiles = (int64_t)a.m_tiles * a.n_tiles;
+    const unsigned grid = (unsigned)(tiles < sms ? tiles : sms);
+
+    // epilogue evaluation mode
+    int epi = EPI_NONE;
+    if (p->npo > 0) {
+        bool simple = true;
+        for (int i = 0; i < p->npo; ++i) {
+            const b200_postop_t &e = p->po[i];
+            const bool elt_ok = e.kind == B200_PO_ELTWISE
+                    && (e.alg == ALG_RELU || e.alg == ALG_RELU_DST || e.alg == ALG_SQUARE || e.alg == ALG_ABS
+                            || e.alg == ALG_LINEAR || e.alg == ALG_HARDSIGMOID || e.alg == ALG_CLIP || e.alg == ALG_CLIP_V2
+                            || e.alg == ALG_CLIP_V2_DST || e.alg == ALG_ROUND || e.alg == ALG_HARDSWISH
+                            || e.alg == ALG_SQRT || e.alg == ALG_SQRT_DST);
+            if (!(e.kind == B200_PO_SUM || elt_ok)) simple = false;
+        }
+        const bool int_dst = p->dst_dt == B200_DT_S8 || p->dst_dt == B200_DT_U8;
+        const bool gelu_q = int_dst && p->po[0].kind == B200_PO_ELTWISE && p->po[0].alg == ALG_GELU_TANH
+                && (p->npo == 1 || (p->npo == 2 && p->po[1].kind == B200_PO_SUM));
+        epi = simple ? EPI_SIMPLE : gelu_q ? EPI_GELU_Q : EPI_GENERIC;
+    }
+
+    typedef void (*kernel_t)(const CUtensorMap, const CUtensorMap, const tc8_args_t);
+    static const kernel_t table[2][4] = {
+            {matmul_tc8_kernel<false, EPI_NONE>, matmul_tc8_kernel<false, EPI_SIMPLE>, matmul_tc8_kernel<false, EPI_GELU_Q>,
+                    matmul_tc8_kernel<false, EPI_GENERIC>},
+            {matmul_tc8_kernel<true, EPI_NONE>, matmul_tc8_kernel<true, EPI_SIMPLE>, matmul_tc8_kernel<true, EPI_GELU_Q>,
+                    matmul_tc8_kernel<true, EPI_GENERIC>}};
+    kernel_t kern = table[f8 ? 1 : 0][epi];
+    // opt in to the large dynamic shared memory once per kernel and device
+    static std::mutex attr_mu;
+    static bool attr_done[64][2][4] = {};
+    {
+        std::lock_guard<std::mutex> g(attr_mu);
+        if (dev < 64 && !attr_done[dev][f8 ? 1 : 0][epi]) {
+            cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
+            if (e != cudaSuccess) return (int)e;
+            attr_done[dev][f8 ? 1 : 0][epi] = true;
+        }
+    }
+    kern<<<grid, NUM_THREADS, SMEM_BYTES, (cudaStream_t)stream>>>(ta, tb, a);
+    return after_launch();
 }

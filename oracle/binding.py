@@ -40,6 +40,7 @@ class Problem(C.Structure):
         ("apply_to_int", C.c_int32), ("npo", C.c_int32), ("po", PostOp * MAX_PO),
         ("tanh_mode", C.c_int32), ("nthreads", C.c_int32),
         ("m0", C.c_int64), ("m_step", C.c_int64), ("n0", C.c_int64), ("n_step", C.c_int64),
+        ("exact_acc", C.c_int32), ("pad4", C.c_int32),
     ]
 
 
@@ -104,7 +105,7 @@ def _quant(q, kind, case):
     return out
 
 
-def make_problem(case, dst, tanh_mode=0, nthreads=0, m0=0, m_step=1, n0=0, n_step=1):
+def make_problem(case, dst, tanh_mode=0, nthreads=0, m0=0, m_step=1, n0=0, n_step=1, exact_acc=0):
     """Fill an orc_problem_t for ``case``; ``dst`` is the raw (M, N) output array
     (pre-loaded with the prior dst contents when a sum post-op is present)."""
     p = Problem()
@@ -140,6 +141,7 @@ def make_problem(case, dst, tanh_mode=0, nthreads=0, m0=0, m_step=1, n0=0, n_ste
             o.sm = (sn_ if sn_ > 1 else 1) if sm_ > 1 else 0
     p.tanh_mode, p.nthreads = tanh_mode, nthreads
     p.m0, p.m_step, p.n0, p.n_step = m0, m_step, n0, n_step
+    p.exact_acc = exact_acc
     return p
 
 
@@ -150,9 +152,9 @@ def new_dst(case):
     return np.zeros((case.M, case.N), dtype=dt.RAW[case.dst_dt])
 
 
-def run_oracle(case, tanh_mode=0, nthreads=0, m_step=1, n_step=1, m0=0, n0=0):
+def run_oracle(case, tanh_mode=0, nthreads=0, m_step=1, n_step=1, m0=0, n0=0, exact_acc=0):
     dst = new_dst(case)
-    p = make_problem(case, dst, tanh_mode, nthreads, m0, m_step, n0, n_step)
+    p = make_problem(case, dst, tanh_mode, nthreads, m0, m_step, n0, n_step, exact_acc)
     rc = lib().orc_matmul(C.byref(p))
     if rc != 0:
         raise RuntimeError("orc_matmul failed: %d" % rc)

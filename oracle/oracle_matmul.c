@@ -378,10 +378,22 @@ static float single_scale(const orc_quant_t *q) { return orc_load_float(q->dt, q
 /* src/cpu/matmul/ref_matmul_int8.cpp:154-261 */
 static void matmul_int8(const orc_problem_t *p) {
     const int64_t M = p->M, N = p->N, K = p->K;
-    int64_t src_zp_ng = p->src_zp.ptr ? K / p->src_zp.g1 : 1;
-    int64_t wei_zp_ng = p->wei_zp.ptr ? K / p->wei_zp.g0 : 1;
-    int64_t src_sc_ng = p->src_scale.ptr ? K / p->src_scale.g1 : 1;
-    int64_t wei_sc_ng = p->wei_scale.ptr ? K / p->wei_scale.g0 : 1;
+    /* ref_matmul_int8.cpp:83-144: the number of K groups is the largest among the
+     * four arguments, and quant_entry_t::get_group returns 1 when no groups were
+     * requested (primitive_attr_quant.hpp:83-90) -- for arguments that are not set
+     * at all, too -- so without explicit groups the loop runs in K groups of 1. */
+    int64_t src_zp_ng = K, wei_zp_ng = K, src_sc_ng = K, wei_sc_ng = K;
+    if (p->src_zp.ptr && p->src_zp.g1 > 1) src_zp_ng = K / p->src_zp.g1;
+    if (p->wei_zp.ptr && p->wei_zp.g0 > 1) wei_zp_ng = K / p->wei_zp.g0;
+    if (p->src_scale.ptr && p->src_scale.g1 > 1) src_sc_ng = K / p->src_scale.g1;
+    if (p->wei_scale.ptr && p->wei_scale.g0 > 1) wei_sc_ng = K / p->wei_scale.g0;
+    if (p->exact_acc) {
+        /* only explicit groups count */
+        if (!(p->src_zp.ptr && p->src_zp.g1 > 1)) src_zp_ng = 1;
+        if (!(p->wei_zp.ptr && p->wei_zp.g0 > 1)) wei_zp_ng = 1;
+        if (!(p->src_scale.ptr && p->src_scale.g1 > 1)) src_sc_ng = 1;
+        if (!(p->wei_scale.ptr && p->wei_scale.g0 > 1)) wei_sc_ng = 1;
+    }
     int64_t ng = src_zp_ng;
     if (wei_zp_ng > ng) ng = wei_zp_ng;
     if (src_sc_ng > ng) ng = src_sc_ng;

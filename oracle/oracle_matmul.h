@@ -78,6 +78,17 @@ typedef struct {
      * untouched.  Lets a test sample a problem that is too large to compute
      * in full on the CPU. */
     int64_t m0, m_step, n0, n_step;
+    /* int8 sources only.  0: exactly what the reference's scalar implementation
+     * does -- its K loop is cut into groups of the smallest group size among
+     * the scale / zero-point arguments, and an argument without explicit
+     * groups counts as group size 1, so that in practice every product s*w is
+     * converted to f32, scaled and accumulated in f32.
+     * 1: "exact accumulation": only explicitly requested groups cut the K
+     * loop; within a group the products are summed exactly in s32 and scaled
+     * once.  This is the library's documented formula and what its optimised
+     * (JIT) implementation and the tensor-core kernel compute. */
+    int32_t exact_acc;
+    int32_t pad4;
 } orc_problem_t;
 
 /* returns 0 on success, non-zero for an unsupported combination */

@@ -7,10 +7,15 @@ that accepts it and compared with the oracle on the same seeded inputs:
     (the oracle runs with the portable tanh the kernels share; transcendental
     eltwise kinds other than tanh may differ by an ulp of the function value and
     are compared with rtol 1e-5);
-  * the tensor-core and decode kernels accumulate in another order: integer
-    destinations are still bit-exact (s32 accumulation is exact), float
-    destinations are held to the case's tolerance (1e-5 relative for f32 after
-    int8, rtol 1e-2 for bf16 / fp8 / weight-decompression).
+  * the int8 tensor-core kernel sums the products exactly in s32 and applies the
+    scales once, as the reference's optimised CPU implementation and its
+    documented formula do, whereas the reference's scalar implementation converts
+    every product to f32 and accumulates in f32.  It is therefore compared with
+    the oracle in its exact-accumulation mode: integer destinations bit-exact,
+    f32 within 1e-5.  tests/test_oracle_vs_reference.py bounds the distance
+    between the two accumulation modes;
+  * the fp8 and decode kernels accumulate in f32 in another order and are held to
+    the case's tolerance (rtol 1e-2).
 """
 import numpy as np
 import pytest
@@ -59,7 +64,8 @@ def test_dispatched_kernel(ctx, name, weights):
         pytest.skip("only the generic kernel accepts this case")
     plan.execute()
     got = plan.result()
-    want = B.run_oracle(c, tanh_mode=1)
+    # the tensor-core kernel sums the products exactly in s32 and scales once
+    want = B.run_oracle(c, tanh_mode=1, exact_acc=1 if "tcgen05_i8" in plan.impl else 0)
     assert_close(c, got, want, "%s via %s" % (name, plan.impl))
 
 
@@ -80,7 +86,7 @@ def test_repeated_execution_and_sum_in_place(ctx):
     second = plan.result()
     c2 = cases.build("c1_small_nonsat")
     c2.dst_init = first
-    assert_bit_exact(second, B.run_oracle(c2, tanh_mode=1))
+    assert_bit_exact(second, B.run_oracle(c2, tanh_mode=1, exact_acc=1))
 
 
 def test_zero_dim_is_a_no_op(ctx):

@@ -49,3 +49,24 @@ def test_sampled_oracle_equals_full():
     mask = np.ones_like(full, dtype=bool)
     mask[3::7, 1::5] = False
     assert np.array_equal(part[mask], c.dst_init[mask])
+
+
+def test_exact_accumulation_mode_is_within_one_lsb_of_the_scalar_reference():
+    """The tensor-core kernel is checked against the oracle's exact-accumulation mode; this
+    bounds how far that mode is from the reference's scalar implementation (which
+    accumulates the scaled products in f32) and from its JIT implementation."""
+    c = W.config1(512, 512, 512, dst_scale=1.0)
+    ref, _, _, _ = B.run_reference(c, impl="ref")
+    jit, _, _, _ = B.run_reference(c, impl="", weights_any=True)
+    exact = B.run_oracle(c, tanh_mode=1, exact_acc=1)
+    for other in (ref, jit):
+        d = np.abs(exact.astype(np.int32) - other.astype(np.int32))
+        assert d.max() <= 1
+        assert (d != 0).mean() < 2e-4
+
+
+def test_exact_accumulation_equals_reference_when_sums_are_exact():
+    """Integer products summed in f32 are exact while they stay below 2^24: there the two modes agree."""
+    c = cases.build("int8_plain_s32")
+    ref, _, _, _ = B.run_reference(c, impl="ref")
+    assert np.array_equal(B.run_oracle(c, exact_acc=1), ref)

@@ -1,0 +1,377 @@
+#!/usr/bin/env python3
+"""Benchmark of the quantized matmul hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+A step is one execution of the int8 matmul primitive with its full epilogue
+(M = N = K = 4096 per GPU: s8 x s8 -> s8, per-N weight scales, bf16 bias,
+GELU-tanh, sum 0.5 over the prior s8 destination, destination scale and
+zero-point) through the public C API of libonednn_b200.so.  Inputs are seeded
+synthetic tensors with the benchmark's value distributions.
+
+Timing: W warm-up steps, then K steps bracketed by a barrier and a device
+synchronisation on both sides and timed with CUDA events on the stream the
+kernels run on; the maximum over ranks is reported.  Successive steps rotate
+over several independent input sets whose total size exceeds the L2 cache, so
+no step finds its operands cached by the previous one.
+
+With N > 1 every rank runs the same per-GPU problem on its own rows of a
+(4096*N) x 4096 x 4096 problem with replicated weights (M-split, no data-path
+collective): weak scaling.
+
+One JSON line is printed by rank 0.  `value` has the operands resident in HBM;
+`e2e` repeats the measurement through the same API with host buffers, the
+host-to-device copies of the step's activations and prior destination and the
+device-to-host copy of the result inside the timed region.
+`--impl reference` times the reference library's own CPU implementation
+(oracle/_ref, all host threads) on the same configuration.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+METRIC = "int8_matmul_4096x4096x4096_postops_throughput"
+UNIT = "TOPS"
+WORKLOAD = "int8 s8:s8:s8 4096x4096:4096x4096, per-N wei scales, bf16 bias, gelu_tanh + sum:0.5, dst scale 0.1 zp 3"
+
+
+def read_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return dict(hbm=float(d["hbm_gbs"]), bf16=float(d["bf16_tflops"]), bf16_sustained=float(d["bf16_tflops_sustained"]),
+                    source="measured")
+    return dict(hbm=6650.0, bf16=1590.0, bf16_sustained=1400.0, source="fallback")
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons, sampled while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.f = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        self.p = None
+
+    def start(self):
+        try:
+            self.p = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q,
+                                       "--format=csv,noheader,nounits", "-lms", "100"], stdout=self.f,
+                                      stderr=subprocess.DEVNULL)
+        except OSError:
+            self.p = None
+
+    def stop(self):
+        if self.p is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.p.terminate()
+        self.p.wait()
+        self.f.flush()
+        rows = [r.split(", ") for r in Path(self.f.name).read_text().strip().splitlines() if r.count(",") >= 8]
+        os.unlink(self.f.name)
+        if not rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        sm = sorted(float(r[1]) for r in rows)
+        reasons = set()
+        for r in rows:
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
+                if v.strip().lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": float(rows[0][2]), "samples": len(rows),
+                "power_w_max": max(float(r[3]) for r in rows), "reasons": sorted(reasons)}
+
+
+def reference_arm(args):
+    """The reference library's own CPU matmul (its JIT implementation, packed weights) on
+    the benchmark configuration, all host threads."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    from onednn_b200 import workloads as W
+    from oracle import binding as B
+    if not B.have_reference():
+        print(json.dumps({"impl": "reference", "unavailable": "oracle/_ref was not built (reference tree absent at build time)"}))
+        return 0
+    case = W.config1()
+    cores = os.cpu_count() or 1
+    steps = max(1, args.steps)
+    _, impl, _, _ = B.run_reference(case, weights_any=True, iters=max(1, args.warmup))
+    _, impl, ms_min, ms_avg = B.run_reference(case, weights_any=True, iters=steps)
+    value = case.ops / (ms_avg * 1e-3) / 1e12
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
+        "warmup": args.warmup, "ms_per_step": ms_avg, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "s8", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "reference_impl": impl, "weights": "packed by the reference's own reorder (not timed)"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "reference",
+                         "sample": "the full 4096^3 problem, %d executions, mean (min %.2f ms)" % (steps, ms_min)},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=40)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200")
+    ap.add_argument("--sets", type=int, default=4, help="independent input sets rotated over (L2 defeat)")
+    ap.add_argument("--no-extras", action="store_true", help="skip the secondary configurations")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return reference_arm(args)
+    args.warmup = max(args.warmup, 3)
+
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    from onednn_b200 import api, dtypes as dt, workloads as W
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the engine has no CPU fallback")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    peaks = read_peaks()
+    eng = api.Engine(index=local)
+    tstream = torch.cuda.current_stream()
+    strm = api.Stream(eng, cuda_stream=tstream.cuda_stream)
+
+    # ---- per-GPU problem: rows [rank*4096, (rank+1)*4096) of the M-split problem ----
+    case = W.config1(seed=20240612 + rank)
+    plan = api.CasePlan(case, eng, strm, weights="any")       # packs the weights once (not timed)
+    impl = plan.impl
+    M, N, K = case.M, case.N, case.K
+
+    def dev(a):
+        return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+    def wrap(t, md):
+        return api.Memory(md, eng, handle=t.data_ptr())
+
+    # rotating input sets: src, prior dst / dst (weights and per-N vectors are shared)
+    sets = []
+    for i in range(args.sets):
+        src_t = dev(np.roll(case.src, i, axis=0))
+        dst0_t = dev(np.roll(case.dst_init, i, axis=0))
+        dst_t = dst0_t.clone()
+        a = dict(plan.args)
+        a[api.ARG_SRC] = wrap(src_t, plan.mds["src"])
+        a[api.ARG_DST] = wrap(dst_t, plan.mds["dst"])
+        sets.append(dict(src=src_t, dst0=dst0_t, dst=dst_t, args=a))
+    set_bytes = (M * K + 2 * M * N) * args.sets + K * N
+
+    def step(i):
+        plan.prim.execute(strm, sets[i % args.sets]["args"])
+
+    for i in range(args.warmup):
+        step(i)
+    barrier()
+    sampler = ClockSampler(local)
+    sampler.start()
+    launches0 = api.lib().b200_launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record(tstream)
+    for i in range(args.steps):
+        step(i)
+    e1.record(tstream)
+    barrier()
+    ms_total = e0.elapsed_time(e1)
+    launches = api.lib().b200_launch_count() - launches0
+    clocks = sampler.stop()
+    strm.wait()
+
+    # ---- the dominant kernel alone: one launch per event pair ----
+    kern_ms = []
+    for i in range(min(args.steps, 20)):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(tstream)
+        step(i)
+        b.record(tstream)
+        b.synchronize()
+        kern_ms.append(a.elapsed_time(b))
+    kern_avg = sum(kern_ms) / len(kern_ms)
+
+    # ---- end to end: host buffers in, host buffer out, same API ----
+    h_src = [torch.from_numpy(np.roll(case.src, i, axis=0).copy()).pin_memory() for i in range(2)]
+    h_dst0 = [torch.from_numpy(np.roll(case.dst_init, i, axis=0).copy()).pin_memory() for i in range(2)]
+    h_out = torch.empty((M, N), dtype=torch.int8).pin_memory()
+
+    def e2e_step(i):
+        s = sets[i % args.sets]
+        s["src"].copy_(h_src[i % 2], non_blocking=True)
+        s["dst"].copy_(h_dst0[i % 2], non_blocking=True)
+        plan.prim.execute(strm, s["args"])
+        h_out.copy_(s["dst"], non_blocking=True)
+
+    e2e_steps = max(3, min(args.steps, 10))
+    for i in range(3):
+        e2e_step(i)
+    barrier()
+    e0.record(tstream)
+    for i in range(e2e_steps):
+        e2e_step(i)
+    e1.record(tstream)
+    barrier()
+    e2e_ms = e0.elapsed_time(e1) / e2e_steps
+
+    # ---- max over ranks ----
+    t = torch.tensor([ms_total, e2e_ms, kern_avg], device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_total, e2e_ms, kern_avg = (float(x) for x in t.tolist())
+    ms_per_step = ms_total / args.steps
+    ops = case.ops * world
+    value = ops / (ms_per_step * 1e-3) / 1e12
+    e2e_value = ops / (e2e_ms * 1e-3) / 1e12
+
+    # ---- correctness of what was timed: sampled rows / columns against the CPU oracle ----
+    check = None
+    extras = {}
+    cpu_baseline = None
+    if rank == 0:
+        try:
+            from oracle import binding as B
+            s = sets[0]
+            s["dst"].copy_(s["dst0"])
+            plan.prim.execute(strm, s["args"])
+            strm.wait()
+            got = s["dst"].cpu().numpy()
+            c0 = W.config1(seed=20240612 + rank)
+            want = B.run_oracle(c0, tanh_mode=1, exact_acc=1, m_step=61, n_step=53)
+            diff = int((got[::61, ::53] != want[::61, ::53]).sum())
+            check = {"sampled_elements": int(want[::61, ::53].size), "mismatches_vs_cpu_oracle": diff}
+        except Exception as ex:  # the check must not hide the measurement
+            check = {"error": repr(ex)}
+
+        if not args.no_extras:
+            extras = run_extras(api, W, dt, eng, strm, tstream, torch, np, peaks)
+
+        if not args.no_cpu_baseline:
+            try:
+                from oracle import binding as B
+                if B.have_reference():
+                    _, rimpl, rmin, ravg = B.run_reference(W.config1(), weights_any=True, iters=10)
+                    cpu_baseline = {"value": case.ops / (ravg * 1e-3) / 1e12, "unit": UNIT, "cores": os.cpu_count(),
+                                    "kind": "reference",
+                                    "sample": "the full 4096^3 problem, 10 executions of %s (weights packed by its own reorder), mean" % rimpl}
+                else:
+                    small = W.config1(512, 512, 1024)
+                    t0 = time.time()
+                    B.run_oracle(small)
+                    sec = time.time() - t0
+                    cpu_baseline = {"value": small.ops / sec / 1e12, "unit": UNIT, "cores": os.cpu_count(), "kind": "port",
+                                    "sample": "512x1024x512 slice of the workload, one execution of the C oracle"}
+            except Exception as ex:
+                cpu_baseline = {"error": repr(ex)}
+
+    if rank == 0:
+        int8_peak = 2.0 * peaks["bf16"]
+        achieved = case.ops / (kern_avg * 1e-3) / 1e12
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "s8", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "per_gpu": "4096x4096x4096", "parallelism": "m-split x%d, replicated weights" % world,
+                       "impl": impl, "l2": "rotating %d input sets, %.0f MB in total (> 126 MB L2)" % (args.sets, set_bytes / 1e6)},
+            "roofline": {"bound": "tensor", "achieved": achieved, "peak": int8_peak, "unit": "TFLOP/s",
+                         "frac": achieved / int8_peak, "traffic": None,
+                         "kernel": "matmul_tc8_kernel<int8, gelu+sum requant>", "kernel_ms": kern_avg,
+                         "peak_note": "2 x %s bf16 dense burst (%.1f TF/s); no measured int8 figure exists; nominal 4500"
+                                      % (peaks["source"], peaks["bf16"])},
+            "cpu_baseline": cpu_baseline,
+            "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms, "h2d_bytes_per_step": M * K + M * N,
+                    "d2h_bytes_per_step": M * N},
+            "gpu_launches": int(launches),
+            "clocks": clocks,
+            "check": check,
+            "also": extras,
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+def run_extras(api, W, dt, eng, strm, tstream, torch, np, peaks):
+    """Secondary configurations of the same path, each timed alone with an L2 flush between launches."""
+    out = {}
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+
+    def timed(plan, iters):
+        ts = []
+        for _ in range(iters):
+            flush.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(tstream)
+            plan.execute()
+            b.record(tstream)
+            b.synchronize()
+            ts.append(a.elapsed_time(b))
+        ts.sort()
+        return ts[len(ts) // 2], ts[0]
+
+    try:
+        for m in (1, 16, 128):
+            c = W.config2(m)
+            plan = api.CasePlan(c, eng, strm, weights="any")
+            for _ in range(3):
+                plan.execute()
+            med, best = timed(plan, 15)
+            nbytes = c.algorithmic_bytes()
+            gbs = nbytes / (med * 1e-3) / 1e9
+            out["c2_wc_u4_m%d" % m] = {"impl": plan.impl, "ms": med, "ms_min": best, "algorithmic_bytes": nbytes, "GB/s": gbs,
+                                       "frac_of_hbm_%s" % peaks["source"]: gbs / peaks["hbm"], "GOPS": c.ops / (med * 1e-3) / 1e9}
+            del plan
+    except Exception as ex:
+        out["c2_error"] = repr(ex)
+    try:
+        c = W.config0()
+        plan = api.CasePlan(c, eng, strm, weights="any")
+        for _ in range(3):
+            plan.execute()
+        med, best = timed(plan, 15)
+        out["c0_int8_128x1024x1024"] = {"impl": plan.impl, "us": med * 1e3, "us_min": best * 1e3}
+        del plan
+    except Exception as ex:
+        out["c0_error"] = repr(ex)
+    try:
+        c = W.config3(4096, 4096, 4096)
+        plan = api.CasePlan(c, eng, strm, weights="any")
+        for _ in range(3):
+            plan.execute()
+        med, best = timed(plan, 10)
+        out["c3_fp8_4096"] = {"impl": plan.impl, "ms": med, "TFLOPS": c.ops / (med * 1e-3) / 1e12,
+                              "note": "4096^3 slice of the 8192^3 configuration"}
+        del plan
+    except Exception as ex:
+        out["c3_error"] = repr(ex)
+    return out
+
+
+if __name__ == "__main__":
+    sys.exit(main())

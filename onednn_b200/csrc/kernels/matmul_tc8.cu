@@ -10,7 +10,7 @@
 // place of the reference's AMX brgemm kernel
 // (src/cpu/x64/matmul/brgemm_matmul.cpp:383-496, jit_brgemm_amx_uker.cpp:1286-1445).
 //
-// Structure (one persistent CTA per SM, 192 threads):
+// Structure (one persistent CTA per SM, 320 threads):
 //   warp 0      TMA producer: cp.async.bulk.tensor 2-D loads (no multicast) of a
 //               128 x 128-byte A tile and a 256 x 128-byte W tile per k-block into a
 //               4-stage ring of 128-byte-swizzled shared memory, completion on
@@ -21,7 +21,8 @@
 //               stage ("empty" mbarrier) and, after the last k-block, publishes the
 //               accumulator ("tmem_full").  Also owns the TMEM allocation (512
 //               columns = two 128 x 256 x 32-bit accumulators).
-//   warps 2-5   epilogue: tcgen05.ld 32 lanes x 32 columns at a time, exact s32
+//   warps 2-9   epilogue (two per TMEM lane quarter, each converts half of the
+//               tile's columns): tcgen05.ld 32 lanes x 16 columns at a time, exact s32
 //               zero-point compensation (acc - zp_src * colsum_W[n]), the f32
 //               epilogue chain, packed 16-byte stores.  With two accumulator
 //               stages the epilogue of tile i overlaps the main loop of tile i+1.
@@ -46,8 +47,10 @@ constexpr int STAGES = 4;
 constexpr int A_BYTES = BM * BK; // 16 KiB
 constexpr int B_BYTES = BN * BK; // 32 KiB
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-constexpr int NUM_THREADS = 192;
-constexpr int EPI_WARPS = 4;
+constexpr int EPI_WARPS = 8;                  // two per TMEM lane quarter, each takes half of the columns
+constexpr int NUM_THREADS = 64 + 32 * EPI_WARPS;
+constexpr int EPI_COLS = BN / 2;              // columns per epilogue warp
+constexpr int CH = 16;                        // columns per epilogue chunk (held in registers)
 constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t WAIT_SPINS = 1u << 24; // bounded wait: of the order of a second with the back-off below
 
@@ -60,10 +63,14 @@ struct smem_ctrl_t {
     uint64_t tmem_empty[2];
     uint32_t tmem_base;
     volatile uint32_t abort;
-    // per epilogue warp: per-column vectors of the current tile
-    float wscale[EPI_WARPS][BN];
-    float bias[EPI_WARPS][BN];
-    int32_t comp[EPI_WARPS][BN]; // zp_src * colsum_W[n]
+    // per epilogue warp: per-column vectors of its half of the current tile
+    float wscale[EPI_WARPS][EPI_COLS];   // weights scale, 1 when unset
+    float bias[EPI_WARPS][EPI_COLS];     // bias, -0 when unset (x + -0 == x for every x)
+    int32_t comp[EPI_WARPS][EPI_COLS];   // zp_src * colsum_W[n], 0 when unset
+    float zp[EPI_WARPS][EPI_COLS];       // destination zero-point addend
+    // per epilogue warp: staging of one chunk for the interpreted (EPI_GENERIC) path;
+    // pitch 33 keeps it free of bank conflicts
+    float stage[EPI_WARPS][CH][33];
 };
 
 constexpr size_t SMEM_BYTES = 1024 /* alignment slack */ + (size_t)STAGES * STAGE_BYTES + sizeof(smem_ctrl_t);
@@ -139,16 +146,13 @@ __device__ __forceinline__ void tcgen05_mma(uint32_t tmem_d, uint64_t adesc, uin
     }
 }
 
-// 32 consecutive 32-bit columns of this thread's TMEM lane
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+// 16 consecutive 32-bit columns of this thread's TMEM lane
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
     asm volatile(
-            "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-            "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-            "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+            "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+            "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
             : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
-            "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
-            "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
-            "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+            "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
             : "r"(taddr)
             : "memory");
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
@@ -172,53 +176,28 @@ struct tc8_args_t {
     uint32_t idesc;
 };
 
-// ---- epilogue on 32 columns of one row ------------------------------------------------
+// ---- epilogue on CH columns of one row ---------------------------------------------------
 //
 // The post-op chain is evaluated in one of four ways, chosen on the host:
 //   EPI_NONE    no post-ops;
-//   EPI_SIMPLE  only sum and non-transcendental eltwise kinds: a small inline interpreter;
+//   EPI_SIMPLE  only sum and non-transcendental eltwise kinds;
 //   EPI_GELU_Q  [gelu_tanh] or [gelu_tanh, sum] into an s8 / u8 destination: see below;
-//   EPI_GENERIC anything else: the shared interpreter, called out of line per element.
+//   EPI_GENERIC anything else: the interpreter shared with the generic kernel.
+//
+// The first three keep the CH values of a chunk in registers and are written
+// without per-element branches, so that the compiler can interleave the CH
+// independent dependency chains: an epilogue warp has at most one other warp on
+// its scheduler to hide latency behind.  Unset scales / bias / zero-points are
+// neutral elements (x * 1, x + -0) instead of branches.
 enum { EPI_NONE = 0, EPI_SIMPLE = 1, EPI_GELU_Q = 2, EPI_GENERIC = 3 };
 
-__device__ __noinline__ float post_ops_out_of_line(const b200_matmul_params_t *p, float x, float old, int64_t m, int64_t n) {
-    return apply_post_ops(*p, x, old, m, n);
-}
-__device__ __noinline__ float gelu_tanh_exact(float x) { return gelu_tanh_f32(x); }
-
-__device__ __forceinline__ bool eltwise_is_simple(int alg) {
-    switch (alg) {
-        case ALG_RELU: case ALG_RELU_DST: case ALG_SQUARE: case ALG_ABS: case ALG_LINEAR: case ALG_HARDSIGMOID:
-        case ALG_CLIP: case ALG_CLIP_V2: case ALG_CLIP_V2_DST: case ALG_ROUND: case ALG_HARDSWISH: case ALG_SQRT:
-        case ALG_SQRT_DST: return true;
-        default: return false;
-    }
-}
-
-__device__ __forceinline__ float post_ops_simple(const b200_matmul_params_t &p, float x, float old) {
-    for (int i = 0; i < p.npo; ++i) {
-        const b200_postop_t &e = p.po[i];
-        if (e.kind == B200_PO_SUM) {
-            x = __fadd_rn(x, __fmul_rn(e.scale, __fsub_rn(old, (float)e.zero_point)));
-        } else {
-            float r;
-            switch (e.alg) {
-                case ALG_RELU: case ALG_RELU_DST: r = x > 0 ? x : __fmul_rn(x, e.alpha); break;
-                case ALG_SQUARE: r = __fmul_rn(x, x); break;
-                case ALG_ABS: r = x > 0 ? x : -x; break;
-                case ALG_SQRT: case ALG_SQRT_DST: r = __fsqrt_rn(x); break;
-                case ALG_LINEAR: r = __fadd_rn(__fmul_rn(e.alpha, x), e.beta); break;
-                case ALG_HARDSIGMOID: r = hardsigmoid_f32(x, e.alpha, e.beta); break;
-                case ALG_HARDSWISH: r = __fmul_rn(x, hardsigmoid_f32(x, e.alpha, e.beta)); break;
-                case ALG_CLIP: { float t = x > e.alpha ? x : e.alpha; r = t > e.beta ? e.beta : t; } break;
-                case ALG_ROUND: r = rintf(x); break;
-                default: { float t = x > e.alpha ? x : e.alpha; r = t < e.beta ? t : e.beta; } break; // clip_v2
-            }
-            x = __fmul_rn(r, e.scale);
-        }
-    }
-    return x;
-}
+struct epi_consts_t {
+    float src_scale;   // 1 when unset
+    float dst_inv;     // 1 when unset
+    bool any_sum;
+    int sum_dt;
+    bool int8_nondefault; // the int8 path adds the destination zero-point (0 when unset) whenever any attribute is set
+};
 
 // tanh by ex2.approx / rcp.approx: absolute error below 1e-6 on the whole range
 __device__ __forceinline__ float tanh_fast(float a) {
@@ -228,127 +207,67 @@ __device__ __forceinline__ float tanh_fast(float a) {
     return fmaf(-2.f, r, 1.f);
 }
 
-template <bool FP8, int EPI>
-__device__ __forceinline__ void epilogue_chunk(const b200_matmul_params_t &p, const uint32_t (&v)[32], int64_t m,
-        int64_t n0, const float *wscale, const float *bias, const int32_t *comp, float src_scale, float dst_inv,
-        bool has_comp, bool any_sum, int sum_dt, bool non_default) {
-    const int64_t nvalid = m < p.M ? (p.N - n0 < 32 ? p.N - n0 : 32) : 0;
-    // no early return: the exact-path fallback below votes across the warp
-    char *drow = (char *)p.dst + (size_t)((m < p.M ? m : 0) * p.dst_sm + n0) * (dt_bits(p.dst_dt) / 8);
-    const bool full = nvalid == 32;
-
-    // old destination values for the sum post-op, read before anything is stored
-    float old[32];
-    if (any_sum) {
-        const char *srow = drow; // in place by definition
-        if (full && (sum_dt == B200_DT_S8 || sum_dt == B200_DT_U8) && ((uintptr_t)srow & 15) == 0) {
-            uint4 a = ((const uint4 *)srow)[0], b = ((const uint4 *)srow)[1];
-            const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+// one non-transcendental eltwise kind applied to the CH values in registers
+__device__ __forceinline__ void eltwise_simple_chunk(const b200_postop_t &e, float (&y)[CH]) {
+    const float al = e.alpha, be = e.beta, sc = e.scale;
+    switch (e.alg) {
+        case ALG_RELU: case ALG_RELU_DST:
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-                const uint32_t byte = (w[j >> 2] >> ((j & 3) * 8)) & 0xff;
-                old[j] = sum_dt == B200_DT_S8 ? (float)(int8_t)byte : (float)byte;
+            for (int j = 0; j < CH; ++j) y[j] = __fmul_rn(y[j] > 0 ? y[j] : __fmul_rn(y[j], al), sc);
+            break;
+        case ALG_SQUARE:
+#pragma unroll
+            for (int j = 0; j < CH; ++j) y[j] = __fmul_rn(__fmul_rn(y[j], y[j]), sc);
+            break;
+        case ALG_ABS:
+#pragma unroll
+            for (int j = 0; j < CH; ++j) y[j] = __fmul_rn(y[j] > 0 ? y[j] : -y[j], sc);
+            break;
+        case ALG_SQRT: case ALG_SQRT_DST:
+#pragma unroll
+            for (int j = 0; j < CH; ++j) y[j] = __fmul_rn(__fsqrt_rn(y[j]), sc);
+            break;
+        case ALG_LINEAR:
+#pragma unroll
+            for (int j = 0; j < CH; ++j) y[j] = __fmul_rn(__fadd_rn(__fmul_rn(al, y[j]), be), sc);
+            break;
+        case ALG_HARDSIGMOID:
+#pragma unroll
+            for (int j = 0; j < CH; ++j) y[j] = __fmul_rn(hardsigmoid_f32(y[j], al, be), sc);
+            break;
+        case ALG_HARDSWISH:
+#pragma unroll
+            for (int j = 0; j < CH; ++j) y[j] = __fmul_rn(__fmul_rn(y[j], hardsigmoid_f32(y[j], al, be)), sc);
+            break;
+        case ALG_CLIP:
+#pragma unroll
+            for (int j = 0; j < CH; ++j) {
+                const float t = y[j] > al ? y[j] : al;
+                y[j] = __fmul_rn(t > be ? be : t, sc);
             }
-        } else {
+            break;
+        case ALG_ROUND:
 #pragma unroll
-            for (int j = 0; j < 32; ++j) old[j] = j < nvalid ? load_f32(sum_dt, srow, j) : 0.f;
-        }
+            for (int j = 0; j < CH; ++j) y[j] = __fmul_rn(rintf(y[j]), sc);
+            break;
+        default: // clip_v2
+#pragma unroll
+            for (int j = 0; j < CH; ++j) {
+                const float t = y[j] > al ? y[j] : al;
+                y[j] = __fmul_rn(t < be ? t : be, sc);
+            }
+            break;
     }
+}
 
-    float y[32];
-#pragma unroll
-    for (int j = 0; j < 32; ++j) {
-        float x;
-        if (FP8) {
-            x = __uint_as_float(v[j]);
-        } else {
-            int acc = (int)v[j];
-            if (has_comp) acc -= comp[j];
-            x = (float)acc;
-        }
-        if (p.src_scale.ptr) x = __fmul_rn(x, src_scale);
-        if (p.wei_scale.ptr) x = __fmul_rn(x, wscale[j]);
-        if (p.bias) {
-            const float bv = p.bias_sm ? (j < nvalid ? load_f32(p.bias_dt, p.bias, m * p.bias_sm + (n0 + j) * p.bias_sn) : 0.f)
-                                       : bias[j];
-            x = __fadd_rn(x, bv);
-        }
-        y[j] = x;
-    }
-
-    const float zp_add_common = (!FP8 && p.dst_zp.ptr && !p.dst_zp.s1) ? (float)((const int32_t *)p.dst_zp.ptr)[0] : 0.f;
-    auto tail = [&](float x, int j) -> float {
-        if (p.dst_scale.ptr) x = __fmul_rn(x, dst_inv);
-        if (!FP8 && non_default) {
-            const float z = (p.dst_zp.ptr && p.dst_zp.s1) ? (j < nvalid ? (float)((const int32_t *)p.dst_zp.ptr)[n0 + j] : 0.f)
-                                                           : zp_add_common;
-            x = __fadd_rn(x, z);
-        }
-        return x;
-    };
-
-    if (EPI == EPI_NONE) {
-#pragma unroll
-        for (int j = 0; j < 32; ++j) y[j] = tail(y[j], j);
-    } else if (EPI == EPI_SIMPLE) {
-#pragma unroll
-        for (int j = 0; j < 32; ++j) y[j] = tail(post_ops_simple(p, y[j], any_sum ? old[j] : 0.f), j);
-    } else if (EPI == EPI_GENERIC) {
-#pragma unroll
-        for (int j = 0; j < 32; ++j)
-            y[j] = tail(j < nvalid ? post_ops_out_of_line(&p, y[j], any_sum ? old[j] : 0.f, m, n0 + j) : 0.f, j);
-    } else {
-        // EPI_GELU_Q: gelu_tanh (then optionally sum) into an integer destination, bit-exact.
-        // The exact value needs a double-precision tanh; almost always it is not needed:
-        //  * |tanh argument| >= 9.02: the float tanh is exactly +-1, gelu(x) is x or -0;
-        //  * otherwise evaluate with a fast tanh (absolute error < 1e-6) and check how far the
-        //    value to be rounded is from a rounding boundary (k + 0.5).  The fast and the
-        //    exact value differ by less than tau (propagated error bound with a 4x margin),
-        //    so away from a boundary both round to the same integer; only elements within
-        //    tau of one are recomputed exactly.
-        const float sqrt_2_over_pi = 0.79788458347320556640625f, fitting_const = 0.044715f;
-        const float sum_scale = any_sum ? p.po[p.npo - 1].scale : 0.f;
-        const float sum_zp = any_sum ? (float)p.po[p.npo - 1].zero_point : 0.f;
-        const float inv_abs = p.dst_scale.ptr ? fabsf(dst_inv) : 1.f;
-        const float lo = p.dst_dt == B200_DT_S8 ? -128.f : 0.f, hi = p.dst_dt == B200_DT_S8 ? 127.f : 255.f;
-        const float elt_scale = p.po[0].scale;
-#pragma unroll
-        for (int j = 0; j < 32; ++j) {
-            const float x = y[j];
-            const float g = __fmul_rn(__fmul_rn(sqrt_2_over_pi, x), __fadd_rn(1.f, __fmul_rn(__fmul_rn(fitting_const, x), x)));
-            const bool sat_arg = fabsf(g) >= 9.02f;
-            float gelu;
-            if (sat_arg) {
-                gelu = g > 0 ? x : -0.f;
-            } else {
-                const float h = 0.5f * x;
-                gelu = fmaf(h, tanh_fast(g), h);
-            }
-            auto rest = [&](float ge) -> float {
-                float r = __fmul_rn(ge, elt_scale);
-                if (any_sum) r = __fadd_rn(r, __fmul_rn(sum_scale, __fsub_rn(old[j], sum_zp)));
-                return tail(r, j);
-            };
-            float out = rest(gelu);
-            bool risky = false;
-            if (!sat_arg && out > lo - 1.f && out < hi + 1.f) {
-                const float tau = (2e-6f * fabsf(x) + 2e-6f) * inv_abs * fabsf(elt_scale) + 4e-7f * fabsf(out);
-                const float fr = out - floorf(out);
-                risky = fabsf(fr - 0.5f) < tau;
-            }
-            if (__any_sync(0xffffffffu, risky)) {
-                if (risky) out = rest(gelu_tanh_exact(x));
-            }
-            y[j] = out;
-        }
-    }
+// pack CH final f32 values of one row and store them (or the valid part of them)
+__device__ __forceinline__ void store_row(const b200_matmul_params_t &p, const float (&y)[CH], char *drow, int64_t nvalid) {
     if (nvalid <= 0) return;
-
-    const bool aligned = full && ((uintptr_t)drow & 15) == 0;
+    const bool aligned = nvalid == CH && ((uintptr_t)drow & 15) == 0;
     if (aligned && (p.dst_dt == B200_DT_S8 || p.dst_dt == B200_DT_U8)) {
-        uint32_t w[8];
+        uint32_t w[CH / 4];
 #pragma unroll
-        for (int q = 0; q < 8; ++q) {
+        for (int q = 0; q < CH / 4; ++q) {
             uint32_t r = 0;
 #pragma unroll
             for (int b = 0; b < 4; ++b) {
@@ -358,10 +277,9 @@ __device__ __forceinline__ void epilogue_chunk(const b200_matmul_params_t &p, co
             w[q] = r;
         }
         ((uint4 *)drow)[0] = make_uint4(w[0], w[1], w[2], w[3]);
-        ((uint4 *)drow)[1] = make_uint4(w[4], w[5], w[6], w[7]);
     } else if (aligned && p.dst_dt == B200_DT_BF16) {
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
+        for (int q = 0; q < CH / 8; ++q) {
             uint32_t w[4];
 #pragma unroll
             for (int b = 0; b < 4; ++b)
@@ -370,13 +288,131 @@ __device__ __forceinline__ void epilogue_chunk(const b200_matmul_params_t &p, co
         }
     } else if (aligned && p.dst_dt == B200_DT_F32) {
 #pragma unroll
-        for (int q = 0; q < 8; ++q)
+        for (int q = 0; q < CH / 4; ++q)
             ((float4 *)drow)[q] = make_float4(y[q * 4], y[q * 4 + 1], y[q * 4 + 2], y[q * 4 + 3]);
     } else {
 #pragma unroll
-        for (int j = 0; j < 32; ++j)
+        for (int j = 0; j < CH; ++j)
             if (j < nvalid) store_f32(p.dst_dt, y[j], drow, j);
     }
+}
+
+template <bool FP8, int EPI>
+__device__ __forceinline__ void epilogue_chunk(const b200_matmul_params_t &p, const uint32_t (&v)[CH], int64_t m,
+        int64_t n0, const float *wscale, const float *bias, const int32_t *comp, const float *zp, const epi_consts_t &k,
+        float (*stage)[33], int lane) {
+    const int64_t nvalid = m < p.M ? (p.N - n0 < CH ? p.N - n0 : CH) : 0;
+    char *drow = (char *)p.dst + (size_t)((m < p.M ? m : 0) * p.dst_sm + n0) * (dt_bits(p.dst_dt) / 8);
+
+    // accumulator -> scaled value + bias (neutral elements where unset)
+    float y[CH];
+#pragma unroll
+    for (int j = 0; j < CH; ++j) {
+        const float x = FP8 ? __uint_as_float(v[j]) : (float)((int)v[j] - comp[j]);
+        y[j] = __fadd_rn(__fmul_rn(__fmul_rn(x, k.src_scale), wscale[j]), bias[j]);
+    }
+
+    // prior destination values for sum (read before anything is stored)
+    float old[CH];
+    if (EPI != EPI_NONE && k.any_sum) {
+        const bool fast = nvalid == CH && (k.sum_dt == B200_DT_S8 || k.sum_dt == B200_DT_U8) && ((uintptr_t)drow & 15) == 0;
+        if (fast) {
+            const uint4 a = ((const uint4 *)drow)[0];
+            const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+            for (int j = 0; j < CH; ++j) {
+                const uint32_t byte = (w[j >> 2] >> ((j & 3) * 8)) & 0xff;
+                old[j] = k.sum_dt == B200_DT_S8 ? (float)(int8_t)byte : (float)byte;
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < CH; ++j) old[j] = j < nvalid ? load_f32(k.sum_dt, drow, j) : 0.f;
+        }
+    }
+    // destination scale and zero-point
+    auto tail = [&](float x, int j) -> float {
+        x = __fmul_rn(x, k.dst_inv);
+        return (!FP8 && k.int8_nondefault) ? __fadd_rn(x, zp[j]) : x;
+    };
+
+    if (EPI == EPI_NONE) {
+#pragma unroll
+        for (int j = 0; j < CH; ++j) y[j] = tail(y[j], j);
+    } else if (EPI == EPI_SIMPLE) {
+        for (int i = 0; i < p.npo; ++i) {
+            const b200_postop_t &e = p.po[i];
+            if (e.kind == B200_PO_SUM) {
+                const float sc = e.scale, z = (float)e.zero_point;
+#pragma unroll
+                for (int j = 0; j < CH; ++j) y[j] = __fadd_rn(y[j], __fmul_rn(sc, __fsub_rn(old[j], z)));
+            } else {
+                eltwise_simple_chunk(e, y);
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < CH; ++j) y[j] = tail(y[j], j);
+    } else if (EPI == EPI_GELU_Q) {
+        // gelu_tanh (then optionally sum) into an integer destination, bit-exact.  The exact
+        // value needs a double-precision tanh; almost always it is not needed:
+        //  * |tanh argument| >= 9.02: the float tanh is exactly +-1, gelu(x) is x or -0;
+        //  * otherwise evaluate with a fast tanh (absolute error < 1e-6) and check how far the
+        //    value to be rounded is from a rounding boundary (k + 0.5).  The fast and the
+        //    exact value differ by less than tau (propagated error bound with a 4x margin),
+        //    so away from a boundary both round to the same integer; only elements within
+        //    tau of one are recomputed exactly (one warp vote per chunk).
+        const float sqrt_2_over_pi = 0.79788458347320556640625f, fitting_const = 0.044715f;
+        const float elt_scale = p.po[0].scale;
+        const float sum_scale = k.any_sum ? p.po[1].scale : 0.f, sum_zp = k.any_sum ? (float)p.po[1].zero_point : 0.f;
+        const float inv_abs = fabsf(k.dst_inv) * fabsf(elt_scale);
+        const float lo = p.dst_dt == B200_DT_S8 ? -128.f : 0.f, hi = p.dst_dt == B200_DT_S8 ? 127.f : 255.f;
+        auto rest = [&](float ge, int j) -> float {
+            float r = __fmul_rn(ge, elt_scale);
+            if (k.any_sum) r = __fadd_rn(r, __fmul_rn(sum_scale, __fsub_rn(old[j], sum_zp)));
+            return tail(r, j);
+        };
+        uint32_t risky = 0;
+        float xs[CH];
+#pragma unroll
+        for (int j = 0; j < CH; ++j) {
+            const float x = y[j];
+            xs[j] = x;
+            const float g = __fmul_rn(__fmul_rn(sqrt_2_over_pi, x), __fadd_rn(1.f, __fmul_rn(__fmul_rn(fitting_const, x), x)));
+            const bool sat_arg = fabsf(g) >= 9.02f;
+            const float h = 0.5f * x;
+            const float approx = fmaf(h, tanh_fast(g), h);
+            const float gelu = sat_arg ? (g > 0 ? x : -0.f) : approx;
+            const float out = rest(gelu, j);
+            const float tau = fmaf(2e-6f * inv_abs, fabsf(x) + 1.f, 4e-7f * fabsf(out));
+            const float fr = out - floorf(out);
+            const bool r = !sat_arg && out > lo - 1.f && out < hi + 1.f && fabsf(fr - 0.5f) < tau;
+            risky |= (r ? 1u : 0u) << j;
+            y[j] = out;
+        }
+        if (__any_sync(0xffffffffu, risky != 0)) {
+#pragma unroll
+            for (int j = 0; j < CH; ++j)
+                if (risky & (1u << j)) y[j] = rest(gelu_tanh_f32(xs[j]), j);
+        }
+    } else {
+        // interpreted chain: one copy of the code in a rolled loop over the chunk, staged
+        // through shared memory (registers cannot be indexed dynamically)
+        __syncwarp();
+#pragma unroll
+        for (int j = 0; j < CH; ++j) stage[j][lane] = y[j];
+        __syncwarp();
+#pragma unroll 1
+        for (int j = 0; j < CH; ++j) {
+            float x = stage[j][lane];
+            if (p.bias && p.bias_sm) // a bias that varies along M was not folded into the per-column vector
+                x = __fadd_rn(x, j < nvalid ? load_f32(p.bias_dt, p.bias, m * p.bias_sm + (n0 + j) * p.bias_sn) : 0.f);
+            const float o = (k.any_sum && j < nvalid) ? load_f32(k.sum_dt, drow, j) : 0.f;
+            stage[j][lane] = tail(j < nvalid ? apply_post_ops(p, x, o, m, n0 + j) : 0.f, j);
+        }
+        __syncwarp();
+#pragma unroll
+        for (int j = 0; j < CH; ++j) y[j] = stage[j][lane];
+    }
+    store_row(p, y, drow, nvalid);
 }
 
 // ---- the kernel -------------------------------------------------------------------------
@@ -468,32 +504,38 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) matmul_tc8_kernel(const __grid
         }
     } else {
         // ---------------- epilogue warps ----------------
-        const int ew = warp - 2;           // private staging slot
+        const int ew = warp - 2;           // 0..7
         const int quarter = warp & 3;      // TMEM lanes this warp may read: 32*quarter .. +31
-        float *wscale = ctrl->wscale[ew], *bias = ctrl->bias[ew];
+        const int half = ew >> 2;          // which half of the tile's columns this warp converts
+        float *wscale = ctrl->wscale[ew], *bias = ctrl->bias[ew], *zpv = ctrl->zp[ew];
         int32_t *comp = ctrl->comp[ew];
-        const bool int8_path = !FP8;
-        const bool has_comp = int8_path && p.src_zp.ptr && p.wei_colsum;
+        float(*stage)[33] = ctrl->stage[ew];
+        const bool has_comp = !FP8 && p.src_zp.ptr && p.wei_colsum;
         const int zp_src = has_comp ? load_int(p.src_zp.dt, p.src_zp.ptr, 0) : 0;
-        const float src_scale = p.src_scale.ptr ? load_f32(p.src_scale.dt, p.src_scale.ptr, 0) : 1.f;
-        const float dst_inv = dst_scale_reciprocal(p);
-        const bool any_sum = has_sum(p);
-        const int sum_dt = sum_dt_of(p);
-        const bool non_default = p.npo > 0 || p.src_scale.ptr || p.wei_scale.ptr || p.dst_scale.ptr || p.src_zp.ptr
-                || p.wei_zp.ptr || p.dst_zp.ptr;
+        epi_consts_t k;
+        k.src_scale = p.src_scale.ptr ? load_f32(p.src_scale.dt, p.src_scale.ptr, 0) : 1.f;
+        k.dst_inv = dst_scale_reciprocal(p);
+        k.any_sum = has_sum(p);
+        k.sum_dt = sum_dt_of(p);
+        k.int8_nondefault = !FP8
+                && (p.npo > 0 || p.src_scale.ptr || p.wei_scale.ptr || p.dst_scale.ptr || p.src_zp.ptr || p.wei_zp.ptr
+                        || p.dst_zp.ptr);
+        const bool bias_per_col = p.bias && !p.bias_sm;
         uint32_t tile_i = 0;
         bool ok = true;
         for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tile_i) {
-            const int64_t m0 = (int64_t)(tile % args.m_tiles) * BM, n0 = (int64_t)(tile / args.m_tiles) * BN;
+            const int64_t m0 = (int64_t)(tile % args.m_tiles) * BM;
+            const int64_t n0 = (int64_t)(tile / args.m_tiles) * BN + half * EPI_COLS;
             const uint32_t a = tile_i & 1, use = tile_i >> 1;
-            // per-column vectors of this tile (8 columns per lane)
+            // per-column vectors of this warp's columns (4 per lane)
             __syncwarp();
-            for (int j = lane; j < BN; j += 32) {
+            for (int j = lane; j < EPI_COLS; j += 32) {
                 const int64_t n = n0 + j;
                 const bool in = n < p.N;
                 wscale[j] = (in && p.wei_scale.ptr) ? load_f32(p.wei_scale.dt, p.wei_scale.ptr, n * p.wei_scale.s1) : 1.f;
-                bias[j] = (in && p.bias && !p.bias_sm) ? load_f32(p.bias_dt, p.bias, n * p.bias_sn) : 0.f;
+                bias[j] = (in && bias_per_col) ? load_f32(p.bias_dt, p.bias, n * p.bias_sn) : -0.f;
                 comp[j] = (in && has_comp) ? zp_src * p.wei_colsum[n] : 0;
+                zpv[j] = (in && p.dst_zp.ptr) ? (float)((const int32_t *)p.dst_zp.ptr)[p.dst_zp.s1 ? n : 0] : 0.f;
             }
             __syncwarp();
             ok = mbar_wait(&ctrl->tmem_full[a], use & 1, ctrl, p.status, ST_WAIT_TMEM_FULL);
@@ -501,13 +543,13 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) matmul_tc8_kernel(const __grid
             if (!ok) break;
             tcgen05_fence_after();
             const int64_t m = m0 + quarter * 32 + lane;
-            const uint32_t trow = tmem_base + ((uint32_t)(quarter * 32) << 16) + a * BN;
+            const uint32_t trow = tmem_base + ((uint32_t)(quarter * 32) << 16) + a * BN + half * EPI_COLS;
 #pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
-                uint32_t v[32];
-                tmem_ld32(trow + c * 32, v);
-                epilogue_chunk<FP8, EPI>(p, v, m, n0 + c * 32, wscale + c * 32, bias + c * 32, comp + c * 32, src_scale,
-                        dst_inv, has_comp, any_sum, sum_dt, non_default);
+            for (int c = 0; c < EPI_COLS / CH; ++c) {
+                uint32_t v[CH];
+                tmem_ld16(trow + c * CH, v);
+                epilogue_chunk<FP8, EPI>(p, v, m, n0 + c * CH, wscale + c * CH, bias + c * CH, comp + c * CH, zpv + c * CH, k,
+                        stage, lane);
             }
             tcgen05_fence_before();
             __syncwarp();
@@ -637,6 +679,7 @@ extern "C" int b200_matmul_tc8_launch(const b200_matmul_params_t *p, b200_stream
                 && (p->npo == 1 || (p->npo == 2 && p->po[1].kind == B200_PO_SUM));
         epi = simple ? EPI_SIMPLE : gelu_q ? EPI_GELU_Q : EPI_GENERIC;
     }
+    if (p->bias && p->bias_sm) epi = EPI_GENERIC; // a bias that varies along M is added by the interpreted path
 
     typedef void (*kernel_t)(const CUtensorMap, const CUtensorMap, const tc8_args_t);
     static const kernel_t table[2][4] = {

@@ -318,58 +318,81 @@ def main():
 
 
 def run_extras(api, W, dt, eng, strm, tstream, torch, np, peaks):
-    """Secondary configurations of the same path, each timed alone with an L2 flush between launches."""
-    out = {}
-    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    """Secondary configurations of the same path.
 
-    def timed(plan, iters):
+    These kernels run for microseconds, less than a host-side launch takes, so each is
+    captured into a CUDA graph and the replay is timed: the launches then run back to back
+    on the device.  To keep the operands out of L2 the graph cycles over several independent
+    copies of the weights whose total size exceeds the cache (the decode GEMV is judged on
+    HBM bandwidth, and its 28 MiB of weights would otherwise stay cache-resident)."""
+    out = {}
+    gs = torch.cuda.Stream()
+    gstrm = api.Stream(eng, cuda_stream=gs.cuda_stream)
+
+    def graph_time(plans, reps=5):
+        for pl in plans:
+            pl.execute()
+        gstrm.wait()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=gs):
+            for pl in plans:
+                pl.execute()
+        g.replay()
+        torch.cuda.synchronize()
         ts = []
-        for _ in range(iters):
-            flush.zero_()
+        for _ in range(reps):
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            a.record(tstream)
-            plan.execute()
-            b.record(tstream)
+            a.record()
+            g.replay()
+            b.record()
             b.synchronize()
-            ts.append(a.elapsed_time(b))
+            ts.append(a.elapsed_time(b) / len(plans))
         ts.sort()
         return ts[len(ts) // 2], ts[0]
 
     try:
         for m in (1, 16, 128):
             c = W.config2(m)
-            plan = api.CasePlan(c, eng, strm, weights="any")
-            for _ in range(3):
-                plan.execute()
-            med, best = timed(plan, 15)
+            copies = 9  # 9 x 29.4 MB of packed weights = 264 MB > L2
+            plans = [api.CasePlan(c, eng, gstrm, weights="any") for _ in range(copies)]
+            med, best = graph_time(plans)
             nbytes = c.algorithmic_bytes()
             gbs = nbytes / (med * 1e-3) / 1e9
-            out["c2_wc_u4_m%d" % m] = {"impl": plan.impl, "ms": med, "ms_min": best, "algorithmic_bytes": nbytes, "GB/s": gbs,
-                                       "frac_of_hbm_%s" % peaks["source"]: gbs / peaks["hbm"], "GOPS": c.ops / (med * 1e-3) / 1e9}
-            del plan
+            out["c2_wc_u4_m%d" % m] = {
+                "impl": plans[0].impl, "us": med * 1e3, "us_min": best * 1e3, "algorithmic_bytes": nbytes, "GB/s": gbs,
+                "frac_of_hbm_%s" % peaks["source"]: gbs / peaks["hbm"], "frac_of_8TBs_nominal": gbs / 8000.0,
+                "GOPS": c.ops / (med * 1e-3) / 1e9,
+                "timing": "CUDA graph of %d executions over %d weight copies (L2-cold), median of 5 replays" % (copies, copies)}
+            del plans
     except Exception as ex:
         out["c2_error"] = repr(ex)
     try:
         c = W.config0()
-        plan = api.CasePlan(c, eng, strm, weights="any")
-        for _ in range(3):
-            plan.execute()
-        med, best = timed(plan, 15)
-        out["c0_int8_128x1024x1024"] = {"impl": plan.impl, "us": med * 1e3, "us_min": best * 1e3}
-        del plan
+        plans = [api.CasePlan(c, eng, gstrm, weights="any") for _ in range(4)]
+        med, best = graph_time(plans)
+        out["c0_int8_128x1024x1024"] = {"impl": plans[0].impl, "us": med * 1e3, "us_min": best * 1e3,
+                                        "timing": "CUDA graph of 4 executions, median of 5 replays"}
+        del plans
     except Exception as ex:
         out["c0_error"] = repr(ex)
     try:
-        c = W.config3(4096, 4096, 4096)
-        plan = api.CasePlan(c, eng, strm, weights="any")
-        for _ in range(3):
-            plan.execute()
-        med, best = timed(plan, 10)
-        out["c3_fp8_4096"] = {"impl": plan.impl, "ms": med, "TFLOPS": c.ops / (med * 1e-3) / 1e12,
-                              "note": "4096^3 slice of the 8192^3 configuration"}
-        del plan
+        c = W.config3()
+        plans = [api.CasePlan(c, eng, gstrm, weights="any")]
+        med, best = graph_time(plans, reps=3)
+        out["c3_fp8_8192"] = {"impl": plans[0].impl, "ms": med, "TFLOPS": c.ops / (med * 1e-3) / 1e12,
+                              "frac_of_2x_bf16_%s" % peaks["source"]: c.ops / (med * 1e-3) / 1e12 / (2 * peaks["bf16"])}
+        del plans
     except Exception as ex:
         out["c3_error"] = repr(ex)
+    try:
+        c = W.config4()
+        plans = [api.CasePlan(c, eng, gstrm, weights="any")]
+        med, best = graph_time(plans, reps=3)
+        out["c4_int8_16384x8192x28672_1gpu"] = {"impl": plans[0].impl, "ms": med, "TOPS": c.ops / (med * 1e-3) / 1e12,
+                                                "frac_of_2x_bf16_%s" % peaks["source"]: c.ops / (med * 1e-3) / 1e12 / (2 * peaks["bf16"])}
+        del plans
+    except Exception as ex:
+        out["c4_error"] = repr(ex)
     return out
 
 

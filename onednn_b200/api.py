@@ -73,6 +73,17 @@ def _ck(status, what):
         raise Error(status, what)
 
 
+def _destroy(obj, fn):
+    """Release a native handle; quiet during interpreter shutdown, when module globals are gone."""
+    h = getattr(obj, "h", None)
+    if h and _lib is not None:
+        try:
+            getattr(_lib, fn)(h)
+        except Exception:
+            pass
+    obj.h = None
+
+
 def _dims(v):
     a = (C.c_int64 * 12)()
     for i, x in enumerate(v):
@@ -90,9 +101,7 @@ class Engine:
         return int(lib().dnnl_engine_get_count(kind))
 
     def __del__(self):
-        if getattr(self, "h", None):
-            lib().dnnl_engine_destroy(self.h)
-            self.h = None
+        _destroy(self, "dnnl_engine_destroy")
 
 
 class Stream:
@@ -115,9 +124,7 @@ class Stream:
         return p.value or 0
 
     def __del__(self):
-        if getattr(self, "h", None):
-            lib().dnnl_stream_destroy(self.h)
-            self.h = None
+        _destroy(self, "dnnl_stream_destroy")
 
 
 class MemoryDesc:
@@ -170,9 +177,8 @@ class MemoryDesc:
         return self._query(262, C.c_int).value
 
     def __del__(self):
-        if getattr(self, "h", None) and not self.borrowed:
-            lib().dnnl_memory_desc_destroy(self.h)
-            self.h = None
+        if not getattr(self, "borrowed", True):
+            _destroy(self, "dnnl_memory_desc_destroy")
 
 
 class Memory:
@@ -211,9 +217,7 @@ class Memory:
         return out
 
     def __del__(self):
-        if getattr(self, "h", None):
-            lib().dnnl_memory_destroy(self.h)
-            self.h = None
+        _destroy(self, "dnnl_memory_destroy")
 
 
 class PostOps:
@@ -239,9 +243,7 @@ class PostOps:
         return lib().dnnl_post_ops_len(self.h)
 
     def __del__(self):
-        if getattr(self, "h", None):
-            lib().dnnl_post_ops_destroy(self.h)
-            self.h = None
+        _destroy(self, "dnnl_post_ops_destroy")
 
 
 class PrimitiveAttr:
@@ -272,9 +274,7 @@ class PrimitiveAttr:
         _ck(lib().dnnl_primitive_attr_set_post_ops(self.h, po.h), "set_post_ops")
 
     def __del__(self):
-        if getattr(self, "h", None):
-            lib().dnnl_primitive_attr_destroy(self.h)
-            self.h = None
+        _destroy(self, "dnnl_primitive_attr_destroy")
 
 
 class PrimitiveDesc:
@@ -310,9 +310,7 @@ class PrimitiveDesc:
         return self.query_md(QUERY_SCRATCHPAD_MD)
 
     def __del__(self):
-        if getattr(self, "h", None):
-            lib().dnnl_primitive_desc_destroy(self.h)
-            self.h = None
+        _destroy(self, "dnnl_primitive_desc_destroy")
 
 
 def matmul_primitive_desc(engine, src_md, weights_md, dst_md, bias_md=None, attr=None):
@@ -344,9 +342,7 @@ class Primitive:
         _ck(lib().dnnl_primitive_execute(self.h, stream.h, len(args), arr), "primitive_execute")
 
     def __del__(self):
-        if getattr(self, "h", None):
-            lib().dnnl_primitive_destroy(self.h)
-            self.h = None
+        _destroy(self, "dnnl_primitive_destroy")
 
 
 # ---- running a MatmulCase through the public API ------------------------------------------

@@ -43,9 +43,9 @@ struct wc_args_t {
     float *acc;             // scratch [M][N] f32, zero on entry
     int64_t M, N, K;
     int m0;                 // first activation row of this pass
-    const void *scale; int scale_dt; int64_t scale_s0, scale_s1, scale_g0; // g0: K-group size (K if none)
-    const void *zp; int zp_dt; int64_t zp_s0, zp_s1, zp_g0;
-    int64_t fold_k;         // fold period in k (multiple of 16)
+    const void *scale; int scale_dt; int64_t scale_s0, scale_s1; uint32_t scale_g0; // g0: K-group size (K if none)
+    const void *zp; int zp_dt; int64_t zp_s0, zp_s1; uint32_t zp_g0;
+    uint32_t fold_k;        // fold period in k (multiple of 16)
     float nibble_offset;    // 128 (u4) or 136 (s4 stored offset by 8)
 };
 
@@ -71,8 +71,8 @@ __global__ void __launch_bounds__(WC_WARPS * 32) wc_gemv_kernel(const __grid_con
     const int g = lane >> 2, t = lane & 3;
     const int64_t warp = (int64_t)blockIdx.x * WC_WARPS + (threadIdx.x >> 5);
     const int64_t nwarps = (int64_t)gridDim.x * WC_WARPS;
-    const int64_t kchunks = a.K / WC_TILE_K;
-    const int64_t steps = (a.N / WC_TILE_N) * kchunks;
+    const uint32_t kchunks = (uint32_t)(a.K / WC_TILE_K);
+    const int64_t steps = (a.N / WC_TILE_N) * (int64_t)kchunks;
     // equal contiguous ranges: the first (steps % nwarps) warps take one more
     const int64_t base = steps / nwarps, rem = steps % nwarps;
     int64_t s_begin = warp * base + (warp < rem ? warp : rem);
@@ -103,9 +103,11 @@ __global__ void __launch_bounds__(WC_WARPS * 32) wc_gemv_kernel(const __grid_con
     if (s_begin + 2 < s_end) r2 = ldg_stream(wp + 64);
 
     int64_t strip = s_begin / kchunks;
-    int64_t kc = s_begin % kchunks;
+    uint32_t kc = (uint32_t)(s_begin % kchunks);
+    // k position inside the current fold period, advanced by 16 per MMA step (no division in the loop)
+    uint32_t kin = (kc * WC_TILE_K) % a.fold_k;
 
-    auto fold = [&](int64_t k_last) {
+    auto fold = [&](uint32_t k_last) {
         // k_last: any k inside the group being closed
         const int64_t n0 = strip * WC_TILE_N + g, n1 = n0 + 8;
         float s0 = 1.f, s1 = 1.f, c0 = a.nibble_offset, c1 = a.nibble_offset;
@@ -155,7 +157,7 @@ __global__ void __launch_bounds__(WC_WARPS * 32) wc_gemv_kernel(const __grid_con
         const uint32_t words[4] = {w4.x, w4.y, w4.z, w4.w};
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-            const int64_t k0 = kc * WC_TILE_K + j * 16;
+            const uint32_t k0 = kc * WC_TILE_K + j * 16;
             const uint32_t w = words[j];
             uint32_t af[4];
             af[0] = (w & 0x000f000fu) | 0x43004300u;
@@ -172,7 +174,11 @@ __global__ void __launch_bounds__(WC_WARPS * 32) wc_gemv_kernel(const __grid_con
                 mma_bf16_16816(acc[mb], af, b0, b1);
                 mma_bf16_16816(xs[mb], ones, b0, b1);
             }
-            if ((k0 + 16) % a.fold_k == 0) fold(k0);
+            kin += 16;
+            if (kin == a.fold_k) {
+                fold(k0);
+                kin = 0;
+            }
         }
         // next step: same strip unless the k chunks are exhausted
         if (++kc == kchunks) {
@@ -184,8 +190,8 @@ __global__ void __launch_bounds__(WC_WARPS * 32) wc_gemv_kernel(const __grid_con
     }
     if (kc != 0) {
         // range ended inside a strip: close the open group, then publish
-        const int64_t k_done = kc * WC_TILE_K; // k processed so far in this strip
-        if (k_done % a.fold_k != 0) fold(k_done - 1);
+        const uint32_t k_done = kc * WC_TILE_K; // k processed so far in this strip
+        if (kin != 0) fold(k_done - 1);
         flush();
     }
 }
@@ -284,6 +290,7 @@ extern "C" int b200_matmul_wc_launch(const b200_matmul_params_t *p, b200_stream_
     if (!p->apply_to_int) return B200_ERR_UNSUPPORTED;
     if (p->src_dt != B200_DT_BF16 && p->src_dt != B200_DT_F16 && p->src_dt != B200_DT_F32) return B200_ERR_UNSUPPORTED;
     if (p->N % WC_TILE_N != 0 || p->K % WC_TILE_K != 0 || p->src_sk != 1 || p->dst_sn != 1) return B200_ERR_UNSUPPORTED;
+    if (p->K > (int64_t)1 << 30) return B200_ERR_TOO_LARGE;
     if (p->wei_layout == B200_WEI_PLAIN && !(p->wei_sn == 1 && p->wei_sk == p->N)) return B200_ERR_UNSUPPORTED;
     if (p->wei_layout != B200_WEI_PLAIN && p->wei_layout != B200_WEI_WC4_TILED) return B200_ERR_UNSUPPORTED;
     if (p->src_zp.ptr || p->dst_zp.ptr) return B200_ERR_UNSUPPORTED;
@@ -345,13 +352,13 @@ extern "C" int b200_matmul_wc_launch(const b200_matmul_params_t *p, b200_stream_
     a.scale_dt = p->wei_scale.dt;
     a.scale_s0 = p->wei_scale.s0;
     a.scale_s1 = p->wei_scale.s1;
-    a.scale_g0 = gs;
+    a.scale_g0 = (uint32_t)gs;
     a.zp = p->wei_zp.ptr;
     a.zp_dt = p->wei_zp.dt;
     a.zp_s0 = p->wei_zp.s0;
     a.zp_s1 = p->wei_zp.s1;
-    a.zp_g0 = gz;
-    a.fold_k = fold_k;
+    a.zp_g0 = (uint32_t)gz;
+    a.fold_k = (uint32_t)fold_k;
     a.nibble_offset = p->wei_dt == B200_DT_S4 ? 136.f : 128.f;
 
     int dev = 0, sms = 148;

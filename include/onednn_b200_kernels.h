@@ -142,6 +142,35 @@ B200_API int b200_matmul_tc8_launch(const b200_matmul_params_t *p, b200_stream_t
  * reference's JIT decompression.) */
 B200_API int b200_matmul_wc_launch(const b200_matmul_params_t *p, b200_stream_t stream);
 
+/* The weight-compressed kernel for callers that may not allocate device memory.
+ * This entry point has no counterpart in the reference.
+ *
+ * b200_matmul_wc_launch accumulates partial sums in a scratch buffer that the
+ * caller (or the host library, for its primitives) has to allocate.  Code that
+ * runs where allocation is off limits -- a plugin inside a host runtime that
+ * owns all device memory and only passes pointers in, a decode loop inside a
+ * serving engine's captured or latency-critical section, a callback of a
+ * memory pool -- can call this variant instead: its scratch is a fixed 2 MiB
+ * array inside the library's device image, held by every GPU that loads the
+ * library until the process exits.  It calls neither cudaMalloc nor cudaFree
+ * nor any allocating library routine; src, weights, scales, zero-points, bias
+ * and dst are still passed in by the caller (p->scratch is ignored).
+ *
+ * Limits: bf16 activations (src_dt == B200_DT_BF16), weights already in
+ * B200_WEI_WC4_TILED layout, and M * N * 4 bytes must fit the array
+ * (b200_matmul_wc_noalloc_max_bytes(), i.e. M * N <= 524288); anything larger
+ * returns B200_ERR_TOO_LARGE, anything else unsupported B200_ERR_UNSUPPORTED,
+ * and nothing is launched.
+ *
+ * The first call on a device looks up the array's device address
+ * (cudaGetSymbolAddress) with that device current; make that first call before
+ * any stream capture begins.  All calls on a device share the one array and it
+ * keeps the last call's contents: each call clears the part it uses on the
+ * given stream first, and two calls whose kernels overlap on the GPU (different
+ * streams without ordering between them) race on it -- serialise them. */
+B200_API int b200_matmul_wc_noalloc_launch(const b200_matmul_params_t *p, b200_stream_t stream);
+B200_API size_t b200_matmul_wc_noalloc_max_bytes(void);
+
 /* plain dense (K, N) 4-bit weights (two per byte along N) -> B200_WEI_WC4_TILED;
  * needs K % 64 == 0 and N % 16 == 0 */
 B200_API int b200_wc_pack_launch(const void *src, void *dst, int64_t K, int64_t N, int32_t dt, b200_stream_t stream);

@@ -27,6 +27,8 @@
 //    SM count, each warp streams its range with a 3-deep register prefetch ring
 //    and adds its partial sums into an f32 scratch [M][N] with red.global.add;
 //    a small second kernel applies the epilogue and leaves the scratch zeroed.
+#include <mutex>
+
 #include "common.cuh"
 #include "launch.hpp"
 
@@ -375,6 +377,116 @@ extern "C" int b200_matmul_wc_launch(const b200_matmul_params_t *p, b200_stream_
         else if (rows <= 16) wc_gemv_kernel<2><<<(unsigned)ctas, WC_WARPS * 32, 0, cs>>>(a);
         else wc_gemv_kernel<4><<<(unsigned)ctas, WC_WARPS * 32, 0, cs>>>(a);
         int rc = after_launch();
+        if (rc) return rc;
+    }
+    int64_t eblocks = (p->M * p->N + 255) / 256;
+    if (eblocks > (int64_t)sms * 8) eblocks = (int64_t)sms * 8;
+    wc_epilogue_kernel<<<(unsigned)eblocks, 256, 0, cs>>>(*p, acc);
+    return after_launch();
+}
+
+// ---- entry point that allocates nothing ---------------------------------------------------
+//
+// b200_matmul_wc_launch needs an f32 accumulation scratch that somebody has to
+// allocate.  Some callers cannot: code that runs inside another framework's
+// CUDA-graph capture or inside its memory-pool callbacks, plugins that are only
+// handed device pointers by a host runtime that owns every allocation, and
+// real-time decode loops that must not touch the allocator.  For them the same
+// kernels are offered with the scratch in a fixed array that lives in the
+// library's device image: every GPU that loads the library holds these 2 MiB
+// until the process exits.
+static constexpr size_t WC_STATIC_SCRATCH_BYTES = (size_t)2 << 20; // room for M * N <= 524288 partial sums
+static __device__ __align__(256) unsigned char g_wc_static_scratch[WC_STATIC_SCRATCH_BYTES];
+
+// In host code the array's name is only a handle for the runtime, not a device
+// address.  The address is looked up once per device, with that device current.
+static int wc_static_scratch_ptr(float **out) {
+    static std::mutex mu;
+    static float *ptrs[64] = {nullptr};
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return (int)cudaErrorInvalidDevice;
+    std::lock_guard<std::mutex> g(mu);
+    if (!ptrs[dev]) {
+        void *p = nullptr;
+        const cudaError_t e = cudaGetSymbolAddress(&p, g_wc_static_scratch);
+        if (e != cudaSuccess) return (int)e;
+        ptrs[dev] = (float *)p;
+    }
+    *out = ptrs[dev];
+    return 0;
+}
+
+extern "C" size_t b200_matmul_wc_noalloc_max_bytes(void) {
+    return WC_STATIC_SCRATCH_BYTES;
+}
+
+extern "C" int b200_matmul_wc_noalloc_launch(const b200_matmul_params_t *p, b200_stream_t stream) {
+    if (!p || !p->src || !p->wei || !p->dst) return B200_ERR_BAD_ARG;
+    if (p->M <= 0 || p->N <= 0 || p->K <= 0) return p->M < 0 || p->N < 0 || p->K < 0 ? B200_ERR_BAD_ARG : 0;
+    // only the forms that need no other scratch: bf16 activations, weights already packed
+    if (p->wei_dt != B200_DT_U4 && p->wei_dt != B200_DT_S4) return B200_ERR_UNSUPPORTED;
+    if (!p->apply_to_int || p->src_dt != B200_DT_BF16 || p->wei_layout != B200_WEI_WC4_TILED) return B200_ERR_UNSUPPORTED;
+    if (p->N % WC_TILE_N != 0 || p->K % WC_TILE_K != 0 || p->src_sk != 1 || p->dst_sn != 1) return B200_ERR_UNSUPPORTED;
+    if (p->K > (int64_t)1 << 30) return B200_ERR_TOO_LARGE;
+    if (p->src_zp.ptr || p->dst_zp.ptr) return B200_ERR_UNSUPPORTED;
+    if (p->src_scale.ptr && (p->src_scale.s0 || p->src_scale.s1)) return B200_ERR_UNSUPPORTED;
+    int64_t gs = p->K, gz = p->K;
+    if (p->wei_scale.ptr) {
+        if (p->wei_scale.g1 != 1) return B200_ERR_UNSUPPORTED;
+        if (p->wei_scale.s0) gs = p->wei_scale.g0;
+    }
+    if (p->wei_zp.ptr) {
+        if (p->wei_zp.g1 != 1) return B200_ERR_UNSUPPORTED;
+        if (p->wei_zp.s0) gz = p->wei_zp.g0;
+    }
+    if (gs % 16 || gz % 16 || p->K % gs || p->K % gz) return B200_ERR_UNSUPPORTED;
+    const int64_t fold_k = gs < gz ? gs : gz;
+    if (gs % fold_k || gz % fold_k) return B200_ERR_UNSUPPORTED;
+    if (((uintptr_t)p->src & 3) || (p->src_sm & 1) || ((uintptr_t)p->wei & 15)) return B200_ERR_BAD_ARG;
+    // the fixed array bounds the problem: M * N partial sums of 4 bytes
+    if ((uint64_t)p->M * (uint64_t)p->N * sizeof(float) > WC_STATIC_SCRATCH_BYTES) return B200_ERR_TOO_LARGE;
+
+    float *acc = nullptr;
+    int rc = wc_static_scratch_ptr(&acc);
+    if (rc) return rc;
+    cudaStream_t cs = (cudaStream_t)stream;
+    // the array keeps whatever the last call left behind: clear the part used now
+    if (cudaMemsetAsync(acc, 0, (size_t)p->M * p->N * sizeof(float), cs) != cudaSuccess) return (int)cudaGetLastError();
+
+    wc_args_t a;
+    a.wei = (const uint4 *)p->wei;
+    a.x = (const __nv_bfloat16 *)p->src;
+    a.x_ld = p->src_sm;
+    a.acc = acc;
+    a.M = p->M;
+    a.N = p->N;
+    a.K = p->K;
+    a.scale = p->wei_scale.ptr;
+    a.scale_dt = p->wei_scale.dt;
+    a.scale_s0 = p->wei_scale.s0;
+    a.scale_s1 = p->wei_scale.s1;
+    a.scale_g0 = (uint32_t)gs;
+    a.zp = p->wei_zp.ptr;
+    a.zp_dt = p->wei_zp.dt;
+    a.zp_s0 = p->wei_zp.s0;
+    a.zp_s1 = p->wei_zp.s1;
+    a.zp_g0 = (uint32_t)gz;
+    a.fold_k = (uint32_t)fold_k;
+    a.nibble_offset = p->wei_dt == B200_DT_S4 ? 136.f : 128.f;
+
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int64_t steps = (p->N / WC_TILE_N) * (p->K / WC_TILE_K);
+    int64_t ctas = (int64_t)sms * 4;
+    if (ctas * WC_WARPS > steps) ctas = (steps + WC_WARPS - 1) / WC_WARPS;
+    for (int64_t m0 = 0; m0 < p->M; m0 += 32) {
+        a.m0 = (int)m0;
+        const int64_t rows = p->M - m0;
+        if (rows <= 8) wc_gemv_kernel<1><<<(unsigned)ctas, WC_WARPS * 32, 0, cs>>>(a);
+        else if (rows <= 16) wc_gemv_kernel<2><<<(unsigned)ctas, WC_WARPS * 32, 0, cs>>>(a);
+        else wc_gemv_kernel<4><<<(unsigned)ctas, WC_WARPS * 32, 0, cs>>>(a);
+        rc = after_launch();
         if (rc) return rc;
     }
     int64_t eblocks = (p->M * p->N + 255) / 256;

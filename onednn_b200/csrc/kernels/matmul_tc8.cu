@@ -10,10 +10,10 @@
 // place of the reference's AMX brgemm kernel
 // (src/cpu/x64/matmul/brgemm_matmul.cpp:383-496, jit_brgemm_amx_uker.cpp:1286-1445).
 //
-// Structure (one persistent CTA per SM, 320 threads):
+// Structure (one persistent CTA per SM, 576 threads):
 //   warp 0      TMA producer: cp.async.bulk.tensor 2-D loads (no multicast) of a
 //               128 x 128-byte A tile and a 256 x 128-byte W tile per k-block into a
-//               4-stage ring of 128-byte-swizzled shared memory, completion on
+//               3-stage ring of 128-byte-swizzled shared memory, completion on
 //               "full" mbarriers.
 //   warp 1      MMA issuer: one lane issues tcgen05.mma.cta_group::1 (kind::i8 or
 //               kind::f8f6f4), 128 x 256 x 32 per instruction, four per k-block,
@@ -21,7 +21,7 @@
 //               stage ("empty" mbarrier) and, after the last k-block, publishes the
 //               accumulator ("tmem_full").  Also owns the TMEM allocation (512
 //               columns = two 128 x 256 x 32-bit accumulators).
-//   warps 2-9   epilogue (two per TMEM lane quarter, each converts half of the
+//   warps 2-17  epilogue (four per TMEM lane quarter, each converts a quarter of the
 //               tile's columns): tcgen05.ld 32 lanes x 16 columns at a time, exact s32
 //               zero-point compensation (acc - zp_src * colsum_W[n]), the f32
 //               epilogue chain, packed 16-byte stores.  With two accumulator
@@ -33,6 +33,7 @@
 // and the kernel returns; dnnl_stream_wait then reports dnnl_runtime_error.
 #include <cuda.h>
 
+#include <cstddef>
 #include <mutex>
 
 #include "common.cuh"
@@ -43,13 +44,13 @@ namespace b200 {
 constexpr int BM = 128;          // rows of dst per tile (= TMEM lanes)
 constexpr int BN = 256;          // columns of dst per tile (= one MMA's N)
 constexpr int BK = 128;          // bytes of K per stage (= one 128-byte swizzle row)
-constexpr int STAGES = 4;
+constexpr int STAGES = 3;
 constexpr int A_BYTES = BM * BK; // 16 KiB
 constexpr int B_BYTES = BN * BK; // 32 KiB
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-constexpr int EPI_WARPS = 8;                  // two per TMEM lane quarter, each takes half of the columns
+constexpr int EPI_WARPS = 16;                 // four per TMEM lane quarter, each takes a quarter of the columns
 constexpr int NUM_THREADS = 64 + 32 * EPI_WARPS;
-constexpr int EPI_COLS = BN / 2;              // columns per epilogue warp
+constexpr int EPI_COLS = BN / (EPI_WARPS / 4); // columns per epilogue warp
 constexpr int CH = 16;                        // columns per epilogue chunk (held in registers)
 constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t WAIT_SPINS = 1u << 24; // bounded wait: of the order of a second with the back-off below
@@ -64,14 +65,20 @@ struct smem_ctrl_t {
     uint32_t tmem_base;
     volatile uint32_t abort;
     // per epilogue warp: per-column vectors of its half of the current tile
-    float wscale[EPI_WARPS][EPI_COLS];   // weights scale, 1 when unset
-    float bias[EPI_WARPS][EPI_COLS];     // bias, -0 when unset (x + -0 == x for every x)
-    int32_t comp[EPI_WARPS][EPI_COLS];   // zp_src * colsum_W[n], 0 when unset
-    float zp[EPI_WARPS][EPI_COLS];       // destination zero-point addend
+    // (16-byte aligned: the epilogue reads these four columns at a time)
+    alignas(16) float wscale[EPI_WARPS][EPI_COLS];   // weights scale, 1 when unset
+    alignas(16) float bias[EPI_WARPS][EPI_COLS];     // bias, -0 when unset (x + -0 == x for every x)
+    alignas(16) int32_t comp[EPI_WARPS][EPI_COLS];   // zp_src * colsum_W[n], 0 when unset
+    alignas(16) float zp[EPI_WARPS][EPI_COLS];       // destination zero-point addend
     // per epilogue warp: staging of one chunk for the interpreted (EPI_GENERIC) path;
     // pitch 33 keeps it free of bank conflicts
     float stage[EPI_WARPS][CH][33];
 };
+
+static_assert(offsetof(smem_ctrl_t, wscale) % 16 == 0 && offsetof(smem_ctrl_t, bias) % 16 == 0
+                && offsetof(smem_ctrl_t, comp) % 16 == 0 && offsetof(smem_ctrl_t, zp) % 16 == 0,
+        "per-column vectors are read with 128-bit loads");
+static_assert((EPI_COLS * sizeof(float)) % 16 == 0 && (CH * sizeof(float)) % 16 == 0, "chunk offsets keep the alignment");
 
 constexpr size_t SMEM_BYTES = 1024 /* alignment slack */ + (size_t)STAGES * STAGE_BYTES + sizeof(smem_ctrl_t);
 
@@ -146,8 +153,10 @@ __device__ __forceinline__ void tcgen05_mma(uint32_t tmem_d, uint64_t adesc, uin
     }
 }
 
-// 16 consecutive 32-bit columns of this thread's TMEM lane
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
+// 16 consecutive 32-bit columns of this thread's TMEM lane.  The load is asynchronous:
+// the registers are valid only after tmem_ld_wait, which names them as operands so that
+// the compiler cannot move a use above the wait.
+__device__ __forceinline__ void tmem_ld16_issue(uint32_t taddr, uint32_t (&v)[16]) {
     asm volatile(
             "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
             "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
@@ -155,7 +164,13 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
             "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
             : "r"(taddr)
             : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait(uint32_t (&v)[16]) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7]), "+r"(v[8]),
+                 "+r"(v[9]), "+r"(v[10]), "+r"(v[11]), "+r"(v[12]), "+r"(v[13]), "+r"(v[14]), "+r"(v[15])
+                 :
+                 : "memory");
 }
 
 // shared-memory matrix descriptor: K-major operand, 128-byte swizzle, rows of 128
@@ -198,6 +213,10 @@ struct epi_consts_t {
     int sum_dt;
     bool int8_nondefault; // the int8 path adds the destination zero-point (0 when unset) whenever any attribute is set
 };
+
+// the exact gelu_tanh, kept out of line: it is needed for about one element in ten thousand
+// and would otherwise sit in the middle of the hot epilogue code
+__device__ __noinline__ float gelu_tanh_exact(float x) { return gelu_tanh_f32(x); }
 
 // tanh by ex2.approx / rcp.approx: absolute error below 1e-6 on the whole range
 __device__ __forceinline__ float tanh_fast(float a) {
@@ -260,20 +279,32 @@ __device__ __forceinline__ void eltwise_simple_chunk(const b200_postop_t &e, flo
     }
 }
 
+// f32 -> s8 / u8: round to nearest even and saturate in one instruction.  Rounding and
+// clamping to integer bounds commute, so this equals the reference's clamp-then-round; NaN
+// gives 0 in both.  The result is the byte, zero-extended.
+__device__ __forceinline__ uint32_t cvt_sat_s8(float v) {
+    int r;
+    asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(r) : "f"(v));
+    return (uint32_t)r & 0xffu;
+}
+__device__ __forceinline__ uint32_t cvt_sat_u8(float v) {
+    uint32_t r;
+    asm("cvt.rni.sat.u8.f32 %0, %1;" : "=r"(r) : "f"(v));
+    return r & 0xffu;
+}
+
 // pack CH final f32 values of one row and store them (or the valid part of them)
 __device__ __forceinline__ void store_row(const b200_matmul_params_t &p, const float (&y)[CH], char *drow, int64_t nvalid) {
     if (nvalid <= 0) return;
     const bool aligned = nvalid == CH && ((uintptr_t)drow & 15) == 0;
     if (aligned && (p.dst_dt == B200_DT_S8 || p.dst_dt == B200_DT_U8)) {
+        const bool is_s8 = p.dst_dt == B200_DT_S8;
         uint32_t w[CH / 4];
 #pragma unroll
         for (int q = 0; q < CH / 4; ++q) {
             uint32_t r = 0;
 #pragma unroll
-            for (int b = 0; b < 4; ++b) {
-                const int iv = p.dst_dt == B200_DT_S8 ? sat_rne_s8(y[q * 4 + b]) : sat_rne_u8(y[q * 4 + b]);
-                r |= ((uint32_t)iv & 0xff) << (8 * b);
-            }
+            for (int b = 0; b < 4; ++b) r |= (is_s8 ? cvt_sat_s8(y[q * 4 + b]) : cvt_sat_u8(y[q * 4 + b])) << (8 * b);
             w[q] = r;
         }
         ((uint4 *)drow)[0] = make_uint4(w[0], w[1], w[2], w[3]);
@@ -297,42 +328,162 @@ __device__ __forceinline__ void store_row(const b200_matmul_params_t &p, const f
     }
 }
 
-template <bool FP8, int EPI>
+// SUM: how the sum post-op's prior destination values are obtained
+//   0 no sum;  1 the sum type is s8 / u8: 16 bytes per chunk, kept packed in four registers;
+//   2 any other sum type: converted to f32 up front.
+enum { SUM_NONE = 0, SUM_8BIT = 1, SUM_OTHER = 2 };
+
+template <bool FP8, int EPI, int SUM>
 __device__ __forceinline__ void epilogue_chunk(const b200_matmul_params_t &p, const uint32_t (&v)[CH], int64_t m,
         int64_t n0, const float *wscale, const float *bias, const int32_t *comp, const float *zp, const epi_consts_t &k,
-        float (*stage)[33], int lane) {
+        float (*stage)[33], int lane, uint4 old_raw, bool old_prefetched) {
     const int64_t nvalid = m < p.M ? (p.N - n0 < CH ? p.N - n0 : CH) : 0;
     char *drow = (char *)p.dst + (size_t)((m < p.M ? m : 0) * p.dst_sm + n0) * (dt_bits(p.dst_dt) / 8);
 
-    // accumulator -> scaled value + bias (neutral elements where unset)
-    float y[CH];
+    // Prior destination values.  All control flow happens here, once per chunk; the element
+    // loops below are straight-line so that the compiler can interleave the CH chains.
+    uint32_t ow[4] = {old_raw.x, old_raw.y, old_raw.z, old_raw.w};
+    float oldf[SUM == SUM_OTHER ? CH : 1];
+    if (SUM == SUM_8BIT && !old_prefetched) {
+        // ragged or unaligned row: gather the bytes one by one into the same packed form
 #pragma unroll
-    for (int j = 0; j < CH; ++j) {
-        const float x = FP8 ? __uint_as_float(v[j]) : (float)((int)v[j] - comp[j]);
-        y[j] = __fadd_rn(__fmul_rn(__fmul_rn(x, k.src_scale), wscale[j]), bias[j]);
+        for (int q = 0; q < 4; ++q) ow[q] = 0;
+        for (int j = 0; j < nvalid; ++j) ow[j >> 2] |= (uint32_t)((const uint8_t *)drow)[j] << ((j & 3) * 8);
     }
-
-    // prior destination values for sum (read before anything is stored)
-    float old[CH];
-    if (EPI != EPI_NONE && k.any_sum) {
-        const bool fast = nvalid == CH && (k.sum_dt == B200_DT_S8 || k.sum_dt == B200_DT_U8) && ((uintptr_t)drow & 15) == 0;
-        if (fast) {
-            const uint4 a = ((const uint4 *)drow)[0];
-            const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+    if (SUM == SUM_OTHER) {
 #pragma unroll
-            for (int j = 0; j < CH; ++j) {
-                const uint32_t byte = (w[j >> 2] >> ((j & 3) * 8)) & 0xff;
-                old[j] = k.sum_dt == B200_DT_S8 ? (float)(int8_t)byte : (float)byte;
+        for (int j = 0; j < CH; ++j) oldf[j] = j < nvalid ? load_f32(k.sum_dt, drow, j) : 0.f;
+    }
+    // byte b of a packed word, sign- or zero-extended by one byte permute: selector nibble
+    // 8|b replicates the byte's sign bit, nibble 4 picks a zero byte of the second operand
+    const uint32_t ext = k.sum_dt == B200_DT_S8 ? 0x8880u : 0x4440u;
+    auto old_val = [&](int j) -> float {
+        if (SUM == SUM_OTHER) return oldf[j];
+        const uint32_t b = j & 3;
+        const uint32_t sel = k.sum_dt == B200_DT_S8 ? (ext | b | (b << 4) | (b << 8) | (b << 12)) : (ext | b);
+        uint32_t e;
+        asm("prmt.b32 %0, %1, %2, %3;" : "=r"(e) : "r"(ow[j >> 2]), "r"(0u), "r"(sel));
+        return (float)(int)e;
+    };
+
+    // per-column vectors of the chunk as 128-bit shared-memory reads
+    if (EPI == EPI_GELU_Q) {
+        // gelu_tanh (then optionally sum) into an s8 / u8 destination, bit-exact.  The exact
+        // value needs a double-precision tanh; almost always it is not needed:
+        //  * |tanh argument| >= 9.02: the float tanh is exactly +-1, gelu(x) is x or -0;
+        //  * otherwise evaluate with a fast tanh (absolute error < 1e-6) and check how far the
+        //    value to be rounded is from a rounding boundary (k + 0.5).  The fast and the
+        //    exact value differ by less than tau (propagated error bound with a 4x margin),
+        //    so away from a boundary both round to the same integer; only elements within
+        //    tau of one are recomputed exactly (one warp vote per chunk).
+        // The chunk is handled as two independent halves of eight columns, each a sequence
+        // of passes of eight independent operations, ending in packed bytes: short live
+        // ranges, no per-element control flow.
+        const float sqrt_2_over_pi = 0.79788458347320556640625f, fitting_const = 0.044715f;
+        const float elt_scale = p.po[0].scale;
+        const float sum_scale = SUM != SUM_NONE ? p.po[1].scale : 0.f;
+        const float sum_zp = SUM != SUM_NONE ? (float)p.po[1].zero_point : 0.f;
+        const float inv_abs = 2e-6f * fabsf(k.dst_inv) * fabsf(elt_scale);
+        const bool is_s8 = p.dst_dt == B200_DT_S8;
+        uint32_t packed[CH / 4];
+        uint32_t risky = 0;
+        __syncwarp();
+#pragma unroll
+        for (int hb = 0; hb < CH; hb += 8) {
+            float x[8], g[8], t[8], o[8];
+#pragma unroll
+            for (int q = 0; q < 2; ++q) {
+                const float4 a = ((const float4 *)wscale)[hb / 4 + q], b = ((const float4 *)bias)[hb / 4 + q];
+                const int4 c = ((const int4 *)comp)[hb / 4 + q];
+                const float ws[4] = {a.x, a.y, a.z, a.w}, bs[4] = {b.x, b.y, b.z, b.w};
+                const int cs[4] = {c.x, c.y, c.z, c.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float acc = FP8 ? __uint_as_float(v[hb + 4 * q + i]) : (float)((int)v[hb + 4 * q + i] - cs[i]);
+                    x[4 * q + i] = __fadd_rn(__fmul_rn(__fmul_rn(acc, k.src_scale), ws[i]), bs[i]);
+                }
             }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                stage[hb + j][lane] = x[j]; // parked for the rare exact recomputation
+                g[j] = __fmul_rn(__fmul_rn(sqrt_2_over_pi, x[j]), __fadd_rn(1.f, __fmul_rn(__fmul_rn(fitting_const, x[j]), x[j])));
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) t[j] = tanh_fast(g[j]);
+            const float4 z0 = ((const float4 *)zp)[hb / 4], z1 = ((const float4 *)zp)[hb / 4 + 1];
+            const float zs[8] = {z0.x, z0.y, z0.z, z0.w, z1.x, z1.y, z1.z, z1.w};
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const bool sat_arg = fabsf(g[j]) >= 9.02f;
+                const float h = 0.5f * x[j];
+                const float gelu = sat_arg ? (g[j] > 0 ? x[j] : -0.f) : fmaf(h, t[j], h);
+                float r = __fmul_rn(gelu, elt_scale);
+                if (SUM != SUM_NONE) r = __fadd_rn(r, __fmul_rn(sum_scale, __fsub_rn(old_val(hb + j), sum_zp)));
+                r = __fmul_rn(r, k.dst_inv);
+                o[j] = FP8 ? r : __fadd_rn(r, zs[j]);
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                // distance of o from the nearest rounding boundary: 0.5 - |o - rint(o)|
+                const float tau = fmaf(inv_abs, fabsf(x[j]) + 1.f, 4e-7f * fabsf(o[j]));
+                const bool rk = fabsf(g[j]) < 9.02f && fabsf(o[j] - rintf(o[j])) > 0.5f - tau;
+                risky |= (rk ? 1u : 0u) << (hb + j);
+            }
+#pragma unroll
+            for (int q = 0; q < 2; ++q) {
+                uint32_t w = 0;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) w |= (is_s8 ? cvt_sat_s8(o[4 * q + i]) : cvt_sat_u8(o[4 * q + i])) << (8 * i);
+                packed[hb / 4 + q] = w;
+            }
+        }
+        if (__any_sync(0xffffffffu, risky != 0)) {
+            // exact recomputation of the flagged columns, column index known only at run time
+#pragma unroll 1
+            for (int j = 0; j < CH; ++j) {
+                if (!(risky & (1u << j))) continue;
+                float r = __fmul_rn(gelu_tanh_exact(stage[j][lane]), elt_scale);
+                if (SUM != SUM_NONE)
+                    r = __fadd_rn(r, __fmul_rn(sum_scale, __fsub_rn(j < nvalid ? load_f32(k.sum_dt, drow, j) : 0.f, sum_zp)));
+                r = __fmul_rn(r, k.dst_inv);
+                if (!FP8) r = __fadd_rn(r, zp[j]);
+                const uint32_t byte = is_s8 ? cvt_sat_s8(r) : cvt_sat_u8(r);
+                const int sh = (j & 3) * 8;
+#pragma unroll
+                for (int q = 0; q < CH / 4; ++q)
+                    if (q == (j >> 2)) packed[q] = (packed[q] & ~(0xffu << sh)) | (byte << sh);
+            }
+        }
+        if (nvalid == CH && ((uintptr_t)drow & 15) == 0) {
+            ((uint4 *)drow)[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
         } else {
 #pragma unroll
-            for (int j = 0; j < CH; ++j) old[j] = j < nvalid ? load_f32(k.sum_dt, drow, j) : 0.f;
+            for (int j = 0; j < CH; ++j)
+                if (j < nvalid) ((uint8_t *)drow)[j] = (uint8_t)(packed[j >> 2] >> ((j & 3) * 8));
+        }
+        return;
+    }
+
+    // accumulator -> scaled value + bias (neutral elements where unset), four columns per
+    // 128-bit shared-memory read of each per-column vector
+    float y[CH];
+#pragma unroll
+    for (int q = 0; q < CH / 4; ++q) {
+        const float4 a = ((const float4 *)wscale)[q], b = ((const float4 *)bias)[q];
+        const int4 c = ((const int4 *)comp)[q];
+        const float ws[4] = {a.x, a.y, a.z, a.w}, bs[4] = {b.x, b.y, b.z, b.w};
+        const int cs[4] = {c.x, c.y, c.z, c.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int j = 4 * q + i;
+            const float x = FP8 ? __uint_as_float(v[j]) : (float)((int)v[j] - cs[i]);
+            y[j] = __fadd_rn(__fmul_rn(__fmul_rn(x, k.src_scale), ws[i]), bs[i]);
         }
     }
-    // destination scale and zero-point
+    // destination scale and zero-point (zp[] holds -0 when no zero-point is to be added)
     auto tail = [&](float x, int j) -> float {
         x = __fmul_rn(x, k.dst_inv);
-        return (!FP8 && k.int8_nondefault) ? __fadd_rn(x, zp[j]) : x;
+        return FP8 ? x : __fadd_rn(x, zp[j]);
     };
 
     if (EPI == EPI_NONE) {
@@ -342,57 +493,17 @@ __device__ __forceinline__ void epilogue_chunk(const b200_matmul_params_t &p, co
         for (int i = 0; i < p.npo; ++i) {
             const b200_postop_t &e = p.po[i];
             if (e.kind == B200_PO_SUM) {
-                const float sc = e.scale, z = (float)e.zero_point;
+                if (SUM != SUM_NONE) {
+                    const float sc = e.scale, z = (float)e.zero_point;
 #pragma unroll
-                for (int j = 0; j < CH; ++j) y[j] = __fadd_rn(y[j], __fmul_rn(sc, __fsub_rn(old[j], z)));
+                    for (int j = 0; j < CH; ++j) y[j] = __fadd_rn(y[j], __fmul_rn(sc, __fsub_rn(old_val(j), z)));
+                }
             } else {
                 eltwise_simple_chunk(e, y);
             }
         }
 #pragma unroll
         for (int j = 0; j < CH; ++j) y[j] = tail(y[j], j);
-    } else if (EPI == EPI_GELU_Q) {
-        // gelu_tanh (then optionally sum) into an integer destination, bit-exact.  The exact
-        // value needs a double-precision tanh; almost always it is not needed:
-        //  * |tanh argument| >= 9.02: the float tanh is exactly +-1, gelu(x) is x or -0;
-        //  * otherwise evaluate with a fast tanh (absolute error < 1e-6) and check how far the
-        //    value to be rounded is from a rounding boundary (k + 0.5).  The fast and the
-        //    exact value differ by less than tau (propagated error bound with a 4x margin),
-        //    so away from a boundary both round to the same integer; only elements within
-        //    tau of one are recomputed exactly (one warp vote per chunk).
-        const float sqrt_2_over_pi = 0.79788458347320556640625f, fitting_const = 0.044715f;
-        const float elt_scale = p.po[0].scale;
-        const float sum_scale = k.any_sum ? p.po[1].scale : 0.f, sum_zp = k.any_sum ? (float)p.po[1].zero_point : 0.f;
-        const float inv_abs = fabsf(k.dst_inv) * fabsf(elt_scale);
-        const float lo = p.dst_dt == B200_DT_S8 ? -128.f : 0.f, hi = p.dst_dt == B200_DT_S8 ? 127.f : 255.f;
-        auto rest = [&](float ge, int j) -> float {
-            float r = __fmul_rn(ge, elt_scale);
-            if (k.any_sum) r = __fadd_rn(r, __fmul_rn(sum_scale, __fsub_rn(old[j], sum_zp)));
-            return tail(r, j);
-        };
-        uint32_t risky = 0;
-        float xs[CH];
-#pragma unroll
-        for (int j = 0; j < CH; ++j) {
-            const float x = y[j];
-            xs[j] = x;
-            const float g = __fmul_rn(__fmul_rn(sqrt_2_over_pi, x), __fadd_rn(1.f, __fmul_rn(__fmul_rn(fitting_const, x), x)));
-            const bool sat_arg = fabsf(g) >= 9.02f;
-            const float h = 0.5f * x;
-            const float approx = fmaf(h, tanh_fast(g), h);
-            const float gelu = sat_arg ? (g > 0 ? x : -0.f) : approx;
-            const float out = rest(gelu, j);
-            const float tau = fmaf(2e-6f * inv_abs, fabsf(x) + 1.f, 4e-7f * fabsf(out));
-            const float fr = out - floorf(out);
-            const bool r = !sat_arg && out > lo - 1.f && out < hi + 1.f && fabsf(fr - 0.5f) < tau;
-            risky |= (r ? 1u : 0u) << j;
-            y[j] = out;
-        }
-        if (__any_sync(0xffffffffu, risky != 0)) {
-#pragma unroll
-            for (int j = 0; j < CH; ++j)
-                if (risky & (1u << j)) y[j] = rest(gelu_tanh_f32(xs[j]), j);
-        }
     } else {
         // interpreted chain: one copy of the code in a rolled loop over the chunk, staged
         // through shared memory (registers cannot be indexed dynamically)
@@ -417,8 +528,10 @@ __device__ __forceinline__ void epilogue_chunk(const b200_matmul_params_t &p, co
 
 // ---- the kernel -------------------------------------------------------------------------
 
-template <bool FP8, int EPI>
-__global__ void __launch_bounds__(NUM_THREADS, 1) matmul_tc8_kernel(const __grid_constant__ CUtensorMap tmap_a,
+// 18 warps land 5 + 5 + 4 + 4 on the four schedulers, so a thread may use at most
+// 16384 / (5 * 32) = 102 registers; declaring 640 threads makes ptxas stay within that.
+template <bool FP8, int EPI, int SUM>
+__global__ void __launch_bounds__(640, 1) matmul_tc8_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const __grid_constant__ CUtensorMap tmap_b, const __grid_constant__ tc8_args_t args) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -504,9 +617,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) matmul_tc8_kernel(const __grid
         }
     } else {
         // ---------------- epilogue warps ----------------
-        const int ew = warp - 2;           // 0..7
+        const int ew = warp - 2;           // 0..15
         const int quarter = warp & 3;      // TMEM lanes this warp may read: 32*quarter .. +31
-        const int half = ew >> 2;          // which half of the tile's columns this warp converts
+        const int half = ew >> 2;          // which quarter of the tile's columns this warp converts
         float *wscale = ctrl->wscale[ew], *bias = ctrl->bias[ew], *zpv = ctrl->zp[ew];
         int32_t *comp = ctrl->comp[ew];
         float(*stage)[33] = ctrl->stage[ew];
@@ -535,21 +648,45 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) matmul_tc8_kernel(const __grid
                 wscale[j] = (in && p.wei_scale.ptr) ? load_f32(p.wei_scale.dt, p.wei_scale.ptr, n * p.wei_scale.s1) : 1.f;
                 bias[j] = (in && bias_per_col) ? load_f32(p.bias_dt, p.bias, n * p.bias_sn) : -0.f;
                 comp[j] = (in && has_comp) ? zp_src * p.wei_colsum[n] : 0;
-                zpv[j] = (in && p.dst_zp.ptr) ? (float)((const int32_t *)p.dst_zp.ptr)[p.dst_zp.s1 ? n : 0] : 0.f;
+                // the int8 path adds the zero-point (+0 when unset) whenever any attribute is set; -0 adds nothing
+                zpv[j] = !k.int8_nondefault ? -0.f
+                        : (in && p.dst_zp.ptr) ? (float)((const int32_t *)p.dst_zp.ptr)[p.dst_zp.s1 ? n : 0] : 0.f;
             }
             __syncwarp();
+            const int64_t m = m0 + quarter * 32 + lane;
+            const uint32_t trow = tmem_base + ((uint32_t)(quarter * 32) << 16) + a * BN + half * EPI_COLS;
+            // Prior destination bytes of this warp's columns (sum post-op): requested now, for
+            // the whole tile, so that the DRAM latency passes while the accumulator is still
+            // being computed.  One aligned 16-byte read per chunk where that is possible.
+            constexpr int NCH = EPI_COLS / CH;
+            const char *drow0 = (const char *)p.dst + (size_t)((m < p.M ? m : 0) * p.dst_sm + n0) * (dt_bits(p.dst_dt) / 8);
+            const bool sum8 = SUM == SUM_8BIT && EPI != EPI_GENERIC && m < p.M && (((uintptr_t)drow0) & 15) == 0;
+            static_assert(NCH == 4, "the prefetch registers below are named for four chunks");
+            uint4 ob0 = make_uint4(0, 0, 0, 0), ob1 = ob0, ob2 = ob0, ob3 = ob0;
+            const bool of0 = sum8 && n0 + 1 * CH <= p.N, of1 = sum8 && n0 + 2 * CH <= p.N;
+            const bool of2 = sum8 && n0 + 3 * CH <= p.N, of3 = sum8 && n0 + 4 * CH <= p.N;
+            if (of0) ob0 = *(const uint4 *)(drow0);
+            if (of1) ob1 = *(const uint4 *)(drow0 + CH);
+            if (of2) ob2 = *(const uint4 *)(drow0 + 2 * CH);
+            if (of3) ob3 = *(const uint4 *)(drow0 + 3 * CH);
+            uint32_t ofbits = (of0 ? 1u : 0u) | (of1 ? 2u : 0u) | (of2 ? 4u : 0u) | (of3 ? 8u : 0u);
             ok = mbar_wait(&ctrl->tmem_full[a], use & 1, ctrl, p.status, ST_WAIT_TMEM_FULL);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tcgen05_fence_after();
-            const int64_t m = m0 + quarter * 32 + lane;
-            const uint32_t trow = tmem_base + ((uint32_t)(quarter * 32) << 16) + a * BN + half * EPI_COLS;
+            // one copy of the chunk code, executed four times (the unrolled form does not fit
+            // the instruction cache); the prefetched bytes rotate through named registers
 #pragma unroll 1
-            for (int c = 0; c < EPI_COLS / CH; ++c) {
+            for (int c = 0; c < NCH; ++c) {
                 uint32_t v[CH];
-                tmem_ld16(trow + c * CH, v);
-                epilogue_chunk<FP8, EPI>(p, v, m, n0 + c * CH, wscale + c * CH, bias + c * CH, comp + c * CH, zpv + c * CH, k,
-                        stage, lane);
+                tmem_ld16_issue(trow + c * CH, v);
+                tmem_ld_wait(v);
+                epilogue_chunk<FP8, EPI, SUM>(p, v, m, n0 + c * CH, wscale + c * CH, bias + c * CH, comp + c * CH, zpv + c * CH, k,
+                        stage, lane, ob0, (ofbits & 1u) != 0);
+                ob0 = ob1;
+                ob1 = ob2;
+                ob2 = ob3;
+                ofbits >>= 1;
             }
             tcgen05_fence_before();
             __syncwarp();
@@ -681,22 +818,37 @@ extern "C" int b200_matmul_tc8_launch(const b200_matmul_params_t *p, b200_stream
     }
     if (p->bias && p->bias_sm) epi = EPI_GENERIC; // a bias that varies along M is added by the interpreted path
 
+    // how the sum post-op reads the prior destination
+    int sum = SUM_NONE;
+    if (epi == EPI_SIMPLE || epi == EPI_GELU_Q) {
+        for (int i = 0; i < p->npo; ++i)
+            if (p->po[i].kind == B200_PO_SUM) {
+                const int sdt = p->po[i].dt != B200_DT_UNDEF ? p->po[i].dt : p->dst_dt;
+                sum = (sdt == B200_DT_S8 || sdt == B200_DT_U8) ? SUM_8BIT : SUM_OTHER;
+            }
+        if (epi == EPI_GELU_Q && sum == SUM_OTHER) epi = EPI_GENERIC, sum = SUM_NONE;
+    }
+
     typedef void (*kernel_t)(const CUtensorMap, const CUtensorMap, const tc8_args_t);
-    static const kernel_t table[2][4] = {
-            {matmul_tc8_kernel<false, EPI_NONE>, matmul_tc8_kernel<false, EPI_SIMPLE>, matmul_tc8_kernel<false, EPI_GELU_Q>,
-                    matmul_tc8_kernel<false, EPI_GENERIC>},
-            {matmul_tc8_kernel<true, EPI_NONE>, matmul_tc8_kernel<true, EPI_SIMPLE>, matmul_tc8_kernel<true, EPI_GELU_Q>,
-                    matmul_tc8_kernel<true, EPI_GENERIC>}};
-    kernel_t kern = table[f8 ? 1 : 0][epi];
+#define TC8_ROW(F) \
+    {{matmul_tc8_kernel<F, EPI_NONE, SUM_NONE>, nullptr, nullptr}, \
+            {matmul_tc8_kernel<F, EPI_SIMPLE, SUM_NONE>, matmul_tc8_kernel<F, EPI_SIMPLE, SUM_8BIT>, \
+                    matmul_tc8_kernel<F, EPI_SIMPLE, SUM_OTHER>}, \
+            {matmul_tc8_kernel<F, EPI_GELU_Q, SUM_NONE>, matmul_tc8_kernel<F, EPI_GELU_Q, SUM_8BIT>, nullptr}, \
+            {matmul_tc8_kernel<F, EPI_GENERIC, SUM_NONE>, nullptr, nullptr}}
+    static const kernel_t table[2][4][3] = {TC8_ROW(false), TC8_ROW(true)};
+#undef TC8_ROW
+    kernel_t kern = table[f8 ? 1 : 0][epi][sum];
+    if (!kern) return B200_ERR_UNSUPPORTED;
     // opt in to the large dynamic shared memory once per kernel and device
     static std::mutex attr_mu;
-    static bool attr_done[64][2][4] = {};
+    static bool attr_done[64][2][4][3] = {};
     {
         std::lock_guard<std::mutex> g(attr_mu);
-        if (dev < 64 && !attr_done[dev][f8 ? 1 : 0][epi]) {
+        if (dev < 64 && !attr_done[dev][f8 ? 1 : 0][epi][sum]) {
             cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
             if (e != cudaSuccess) return (int)e;
-            attr_done[dev][f8 ? 1 : 0][epi] = true;
+            attr_done[dev][f8 ? 1 : 0][epi][sum] = true;
         }
     }
     kern<<<grid, NUM_THREADS, SMEM_BYTES, (cudaStream_t)stream>>>(ta, tb, a);

@@ -13,7 +13,7 @@
 // Structure (one persistent CTA per SM, 576 threads):
 //   warp 0      TMA producer: cp.async.bulk.tensor 2-D loads (no multicast) of a
 //               128 x 128-byte A tile and a 256 x 128-byte W tile per k-block into a
-//               3-stage ring of 128-byte-swizzled shared memory, completion on
+//               4-stage ring of 128-byte-swizzled shared memory, completion on
 //               "full" mbarriers.
 //   warp 1      MMA issuer: one lane issues tcgen05.mma.cta_group::1 (kind::i8 or
 //               kind::f8f6f4), 128 x 256 x 32 per instruction, four per k-block,
@@ -44,7 +44,7 @@ namespace b200 {
 constexpr int BM = 128;          // rows of dst per tile (= TMEM lanes)
 constexpr int BN = 256;          // columns of dst per tile (= one MMA's N)
 constexpr int BK = 128;          // bytes of K per stage (= one 128-byte swizzle row)
-constexpr int STAGES = 3;
+constexpr int STAGES = 4;
 constexpr int A_BYTES = BM * BK; // 16 KiB
 constexpr int B_BYTES = BN * BK; // 32 KiB
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
@@ -70,9 +70,6 @@ struct smem_ctrl_t {
     alignas(16) float bias[EPI_WARPS][EPI_COLS];     // bias, -0 when unset (x + -0 == x for every x)
     alignas(16) int32_t comp[EPI_WARPS][EPI_COLS];   // zp_src * colsum_W[n], 0 when unset
     alignas(16) float zp[EPI_WARPS][EPI_COLS];       // destination zero-point addend
-    // per epilogue warp: staging of one chunk for the interpreted (EPI_GENERIC) path;
-    // pitch 33 keeps it free of bank conflicts
-    float stage[EPI_WARPS][CH][33];
 };
 
 static_assert(offsetof(smem_ctrl_t, wscale) % 16 == 0 && offsetof(smem_ctrl_t, bias) % 16 == 0
@@ -171,6 +168,14 @@ __device__ __forceinline__ void tmem_ld_wait(uint32_t (&v)[16]) {
                  "+r"(v[9]), "+r"(v[10]), "+r"(v[11]), "+r"(v[12]), "+r"(v[13]), "+r"(v[14]), "+r"(v[15])
                  :
                  : "memory");
+}
+
+// one 32-bit column of this thread's TMEM lane (interpreted epilogue, exact recomputation)
+__device__ __forceinline__ uint32_t tmem_ld1(uint32_t taddr) {
+    uint32_t v;
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(v) : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" : "+r"(v) : : "memory");
+    return v;
 }
 
 // shared-memory matrix descriptor: K-major operand, 128-byte swizzle, rows of 128
@@ -336,7 +341,7 @@ enum { SUM_NONE = 0, SUM_8BIT = 1, SUM_OTHER = 2 };
 template <bool FP8, int EPI, int SUM>
 __device__ __forceinline__ void epilogue_chunk(const b200_matmul_params_t &p, const uint32_t (&v)[CH], int64_t m,
         int64_t n0, const float *wscale, const float *bias, const int32_t *comp, const float *zp, const epi_consts_t &k,
-        float (*stage)[33], int lane, uint4 old_raw, bool old_prefetched) {
+        uint32_t taddr, int lane, uint4 old_raw, bool old_prefetched) {
     const int64_t nvalid = m < p.M ? (p.N - n0 < CH ? p.N - n0 : CH) : 0;
     char *drow = (char *)p.dst + (size_t)((m < p.M ? m : 0) * p.dst_sm + n0) * (dt_bits(p.dst_dt) / 8);
 
@@ -367,6 +372,25 @@ __device__ __forceinline__ void epilogue_chunk(const b200_matmul_params_t &p, co
     };
 
     // per-column vectors of the chunk as 128-bit shared-memory reads
+    if (EPI == EPI_GENERIC) {
+        // interpreted chain: one copy of the code in a rolled loop over the chunk; each
+        // column of the accumulator is read from tensor memory when its turn comes
+#pragma unroll 1
+        for (int j = 0; j < CH; ++j) {
+            const uint32_t raw = tmem_ld1(taddr + j);
+            if (j >= nvalid) continue;
+            const float acc = FP8 ? __uint_as_float(raw) : (float)((int)raw - comp[j]);
+            float x = __fadd_rn(__fmul_rn(__fmul_rn(acc, k.src_scale), wscale[j]), bias[j]);
+            if (p.bias && p.bias_sm) // a bias that varies along M is not part of the per-column vector
+                x = __fadd_rn(x, load_f32(p.bias_dt, p.bias, m * p.bias_sm + (n0 + j) * p.bias_sn));
+            const float o = k.any_sum ? load_f32(k.sum_dt, drow, j) : 0.f;
+            x = __fmul_rn(apply_post_ops(p, x, o, m, n0 + j), k.dst_inv);
+            if (!FP8) x = __fadd_rn(x, zp[j]);
+            store_f32(p.dst_dt, x, drow, j);
+        }
+        return;
+    }
+
     if (EPI == EPI_GELU_Q) {
         // gelu_tanh (then optionally sum) into an s8 / u8 destination, bit-exact.  The exact
         // value needs a double-precision tanh; almost always it is not needed:
@@ -387,7 +411,6 @@ __device__ __forceinline__ void epilogue_chunk(const b200_matmul_params_t &p, co
         const bool is_s8 = p.dst_dt == B200_DT_S8;
         uint32_t packed[CH / 4];
         uint32_t risky = 0;
-        __syncwarp();
 #pragma unroll
         for (int hb = 0; hb < CH; hb += 8) {
             float x[8], g[8], t[8], o[8];
@@ -405,7 +428,6 @@ __device__ __forceinline__ void epilogue_chunk(const b200_matmul_params_t &p, co
             }
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
-                stage[hb + j][lane] = x[j]; // parked for the rare exact recomputation
                 g[j] = __fmul_rn(__fmul_rn(sqrt_2_over_pi, x[j]), __fadd_rn(1.f, __fmul_rn(__fmul_rn(fitting_const, x[j]), x[j])));
             }
 #pragma unroll
@@ -438,11 +460,18 @@ __device__ __forceinline__ void epilogue_chunk(const b200_matmul_params_t &p, co
             }
         }
         if (__any_sync(0xffffffffu, risky != 0)) {
-            // exact recomputation of the flagged columns, column index known only at run time
+            // Exact recomputation of the flagged columns (column index known only at run
+            // time).  The accumulator is still in tensor memory: it is read again, one column
+            // at a time, by the whole warp; lanes that did not flag the column discard it.
+            const uint32_t any_mask = __reduce_or_sync(0xffffffffu, risky);
 #pragma unroll 1
             for (int j = 0; j < CH; ++j) {
+                if (!(any_mask & (1u << j))) continue;
+                const uint32_t raw = tmem_ld1(taddr + j);
                 if (!(risky & (1u << j))) continue;
-                float r = __fmul_rn(gelu_tanh_exact(stage[j][lane]), elt_scale);
+                const float acc = FP8 ? __uint_as_float(raw) : (float)((int)raw - comp[j]);
+                const float xj = __fadd_rn(__fmul_rn(__fmul_rn(acc, k.src_scale), wscale[j]), bias[j]);
+                float r = __fmul_rn(gelu_tanh_exact(xj), elt_scale);
                 if (SUM != SUM_NONE)
                     r = __fadd_rn(r, __fmul_rn(sum_scale, __fsub_rn(j < nvalid ? load_f32(k.sum_dt, drow, j) : 0.f, sum_zp)));
                 r = __fmul_rn(r, k.dst_inv);
@@ -504,24 +533,6 @@ __device__ __forceinline__ void epilogue_chunk(const b200_matmul_params_t &p, co
         }
 #pragma unroll
         for (int j = 0; j < CH; ++j) y[j] = tail(y[j], j);
-    } else {
-        // interpreted chain: one copy of the code in a rolled loop over the chunk, staged
-        // through shared memory (registers cannot be indexed dynamically)
-        __syncwarp();
-#pragma unroll
-        for (int j = 0; j < CH; ++j) stage[j][lane] = y[j];
-        __syncwarp();
-#pragma unroll 1
-        for (int j = 0; j < CH; ++j) {
-            float x = stage[j][lane];
-            if (p.bias && p.bias_sm) // a bias that varies along M was not folded into the per-column vector
-                x = __fadd_rn(x, j < nvalid ? load_f32(p.bias_dt, p.bias, m * p.bias_sm + (n0 + j) * p.bias_sn) : 0.f);
-            const float o = (k.any_sum && j < nvalid) ? load_f32(k.sum_dt, drow, j) : 0.f;
-            stage[j][lane] = tail(j < nvalid ? apply_post_ops(p, x, o, m, n0 + j) : 0.f, j);
-        }
-        __syncwarp();
-#pragma unroll
-        for (int j = 0; j < CH; ++j) y[j] = stage[j][lane];
     }
     store_row(p, y, drow, nvalid);
 }
@@ -622,7 +633,6 @@ __global__ void __launch_bounds__(640, 1) matmul_tc8_kernel(const __grid_constan
         const int half = ew >> 2;          // which quarter of the tile's columns this warp converts
         float *wscale = ctrl->wscale[ew], *bias = ctrl->bias[ew], *zpv = ctrl->zp[ew];
         int32_t *comp = ctrl->comp[ew];
-        float(*stage)[33] = ctrl->stage[ew];
         const bool has_comp = !FP8 && p.src_zp.ptr && p.wei_colsum;
         const int zp_src = has_comp ? load_int(p.src_zp.dt, p.src_zp.ptr, 0) : 0;
         epi_consts_t k;
@@ -682,7 +692,7 @@ __global__ void __launch_bounds__(640, 1) matmul_tc8_kernel(const __grid_constan
                 tmem_ld16_issue(trow + c * CH, v);
                 tmem_ld_wait(v);
                 epilogue_chunk<FP8, EPI, SUM>(p, v, m, n0 + c * CH, wscale + c * CH, bias + c * CH, comp + c * CH, zpv + c * CH, k,
-                        stage, lane, ob0, (ofbits & 1u) != 0);
+                        trow + c * CH, lane, ob0, (ofbits & 1u) != 0);
                 ob0 = ob1;
                 ob1 = ob2;
                 ob2 = ob3;

@@ -353,7 +353,9 @@ __device__ __forceinline__ void epilogue_chunk(const b200_matmul_params_t &p, co
         // ragged or unaligned row: gather the bytes one by one into the same packed form
 #pragma unroll
         for (int q = 0; q < 4; ++q) ow[q] = 0;
-        for (int j = 0; j < nvalid; ++j) ow[j >> 2] |= (uint32_t)((const uint8_t *)drow)[j] << ((j & 3) * 8);
+#pragma unroll
+        for (int j = 0; j < CH; ++j) // unrolled: a run-time index would push the array to local memory
+            if (j < nvalid) ow[j >> 2] |= (uint32_t)((const uint8_t *)drow)[j] << ((j & 3) * 8);
     }
     if (SUM == SUM_OTHER) {
 #pragma unroll
@@ -409,7 +411,8 @@ __device__ __forceinline__ void epilogue_chunk(const b200_matmul_params_t &p, co
         const float sum_zp = SUM != SUM_NONE ? (float)p.po[1].zero_point : 0.f;
         const float inv_abs = 2e-6f * fabsf(k.dst_inv) * fabsf(elt_scale);
         const bool is_s8 = p.dst_dt == B200_DT_S8;
-        uint32_t packed[CH / 4];
+        static_assert(CH == 16, "four packed words per chunk");
+        uint32_t packed[4];
         uint32_t risky = 0;
 #pragma unroll
         for (int hb = 0; hb < CH; hb += 8) {
@@ -478,9 +481,12 @@ __device__ __forceinline__ void epilogue_chunk(const b200_matmul_params_t &p, co
                 if (!FP8) r = __fadd_rn(r, zp[j]);
                 const uint32_t byte = is_s8 ? cvt_sat_s8(r) : cvt_sat_u8(r);
                 const int sh = (j & 3) * 8;
-#pragma unroll
-                for (int q = 0; q < CH / 4; ++q)
-                    if (q == (j >> 2)) packed[q] = (packed[q] & ~(0xffu << sh)) | (byte << sh);
+                const uint32_t keep = ~(0xffu << sh), put = byte << sh;
+                const int q = j >> 2;
+                packed[0] = q == 0 ? (packed[0] & keep) | put : packed[0];
+                packed[1] = q == 1 ? (packed[1] & keep) | put : packed[1];
+                packed[2] = q == 2 ? (packed[2] & keep) | put : packed[2];
+                packed[3] = q == 3 ? (packed[3] & keep) | put : packed[3];
             }
         }
         if (nvalid == CH && ((uintptr_t)drow & 15) == 0) {

@@ -40,6 +40,9 @@ sys.path.insert(0, str(ROOT))
 
 METRIC = "int8_matmul_4096x4096x4096_postops_throughput"
 UNIT = "TOPS"
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the benchmark kernel, from the ncu
+# capture summarised in profiles/tc8_int8_c1_full.md (50.42 MB + 0.50 MB)
+NCU_DRAM_BYTES_PER_LAUNCH = 50.92e6
 WORKLOAD = "int8 s8:s8:s8 4096x4096:4096x4096, per-N wei scales, bf16 bias, gelu_tanh + sum:0.5, dst scale 0.1 zp 3"
 
 
@@ -131,9 +134,14 @@ def main():
     ap.add_argument("--sets", type=int, default=4, help="independent input sets rotated over (L2 defeat)")
     ap.add_argument("--no-extras", action="store_true", help="skip the secondary configurations")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--case", default=None,
+                    help="profiling aid: execute one named configuration --steps times and exit "
+                         "(c0, c1, c2_m1, c2_m16, c2_m128, c3, c3_4096, c4); prints no benchmark line")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
+    if args.case:
+        return run_one_case(args)
     args.warmup = max(args.warmup, 3)
 
     import numpy as np
@@ -299,8 +307,10 @@ def main():
             "config": {"workload": WORKLOAD, "per_gpu": "4096x4096x4096", "parallelism": "m-split x%d, replicated weights" % world,
                        "impl": impl, "l2": "rotating %d input sets, %.0f MB in total (> 126 MB L2)" % (args.sets, set_bytes / 1e6)},
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": int8_peak, "unit": "TFLOP/s",
-                         "frac": achieved / int8_peak, "traffic": None,
-                         "kernel": "matmul_tc8_kernel<int8, gelu+sum requant>", "kernel_ms": kern_avg,
+                         "frac": achieved / int8_peak, "traffic": NCU_DRAM_BYTES_PER_LAUNCH,
+                         "traffic_note": "dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of this kernel on "
+                                         "this workload (profiles/tc8_int8_c1_full.md); algorithmic bytes 67.1e6",
+                         "kernel": "matmul_tc8_kernel<int8, EPI_GELU_Q, SUM_8BIT>", "kernel_ms": kern_avg,
                          "peak_note": "2 x %s bf16 dense burst (%.1f TF/s); no measured int8 figure exists; nominal 4500"
                                       % (peaks["source"], peaks["bf16"])},
             "cpu_baseline": cpu_baseline,
@@ -314,6 +324,22 @@ def main():
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
+    return 0
+
+
+def run_one_case(args):
+    """Executes one configuration a few times through the public API; meant to be run under ncu."""
+    from onednn_b200 import api, workloads as W
+    cases = {"c0": W.config0, "c1": W.config1, "c2_m1": lambda: W.config2(1), "c2_m16": lambda: W.config2(16),
+             "c2_m128": lambda: W.config2(128), "c3": W.config3, "c3_4096": lambda: W.config3(4096, 4096, 4096),
+             "c4": W.config4}
+    eng = api.Engine()
+    strm = api.Stream(eng)
+    plan = api.CasePlan(cases[args.case](), eng, strm, weights="any")
+    for _ in range(max(1, args.steps)):
+        plan.execute()
+    strm.wait()
+    print("executed %s x%d with %s" % (args.case, max(1, args.steps), plan.impl))
     return 0
 
 

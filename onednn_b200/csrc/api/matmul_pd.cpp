@@ -251,7 +251,8 @@ static bool accept_wc(dnnl_primitive_desc *pd) {
     if (M == 0 || N == 0 || K == 0) return reject(name, "zero dim"), false;
     if (M > 512) return reject(name, "M too large for the decode kernel"), false;
     if (N % 16 != 0 || K % 64 != 0) return reject(name, "needs N % 16 == 0 and K % 64 == 0"), false;
-    if (src.is_plain() && src.strides[1] != 1) return reject(name, "src must be row-major"), false;
+    if (src.is_plain() && !(src.strides[1] == 1 && src.strides[0] % 8 == 0 && src.offset0 % 8 == 0))
+        return reject(name, "src must be row-major with 16-byte aligned rows"), false;
     if (dst.is_plain() && dst.strides[1] != 1) return reject(name, "dst must be row-major"), false;
     if (wei.is_plain() && !(wei.strides[1] == 1 && wei.strides[0] == N && wei.offset0 == 0))
         return reject(name, "weights must be dense ab"), false;
@@ -266,7 +267,7 @@ static bool accept_wc(dnnl_primitive_desc *pd) {
         if (!q->set) continue;
         if (q->group_ndims && (q->mask & 2) && q->groups[1] != 1) return reject(name, "groups along N not supported"), false;
         const int64_t gk = (q->mask & 1) ? (q->group_ndims ? q->groups[0] : 1) : K;
-        if (gk % 16 != 0 || K % gk != 0) return reject(name, "K group must be a multiple of 16 that divides K"), false;
+        if (gk % 64 != 0 || K % gk != 0) return reject(name, "K group must be a multiple of 64 that divides K"), false;
         gks[i] = gk;
     }
     if (gks[0] % gks[1] != 0 && gks[1] % gks[0] != 0) return reject(name, "scale and zero-point groups must nest"), false;

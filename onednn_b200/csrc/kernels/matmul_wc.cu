@@ -66,20 +66,65 @@ __device__ __forceinline__ uint4 ldg_stream(const uint4 *p) {
     return v;
 }
 
-// MB = number of 8-row activation blocks handled per pass (1, 2 or 4)
-template <int MB>
+// Scale and zero-point of output column n for K group `grp` (FASTQ) or for the group that
+// contains k (generic).  FASTQ: bf16 scales and u4 zero-points, both [K / group][N] with
+// the same group (the common decode configuration): two direct loads.
+template <bool FASTQ>
+__device__ __forceinline__ void wc_group_params(const wc_args_t &a, uint32_t grp, uint32_t k, uint32_t n, float &s,
+        float &c) {
+    if (FASTQ) {
+        const uint32_t row = grp * (uint32_t)a.N + n;
+        s = __uint_as_float((uint32_t)((const uint16_t *)a.scale)[row] << 16);
+        const uint32_t byte = ((const uint8_t *)a.zp)[row >> 1];
+        c = a.nibble_offset + (float)((byte >> ((row & 1) * 4)) & 0xf);
+    } else {
+        s = 1.f;
+        c = a.nibble_offset;
+        if (a.scale) s = load_f32(a.scale_dt, a.scale, (int64_t)(k / a.scale_g0) * a.scale_s0 + (int64_t)n * a.scale_s1);
+        if (a.zp) c += (float)load_int(a.zp_dt, a.zp, (int64_t)(k / a.zp_g0) * a.zp_s0 + (int64_t)n * a.zp_s1);
+    }
+}
+
+// MB   = number of 8-row activation blocks handled per pass (1, 2 or 4)
+// XTAB = single activation row: sum_k x per tile step comes from a table the CTA builds
+//        in shared memory; otherwise a second MMA with an all-ones A tile accumulates it.
+//
+// One tile step = 16 output columns x 64 k = 512 bytes of weights = four MMA k-steps.  Within
+// a step the MMA's k slots are permuted so that everything a lane needs is contiguous in
+// memory: lane (g, t) owns k = 16 t + 4 j + {0,1,2,3} of MMA step j, i.e. 32 contiguous
+// bytes of its activation row per tile step (two 128-bit loads), and the pack kernel lays
+// the weight nibbles out for the same permutation.  A dot product does not care in which
+// order k is visited, as long as both operands agree.
+template <int MB, bool FASTQ, bool XTAB>
 __global__ void __launch_bounds__(WC_WARPS * 32) wc_gemv_kernel(const __grid_constant__ wc_args_t a) {
-    const int lane = threadIdx.x & 31;
-    const int g = lane >> 2, t = lane & 3;
-    const int64_t warp = (int64_t)blockIdx.x * WC_WARPS + (threadIdx.x >> 5);
-    const int64_t nwarps = (int64_t)gridDim.x * WC_WARPS;
+    __shared__ float xtab[XTAB ? 1024 : 1]; // sum of the activation row over each tile step (K <= 65536)
+    const uint32_t lane = threadIdx.x & 31;
+    const uint32_t g = lane >> 2, t = lane & 3;
     const uint32_t kchunks = (uint32_t)(a.K / WC_TILE_K);
-    const int64_t steps = (a.N / WC_TILE_N) * (int64_t)kchunks;
-    // equal contiguous ranges: the first (steps % nwarps) warps take one more
-    const int64_t base = steps / nwarps, rem = steps % nwarps;
-    int64_t s_begin = warp * base + (warp < rem ? warp : rem);
-    const int64_t s_end = s_begin + base + (warp < rem ? 1 : 0);
-    if (s_begin >= s_end) return;
+    if (XTAB) {
+        // thread i sums 16 consecutive activations; four neighbours make one tile step
+        const __nv_bfloat16 *xr = a.x + (int64_t)a.m0 * a.x_ld;
+        for (uint32_t i = threadIdx.x; i < kchunks * 4; i += blockDim.x) {
+            const uint4 *xp = reinterpret_cast<const uint4 *>(xr + i * 16);
+            const uint4 u0 = xp[0], u1 = xp[1];
+            const uint32_t w[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
+            float sum = 0.f;
+#pragma unroll
+            for (int q = 0; q < 8; ++q) sum += __uint_as_float(w[q] << 16) + __uint_as_float(w[q] & 0xffff0000u);
+            sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+            sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+            if ((i & 3) == 0) xtab[i >> 2] = sum;
+        }
+        __syncthreads();
+    }
+    // equal contiguous ranges of tile steps: the first (steps % nwarps) warps take one more
+    const uint32_t warp = blockIdx.x * WC_WARPS + (threadIdx.x >> 5);
+    const uint32_t nwarps = gridDim.x * WC_WARPS;
+    const uint32_t steps = (uint32_t)(a.N / WC_TILE_N) * kchunks;
+    const uint32_t base = steps / nwarps, rem = steps % nwarps;
+    const uint32_t s_begin = warp * base + (warp < rem ? warp : rem);
+    const uint32_t count = base + (warp < rem ? 1 : 0);
+    if (count == 0) return;
 
     const uint32_t ones[4] = {0x3f803f80u, 0x3f803f80u, 0x3f803f80u, 0x3f803f80u};
     float acc[MB][4], xs[MB][4], tot[MB][4];
@@ -88,40 +133,51 @@ __global__ void __launch_bounds__(WC_WARPS * 32) wc_gemv_kernel(const __grid_con
 #pragma unroll
         for (int i = 0; i < 4; ++i) acc[mb][i] = xs[mb][i] = tot[mb][i] = 0.f;
 
-    // activation rows this lane feeds into the B fragments (column g of each block)
+    // activation rows this lane feeds into the B fragments (MMA column g of each block),
+    // already offset to this lane's 16 k of a tile step
     const __nv_bfloat16 *xrow[MB];
     bool xok[MB];
 #pragma unroll
     for (int mb = 0; mb < MB; ++mb) {
         const int64_t m = a.m0 + mb * 8 + g;
         xok[mb] = m < a.M;
-        xrow[mb] = a.x + (xok[mb] ? m : 0) * a.x_ld;
+        xrow[mb] = a.x + (xok[mb] ? m : 0) * a.x_ld + 16 * t;
     }
 
-    const uint4 *wp = a.wei + s_begin * 32 + lane;
-    // 3-deep prefetch ring held in named registers (rotated by moves, never indexed)
-    uint4 r0 = ldg_stream(wp), r1 = r0, r2 = r0;
-    if (s_begin + 1 < s_end) r1 = ldg_stream(wp + 32);
-    if (s_begin + 2 < s_end) r2 = ldg_stream(wp + 64);
+    uint32_t strip = s_begin / kchunks;
+    uint32_t kc = s_begin - strip * kchunks;
+    const uint32_t fold_steps = a.fold_k / WC_TILE_K;  // tile steps per quantisation group
+    uint32_t grp = kc / fold_steps;                    // current K group (FASTQ)
+    uint32_t kin = kc - grp * fold_steps;              // tile steps done inside it
 
-    int64_t strip = s_begin / kchunks;
-    uint32_t kc = (uint32_t)(s_begin % kchunks);
-    // k position inside the current fold period, advanced by 16 per MMA step (no division in the loop)
-    uint32_t kin = (kc * WC_TILE_K) % a.fold_k;
-
-    auto fold = [&](uint32_t k_last) {
-        // k_last: any k inside the group being closed
-        const int64_t n0 = strip * WC_TILE_N + g, n1 = n0 + 8;
-        float s0 = 1.f, s1 = 1.f, c0 = a.nibble_offset, c1 = a.nibble_offset;
-        if (a.scale) {
-            const int64_t gi = (k_last / a.scale_g0) * a.scale_s0;
-            s0 = load_f32(a.scale_dt, a.scale, gi + n0 * a.scale_s1);
-            s1 = load_f32(a.scale_dt, a.scale, gi + n1 * a.scale_s1);
+    // FASTQ: the raw scale and zero-point bytes of the group being accumulated are requested
+    // one group ahead (right after the previous fold), so that their latency is not paid at
+    // the fold itself.
+    uint32_t q_s0 = 0, q_s1 = 0, q_z0 = 0, q_z1 = 0;
+    auto request_group = [&]() {
+        if (FASTQ) {
+            const uint32_t row = grp * (uint32_t)a.N + strip * WC_TILE_N + g;
+            q_s0 = ((const uint16_t *)a.scale)[row];
+            q_s1 = ((const uint16_t *)a.scale)[row + 8];
+            q_z0 = ((const uint8_t *)a.zp)[row >> 1];
+            q_z1 = ((const uint8_t *)a.zp)[(row + 8) >> 1];
         }
-        if (a.zp) {
-            const int64_t gi = (k_last / a.zp_g0) * a.zp_s0;
-            c0 += (float)load_int(a.zp_dt, a.zp, gi + n0 * a.zp_s1);
-            c1 += (float)load_int(a.zp_dt, a.zp, gi + n1 * a.zp_s1);
+    };
+    request_group();
+    auto fold = [&]() {
+        const uint32_t n0 = strip * WC_TILE_N + g;
+        float s0, s1, c0, c1;
+        if (FASTQ) {
+            // n0 and n0 + 8 have the same parity: the same nibble of their bytes
+            const uint32_t sh = (n0 & 1) * 4;
+            s0 = __uint_as_float(q_s0 << 16);
+            s1 = __uint_as_float(q_s1 << 16);
+            c0 = a.nibble_offset + (float)((q_z0 >> sh) & 0xf);
+            c1 = a.nibble_offset + (float)((q_z1 >> sh) & 0xf);
+        } else {
+            const uint32_t k_in_group = grp * a.fold_k; // any k of the group being closed
+            wc_group_params<false>(a, grp, k_in_group, n0, s0, c0);
+            wc_group_params<false>(a, grp, k_in_group, n0 + 8, s1, c1);
         }
 #pragma unroll
         for (int mb = 0; mb < MB; ++mb) {
@@ -134,32 +190,44 @@ __global__ void __launch_bounds__(WC_WARPS * 32) wc_gemv_kernel(const __grid_con
         }
     };
     auto flush = [&]() {
-        const int64_t n0 = strip * WC_TILE_N + g, n1 = n0 + 8;
+        float *out = a.acc + (size_t)strip * WC_TILE_N + g;
 #pragma unroll
         for (int mb = 0; mb < MB; ++mb) {
             const int64_t mA = a.m0 + mb * 8 + 2 * t, mB = mA + 1;
             if (mA < a.M) {
-                atomicAdd(a.acc + mA * a.N + n0, tot[mb][0]);
-                atomicAdd(a.acc + mA * a.N + n1, tot[mb][2]);
+                atomicAdd(out + mA * a.N, tot[mb][0]);
+                atomicAdd(out + mA * a.N + 8, tot[mb][2]);
             }
             if (mB < a.M) {
-                atomicAdd(a.acc + mB * a.N + n0, tot[mb][1]);
-                atomicAdd(a.acc + mB * a.N + n1, tot[mb][3]);
+                atomicAdd(out + mB * a.N, tot[mb][1]);
+                atomicAdd(out + mB * a.N + 8, tot[mb][3]);
             }
 #pragma unroll
             for (int i = 0; i < 4; ++i) tot[mb][i] = 0.f;
         }
     };
-
-    for (int64_t s = s_begin; s < s_end; ++s) {
-        const uint4 w4 = r0;
-        r0 = r1;
-        r1 = r2;
-        if (s + 3 < s_end) r2 = ldg_stream(wp + (s + 3 - s_begin) * 32);
+    // one tile step on the 16 bytes of weights w4
+    auto step = [&](const uint4 &w4) {
+        uint4 xa[MB], xb[MB];
+#pragma unroll
+        for (int mb = 0; mb < MB; ++mb) {
+            xa[mb] = make_uint4(0, 0, 0, 0);
+            xb[mb] = xa[mb];
+            if (xok[mb]) {
+                const uint4 *xp = reinterpret_cast<const uint4 *>(xrow[mb] + kc * WC_TILE_K);
+                xa[mb] = xp[0];
+                xb[mb] = xp[1];
+            }
+        }
+        if (XTAB) {
+            // the row's sum over this step; only MMA column 0 (accumulator slots 0 and 2) is real
+            const float sx = xtab[kc];
+            xs[0][0] += sx;
+            xs[0][2] += sx;
+        }
         const uint32_t words[4] = {w4.x, w4.y, w4.z, w4.w};
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-            const uint32_t k0 = kc * WC_TILE_K + j * 16;
             const uint32_t w = words[j];
             uint32_t af[4];
             af[0] = (w & 0x000f000fu) | 0x43004300u;
@@ -168,32 +236,57 @@ __global__ void __launch_bounds__(WC_WARPS * 32) wc_gemv_kernel(const __grid_con
             af[3] = ((w >> 12) & 0x000f000fu) | 0x43004300u;
 #pragma unroll
             for (int mb = 0; mb < MB; ++mb) {
-                uint32_t b0 = 0, b1 = 0;
-                if (xok[mb]) {
-                    b0 = *reinterpret_cast<const uint32_t *>(xrow[mb] + k0 + 2 * t);
-                    b1 = *reinterpret_cast<const uint32_t *>(xrow[mb] + k0 + 2 * t + 8);
-                }
+                const uint32_t b0 = j == 0 ? xa[mb].x : j == 1 ? xa[mb].z : j == 2 ? xb[mb].x : xb[mb].z;
+                const uint32_t b1 = j == 0 ? xa[mb].y : j == 1 ? xa[mb].w : j == 2 ? xb[mb].y : xb[mb].w;
                 mma_bf16_16816(acc[mb], af, b0, b1);
-                mma_bf16_16816(xs[mb], ones, b0, b1);
-            }
-            kin += 16;
-            if (kin == a.fold_k) {
-                fold(k0);
-                kin = 0;
+                if (!XTAB) mma_bf16_16816(xs[mb], ones, b0, b1);
             }
         }
-        // next step: same strip unless the k chunks are exhausted
+        const bool group_done = ++kin == fold_steps;
+        if (group_done) {
+            fold();
+            kin = 0;
+            ++grp;
+        }
         if (++kc == kchunks) {
-            // the last fold of the strip has happened (fold_k divides K)
+            // the last fold of the strip has happened (the fold period divides K)
             flush();
             kc = 0;
+            grp = 0;
             ++strip;
         }
+        if (group_done) request_group(); // for the group that starts now
+    };
+
+    // Four tile steps per iteration with the weights of the next four already requested:
+    // 2 KiB in flight per warp, no register shuffling.
+    const uint4 *wp = a.wei + (size_t)s_begin * 32 + lane;
+    auto fetch = [&](uint32_t i, uint4 &r) {
+        if (i < count) r = ldg_stream(wp + (size_t)i * 32);
+    };
+    uint4 r0 = make_uint4(0, 0, 0, 0), r1 = r0, r2 = r0, r3 = r0;
+    fetch(0, r0);
+    fetch(1, r1);
+    fetch(2, r2);
+    fetch(3, r3);
+    uint32_t s = 0;
+#pragma unroll 1
+    for (; s + 4 <= count; s += 4) {
+        step(r0);
+        fetch(s + 4, r0);
+        step(r1);
+        fetch(s + 5, r1);
+        step(r2);
+        fetch(s + 6, r2);
+        step(r3);
+        fetch(s + 7, r3);
     }
+    if (s < count) step(r0);
+    if (s + 1 < count) step(r1);
+    if (s + 2 < count) step(r2);
     if (kc != 0) {
-        // range ended inside a strip: close the open group, then publish
-        const uint32_t k_done = kc * WC_TILE_K; // k processed so far in this strip
-        if (kin != 0) fold(k_done - 1);
+        // the range ended inside a strip: close the open group, then publish
+        if (kin != 0) fold();
         flush();
     }
 }
@@ -239,7 +332,7 @@ __global__ void __launch_bounds__(256) wc_pack_kernel(const uint8_t *__restrict_
         for (int i = 0; i < 8; ++i) {
             const int p = i & 3, half = i >> 2;
             const int64_t n = strip * WC_TILE_N + g + 8 * (p & 1);
-            const int64_t k = kc * WC_TILE_K + j * 16 + 2 * t + 8 * (p >> 1) + half;
+            const int64_t k = kc * WC_TILE_K + 16 * t + 4 * j + 2 * (p >> 1) + half;
             const int64_t e = k * N + n;
             uint32_t q = (src[e >> 1] >> ((e & 1) * 4)) & 0xf;
             if (is_signed) q ^= 8u; // two's complement nibble -> offset binary (value + 8)
@@ -255,6 +348,29 @@ static inline size_t align256(size_t x) { return (x + 255) / 256 * 256; }
 } // namespace b200
 
 using namespace b200;
+
+// bf16 scales and u4 zero-points, both [K / group][N] over the same K groups
+static bool wc_fast_quant(const b200_matmul_params_t *p, int64_t gs, int64_t gz) {
+    return p->wei_scale.ptr && p->wei_zp.ptr && p->wei_scale.dt == B200_DT_BF16 && p->wei_zp.dt == B200_DT_U4 && gs == gz
+            && p->wei_scale.s0 == p->N && p->wei_scale.s1 == 1 && p->wei_zp.s0 == p->N && p->wei_zp.s1 == 1
+            && p->N * (p->K / gs) < ((int64_t)1 << 31);
+}
+
+static void wc_launch_pass(const wc_args_t &a, int64_t rows, bool fastq, unsigned ctas, cudaStream_t cs) {
+    const unsigned threads = WC_WARPS * 32;
+    const bool xtab = rows == 1 && a.K <= 65536;
+    if (fastq) {
+        if (xtab) wc_gemv_kernel<1, true, true><<<ctas, threads, 0, cs>>>(a);
+        else if (rows <= 8) wc_gemv_kernel<1, true, false><<<ctas, threads, 0, cs>>>(a);
+        else if (rows <= 16) wc_gemv_kernel<2, true, false><<<ctas, threads, 0, cs>>>(a);
+        else wc_gemv_kernel<4, true, false><<<ctas, threads, 0, cs>>>(a);
+    } else {
+        if (xtab) wc_gemv_kernel<1, false, true><<<ctas, threads, 0, cs>>>(a);
+        else if (rows <= 8) wc_gemv_kernel<1, false, false><<<ctas, threads, 0, cs>>>(a);
+        else if (rows <= 16) wc_gemv_kernel<2, false, false><<<ctas, threads, 0, cs>>>(a);
+        else wc_gemv_kernel<4, false, false><<<ctas, threads, 0, cs>>>(a);
+    }
+}
 
 // scratch layout of the wc kernel: [f32 acc M*N][bf16 x copy M*K if src is not bf16][packed weights if plain]
 static void wc_scratch_layout(const b200_matmul_params_t *p, size_t *acc, size_t *xcopy, size_t *packed) {
@@ -292,7 +408,7 @@ extern "C" int b200_matmul_wc_launch(const b200_matmul_params_t *p, b200_stream_
     if (!p->apply_to_int) return B200_ERR_UNSUPPORTED;
     if (p->src_dt != B200_DT_BF16 && p->src_dt != B200_DT_F16 && p->src_dt != B200_DT_F32) return B200_ERR_UNSUPPORTED;
     if (p->N % WC_TILE_N != 0 || p->K % WC_TILE_K != 0 || p->src_sk != 1 || p->dst_sn != 1) return B200_ERR_UNSUPPORTED;
-    if (p->K > (int64_t)1 << 30) return B200_ERR_TOO_LARGE;
+    if (p->K > (int64_t)1 << 30 || (p->N / WC_TILE_N) * (p->K / WC_TILE_K) >= ((int64_t)1 << 31)) return B200_ERR_TOO_LARGE;
     if (p->wei_layout == B200_WEI_PLAIN && !(p->wei_sn == 1 && p->wei_sk == p->N)) return B200_ERR_UNSUPPORTED;
     if (p->wei_layout != B200_WEI_PLAIN && p->wei_layout != B200_WEI_WC4_TILED) return B200_ERR_UNSUPPORTED;
     if (p->src_zp.ptr || p->dst_zp.ptr) return B200_ERR_UNSUPPORTED;
@@ -307,10 +423,12 @@ extern "C" int b200_matmul_wc_launch(const b200_matmul_params_t *p, b200_stream_
         if (p->wei_zp.g1 != 1) return B200_ERR_UNSUPPORTED;
         if (p->wei_zp.s0) gz = p->wei_zp.g0;
     }
-    if (gs % 16 || gz % 16 || p->K % gs || p->K % gz) return B200_ERR_UNSUPPORTED;
+    // a tile step covers 64 k in a permuted order, so groups must be whole tile steps
+    if (gs % WC_TILE_K || gz % WC_TILE_K || p->K % gs || p->K % gz) return B200_ERR_UNSUPPORTED;
     const int64_t fold_k = gs < gz ? gs : gz;
     if (gs % fold_k || gz % fold_k) return B200_ERR_UNSUPPORTED;
-    if (((uintptr_t)p->src & 3) || (p->src_dt == B200_DT_BF16 && (p->src_sm & 1))) return B200_ERR_BAD_ARG;
+    // activations are read 16 bytes at a time
+    if (p->src_dt == B200_DT_BF16 && (((uintptr_t)p->src & 15) || (p->src_sm & 7))) return B200_ERR_BAD_ARG;
 
     size_t acc_b, x_b, w_b;
     wc_scratch_layout(p, &acc_b, &x_b, &w_b);
@@ -363,19 +481,18 @@ extern "C" int b200_matmul_wc_launch(const b200_matmul_params_t *p, b200_stream_
     a.fold_k = (uint32_t)fold_k;
     a.nibble_offset = p->wei_dt == B200_DT_S4 ? 136.f : 128.f;
 
+    const bool fastq = wc_fast_quant(p, gs, gz);
     int dev = 0, sms = 148;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     const int64_t steps = (p->N / WC_TILE_N) * (p->K / WC_TILE_K);
-    int64_t ctas = (int64_t)sms * 4;
+    int64_t ctas = (int64_t)sms * 3;
     if (ctas * WC_WARPS > steps) ctas = (steps + WC_WARPS - 1) / WC_WARPS;
     // activation rows in passes of up to 32 (the weights are re-read from L2)
     for (int64_t m0 = 0; m0 < p->M; m0 += 32) {
         a.m0 = (int)m0;
         const int64_t rows = p->M - m0;
-        if (rows <= 8) wc_gemv_kernel<1><<<(unsigned)ctas, WC_WARPS * 32, 0, cs>>>(a);
-        else if (rows <= 16) wc_gemv_kernel<2><<<(unsigned)ctas, WC_WARPS * 32, 0, cs>>>(a);
-        else wc_gemv_kernel<4><<<(unsigned)ctas, WC_WARPS * 32, 0, cs>>>(a);
+        wc_launch_pass(a, rows, fastq, (unsigned)ctas, cs);
         int rc = after_launch();
         if (rc) return rc;
     }
@@ -427,7 +544,7 @@ extern "C" int b200_matmul_wc_noalloc_launch(const b200_matmul_params_t *p, b200
     if (p->wei_dt != B200_DT_U4 && p->wei_dt != B200_DT_S4) return B200_ERR_UNSUPPORTED;
     if (!p->apply_to_int || p->src_dt != B200_DT_BF16 || p->wei_layout != B200_WEI_WC4_TILED) return B200_ERR_UNSUPPORTED;
     if (p->N % WC_TILE_N != 0 || p->K % WC_TILE_K != 0 || p->src_sk != 1 || p->dst_sn != 1) return B200_ERR_UNSUPPORTED;
-    if (p->K > (int64_t)1 << 30) return B200_ERR_TOO_LARGE;
+    if (p->K > (int64_t)1 << 30 || (p->N / WC_TILE_N) * (p->K / WC_TILE_K) >= ((int64_t)1 << 31)) return B200_ERR_TOO_LARGE;
     if (p->src_zp.ptr || p->dst_zp.ptr) return B200_ERR_UNSUPPORTED;
     if (p->src_scale.ptr && (p->src_scale.s0 || p->src_scale.s1)) return B200_ERR_UNSUPPORTED;
     int64_t gs = p->K, gz = p->K;
@@ -439,10 +556,11 @@ extern "C" int b200_matmul_wc_noalloc_launch(const b200_matmul_params_t *p, b200
         if (p->wei_zp.g1 != 1) return B200_ERR_UNSUPPORTED;
         if (p->wei_zp.s0) gz = p->wei_zp.g0;
     }
-    if (gs % 16 || gz % 16 || p->K % gs || p->K % gz) return B200_ERR_UNSUPPORTED;
+    // a tile step covers 64 k in a permuted order, so groups must be whole tile steps
+    if (gs % WC_TILE_K || gz % WC_TILE_K || p->K % gs || p->K % gz) return B200_ERR_UNSUPPORTED;
     const int64_t fold_k = gs < gz ? gs : gz;
     if (gs % fold_k || gz % fold_k) return B200_ERR_UNSUPPORTED;
-    if (((uintptr_t)p->src & 3) || (p->src_sm & 1) || ((uintptr_t)p->wei & 15)) return B200_ERR_BAD_ARG;
+    if (((uintptr_t)p->src & 15) || (p->src_sm & 7) || ((uintptr_t)p->wei & 15)) return B200_ERR_BAD_ARG;
     // the fixed array bounds the problem: M * N partial sums of 4 bytes
     if ((uint64_t)p->M * (uint64_t)p->N * sizeof(float) > WC_STATIC_SCRATCH_BYTES) return B200_ERR_TOO_LARGE;
 
@@ -474,18 +592,17 @@ extern "C" int b200_matmul_wc_noalloc_launch(const b200_matmul_params_t *p, b200
     a.fold_k = (uint32_t)fold_k;
     a.nibble_offset = p->wei_dt == B200_DT_S4 ? 136.f : 128.f;
 
+    const bool fastq = wc_fast_quant(p, gs, gz);
     int dev = 0, sms = 148;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     const int64_t steps = (p->N / WC_TILE_N) * (p->K / WC_TILE_K);
-    int64_t ctas = (int64_t)sms * 4;
+    int64_t ctas = (int64_t)sms * 3;
     if (ctas * WC_WARPS > steps) ctas = (steps + WC_WARPS - 1) / WC_WARPS;
     for (int64_t m0 = 0; m0 < p->M; m0 += 32) {
         a.m0 = (int)m0;
         const int64_t rows = p->M - m0;
-        if (rows <= 8) wc_gemv_kernel<1><<<(unsigned)ctas, WC_WARPS * 32, 0, cs>>>(a);
-        else if (rows <= 16) wc_gemv_kernel<2><<<(unsigned)ctas, WC_WARPS * 32, 0, cs>>>(a);
-        else wc_gemv_kernel<4><<<(unsigned)ctas, WC_WARPS * 32, 0, cs>>>(a);
+        wc_launch_pass(a, rows, fastq, (unsigned)ctas, cs);
         rc = after_launch();
         if (rc) return rc;
     }

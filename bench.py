@@ -107,7 +107,7 @@ def reference_arm(args):
         print(json.dumps({"impl": "reference", "unavailable": "oracle/_ref was not built (reference tree absent at build time)"}))
         return 0
     case = W.config1()
-    cores = os.cpu_count() or 1
+    cores = B.set_threads(0)
     steps = max(1, args.steps)
     _, impl, _, _ = B.run_reference(case, weights_any=True, iters=max(1, args.warmup))
     _, impl, ms_min, ms_avg = B.run_reference(case, weights_any=True, iters=steps)
@@ -128,7 +128,7 @@ def reference_arm(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=40)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200")
     ap.add_argument("--sets", type=int, default=4, help="independent input sets rotated over (L2 defeat)")
@@ -195,11 +195,13 @@ def main():
     def step(i):
         plan.prim.execute(strm, sets[i % args.sets]["args"])
 
+    # clocks are sampled from the warm-up to the end of the end-to-end loop: the timed region
+    # alone lasts a few milliseconds, less than one sampling period
+    sampler = ClockSampler(local)
+    sampler.start()
     for i in range(args.warmup):
         step(i)
     barrier()
-    sampler = ClockSampler(local)
-    sampler.start()
     launches0 = api.lib().b200_launch_count()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
@@ -210,7 +212,6 @@ def main():
     barrier()
     ms_total = e0.elapsed_time(e1)
     launches = api.lib().b200_launch_count() - launches0
-    clocks = sampler.stop()
     strm.wait()
 
     # ---- the dominant kernel alone: one launch per event pair ----
@@ -236,7 +237,7 @@ def main():
         plan.prim.execute(strm, s["args"])
         h_out.copy_(s["dst"], non_blocking=True)
 
-    e2e_steps = max(3, min(args.steps, 10))
+    e2e_steps = max(3, min(args.steps, 50))
     for i in range(3):
         e2e_step(i)
     barrier()
@@ -246,6 +247,7 @@ def main():
     e1.record(tstream)
     barrier()
     e2e_ms = e0.elapsed_time(e1) / e2e_steps
+    clocks = sampler.stop()
 
     # ---- max over ranks ----
     t = torch.tensor([ms_total, e2e_ms, kern_avg], device="cuda", dtype=torch.float64)
@@ -282,9 +284,10 @@ def main():
         if not args.no_cpu_baseline:
             try:
                 from oracle import binding as B
+                cores = B.set_threads(0)
                 if B.have_reference():
                     _, rimpl, rmin, ravg = B.run_reference(W.config1(), weights_any=True, iters=10)
-                    cpu_baseline = {"value": case.ops / (ravg * 1e-3) / 1e12, "unit": UNIT, "cores": os.cpu_count(),
+                    cpu_baseline = {"value": case.ops / (ravg * 1e-3) / 1e12, "unit": UNIT, "cores": cores,
                                     "kind": "reference",
                                     "sample": "the full 4096^3 problem, 10 executions of %s (weights packed by its own reorder), mean" % rimpl}
                 else:
@@ -292,7 +295,7 @@ def main():
                     t0 = time.time()
                     B.run_oracle(small)
                     sec = time.time() - t0
-                    cpu_baseline = {"value": small.ops / sec / 1e12, "unit": UNIT, "cores": os.cpu_count(), "kind": "port",
+                    cpu_baseline = {"value": small.ops / sec / 1e12, "unit": UNIT, "cores": cores, "kind": "port",
                                     "sample": "512x1024x512 slice of the workload, one execution of the C oracle"}
             except Exception as ex:
                 cpu_baseline = {"error": repr(ex)}

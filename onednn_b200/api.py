@@ -75,12 +75,12 @@ def _ck(status, what):
 
 def _destroy(obj, fn):
     """Release a native handle; quiet during interpreter shutdown, when module globals are gone."""
-    h = getattr(obj, "h", None)
-    if h and _lib is not None:
-        try:
+    try:
+        h = getattr(obj, "h", None)
+        if h and _lib is not None:
             getattr(_lib, fn)(h)
-        except Exception:
-            pass
+    except Exception:
+        pass
     obj.h = None
 
 
@@ -100,7 +100,7 @@ class Engine:
     def get_count(kind=GPU):
         return int(lib().dnnl_engine_get_count(kind))
 
-    def __del__(self):
+    def __del__(self, _destroy=_destroy):
         _destroy(self, "dnnl_engine_destroy")
 
 
@@ -123,7 +123,7 @@ class Stream:
         _ck(lib().dnnl_cuda_interop_stream_get(self.h, C.byref(p)), "cuda_interop_stream_get")
         return p.value or 0
 
-    def __del__(self):
+    def __del__(self, _destroy=_destroy):
         _destroy(self, "dnnl_stream_destroy")
 
 
@@ -176,7 +176,7 @@ class MemoryDesc:
     def format_kind(self):
         return self._query(262, C.c_int).value
 
-    def __del__(self):
+    def __del__(self, _destroy=_destroy):
         if not getattr(self, "borrowed", True):
             _destroy(self, "dnnl_memory_desc_destroy")
 
@@ -216,7 +216,7 @@ class Memory:
         _ck(lib().dnnl_memory_unmap_data(self.h, p), "memory_unmap_data")
         return out
 
-    def __del__(self):
+    def __del__(self, _destroy=_destroy):
         _destroy(self, "dnnl_memory_destroy")
 
 
@@ -242,7 +242,7 @@ class PostOps:
     def __len__(self):
         return lib().dnnl_post_ops_len(self.h)
 
-    def __del__(self):
+    def __del__(self, _destroy=_destroy):
         _destroy(self, "dnnl_post_ops_destroy")
 
 
@@ -273,7 +273,7 @@ class PrimitiveAttr:
     def set_post_ops(self, po):
         _ck(lib().dnnl_primitive_attr_set_post_ops(self.h, po.h), "set_post_ops")
 
-    def __del__(self):
+    def __del__(self, _destroy=_destroy):
         _destroy(self, "dnnl_primitive_attr_destroy")
 
 
@@ -309,7 +309,7 @@ class PrimitiveDesc:
     def scratchpad_desc(self):
         return self.query_md(QUERY_SCRATCHPAD_MD)
 
-    def __del__(self):
+    def __del__(self, _destroy=_destroy):
         _destroy(self, "dnnl_primitive_desc_destroy")
 
 
@@ -341,7 +341,7 @@ class Primitive:
             arr[i].arg, arr[i].memory = k, m.h
         _ck(lib().dnnl_primitive_execute(self.h, stream.h, len(args), arr), "primitive_execute")
 
-    def __del__(self):
+    def __del__(self, _destroy=_destroy):
         _destroy(self, "dnnl_primitive_destroy")
 
 

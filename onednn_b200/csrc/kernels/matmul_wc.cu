@@ -22,11 +22,24 @@
 //        total += s * (acc - (128 + zp) * xsum)
 //    applies scale and zero-point to a whole group at once (4 FMAs per thread
 //    per group).  s4 weights are stored offset by 8, so they fold with 136 + zp.
-//  * Work is split by bytes, not by tiles: the S = (N/16)*(K/64) tile steps are
-//    dealt out in equal contiguous ranges to every warp of a grid sized to the
-//    SM count, each warp streams its range with a 3-deep register prefetch ring
-//    and adds its partial sums into an f32 scratch [M][N] with red.global.add;
-//    a small second kernel applies the epilogue and leaves the scratch zeroed.
+//  * Work is split by bytes, not by tiles.  A unit is one or two tile steps (one
+//    quantisation group where the group is 128 k).  Each CTA of a grid of one CTA
+//    per SM takes a contiguous range of units -- whole strips of 16 output
+//    columns when there are enough strips, an even share of all units otherwise
+//    -- and each of its 16 warps a contiguous part of that range.
+//  * Every warp streams its part through a private ring in shared memory filled
+//    by asynchronous copies (cp.async, 16 bytes per lane and tile step, one commit
+//    group per unit): about 100 KiB of weights in flight per SM without spending
+//    registers on them.  Each lane copies exactly the bytes it will feed to the
+//    MMAs itself, so a lane waits for its own copies only and the ring needs no
+//    barrier.  A stage is refilled as soon as its unit has been folded in.
+//  * A strip is usually shared by a few neighbouring warps.  Each leaves its
+//    partial sums in its own slab of shared memory and adds its unit count to
+//    the strip's counter; the warp that completes the count adds the slabs up and
+//    applies the epilogue, so nobody waits for anybody.  A strip shared between
+//    CTAs goes one level further the same way: red.global.add into the f32
+//    scratch [M][N] plus a global per-strip counter, and the CTA that completes
+//    it applies the epilogue and leaves scratch and counter zeroed.
 #include <mutex>
 
 #include "common.cuh"
@@ -34,23 +47,47 @@
 
 namespace b200 {
 
-constexpr int WC_WARPS = 8;           // warps per CTA
+// warps per CTA (one CTA per SM): a single block of 8 rows leaves registers for 24
+__host__ __device__ constexpr int wc_warps(int mb) { return mb == 1 ? 24 : 16; }
 constexpr int WC_TILE_N = 16;         // output columns per tile (MMA M)
 constexpr int WC_TILE_K = 64;         // k per 512-byte tile step
+constexpr int WC_TILE_BYTES = 512;
+constexpr int WC_MAX_STAGES = 16;     // ring stages per warp (512-byte units)
+constexpr int WC_XTAB_MAX_BYTES = 40960;
+__host__ __device__ constexpr int wc_ring_bytes(int mb) { return mb == 2 ? 8192 : 4096; } // per warp: 96 / 128 / 64 KiB per CTA
+
+// n / d for any 32-bit n with one multiply-high, one subtract, two shifts and one add
+// (round-up method of Granlund and Montgomery)
+struct wc_div_t {
+    uint32_t m, s1, s2;
+};
+__device__ __forceinline__ uint32_t wc_div(uint32_t n, const wc_div_t &d) {
+    const uint32_t t = __umulhi(n, d.m);
+    return (t + ((n - t) >> d.s1)) >> d.s2;
+}
 
 struct wc_args_t {
     const uint4 *wei;       // packed tiles
     const __nv_bfloat16 *x; // activations, row-major, converted to bf16 if needed
     int64_t x_ld;
     float *acc;             // scratch [M][N] f32, zero on entry
+    uint32_t *done;         // scratch [N / 16]: units folded in per strip shared between CTAs, zero on entry
     int64_t M, N, K;
     int m0;                 // first activation row of this pass
     const void *scale; int scale_dt; int64_t scale_s0, scale_s1; uint32_t scale_g0; // g0: K-group size (K if none)
     const void *zp; int zp_dt; int64_t zp_s0, zp_s1; uint32_t zp_g0;
-    uint32_t fold_k;        // fold period in k (multiple of 16)
     float nibble_offset;    // 128 (u4) or 136 (s4 stored offset by 8)
+    uint32_t kchunks;       // K / 64
+    uint32_t ups;           // units per strip = kchunks / U
+    uint32_t units;         // total units = (N / 16) * ups
+    wc_div_t div_ups;       // division by ups
+    wc_div_t div_fu;        // division by the number of units per quantisation group
+    int group_is_unit;      // that number is 1
+    int whole_strips;       // CTA ranges are whole strips
+    uint32_t max_segs;      // upper bound of the strips one CTA touches (size of its counter array)
 };
 
+// d += a * b
 __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
     asm volatile(
             "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
@@ -58,251 +95,362 @@ __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a
             : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-__device__ __forceinline__ uint4 ldg_stream(const uint4 *p) {
-    uint4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-                 : "l"(p));
-    return v;
+__device__ __forceinline__ uint32_t wc_smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+// 16 bytes global -> shared, asynchronously, not kept in L1
+__device__ __forceinline__ void wc_copy16(uint32_t dst, const void *src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void wc_copy_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int PENDING>
+__device__ __forceinline__ void wc_copy_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(PENDING) : "memory");
 }
 
-// Scale and zero-point of output column n for K group `grp` (FASTQ) or for the group that
-// contains k (generic).  FASTQ: bf16 scales and u4 zero-points, both [K / group][N] with
-// the same group (the common decode configuration): two direct loads.
-template <bool FASTQ>
-__device__ __forceinline__ void wc_group_params(const wc_args_t &a, uint32_t grp, uint32_t k, uint32_t n, float &s,
-        float &c) {
-    if (FASTQ) {
-        const uint32_t row = grp * (uint32_t)a.N + n;
-        s = __uint_as_float((uint32_t)((const uint16_t *)a.scale)[row] << 16);
-        const uint32_t byte = ((const uint8_t *)a.zp)[row >> 1];
-        c = a.nibble_offset + (float)((byte >> ((row & 1) * 4)) & 0xf);
-    } else {
-        s = 1.f;
-        c = a.nibble_offset;
-        if (a.scale) s = load_f32(a.scale_dt, a.scale, (int64_t)(k / a.scale_g0) * a.scale_s0 + (int64_t)n * a.scale_s1);
-        if (a.zp) c += (float)load_int(a.zp_dt, a.zp, (int64_t)(k / a.zp_g0) * a.zp_s0 + (int64_t)n * a.zp_s1);
+// Scale and (128 + zero-point) of output column n for the K group that contains k: the
+// general form, any supported type and group combination.
+__device__ __forceinline__ void wc_group_params(const wc_args_t &a, uint32_t k, uint32_t n, float &s, float &c) {
+    s = 1.f;
+    c = a.nibble_offset;
+    if (a.scale) s = load_f32(a.scale_dt, a.scale, (int64_t)(k / a.scale_g0) * a.scale_s0 + (int64_t)n * a.scale_s1);
+    if (a.zp) c += (float)load_int(a.zp_dt, a.zp, (int64_t)(k / a.zp_g0) * a.zp_s0 + (int64_t)n * a.zp_s1);
+}
+
+// How a CTA's range of units [begin, begin + T) is cut into the contiguous parts of its warps.
+struct wc_split_t {
+    uint32_t begin, base, rem; // warp w: base + (w < rem) units from begin + w * base + min(w, rem)
+    __device__ __forceinline__ uint32_t first(uint32_t w) const { return begin + w * base + (w < rem ? w : rem); }
+    __device__ __forceinline__ uint32_t count(uint32_t w) const { return base + (w < rem ? 1 : 0); }
+};
+
+// Epilogue of the part [seg_lo, seg_hi) of strip `strip` that lies in this CTA's range, run
+// by the warp that completed it.  Every warp whose part overlaps it has left its sums in one
+// of its three slabs: slab 0 if the strip is the first one the warp touches, slab 1 if it is
+// the last, slab 2 for a strip in between (which it then owns alone).  A slab is
+// [MB][32 lanes][4], the accumulator fragment as it sat in registers: lane (g, t), slot e =
+// row 2t + (e & 1) of the 8-row block, column 2g + (e >> 1) of the strip.
+// If the part is the whole strip it is finished here: src scale, bias, post-ops, dst scale,
+// conversion, store.  Otherwise the sums go into the global scratch, and the CTA that brings
+// the strip's global unit count to a.ups finishes it from there and leaves scratch and
+// counter zeroed.  Kept out of line so that its registers do not weigh on the streaming loop.
+__device__ __noinline__ void wc_strip_epilogue(const b200_matmul_params_t &p, const wc_args_t &a, const float *slabs,
+        uint32_t slab_floats, const uint2 *wspan, uint32_t nwarps, uint32_t strip, uint32_t seg_lo, uint32_t seg_hi,
+        uint32_t rows, uint32_t lane) {
+    // wspan[w] = (first, last) strip warp w touches, first > last if it has no units: one
+    // lane per warp finds out who has a slab for this strip
+    uint32_t who;
+    {
+        const uint2 span = lane < nwarps ? wspan[lane] : make_uint2(1, 0);
+        who = __ballot_sync(0xffffffffu, span.x <= strip && strip <= span.y);
     }
+    const float dst_inv = dst_scale_reciprocal(p);
+    const float src_scale = p.src_scale.ptr ? load_f32(p.src_scale.dt, p.src_scale.ptr, 0) : 1.f;
+    const uint32_t cells = rows * WC_TILE_N;
+    const bool whole = seg_hi - seg_lo == a.ups;
+    float *out = a.acc + (int64_t)a.m0 * a.N + (int64_t)strip * WC_TILE_N;
+    for (uint32_t i = lane; i < cells; i += 32) {
+        const uint32_t row = i / WC_TILE_N, col = i % WC_TILE_N;
+        const uint32_t at = (((row >> 3) * 32 + (col >> 1) * 4 + ((row & 7) >> 1)) << 2) + (row & 1) + 2 * (col & 1);
+        float d = 0.f;
+        for (uint32_t m = who; m; m &= m - 1) {
+            const uint32_t w = __ffs(m) - 1;
+            const uint2 span = wspan[w];
+            const uint32_t slot = strip == span.x ? 0 : (strip == span.y ? 1 : 2);
+            d += slabs[(w * 3 + slot) * slab_floats + at];
+        }
+        if (whole) {
+            if (p.src_scale.ptr) d = __fmul_rn(d, src_scale);
+            finish_element(p, d, a.m0 + row, (int64_t)strip * WC_TILE_N + col, false, dst_inv);
+        } else {
+            atomicAdd(out + (int64_t)row * a.N + col, d);
+        }
+    }
+    if (whole) return;
+    __threadfence(); // the sums above are visible before the count below
+    __syncwarp();
+    uint32_t before = 0;
+    if (lane == 0) before = atomicAdd(a.done + strip, seg_hi - seg_lo);
+    before = __shfl_sync(0xffffffffu, before, 0);
+    if (before + (seg_hi - seg_lo) != a.ups) return;
+    __threadfence();
+    for (uint32_t i = lane; i < cells; i += 32) {
+        float *cell = out + (int64_t)(i / WC_TILE_N) * a.N + i % WC_TILE_N;
+        float d = __ldcg(cell);
+        *cell = 0.f;
+        if (p.src_scale.ptr) d = __fmul_rn(d, src_scale);
+        finish_element(p, d, a.m0 + i / WC_TILE_N, (int64_t)strip * WC_TILE_N + i % WC_TILE_N, false, dst_inv);
+    }
+    if (lane == 0) a.done[strip] = 0;
 }
 
-// MB   = number of 8-row activation blocks handled per pass (1, 2 or 4)
-// XTAB = single activation row: sum_k x per tile step comes from a table the CTA builds
-//        in shared memory; otherwise a second MMA with an all-ones A tile accumulates it.
+// MB    = number of 8-row activation blocks handled per pass (1, 2 or 4)
+// FASTQ = bf16 scales and u4 zero-points, both [K / group][N] over the same groups (the
+//         common decode configuration): one 32-bit and one 8-bit load per lane and unit
+// XTAB  = sum_k x of every activation row over every tile step comes from a table the CTA
+//         builds in shared memory; otherwise a second MMA with an all-ones A tile
+//         accumulates it (K too large for the table)
+// U     = tile steps per unit (2 when the quantisation group is a multiple of 128 k)
 //
 // One tile step = 16 output columns x 64 k = 512 bytes of weights = four MMA k-steps.  Within
 // a step the MMA's k slots are permuted so that everything a lane needs is contiguous in
 // memory: lane (g, t) owns k = 16 t + 4 j + {0,1,2,3} of MMA step j, i.e. 32 contiguous
 // bytes of its activation row per tile step (two 128-bit loads), and the pack kernel lays
 // the weight nibbles out for the same permutation.  A dot product does not care in which
-// order k is visited, as long as both operands agree.
-template <int MB, bool FASTQ, bool XTAB>
-__global__ void __launch_bounds__(WC_WARPS * 32) wc_gemv_kernel(const __grid_constant__ wc_args_t a) {
-    __shared__ float xtab[XTAB ? 1024 : 1]; // sum of the activation row over each tile step (K <= 65536)
-    const uint32_t lane = threadIdx.x & 31;
+// order k is visited, as long as both operands agree.  The MMA's rows g and g + 8 are output
+// columns 2g and 2g + 1 of the strip, so that a lane's two scales are one 32-bit word and its
+// two zero-points one byte.
+//
+// Dynamic shared memory: [rings W x RING][slabs W x 3 x SLAB][strip spans W]
+// [strip counters max_segs][activation-sum table kchunks x R].
+template <int MB, bool FASTQ, bool XTAB, int U>
+__global__ void __launch_bounds__(wc_warps(MB) * 32, 1)
+        wc_gemv_kernel(const __grid_constant__ wc_args_t a, const __grid_constant__ b200_matmul_params_t p) {
+    constexpr int R = MB * 8;                         // activation rows per pass
+    constexpr uint32_t W = wc_warps(MB);
+    constexpr uint32_t RING = wc_ring_bytes(MB);      // bytes of weights in flight per warp
+    constexpr uint32_t UNIT_BYTES = U * WC_TILE_BYTES;
+    constexpr uint32_t S = RING / UNIT_BYTES;         // ring stages (a power of two)
+    constexpr uint32_t SLAB = MB * 32 * 4;            // floats per slab
+    static_assert(S <= WC_MAX_STAGES && (S & (S - 1)) == 0, "ring stages");
+    extern __shared__ __align__(128) unsigned char wc_smem[];
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const uint32_t g = lane >> 2, t = lane & 3;
-    const uint32_t kchunks = (uint32_t)(a.K / WC_TILE_K);
+    unsigned char *ring = wc_smem + warp * RING;
+    float *slabs = reinterpret_cast<float *>(wc_smem + W * RING);                         // [W][3][SLAB]
+    uint2 *wspan = reinterpret_cast<uint2 *>(slabs + W * 3 * SLAB);                       // [W]
+    uint32_t *segcnt = reinterpret_cast<uint32_t *>(wspan + W);                           // [max_segs]
+    float *xtab = reinterpret_cast<float *>(segcnt + a.max_segs);                         // [kchunks][R]
+    const uint32_t rows = a.M - a.m0 < R ? (uint32_t)(a.M - a.m0) : (uint32_t)R;
+
+    // This CTA's range of units [c_begin, c_begin + T), T >= 1.  a.whole_strips: the ranges are
+    // whole strips (the grid has at most one CTA per strip); otherwise the units are split
+    // evenly and a range may start and end inside a strip.
+    uint32_t c_begin, T;
+    {
+        const uint32_t n = a.whole_strips ? a.units / a.ups : a.units;
+        const uint32_t base = n / gridDim.x, rem = n % gridDim.x;
+        c_begin = blockIdx.x * base + (blockIdx.x < rem ? blockIdx.x : rem);
+        T = base + (blockIdx.x < rem ? 1 : 0);
+        if (a.whole_strips) {
+            c_begin *= a.ups;
+            T *= a.ups;
+        }
+    }
+    const uint32_t c_end = c_begin + T;
+    const uint32_t first_strip = wc_div(c_begin, a.div_ups);
+    // this warp's contiguous part [wb, wb + cw)
+    wc_split_t split;
+    split.begin = c_begin;
+    split.base = T / W;
+    split.rem = T % W;
+    const uint32_t wb = split.first(warp), cw = split.count(warp);
+    const uint32_t my_first = wc_div(wb, a.div_ups), my_last = cw ? wc_div(wb + cw - 1, a.div_ups) : my_first;
+    if (lane == 0) wspan[warp] = cw ? make_uint2(my_first, my_last) : make_uint2(1, 0);
+
+    // Ring: every lane copies, asynchronously, the 16 bytes of each tile step that it will
+    // itself feed to the MMAs, so a lane only ever waits for its own copies and no barrier
+    // is involved.  One commit group per unit, S units ahead.
+    const unsigned char *wsrc = reinterpret_cast<const unsigned char *>(a.wei) + (size_t)wb * UNIT_BYTES + lane * 16;
+    const uint32_t ring_s = wc_smem_u32(ring) + lane * 16;
+    auto request = [&](uint32_t unit_index) {
+        if (unit_index < cw) {
+            const uint32_t dst = ring_s + (unit_index & (S - 1)) * UNIT_BYTES;
+            const unsigned char *src = wsrc + (size_t)unit_index * UNIT_BYTES;
+#pragma unroll
+            for (int s = 0; s < U; ++s) wc_copy16(dst + s * WC_TILE_BYTES, src + s * WC_TILE_BYTES);
+        }
+        wc_copy_commit(); // also when nothing was requested: the group count is what the waits rely on
+    };
+#pragma unroll
+    for (uint32_t s = 0; s < S; ++s) request(s);
+
+    // while those copies fly: clear the strip counters, build the activation-sum table
+    for (uint32_t i = threadIdx.x; i < a.max_segs; i += blockDim.x) segcnt[i] = 0;
     if (XTAB) {
-        // thread i sums 16 consecutive activations; four neighbours make one tile step
-        const __nv_bfloat16 *xr = a.x + (int64_t)a.m0 * a.x_ld;
-        for (uint32_t i = threadIdx.x; i < kchunks * 4; i += blockDim.x) {
-            const uint4 *xp = reinterpret_cast<const uint4 *>(xr + i * 16);
+        // thread i sums 16 consecutive activations of one row; four neighbours make one tile step
+        const uint32_t pieces = rows * a.kchunks * 4;
+        for (uint32_t i = threadIdx.x; i < (uint32_t)R * a.kchunks; i += blockDim.x)
+            if (i >= rows * a.kchunks) xtab[(i % a.kchunks) * R + i / a.kchunks] = 0.f; // rows past the last
+        for (uint32_t i = threadIdx.x; i < pieces; i += blockDim.x) {
+            const uint32_t cell = i >> 2, row = cell / a.kchunks, kc = cell - row * a.kchunks;
+            const uint4 *xp = reinterpret_cast<const uint4 *>(
+                    a.x + (int64_t)(a.m0 + row) * a.x_ld + (int64_t)kc * WC_TILE_K + (i & 3) * 16);
             const uint4 u0 = xp[0], u1 = xp[1];
             const uint32_t w[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
             float sum = 0.f;
 #pragma unroll
             for (int q = 0; q < 8; ++q) sum += __uint_as_float(w[q] << 16) + __uint_as_float(w[q] & 0xffff0000u);
-            sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-            sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-            if ((i & 3) == 0) xtab[i >> 2] = sum;
+            // pieces is a multiple of 4, not of 32: only the four lanes of a tile step take part
+            const uint32_t quad = 0xfu << (lane & 28);
+            sum += __shfl_xor_sync(quad, sum, 1);
+            sum += __shfl_xor_sync(quad, sum, 2);
+            if ((i & 3) == 0) xtab[kc * R + row] = sum;
         }
-        __syncthreads();
     }
-    // equal contiguous ranges of tile steps: the first (steps % nwarps) warps take one more
-    const uint32_t warp = blockIdx.x * WC_WARPS + (threadIdx.x >> 5);
-    const uint32_t nwarps = gridDim.x * WC_WARPS;
-    const uint32_t steps = (uint32_t)(a.N / WC_TILE_N) * kchunks;
-    const uint32_t base = steps / nwarps, rem = steps % nwarps;
-    const uint32_t s_begin = warp * base + (warp < rem ? warp : rem);
-    const uint32_t count = base + (warp < rem ? 1 : 0);
-    if (count == 0) return;
-
-    const uint32_t ones[4] = {0x3f803f80u, 0x3f803f80u, 0x3f803f80u, 0x3f803f80u};
-    float acc[MB][4], xs[MB][4], tot[MB][4];
-#pragma unroll
-    for (int mb = 0; mb < MB; ++mb)
-#pragma unroll
-        for (int i = 0; i < 4; ++i) acc[mb][i] = xs[mb][i] = tot[mb][i] = 0.f;
+    __syncthreads();
 
     // activation rows this lane feeds into the B fragments (MMA column g of each block),
-    // already offset to this lane's 16 k of a tile step
+    // already offset to this lane's 16 k of a tile step.  Columns past the last row re-read
+    // the last row: an MMA column only ever reaches its own accumulator column, and those
+    // are never stored.
     const __nv_bfloat16 *xrow[MB];
-    bool xok[MB];
 #pragma unroll
     for (int mb = 0; mb < MB; ++mb) {
         const int64_t m = a.m0 + mb * 8 + g;
-        xok[mb] = m < a.M;
-        xrow[mb] = a.x + (xok[mb] ? m : 0) * a.x_ld + 16 * t;
+        xrow[mb] = a.x + (m < a.M ? m : a.M - 1) * a.x_ld + 16 * t;
     }
 
-    uint32_t strip = s_begin / kchunks;
-    uint32_t kc = s_begin - strip * kchunks;
-    const uint32_t fold_steps = a.fold_k / WC_TILE_K;  // tile steps per quantisation group
-    uint32_t grp = kc / fold_steps;                    // current K group (FASTQ)
-    uint32_t kin = kc - grp * fold_steps;              // tile steps done inside it
+    float tot[MB][4];
+#pragma unroll
+    for (int mb = 0; mb < MB; ++mb)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) tot[mb][i] = 0.f;
 
-    // FASTQ: the raw scale and zero-point bytes of the group being accumulated are requested
-    // one group ahead (right after the previous fold), so that their latency is not paid at
-    // the fold itself.
-    uint32_t q_s0 = 0, q_s1 = 0, q_z0 = 0, q_z1 = 0;
-    auto request_group = [&]() {
-        if (FASTQ) {
-            const uint32_t row = grp * (uint32_t)a.N + strip * WC_TILE_N + g;
-            q_s0 = ((const uint16_t *)a.scale)[row];
-            q_s1 = ((const uint16_t *)a.scale)[row + 8];
-            q_z0 = ((const uint8_t *)a.zp)[row >> 1];
-            q_z1 = ((const uint8_t *)a.zp)[(row + 8) >> 1];
-        }
-    };
-    request_group();
-    auto fold = [&]() {
-        const uint32_t n0 = strip * WC_TILE_N + g;
-        float s0, s1, c0, c1;
-        if (FASTQ) {
-            // n0 and n0 + 8 have the same parity: the same nibble of their bytes
-            const uint32_t sh = (n0 & 1) * 4;
-            s0 = __uint_as_float(q_s0 << 16);
-            s1 = __uint_as_float(q_s1 << 16);
-            c0 = a.nibble_offset + (float)((q_z0 >> sh) & 0xf);
-            c1 = a.nibble_offset + (float)((q_z1 >> sh) & 0xf);
-        } else {
-            const uint32_t k_in_group = grp * a.fold_k; // any k of the group being closed
-            wc_group_params<false>(a, grp, k_in_group, n0, s0, c0);
-            wc_group_params<false>(a, grp, k_in_group, n0 + 8, s1, c1);
-        }
+    uint32_t strip = my_first, kq = wb - my_first * a.ups; // position of the unit being consumed
+    uint32_t in_strip = 0;                                  // units of `strip` folded into tot
+
+    // Publish this warp's sums of `strip`; the warp that completes the strip's count inside
+    // the CTA adds all slabs up and runs the epilogue.
+    auto close_strip = [&]() {
+        const uint32_t slot = strip == my_first ? 0 : (strip == my_last ? 1 : 2);
+        float4 *mine = reinterpret_cast<float4 *>(slabs + (warp * 3 + slot) * SLAB) + lane;
 #pragma unroll
         for (int mb = 0; mb < MB; ++mb) {
-            tot[mb][0] = fmaf(s0, fmaf(-c0, xs[mb][0], acc[mb][0]), tot[mb][0]);
-            tot[mb][1] = fmaf(s0, fmaf(-c0, xs[mb][1], acc[mb][1]), tot[mb][1]);
-            tot[mb][2] = fmaf(s1, fmaf(-c1, xs[mb][2], acc[mb][2]), tot[mb][2]);
-            tot[mb][3] = fmaf(s1, fmaf(-c1, xs[mb][3], acc[mb][3]), tot[mb][3]);
-#pragma unroll
-            for (int i = 0; i < 4; ++i) acc[mb][i] = xs[mb][i] = 0.f;
-        }
-    };
-    auto flush = [&]() {
-        float *out = a.acc + (size_t)strip * WC_TILE_N + g;
-#pragma unroll
-        for (int mb = 0; mb < MB; ++mb) {
-            const int64_t mA = a.m0 + mb * 8 + 2 * t, mB = mA + 1;
-            if (mA < a.M) {
-                atomicAdd(out + mA * a.N, tot[mb][0]);
-                atomicAdd(out + mA * a.N + 8, tot[mb][2]);
-            }
-            if (mB < a.M) {
-                atomicAdd(out + mB * a.N, tot[mb][1]);
-                atomicAdd(out + mB * a.N + 8, tot[mb][3]);
-            }
+            mine[mb * 32] = make_float4(tot[mb][0], tot[mb][1], tot[mb][2], tot[mb][3]);
 #pragma unroll
             for (int i = 0; i < 4; ++i) tot[mb][i] = 0.f;
         }
+        __threadfence_block();
+        __syncwarp();
+        const uint32_t s_lo = strip * a.ups, s_hi = s_lo + a.ups;
+        const uint32_t seg_lo = s_lo > c_begin ? s_lo : c_begin, seg_hi = s_hi < c_end ? s_hi : c_end;
+        uint32_t before = 0;
+        if (lane == 0) before = atomicAdd(&segcnt[strip - first_strip], in_strip);
+        before = __shfl_sync(0xffffffffu, before, 0);
+        if (before + in_strip == seg_hi - seg_lo) {
+            __threadfence_block();
+            wc_strip_epilogue(p, a, slabs, SLAB, wspan, W, strip, seg_lo, seg_hi, rows, lane);
+        }
+        in_strip = 0;
     };
-    // one tile step on the 16 bytes of weights w4
-    auto step = [&](const uint4 &w4) {
-        uint4 xa[MB], xb[MB];
-#pragma unroll
-        for (int mb = 0; mb < MB; ++mb) {
-            xa[mb] = make_uint4(0, 0, 0, 0);
-            xb[mb] = xa[mb];
-            if (xok[mb]) {
-                const uint4 *xp = reinterpret_cast<const uint4 *>(xrow[mb] + kc * WC_TILE_K);
-                xa[mb] = xp[0];
-                xb[mb] = xp[1];
-            }
+
+    const uint32_t ones[4] = {0x3f803f80u, 0x3f803f80u, 0x3f803f80u, 0x3f803f80u};
+
+    // raw scale / zero-point words of a unit (FASTQ)
+    auto load_q = [&](uint32_t qstrip, uint32_t qkq, uint32_t &qs, uint32_t &qz) {
+        if (FASTQ) {
+            const uint32_t grp = a.group_is_unit ? qkq : wc_div(qkq, a.div_fu);
+            const uint32_t row = grp * (uint32_t)a.N + qstrip * WC_TILE_N + 2 * g; // even
+            qs = *reinterpret_cast<const uint32_t *>((const uint16_t *)a.scale + row);
+            qz = ((const uint8_t *)a.zp)[row >> 1];
         }
-        if (XTAB) {
-            // the row's sum over this step; only MMA column 0 (accumulator slots 0 and 2) is real
-            const float sx = xtab[kc];
-            xs[0][0] += sx;
-            xs[0][2] += sx;
+    };
+    // position one unit further
+    auto step_pos = [&](uint32_t &ps, uint32_t &pk) {
+        if (++pk == a.ups) {
+            pk = 0;
+            ++ps;
         }
-        const uint32_t words[4] = {w4.x, w4.y, w4.z, w4.w};
+    };
+
+    // scale / zero-point words are requested two units ahead
+    uint32_t qs0 = 0, qz0 = 0, qs1 = 0, qz1 = 0;
+    uint32_t pstrip = strip, pkq = kq; // position of the unit whose words are requested next
+    if (cw > 0) load_q(pstrip, pkq, qs0, qz0);
+    step_pos(pstrip, pkq);
+    if (cw > 1) load_q(pstrip, pkq, qs1, qz1);
+    step_pos(pstrip, pkq);
+
+    uint32_t n = 0;
+    // one unit: wait for its stage, U tile steps of MMAs, fold, refill the stage
+    auto unit = [&](uint32_t qs, uint32_t qz) {
+        const uint32_t stage = n & (S - 1);
+        wc_copy_wait<S - 1>(); // all but the S - 1 newest groups have landed: unit n is there
+        const uint4 *sp = reinterpret_cast<const uint4 *>(ring + stage * UNIT_BYTES) + lane;
+        float acc[MB][4], xs[MB][4]; // xs: [0] = sum of row 2t, [1] = sum of row 2t + 1 (XTAB)
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const uint32_t w = words[j];
-            uint32_t af[4];
-            af[0] = (w & 0x000f000fu) | 0x43004300u;
-            af[1] = ((w >> 4) & 0x000f000fu) | 0x43004300u;
-            af[2] = ((w >> 8) & 0x000f000fu) | 0x43004300u;
-            af[3] = ((w >> 12) & 0x000f000fu) | 0x43004300u;
+        for (int mb = 0; mb < MB; ++mb)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[mb][e] = xs[mb][e] = 0.f;
+        auto tile_step = [&](const uint4 wv, const uint32_t kc) {
+            uint4 xa[MB], xb[MB];
 #pragma unroll
             for (int mb = 0; mb < MB; ++mb) {
-                const uint32_t b0 = j == 0 ? xa[mb].x : j == 1 ? xa[mb].z : j == 2 ? xb[mb].x : xb[mb].z;
-                const uint32_t b1 = j == 0 ? xa[mb].y : j == 1 ? xa[mb].w : j == 2 ? xb[mb].y : xb[mb].w;
-                mma_bf16_16816(acc[mb], af, b0, b1);
-                if (!XTAB) mma_bf16_16816(xs[mb], ones, b0, b1);
+                const uint4 *xp = reinterpret_cast<const uint4 *>(xrow[mb] + (size_t)kc * WC_TILE_K);
+                xa[mb] = xp[0];
+                xb[mb] = xp[1];
+                if (XTAB) {
+                    const float2 sx = *reinterpret_cast<const float2 *>(xtab + kc * R + mb * 8 + 2 * t);
+                    xs[mb][0] += sx.x;
+                    xs[mb][1] += sx.y;
+                }
             }
+            // four MMA k-steps: word q of the lane's 16 bytes against activation words 2q and 2q + 1
+#define WC_MMA_STEP(WORD, B0, B1)                                              \
+    {                                                                          \
+        const uint32_t v = (WORD);                                             \
+        uint32_t af[4];                                                        \
+        af[0] = (v & 0x000f000fu) | 0x43004300u;                               \
+        af[1] = ((v >> 4) & 0x000f000fu) | 0x43004300u;                        \
+        af[2] = ((v >> 8) & 0x000f000fu) | 0x43004300u;                        \
+        af[3] = ((v >> 12) & 0x000f000fu) | 0x43004300u;                       \
+        _Pragma("unroll") for (int mb = 0; mb < MB; ++mb) {                    \
+            mma_bf16_16816(acc[mb], af, (B0), (B1));                           \
+            if (!XTAB) mma_bf16_16816(xs[mb], ones, (B0), (B1));               \
+        }                                                                      \
+    }
+            WC_MMA_STEP(wv.x, xa[mb].x, xa[mb].y)
+            WC_MMA_STEP(wv.y, xa[mb].z, xa[mb].w)
+            WC_MMA_STEP(wv.z, xb[mb].x, xb[mb].y)
+            WC_MMA_STEP(wv.w, xb[mb].z, xb[mb].w)
+#undef WC_MMA_STEP
+        };
+        tile_step(sp[0], kq * U);
+        if (U == 2) tile_step(sp[32 * (U - 1)], kq * U + 1);
+
+        float s0, s1, c0, c1;
+        if (FASTQ) {
+            s0 = __uint_as_float(qs << 16);
+            s1 = __uint_as_float(qs & 0xffff0000u);
+            c0 = a.nibble_offset + (float)(qz & 0xf);
+            c1 = a.nibble_offset + (float)((qz >> 4) & 0xf);
+        } else {
+            const uint32_t n0 = strip * WC_TILE_N + 2 * g, k = kq * (U * WC_TILE_K);
+            wc_group_params(a, k, n0, s0, c0);
+            wc_group_params(a, k, n0 + 1, s1, c1);
         }
-        const bool group_done = ++kin == fold_steps;
-        if (group_done) {
-            fold();
-            kin = 0;
-            ++grp;
+#pragma unroll
+        for (int mb = 0; mb < MB; ++mb) {
+            // accumulator slots: [0] (row 2t, col 2g), [1] (row 2t+1, col 2g), [2] (row 2t, col 2g+1), [3] (row 2t+1, col 2g+1);
+            // without the table the all-ones MMA left the row sums in xs[.][0] and xs[.][1] as well
+            const float xe = xs[mb][0], xo = xs[mb][1];
+            tot[mb][0] = fmaf(s0, fmaf(-c0, xe, acc[mb][0]), tot[mb][0]);
+            tot[mb][1] = fmaf(s0, fmaf(-c0, xo, acc[mb][1]), tot[mb][1]);
+            tot[mb][2] = fmaf(s1, fmaf(-c1, xe, acc[mb][2]), tot[mb][2]);
+            tot[mb][3] = fmaf(s1, fmaf(-c1, xo, acc[mb][3]), tot[mb][3]);
         }
-        if (++kc == kchunks) {
-            // the last fold of the strip has happened (the fold period divides K)
-            flush();
-            kc = 0;
-            grp = 0;
+        // the stage's bytes have been consumed by the MMAs above: request the unit S further on
+        request(n + S);
+        ++n;
+        ++in_strip;
+        if (++kq == a.ups) {
+            close_strip();
+            kq = 0;
             ++strip;
         }
-        if (group_done) request_group(); // for the group that starts now
     };
 
-    // Four tile steps per iteration with the weights of the next four already requested:
-    // 2 KiB in flight per warp, no register shuffling.
-    const uint4 *wp = a.wei + (size_t)s_begin * 32 + lane;
-    auto fetch = [&](uint32_t i, uint4 &r) {
-        if (i < count) r = ldg_stream(wp + (size_t)i * 32);
-    };
-    uint4 r0 = make_uint4(0, 0, 0, 0), r1 = r0, r2 = r0, r3 = r0;
-    fetch(0, r0);
-    fetch(1, r1);
-    fetch(2, r2);
-    fetch(3, r3);
-    uint32_t s = 0;
 #pragma unroll 1
-    for (; s + 4 <= count; s += 4) {
-        step(r0);
-        fetch(s + 4, r0);
-        step(r1);
-        fetch(s + 5, r1);
-        step(r2);
-        fetch(s + 6, r2);
-        step(r3);
-        fetch(s + 7, r3);
+    while (n < cw) {
+        unit(qs0, qz0);
+        if (n + 1 < cw) load_q(pstrip, pkq, qs0, qz0); // for unit n + 1 after the increment above, i.e. two ahead
+        step_pos(pstrip, pkq);
+        if (n >= cw) break;
+        unit(qs1, qz1);
+        if (n + 1 < cw) load_q(pstrip, pkq, qs1, qz1);
+        step_pos(pstrip, pkq);
     }
-    if (s < count) step(r0);
-    if (s + 1 < count) step(r1);
-    if (s + 2 < count) step(r2);
-    if (kc != 0) {
-        // the range ended inside a strip: close the open group, then publish
-        if (kin != 0) fold();
-        flush();
-    }
-}
-
-// epilogue over the f32 partial sums: src scale, bias, post-ops, dst scale, store;
-// leaves the scratch zeroed for the next execution
-__global__ void __launch_bounds__(256) wc_epilogue_kernel(const __grid_constant__ b200_matmul_params_t p, float *acc) {
-    const int64_t total = p.M * p.N;
-    const float dst_inv = dst_scale_reciprocal(p);
-    const float src_scale = p.src_scale.ptr ? load_f32(p.src_scale.dt, p.src_scale.ptr, 0) : 1.f;
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-        float d = acc[i];
-        acc[i] = 0.f;
-        if (p.src_scale.ptr) d = __fmul_rn(d, src_scale);
-        finish_element(p, d, i / p.N, i % p.N, false, dst_inv);
-    }
+    wc_copy_wait<0>();
+    if (in_strip) close_strip();
 }
 
 // activations of another float type -> bf16 rows (fpmath bf16 permits the down-conversion)
@@ -331,7 +479,7 @@ __global__ void __launch_bounds__(256) wc_pack_kernel(const uint8_t *__restrict_
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
             const int p = i & 3, half = i >> 2;
-            const int64_t n = strip * WC_TILE_N + g + 8 * (p & 1);
+            const int64_t n = strip * WC_TILE_N + 2 * g + (p & 1);
             const int64_t k = kc * WC_TILE_K + 16 * t + 4 * j + 2 * (p >> 1) + half;
             const int64_t e = k * N + n;
             uint32_t q = (src[e >> 1] >> ((e & 1) * 4)) & 0xf;
@@ -353,28 +501,155 @@ using namespace b200;
 static bool wc_fast_quant(const b200_matmul_params_t *p, int64_t gs, int64_t gz) {
     return p->wei_scale.ptr && p->wei_zp.ptr && p->wei_scale.dt == B200_DT_BF16 && p->wei_zp.dt == B200_DT_U4 && gs == gz
             && p->wei_scale.s0 == p->N && p->wei_scale.s1 == 1 && p->wei_zp.s0 == p->N && p->wei_zp.s1 == 1
-            && p->N * (p->K / gs) < ((int64_t)1 << 31);
+            && p->N * (p->K / gs) < ((int64_t)1 << 31) && ((uintptr_t)p->wei_scale.ptr & 3) == 0;
 }
 
-static void wc_launch_pass(const wc_args_t &a, int64_t rows, bool fastq, unsigned ctas, cudaStream_t cs) {
-    const unsigned threads = WC_WARPS * 32;
-    const bool xtab = rows == 1 && a.K <= 65536;
-    if (fastq) {
-        if (xtab) wc_gemv_kernel<1, true, true><<<ctas, threads, 0, cs>>>(a);
-        else if (rows <= 8) wc_gemv_kernel<1, true, false><<<ctas, threads, 0, cs>>>(a);
-        else if (rows <= 16) wc_gemv_kernel<2, true, false><<<ctas, threads, 0, cs>>>(a);
-        else wc_gemv_kernel<4, true, false><<<ctas, threads, 0, cs>>>(a);
+static wc_div_t wc_make_div(uint32_t d) {
+    uint32_t l = 0;
+    while (((uint64_t)1 << l) < d) ++l;
+    wc_div_t f;
+    f.m = (uint32_t)((((uint64_t)1 << 32) * (((uint64_t)1 << l) - d)) / d + 1);
+    f.s1 = l < 1 ? l : 1;
+    f.s2 = l > 0 ? l - 1 : 0;
+    return f;
+}
+
+template <int MB, bool FASTQ>
+static void wc_launch_variant(const wc_args_t &a, const b200_matmul_params_t &p, bool xtab, int unit_steps, unsigned ctas,
+        size_t smem, cudaStream_t cs) {
+    const unsigned threads = wc_warps(MB) * 32;
+    // rings, slabs and table exceed the 48 KiB a kernel gets without asking
+    static std::once_flag once[64];
+    int dev = 0;
+    cudaGetDevice(&dev);
+    std::call_once(once[dev & 63], [] {
+        const int max_smem = 227 * 1024;
+        cudaFuncSetAttribute(wc_gemv_kernel<MB, FASTQ, true, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+        cudaFuncSetAttribute(wc_gemv_kernel<MB, FASTQ, true, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+        cudaFuncSetAttribute(wc_gemv_kernel<MB, FASTQ, false, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+        cudaFuncSetAttribute(wc_gemv_kernel<MB, FASTQ, false, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+    });
+    if (xtab) {
+        if (unit_steps == 2) wc_gemv_kernel<MB, FASTQ, true, 2><<<ctas, threads, smem, cs>>>(a, p);
+        else wc_gemv_kernel<MB, FASTQ, true, 1><<<ctas, threads, smem, cs>>>(a, p);
     } else {
-        if (xtab) wc_gemv_kernel<1, false, true><<<ctas, threads, 0, cs>>>(a);
-        else if (rows <= 8) wc_gemv_kernel<1, false, false><<<ctas, threads, 0, cs>>>(a);
-        else if (rows <= 16) wc_gemv_kernel<2, false, false><<<ctas, threads, 0, cs>>>(a);
-        else wc_gemv_kernel<4, false, false><<<ctas, threads, 0, cs>>>(a);
+        if (unit_steps == 2) wc_gemv_kernel<MB, FASTQ, false, 2><<<ctas, threads, smem, cs>>>(a, p);
+        else wc_gemv_kernel<MB, FASTQ, false, 1><<<ctas, threads, smem, cs>>>(a, p);
     }
+}
+
+// Checks shared by the two entry points; on success the K-group sizes of scales and
+// zero-points and the fold period are returned.
+static int wc_validate(const b200_matmul_params_t *p, int64_t *gs_out, int64_t *gz_out, int64_t *fold_out) {
+    if (p->wei_dt != B200_DT_U4 && p->wei_dt != B200_DT_S4) return B200_ERR_UNSUPPORTED;
+    if (!p->apply_to_int) return B200_ERR_UNSUPPORTED;
+    if (p->N % WC_TILE_N != 0 || p->K % WC_TILE_K != 0 || p->src_sk != 1 || p->dst_sn != 1) return B200_ERR_UNSUPPORTED;
+    if (p->K > (int64_t)1 << 30 || (p->N / WC_TILE_N) * (p->K / WC_TILE_K) >= ((int64_t)1 << 31)) return B200_ERR_TOO_LARGE;
+    if (p->src_zp.ptr || p->dst_zp.ptr) return B200_ERR_UNSUPPORTED;
+    if (p->src_scale.ptr && (p->src_scale.s0 || p->src_scale.s1)) return B200_ERR_UNSUPPORTED;
+    int64_t gs = p->K, gz = p->K;
+    if (p->wei_scale.ptr) {
+        if (p->wei_scale.g1 != 1) return B200_ERR_UNSUPPORTED;
+        if (p->wei_scale.s0) gs = p->wei_scale.g0;
+    }
+    if (p->wei_zp.ptr) {
+        if (p->wei_zp.g1 != 1) return B200_ERR_UNSUPPORTED;
+        if (p->wei_zp.s0) gz = p->wei_zp.g0;
+    }
+    // a tile step covers 64 k in a permuted order, so groups must be whole tile steps;
+    // one group size must divide the other
+    if (gs % WC_TILE_K || gz % WC_TILE_K || p->K % gs || p->K % gz) return B200_ERR_UNSUPPORTED;
+    const int64_t fold_k = gs < gz ? gs : gz;
+    if (gs % fold_k || gz % fold_k) return B200_ERR_UNSUPPORTED;
+    *gs_out = gs;
+    *gz_out = gz;
+    *fold_out = fold_k;
+    return 0;
+}
+
+// All passes over the activation rows.  acc: zeroed f32 [M][N]; done: zeroed [N / 16].
+static int wc_run(const b200_matmul_params_t *p, const uint4 *wei, const __nv_bfloat16 *x, int64_t x_ld, float *acc,
+        uint32_t *done, int64_t gs, int64_t gz, int64_t fold_k, cudaStream_t cs) {
+    wc_args_t a;
+    a.wei = wei;
+    a.x = x;
+    a.x_ld = x_ld;
+    a.acc = acc;
+    a.done = done;
+    a.M = p->M;
+    a.N = p->N;
+    a.K = p->K;
+    a.scale = p->wei_scale.ptr;
+    a.scale_dt = p->wei_scale.dt;
+    a.scale_s0 = p->wei_scale.s0;
+    a.scale_s1 = p->wei_scale.s1;
+    a.scale_g0 = (uint32_t)gs;
+    a.zp = p->wei_zp.ptr;
+    a.zp_dt = p->wei_zp.dt;
+    a.zp_s0 = p->wei_zp.s0;
+    a.zp_s1 = p->wei_zp.s1;
+    a.zp_g0 = (uint32_t)gz;
+    a.nibble_offset = p->wei_dt == B200_DT_S4 ? 136.f : 128.f;
+    // a unit never straddles a quantisation group: two tile steps where the groups allow it
+    const uint32_t fold_steps = (uint32_t)(fold_k / WC_TILE_K);
+    const int unit_steps = fold_steps % 2 == 0 ? 2 : 1;
+    a.kchunks = (uint32_t)(p->K / WC_TILE_K);
+    a.ups = a.kchunks / unit_steps;
+    a.units = (uint32_t)(p->N / WC_TILE_N) * a.ups;
+    a.div_ups = wc_make_div(a.ups);
+    a.div_fu = wc_make_div(fold_steps / unit_steps);
+
+    const bool fastq = wc_fast_quant(p, gs, gz);
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    a.group_is_unit = fold_steps / unit_steps == 1;
+    unsigned ctas = a.units < (uint32_t)sms ? a.units : (unsigned)sms;
+    // Whole strips per CTA need no exchange between CTAs but leave some SMs one strip short of
+    // others; taken when that costs less than the exchange would (about two microseconds at
+    // the rate one GPU streams weights).
+    const uint32_t strips = (uint32_t)(p->N / WC_TILE_N);
+    a.whole_strips = 0;
+    if (strips >= ctas) {
+        const double avg = (double)strips / ctas, most = (double)((strips + ctas - 1) / ctas);
+        const double stream_us = (double)p->K * p->N / 2 / 5e6;
+        if ((most - avg) / avg * stream_us < 2.0) a.whole_strips = 1;
+    }
+    // strips one CTA can touch: those of its share of the units plus one cut at either end
+    {
+        const uint32_t share = a.whole_strips ? (strips + ctas - 1) / ctas * a.ups : (a.units + ctas - 1) / ctas;
+        a.max_segs = (share / a.ups + 2 + 3) / 4 * 4;
+        if (a.max_segs > 8192) return B200_ERR_TOO_LARGE;
+    }
+    // activation rows in passes of up to 32 (the weights are re-read from L2)
+    for (int64_t m0 = 0; m0 < p->M; m0 += 32) {
+        a.m0 = (int)m0;
+        const int64_t rows = p->M - m0;
+        const int mb = rows <= 8 ? 1 : rows <= 16 ? 2 : 4;
+        const size_t table = (size_t)a.kchunks * mb * 8 * sizeof(float);
+        const bool xtab = table <= WC_XTAB_MAX_BYTES;
+        const size_t nw = wc_warps(mb);
+        const size_t smem = nw * wc_ring_bytes(mb) + nw * 3 * mb * 128 * sizeof(float) + nw * sizeof(uint2)
+                + (size_t)a.max_segs * sizeof(uint32_t) + (xtab ? table : 0);
+        if (fastq) {
+            if (mb == 1) wc_launch_variant<1, true>(a, *p, xtab, unit_steps, ctas, smem, cs);
+            else if (mb == 2) wc_launch_variant<2, true>(a, *p, xtab, unit_steps, ctas, smem, cs);
+            else wc_launch_variant<4, true>(a, *p, xtab, unit_steps, ctas, smem, cs);
+        } else {
+            if (mb == 1) wc_launch_variant<1, false>(a, *p, xtab, unit_steps, ctas, smem, cs);
+            else if (mb == 2) wc_launch_variant<2, false>(a, *p, xtab, unit_steps, ctas, smem, cs);
+            else wc_launch_variant<4, false>(a, *p, xtab, unit_steps, ctas, smem, cs);
+        }
+        const int rc = after_launch();
+        if (rc) return rc;
+    }
+    return 0;
 }
 
 // scratch layout of the wc kernel: [f32 acc M*N][bf16 x copy M*K if src is not bf16][packed weights if plain]
 static void wc_scratch_layout(const b200_matmul_params_t *p, size_t *acc, size_t *xcopy, size_t *packed) {
-    *acc = align256((size_t)p->M * p->N * sizeof(float));
+    // partial sums [M][N] followed by one counter per strip of 16 columns
+    *acc = align256((size_t)p->M * p->N * sizeof(float)) + align256((size_t)(p->N / WC_TILE_N) * sizeof(uint32_t));
     *xcopy = p->src_dt == B200_DT_BF16 ? 0 : align256((size_t)p->M * p->K * 2);
     *packed = p->wei_layout == B200_WEI_WC4_TILED ? 0 : align256((size_t)(p->K * p->N / 2));
 }
@@ -404,29 +679,12 @@ extern "C" int b200_wc_pack_launch(const void *src, void *dst, int64_t K, int64_
 extern "C" int b200_matmul_wc_launch(const b200_matmul_params_t *p, b200_stream_t stream) {
     if (!p || !p->src || !p->wei || !p->dst) return B200_ERR_BAD_ARG;
     if (p->M <= 0 || p->N <= 0 || p->K <= 0) return p->M < 0 || p->N < 0 || p->K < 0 ? B200_ERR_BAD_ARG : 0;
-    if (p->wei_dt != B200_DT_U4 && p->wei_dt != B200_DT_S4) return B200_ERR_UNSUPPORTED;
-    if (!p->apply_to_int) return B200_ERR_UNSUPPORTED;
     if (p->src_dt != B200_DT_BF16 && p->src_dt != B200_DT_F16 && p->src_dt != B200_DT_F32) return B200_ERR_UNSUPPORTED;
-    if (p->N % WC_TILE_N != 0 || p->K % WC_TILE_K != 0 || p->src_sk != 1 || p->dst_sn != 1) return B200_ERR_UNSUPPORTED;
-    if (p->K > (int64_t)1 << 30 || (p->N / WC_TILE_N) * (p->K / WC_TILE_K) >= ((int64_t)1 << 31)) return B200_ERR_TOO_LARGE;
     if (p->wei_layout == B200_WEI_PLAIN && !(p->wei_sn == 1 && p->wei_sk == p->N)) return B200_ERR_UNSUPPORTED;
     if (p->wei_layout != B200_WEI_PLAIN && p->wei_layout != B200_WEI_WC4_TILED) return B200_ERR_UNSUPPORTED;
-    if (p->src_zp.ptr || p->dst_zp.ptr) return B200_ERR_UNSUPPORTED;
-    if (p->src_scale.ptr && (p->src_scale.s0 || p->src_scale.s1)) return B200_ERR_UNSUPPORTED;
-    // K-group sizes: multiples of 16 that divide K, and one must divide the other
-    int64_t gs = p->K, gz = p->K;
-    if (p->wei_scale.ptr) {
-        if (p->wei_scale.g1 != 1) return B200_ERR_UNSUPPORTED;
-        if (p->wei_scale.s0) gs = p->wei_scale.g0;
-    }
-    if (p->wei_zp.ptr) {
-        if (p->wei_zp.g1 != 1) return B200_ERR_UNSUPPORTED;
-        if (p->wei_zp.s0) gz = p->wei_zp.g0;
-    }
-    // a tile step covers 64 k in a permuted order, so groups must be whole tile steps
-    if (gs % WC_TILE_K || gz % WC_TILE_K || p->K % gs || p->K % gz) return B200_ERR_UNSUPPORTED;
-    const int64_t fold_k = gs < gz ? gs : gz;
-    if (gs % fold_k || gz % fold_k) return B200_ERR_UNSUPPORTED;
+    int64_t gs, gz, fold_k;
+    int rc = wc_validate(p, &gs, &gz, &fold_k);
+    if (rc) return rc;
     // activations are read 16 bytes at a time
     if (p->src_dt == B200_DT_BF16 && (((uintptr_t)p->src & 15) || (p->src_sm & 7))) return B200_ERR_BAD_ARG;
 
@@ -443,7 +701,7 @@ extern "C" int b200_matmul_wc_launch(const b200_matmul_params_t *p, b200_stream_
         int64_t blocks = (p->M * p->K + 255) / 256;
         if (blocks > 148 * 8) blocks = 148 * 8;
         wc_convert_x_kernel<<<(unsigned)blocks, 256, 0, cs>>>(p->src, p->src_dt, p->src_sm, p->M, p->K, xc);
-        int rc = after_launch();
+        rc = after_launch();
         if (rc) return rc;
         x = xc;
         x_ld = p->K;
@@ -451,55 +709,16 @@ extern "C" int b200_matmul_wc_launch(const b200_matmul_params_t *p, b200_stream_
     const void *wei = p->wei;
     if (w_b) {
         void *wp = sc + acc_b + x_b;
-        int rc = b200_wc_pack_launch(p->wei, wp, p->K, p->N, p->wei_dt, stream);
+        rc = b200_wc_pack_launch(p->wei, wp, p->K, p->N, p->wei_dt, stream);
         if (rc) return rc;
         wei = wp;
     }
     if (((uintptr_t)wei & 15)) return B200_ERR_BAD_ARG;
     if (!p->scratch_zeroed) {
-        if (cudaMemsetAsync(acc, 0, (size_t)p->M * p->N * sizeof(float), cs) != cudaSuccess) return (int)cudaGetLastError();
+        if (cudaMemsetAsync(acc, 0, acc_b, cs) != cudaSuccess) return (int)cudaGetLastError();
     }
-
-    wc_args_t a;
-    a.wei = (const uint4 *)wei;
-    a.x = x;
-    a.x_ld = x_ld;
-    a.acc = acc;
-    a.M = p->M;
-    a.N = p->N;
-    a.K = p->K;
-    a.scale = p->wei_scale.ptr;
-    a.scale_dt = p->wei_scale.dt;
-    a.scale_s0 = p->wei_scale.s0;
-    a.scale_s1 = p->wei_scale.s1;
-    a.scale_g0 = (uint32_t)gs;
-    a.zp = p->wei_zp.ptr;
-    a.zp_dt = p->wei_zp.dt;
-    a.zp_s0 = p->wei_zp.s0;
-    a.zp_s1 = p->wei_zp.s1;
-    a.zp_g0 = (uint32_t)gz;
-    a.fold_k = (uint32_t)fold_k;
-    a.nibble_offset = p->wei_dt == B200_DT_S4 ? 136.f : 128.f;
-
-    const bool fastq = wc_fast_quant(p, gs, gz);
-    int dev = 0, sms = 148;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    const int64_t steps = (p->N / WC_TILE_N) * (p->K / WC_TILE_K);
-    int64_t ctas = (int64_t)sms * 3;
-    if (ctas * WC_WARPS > steps) ctas = (steps + WC_WARPS - 1) / WC_WARPS;
-    // activation rows in passes of up to 32 (the weights are re-read from L2)
-    for (int64_t m0 = 0; m0 < p->M; m0 += 32) {
-        a.m0 = (int)m0;
-        const int64_t rows = p->M - m0;
-        wc_launch_pass(a, rows, fastq, (unsigned)ctas, cs);
-        int rc = after_launch();
-        if (rc) return rc;
-    }
-    int64_t eblocks = (p->M * p->N + 255) / 256;
-    if (eblocks > (int64_t)sms * 8) eblocks = (int64_t)sms * 8;
-    wc_epilogue_kernel<<<(unsigned)eblocks, 256, 0, cs>>>(*p, acc);
-    return after_launch();
+    uint32_t *done = (uint32_t *)((char *)acc + align256((size_t)p->M * p->N * sizeof(float)));
+    return wc_run(p, (const uint4 *)wei, x, x_ld, acc, done, gs, gz, fold_k, cs);
 }
 
 // ---- entry point that allocates nothing ---------------------------------------------------
@@ -512,7 +731,7 @@ extern "C" int b200_matmul_wc_launch(const b200_matmul_params_t *p, b200_stream_
 // kernels are offered with the scratch in a fixed array that lives in the
 // library's device image: every GPU that loads the library holds these 2 MiB
 // until the process exits.
-static constexpr size_t WC_STATIC_SCRATCH_BYTES = (size_t)2 << 20; // room for M * N <= 524288 partial sums
+static constexpr size_t WC_STATIC_SCRATCH_BYTES = (size_t)2 << 20; // partial sums (4 bytes per dst element) + strip counters
 static __device__ __align__(256) unsigned char g_wc_static_scratch[WC_STATIC_SCRATCH_BYTES];
 
 // In host code the array's name is only a handle for the runtime, not a device
@@ -541,73 +760,21 @@ extern "C" int b200_matmul_wc_noalloc_launch(const b200_matmul_params_t *p, b200
     if (!p || !p->src || !p->wei || !p->dst) return B200_ERR_BAD_ARG;
     if (p->M <= 0 || p->N <= 0 || p->K <= 0) return p->M < 0 || p->N < 0 || p->K < 0 ? B200_ERR_BAD_ARG : 0;
     // only the forms that need no other scratch: bf16 activations, weights already packed
-    if (p->wei_dt != B200_DT_U4 && p->wei_dt != B200_DT_S4) return B200_ERR_UNSUPPORTED;
-    if (!p->apply_to_int || p->src_dt != B200_DT_BF16 || p->wei_layout != B200_WEI_WC4_TILED) return B200_ERR_UNSUPPORTED;
-    if (p->N % WC_TILE_N != 0 || p->K % WC_TILE_K != 0 || p->src_sk != 1 || p->dst_sn != 1) return B200_ERR_UNSUPPORTED;
-    if (p->K > (int64_t)1 << 30 || (p->N / WC_TILE_N) * (p->K / WC_TILE_K) >= ((int64_t)1 << 31)) return B200_ERR_TOO_LARGE;
-    if (p->src_zp.ptr || p->dst_zp.ptr) return B200_ERR_UNSUPPORTED;
-    if (p->src_scale.ptr && (p->src_scale.s0 || p->src_scale.s1)) return B200_ERR_UNSUPPORTED;
-    int64_t gs = p->K, gz = p->K;
-    if (p->wei_scale.ptr) {
-        if (p->wei_scale.g1 != 1) return B200_ERR_UNSUPPORTED;
-        if (p->wei_scale.s0) gs = p->wei_scale.g0;
-    }
-    if (p->wei_zp.ptr) {
-        if (p->wei_zp.g1 != 1) return B200_ERR_UNSUPPORTED;
-        if (p->wei_zp.s0) gz = p->wei_zp.g0;
-    }
-    // a tile step covers 64 k in a permuted order, so groups must be whole tile steps
-    if (gs % WC_TILE_K || gz % WC_TILE_K || p->K % gs || p->K % gz) return B200_ERR_UNSUPPORTED;
-    const int64_t fold_k = gs < gz ? gs : gz;
-    if (gs % fold_k || gz % fold_k) return B200_ERR_UNSUPPORTED;
+    if (p->src_dt != B200_DT_BF16 || p->wei_layout != B200_WEI_WC4_TILED) return B200_ERR_UNSUPPORTED;
+    int64_t gs, gz, fold_k;
+    int rc = wc_validate(p, &gs, &gz, &fold_k);
+    if (rc) return rc;
     if (((uintptr_t)p->src & 15) || (p->src_sm & 7) || ((uintptr_t)p->wei & 15)) return B200_ERR_BAD_ARG;
-    // the fixed array bounds the problem: M * N partial sums of 4 bytes
-    if ((uint64_t)p->M * (uint64_t)p->N * sizeof(float) > WC_STATIC_SCRATCH_BYTES) return B200_ERR_TOO_LARGE;
+    // the fixed array bounds the problem: M * N partial sums of 4 bytes plus the strip counters
+    const size_t used = align256((size_t)p->M * p->N * sizeof(float)) + align256((size_t)(p->N / WC_TILE_N) * sizeof(uint32_t));
+    if ((uint64_t)p->M * (uint64_t)p->N > ((uint64_t)1 << 40) || used > WC_STATIC_SCRATCH_BYTES) return B200_ERR_TOO_LARGE;
 
     float *acc = nullptr;
-    int rc = wc_static_scratch_ptr(&acc);
+    rc = wc_static_scratch_ptr(&acc);
     if (rc) return rc;
     cudaStream_t cs = (cudaStream_t)stream;
     // the array keeps whatever the last call left behind: clear the part used now
-    if (cudaMemsetAsync(acc, 0, (size_t)p->M * p->N * sizeof(float), cs) != cudaSuccess) return (int)cudaGetLastError();
-
-    wc_args_t a;
-    a.wei = (const uint4 *)p->wei;
-    a.x = (const __nv_bfloat16 *)p->src;
-    a.x_ld = p->src_sm;
-    a.acc = acc;
-    a.M = p->M;
-    a.N = p->N;
-    a.K = p->K;
-    a.scale = p->wei_scale.ptr;
-    a.scale_dt = p->wei_scale.dt;
-    a.scale_s0 = p->wei_scale.s0;
-    a.scale_s1 = p->wei_scale.s1;
-    a.scale_g0 = (uint32_t)gs;
-    a.zp = p->wei_zp.ptr;
-    a.zp_dt = p->wei_zp.dt;
-    a.zp_s0 = p->wei_zp.s0;
-    a.zp_s1 = p->wei_zp.s1;
-    a.zp_g0 = (uint32_t)gz;
-    a.fold_k = (uint32_t)fold_k;
-    a.nibble_offset = p->wei_dt == B200_DT_S4 ? 136.f : 128.f;
-
-    const bool fastq = wc_fast_quant(p, gs, gz);
-    int dev = 0, sms = 148;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    const int64_t steps = (p->N / WC_TILE_N) * (p->K / WC_TILE_K);
-    int64_t ctas = (int64_t)sms * 3;
-    if (ctas * WC_WARPS > steps) ctas = (steps + WC_WARPS - 1) / WC_WARPS;
-    for (int64_t m0 = 0; m0 < p->M; m0 += 32) {
-        a.m0 = (int)m0;
-        const int64_t rows = p->M - m0;
-        wc_launch_pass(a, rows, fastq, (unsigned)ctas, cs);
-        rc = after_launch();
-        if (rc) return rc;
-    }
-    int64_t eblocks = (p->M * p->N + 255) / 256;
-    if (eblocks > (int64_t)sms * 8) eblocks = (int64_t)sms * 8;
-    wc_epilogue_kernel<<<(unsigned)eblocks, 256, 0, cs>>>(*p, acc);
-    return after_launch();
+    if (cudaMemsetAsync(acc, 0, used, cs) != cudaSuccess) return (int)cudaGetLastError();
+    uint32_t *done = (uint32_t *)((char *)acc + align256((size_t)p->M * p->N * sizeof(float)));
+    return wc_run(p, (const uint4 *)p->wei, (const __nv_bfloat16 *)p->src, p->src_sm, acc, done, gs, gz, fold_k, cs);
 }

@@ -83,6 +83,19 @@ def ref():
     return _ref
 
 
+def set_threads(n=0):
+    """Number of OpenMP threads the oracle and the reference library use from now on
+    (0 = all host cores).  Launchers such as torchrun export OMP_NUM_THREADS=1, which would
+    otherwise turn a CPU baseline into a single-core one.  Returns the number in effect."""
+    n = int(n) or (os.cpu_count() or 1)
+    try:
+        gomp = C.CDLL("libgomp.so.1", mode=os.RTLD_GLOBAL)
+        gomp.omp_set_num_threads(n)
+        return int(gomp.omp_get_max_threads())
+    except OSError:
+        return 1
+
+
 def _ptr(a):
     return a.ctypes.data if a is not None else None
 

@@ -167,6 +167,14 @@ CASES = {
     "elt_hardswish": _elt_case("hardswish", 1.0 / 6, 0.5),
     "elt_abs_sqrt": lambda: _two_elt(),
     "wc_u4_g64_m3": _wc_case(3, 64, 256, 64, dt.U4),
+    # decode kernel: whole strips per CTA (N / 16 >= SM count), units of one group
+    "wc_u4_g128_m1_wide": _wc_case(1, 2560, 256, 128, dt.U4, seed=12),
+    "wc_u4_g128_m9_wide": _wc_case(9, 2560, 256, 128, dt.U4, seed=13),
+    "wc_s4_g256_m20_wide": _wc_case(20, 2432, 512, 256, dt.S4, seed=14),
+    # decode kernel: few strips, K split across CTAs, strips shared between CTAs
+    "wc_u4_g128_m1_deep": _wc_case(1, 64, 4096, 128, dt.U4, seed=15),
+    "wc_u4_g64_m5_mid": _wc_case(5, 1040, 192, 64, dt.U4, seed=16),
+    "wc_s4_perN_m2": _wc_case(2, 96, 384, 384, dt.S4, seed=17, zp="none"),
     "wc_s4_g32_m2_f32dst": _wc_case(2, 32, 128, 32, dt.S4, dst_dt=dt.F32),
     "wc_s8_perN_common_zp": _wc_case(5, 48, 96, 96, dt.S8, zp="common"),
     "wc_u8_g32_nozp": _wc_case(4, 40, 64, 32, dt.U8, zp="none"),

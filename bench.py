@@ -360,6 +360,9 @@ def main():
     # ---- correctness of what was timed: sampled rows / columns against the CPU oracle ----
     check = None
     extras = {}
+    nsplit = None
+    if world > 1 and not args.no_extras:
+        nsplit = run_c4_nsplit(W, torch, dist, rank, world, local)   # a collective: every rank takes part
     cpu_baseline = None
     if rank == 0:
         try:
@@ -378,6 +381,8 @@ def main():
 
         if not args.no_extras:
             extras = run_extras(api, W, dt, eng, strm, tstream, torch, np, peaks)
+        if nsplit is not None:
+            extras["c4_int8_16384x8192x28672_n_split"] = nsplit
 
         if not args.no_cpu_baseline:
             try:
@@ -445,6 +450,43 @@ def run_one_case(args):
     strm.wait()
     print("executed %s x%d with %s" % (args.case, max(1, args.steps), plan.impl))
     return 0
+
+
+def run_c4_nsplit(W, torch, dist, rank, world, local, reps=5):
+    """The large configuration with the weights' columns split over the ranks: every rank
+    multiplies the replicated src by its slice, an NCCL all-gather exchanges the dst slices
+    and a layout kernel assembles the row-major dst on every rank.  Device-timed, max over
+    ranks; the matmul alone is timed beside the whole."""
+    from onednn_b200 import multi_gpu
+    try:
+        case = W.config4()
+        op = multi_gpu.NSplitMatmul(case, rank, world, local)
+        for _ in range(2):
+            op.execute()
+        torch.cuda.synchronize()
+        dist.barrier()
+        a, b, c = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+        a.record()
+        for _ in range(reps):
+            op.execute()
+        b.record()
+        for _ in range(reps):
+            op.plan.prim.execute(op.strm, op.args)
+        c.record()
+        c.synchronize()
+        t = torch.tensor([a.elapsed_time(b) / reps, b.elapsed_time(c) / reps], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, ms_mm = (float(x) for x in t.tolist())
+        ns = case.N // world
+        out = {"impl": op.impl, "ranks": world, "ms": ms, "TOPS": case.ops / (ms * 1e-3) / 1e12,
+               "ms_matmul_slice_only": ms_mm,
+               "bytes_received_per_rank": (world - 1) * case.M * ns * 2,
+               "how": "slice matmul -> ncclAllGather of [M][N/g] bf16 slices -> layout kernel; max over ranks"}
+        del op
+        torch.cuda.empty_cache()
+        return out
+    except Exception as ex:
+        return {"error": repr(ex)}
 
 
 def run_extras(api, W, dt, eng, strm, tstream, torch, np, peaks):

@@ -208,6 +208,17 @@ B200_API int b200_reorder_launch(const b200_reorder_params_t *p, b200_stream_t s
 B200_API int b200_colsum_launch(const void *wei, int32_t wei_dt, int64_t K, int64_t N, int64_t sk, int64_t sn,
         int32_t *out, b200_stream_t stream);
 
+/* ---- multi-GPU ----------------------------------------------------------- */
+
+/* N-split matmul: every rank computes the columns [r*N/parts, (r+1)*N/parts) of dst
+ * (its slice of the weights, per-N scales and bias; src replicated), the slices are
+ * all-gathered rank by rank into `staged` = [parts][M][N/parts], and this kernel
+ * lays them out as one row-major (M, N) matrix.  The reference has no multi-device
+ * matmul; the split follows from dst elements being independent given a full K
+ * reduction (ref_matmul_int8.cpp:154-261 computes each (m, n) on its own). */
+B200_API int b200_gather_columns_launch(const void *staged, void *dst, int64_t M, int64_t N, int32_t parts,
+        int32_t elem_bytes, b200_stream_t stream);
+
 /* ---- utilities ----------------------------------------------------------- */
 
 /* number of kernel launches issued by this library since load (for benchmarks) */

@@ -113,6 +113,18 @@ extern "C" size_t b200_packed_weights_bytes(int64_t K, int64_t N, int32_t dt, in
     return (size_t)((K * N * dt_bits(dt) + 7) / 8);
 }
 
+// Column-split results gathered rank by rank ([parts][M][N / parts], what an all-gather of
+// contiguous slices produces) -> one row-major (M, N) matrix.  16 bytes per thread.
+__global__ void __launch_bounds__(256) gather_columns_kernel(const uint4 *__restrict__ staged, uint4 *__restrict__ dst,
+        int64_t M, int64_t row_vecs, int parts) {
+    // row_vecs = 16-byte vectors per row of one part
+    const int64_t total = M * row_vecs * parts;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t v = i % row_vecs, m = (i / row_vecs) % M, part = i / (row_vecs * M);
+        dst[(m * parts + part) * row_vecs + v] = staged[i];
+    }
+}
+
 extern "C" int b200_colsum_launch(const void *wei, int32_t wei_dt, int64_t K, int64_t N, int64_t sk, int64_t sn,
         int32_t *out, b200_stream_t stream) {
     if (!wei || !out || K < 0 || N < 0) return B200_ERR_BAD_ARG;
@@ -165,4 +177,18 @@ extern "C" int b200_reorder_launch(const b200_reorder_params_t *p, b200_stream_t
 
 extern "C" uint64_t b200_launch_count(void) {
     return g_launches.load();
+}
+
+extern "C" int b200_gather_columns_launch(const void *staged, void *dst, int64_t M, int64_t N, int32_t parts,
+        int32_t elem_bytes, b200_stream_t stream) {
+    if (!staged || !dst || M < 0 || N < 0 || parts <= 0 || elem_bytes <= 0) return B200_ERR_BAD_ARG;
+    if (N % parts != 0 || ((N / parts) * elem_bytes) % 16 != 0) return B200_ERR_UNSUPPORTED;
+    if ((((uintptr_t)staged) | ((uintptr_t)dst)) & 15) return B200_ERR_BAD_ARG;
+    if (M == 0 || N == 0) return 0;
+    const int64_t row_vecs = (N / parts) * elem_bytes / 16;
+    int64_t blocks = (M * row_vecs * parts + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    gather_columns_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>((const uint4 *)staged, (uint4 *)dst, M,
+            row_vecs, parts);
+    return after_launch();
 }

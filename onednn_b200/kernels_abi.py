@@ -50,6 +50,8 @@ def quant(ptr, dt, s0=0, s1=0, g0=1, g1=1):
 
 def lib():
     L = api.lib()
+    L.b200_gather_columns_launch.restype = C.c_int
+    L.b200_gather_columns_launch.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int32, C.c_int32, C.c_void_p]
     L.b200_matmul_scratch_bytes.restype = C.c_size_t
     L.b200_matmul_scratch_bytes.argtypes = [C.POINTER(MatmulParams), C.c_int]
     L.b200_matmul_wc_noalloc_max_bytes.restype = C.c_size_t

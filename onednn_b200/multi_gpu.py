@@ -1,0 +1,93 @@
+"""One matmul over the GPUs of a node: one process per GPU, ``torch.distributed`` for the plumbing.
+
+The reference library has no multi-device matmul.  The two splits below follow from
+its arithmetic (``src/cpu/matmul/ref_matmul_int8.cpp:154-261``: every dst element is
+computed on its own from a full K reduction), so any partition of dst rows or columns
+gives results identical to the unsharded primitive:
+
+* M-split: rank r owns rows ``[r*M/g, (r+1)*M/g)`` of src and dst; weights, scales and
+  bias are replicated.  No data moves between GPUs.
+* N-split: rank r owns columns ``[r*N/g, (r+1)*N/g)`` of the weights, per-N scales, bias
+  and dst; src is replicated.  One exchange assembles the full dst on every rank: an
+  all-gather of the column slices.
+
+``NSplitMatmul`` runs the N-split with the library's own primitive for the slice, NCCL
+for the all-gather (contiguous slices into a ``[g][M][N/g]`` staging buffer) and the
+``b200_gather_columns_launch`` kernel to lay the slices out as a row-major ``(M, N)``.
+``gather_columns_host`` is the same layout step in numpy, for tests without a GPU.
+"""
+import numpy as np
+
+from . import dtypes as dt
+from .workloads import MatmulCase, shard
+
+
+def m_split(case: MatmulCase, rank: int, world: int) -> MatmulCase:
+    return shard(case, rank, world, "m")
+
+
+def n_split(case: MatmulCase, rank: int, world: int) -> MatmulCase:
+    return shard(case, rank, world, "n")
+
+
+def gather_columns_host(staged: np.ndarray) -> np.ndarray:
+    """``[g][M][N/g]`` (slices in rank order) -> row-major ``(M, N)``."""
+    g, m, ns = staged.shape
+    return np.ascontiguousarray(np.transpose(staged, (1, 0, 2)).reshape(m, g * ns))
+
+
+def assemble_rows_host(parts) -> np.ndarray:
+    """M-split results in rank order -> the full dst."""
+    return np.concatenate(list(parts), axis=0)
+
+
+class NSplitMatmul:
+    """dst = matmul(src, W) with W's columns split over the ranks of ``group``; after
+    ``execute()`` every rank holds the full row-major dst in ``self.dst`` (a torch tensor
+    of the raw dst type).  Everything is enqueued on torch's current stream."""
+
+    def __init__(self, case: MatmulCase, rank: int, world: int, device_index: int, group=None):
+        import torch
+        from . import api
+        if case.N % world != 0:
+            raise ValueError("N must be a multiple of the number of ranks")
+        self.torch = torch
+        self.api = api
+        self.rank, self.world, self.group = rank, world, group
+        self.case = case
+        self.local = n_split(case, rank, world)
+        self.eng = api.Engine(index=device_index)
+        self.tstream = torch.cuda.current_stream()
+        self.strm = api.Stream(self.eng, cuda_stream=self.tstream.cuda_stream)
+        self.plan = api.CasePlan(self.local, self.eng, self.strm, weights="any")
+        self.elem = np.dtype(dt.RAW[case.dst_dt]).itemsize
+        ns = case.N // world
+        if (ns * self.elem) % 16 != 0:
+            raise ValueError("a column slice must be a multiple of 16 bytes per row")
+        # raw bytes: the collective and the layout kernel move them without looking inside
+        self.staged = torch.empty((world, case.M, ns * self.elem), dtype=torch.uint8, device="cuda")
+        self.dst = torch.empty((case.M, case.N * self.elem), dtype=torch.uint8, device="cuda")
+        # the slice primitive writes straight into this rank's part of the staging buffer
+        self.args = dict(self.plan.args)
+        self.args[api.ARG_DST] = api.Memory(self.plan.mds["dst"], self.eng, handle=self.staged[rank].data_ptr())
+
+    @property
+    def impl(self):
+        return self.plan.impl
+
+    def execute(self):
+        torch = self.torch
+        self.plan.prim.execute(self.strm, self.args)
+        if self.world > 1:
+            import torch.distributed as dist
+            dist.all_gather_into_tensor(self.staged.view(-1), self.staged[self.rank].view(-1), group=self.group)
+        from . import kernels_abi
+        rc = kernels_abi.lib().b200_gather_columns_launch(
+            self.staged.data_ptr(), self.dst.data_ptr(), self.case.M, self.case.N, self.world, self.elem,
+            self.tstream.cuda_stream)
+        if rc != 0:
+            raise RuntimeError("b200_gather_columns_launch failed: %d" % rc)
+
+    def result(self) -> np.ndarray:
+        self.torch.cuda.synchronize()
+        return self.dst.cpu().numpy().view(dt.RAW[self.case.dst_dt]).reshape(self.case.M, self.case.N)

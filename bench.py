@@ -362,7 +362,9 @@ def main():
     extras = {}
     nsplit = None
     if world > 1 and not args.no_extras:
-        nsplit = run_c4_nsplit(W, torch, dist, rank, world, local)   # a collective: every rank takes part
+        # collectives: every rank takes part
+        nsplit = {"nccl_all_gather": run_c4_nsplit(W, torch, dist, rank, world, local, "nccl"),
+                  "epilogue_stores_to_peers": run_c4_nsplit(W, torch, dist, rank, world, local, "p2p")}
     cpu_baseline = None
     if rank == 0:
         try:
@@ -452,15 +454,16 @@ def run_one_case(args):
     return 0
 
 
-def run_c4_nsplit(W, torch, dist, rank, world, local, reps=5):
+def run_c4_nsplit(W, torch, dist, rank, world, local, mode, reps=5):
     """The large configuration with the weights' columns split over the ranks: every rank
-    multiplies the replicated src by its slice, an NCCL all-gather exchanges the dst slices
-    and a layout kernel assembles the row-major dst on every rank.  Device-timed, max over
-    ranks; the matmul alone is timed beside the whole."""
+    multiplies the replicated src by its slice and every rank ends with the full row-major
+    dst -- through an NCCL all-gather plus a layout kernel (mode "nccl"), or by the matmul's
+    epilogue storing its tiles into all GPUs' copies of dst (mode "p2p").  Device-timed, max
+    over ranks; the slice matmul alone (same arguments) is timed beside the whole."""
     from onednn_b200 import multi_gpu
     try:
         case = W.config4()
-        op = multi_gpu.NSplitMatmul(case, rank, world, local)
+        op = multi_gpu.NSplitMatmul(case, rank, world, local, mode=mode)
         for _ in range(2):
             op.execute()
         torch.cuda.synchronize()
@@ -481,7 +484,9 @@ def run_c4_nsplit(W, torch, dist, rank, world, local, reps=5):
         out = {"impl": op.impl, "ranks": world, "ms": ms, "TOPS": case.ops / (ms * 1e-3) / 1e12,
                "ms_matmul_slice_only": ms_mm,
                "bytes_received_per_rank": (world - 1) * case.M * ns * 2,
-               "how": "slice matmul -> ncclAllGather of [M][N/g] bf16 slices -> layout kernel; max over ranks"}
+               "how": ("slice matmul -> ncclAllGather of [M][N/g] bf16 slices -> layout kernel" if mode == "nccl" else
+                       "slice matmul whose epilogue stores each tile into every GPU's copy of dst -> barrier")
+               + "; max over ranks"}
         del op
         torch.cuda.empty_cache()
         return out

@@ -154,6 +154,13 @@ typedef enum { dnnl_profiling_data_kind_undef = 0, dnnl_profiling_data_kind_time
 #define DNNL_ARG_WEIGHTS DNNL_ARG_WEIGHTS_0
 #define DNNL_ARG_BIAS 41
 #define DNNL_ARG_SCRATCHPAD 80
+/* Extension (no counterpart in the reference): up to seven more destinations, i = 0 .. 6,
+ * given consecutively from 0.  Each is a dnnl_memory with the descriptor of DNNL_ARG_DST
+ * whose handle is the mirror of the destination in another GPU's memory, mapped into this
+ * process.  The primitive stores every result there as well as in DNNL_ARG_DST, so that an
+ * N-split layer's slices reach all GPUs from the matmul's own epilogue.  Implementations
+ * that cannot do it return dnnl_unimplemented at execution. */
+#define DNNL_ARG_B200_DST_PEER(i) (3072 + (i))
 #define DNNL_ARG_ATTR_SCALES 4096
 #define DNNL_ARG_ATTR_ZERO_POINTS 8192
 #define DNNL_ARG_ATTR_MULTIPLE_POST_OP_BASE 32768

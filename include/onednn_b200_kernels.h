@@ -80,6 +80,7 @@ typedef struct {
     int64_t sm, sn;     /* element strides of ptr over (m, n); 0 = broadcast */
 } b200_postop_t;
 
+#define B200_MAX_DST_PEERS 7
 #define B200_MAX_POSTOPS 32
 
 /* packed weights layouts produced by b200_pack_weights */
@@ -116,6 +117,14 @@ typedef struct {
     /* non-zero: the caller guarantees that the accumulation part of the scratch
      * is all zero on entry (kernels that use it leave it zeroed on exit) */
     int32_t scratch_zeroed; int32_t reserved3;
+    /* N-split over the GPUs of a node: besides dst, every finished element is also stored at
+     * the same offset from each of these bases -- the same (M, N_full) destination in the
+     * memory of the other GPUs, mapped into this process (peer / symmetric memory) -- so that
+     * the exchange of column slices rides on the epilogue's stores instead of a collective
+     * afterwards.  Plain stores only; nothing is ever loaded from a peer.  Honoured by
+     * b200_matmul_tc8_launch; the other kernels return B200_ERR_UNSUPPORTED when it is set. */
+    int32_t n_dst_peers; int32_t reserved4;
+    void *dst_peer[B200_MAX_DST_PEERS];
 } b200_matmul_params_t;
 
 /* ---- matmul kernels ----------------------------------------------------- */

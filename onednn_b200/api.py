@@ -26,6 +26,7 @@ STATUS = {0: "success", 1: "out_of_memory", 2: "invalid_arguments", 3: "unimplem
 ARG_SRC, ARG_SRC_1, ARG_DST, ARG_WEIGHTS, ARG_BIAS = 1, 2, 17, 33, 41
 ARG_FROM, ARG_TO, ARG_SCRATCHPAD = 1, 17, 80
 ARG_ATTR_SCALES, ARG_ATTR_ZERO_POINTS, ARG_ATTR_MULTIPLE_POST_OP_BASE = 4096, 8192, 32768
+ARG_B200_DST_PEER0 = 3072  # extension: mirrors of dst in other GPUs' memory, up to seven
 TAG_ANY, TAG_A, TAG_AB, TAG_BA, TAG_ABC = 1, 2, 3, 14, 4
 GPU = 2
 QUERY_IMPL_INFO_STR, QUERY_SRC_MD, QUERY_WEIGHTS_MD, QUERY_DST_MD, QUERY_SCRATCHPAD_MD, QUERY_EXEC_ARG_MD = \
@@ -366,14 +367,17 @@ class CasePlan:
     and reorders the plain weights into it once (the reference's recommended usage);
     ``weights="plain"`` hands the plain weights to the primitive as they are."""
 
-    def __init__(self, case, engine, stream, weights="any", impl=None, upload=True):
+    def __init__(self, case, engine, stream, weights="any", impl=None, upload=True, dst_strides=None):
         from . import workloads as W
         self.case, self.engine, self.stream = case, engine, stream
         c = case
         src_md = MemoryDesc((c.M, c.K), c.src_dt, TAG_AB)
         plain_wei_md = MemoryDesc((c.K, c.N), c.wei_dt, TAG_AB if c.wei_tag == "ab" else TAG_BA)
         wei_md = MemoryDesc((c.K, c.N), c.wei_dt, TAG_ANY) if weights == "any" else plain_wei_md
-        dst_md = MemoryDesc((c.M, c.N), c.dst_dt, TAG_AB)
+        # dst_strides: dst is a block of a larger matrix; the caller supplies ARG_DST itself
+        self.own_dst = dst_strides is None
+        dst_md = MemoryDesc((c.M, c.N), c.dst_dt, TAG_AB) if self.own_dst else \
+            MemoryDesc((c.M, c.N), c.dst_dt, strides=tuple(dst_strides))
         bias_md = None
         if c.bias is not None:
             bshape = c.bias.shape if c.bias.ndim == 2 else (1, c.bias.shape[0])
@@ -434,7 +438,8 @@ class CasePlan:
             self.args[ARG_WEIGHTS] = packed
         if c.bias is not None:
             self.args[ARG_BIAS] = self._mem("bias", self.mds["bias"], c.bias)
-        self.args[ARG_DST] = self._mem("dst", self.mds["dst"], c.dst_init)
+        if self.own_dst:
+            self.args[ARG_DST] = self._mem("dst", self.mds["dst"], c.dst_init)
         for name, q, arg in (("src_scale", c.src_scale, ARG_ATTR_SCALES | ARG_SRC),
                              ("wei_scale", c.wei_scale, ARG_ATTR_SCALES | ARG_WEIGHTS),
                              ("dst_scale", c.dst_scale, ARG_ATTR_SCALES | ARG_DST),

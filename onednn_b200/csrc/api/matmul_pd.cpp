@@ -450,6 +450,13 @@ dnnl_status_t matmul_execute(const dnnl_primitive *prim, dnnl_stream *stream, co
     p.dst_dt = pd->dst.data_type;
     p.dst_sm = pd->dst.strides[0];
     p.dst_sn = pd->dst.strides[1];
+    // mirrors of dst on other GPUs (extension arguments): same descriptor, peer-mapped handles
+    for (int i = 0; i < B200_MAX_DST_PEERS; ++i) {
+        dnnl_memory *peer = get(DNNL_ARG_B200_DST_PEER(i));
+        if (!peer) break;
+        if (!peer->handle || !peer->md.equal(dst->md)) return dnnl_invalid_arguments;
+        p.dst_peer[p.n_dst_peers++] = const_cast<void *>(base_ptr(peer));
+    }
 
     const dnnl_primitive_attr &a = pd->attr;
     struct { const quant_entry_t *q; int arg; b200_quant_t *out; int64_t d0, d1; } qs[6] = {

@@ -83,7 +83,7 @@ extern "C" int b200_matmul_generic_launch(const b200_matmul_params_t *p, b200_st
     if (!p || !p->src || !p->wei || !p->dst) return B200_ERR_BAD_ARG;
     if (p->M < 0 || p->N < 0 || p->K < 0 || p->npo < 0 || p->npo > B200_MAX_POSTOPS) return B200_ERR_BAD_ARG;
     if (p->M == 0 || p->N == 0 || p->K == 0) return 0; // a zero dim: dst is left untouched
-    if (p->wei_layout != B200_WEI_PLAIN) return B200_ERR_UNSUPPORTED;
+    if (p->wei_layout != B200_WEI_PLAIN || p->n_dst_peers) return B200_ERR_UNSUPPORTED;
     const int64_t total = p->M * p->N;
     int64_t blocks = (total + 255) / 256;
     if (blocks > 148 * 64) blocks = 148 * 64;

@@ -299,8 +299,7 @@ __device__ __forceinline__ uint32_t cvt_sat_u8(float v) {
 }
 
 // pack CH final f32 values of one row and store them (or the valid part of them)
-__device__ __forceinline__ void store_row(const b200_matmul_params_t &p, const float (&y)[CH], char *drow, int64_t nvalid) {
-    if (nvalid <= 0) return;
+__device__ __forceinline__ void store_row_at(const b200_matmul_params_t &p, const float (&y)[CH], char *drow, int64_t nvalid) {
     const bool aligned = nvalid == CH && ((uintptr_t)drow & 15) == 0;
     if (aligned && (p.dst_dt == B200_DT_S8 || p.dst_dt == B200_DT_U8)) {
         const bool is_s8 = p.dst_dt == B200_DT_S8;
@@ -333,12 +332,25 @@ __device__ __forceinline__ void store_row(const b200_matmul_params_t &p, const f
     }
 }
 
+// the row goes to drow and, in the kernels built for a destination mirrored on other GPUs
+// (PEERS), to the same offset from every peer base
+template <bool PEERS>
+__device__ __forceinline__ void store_row(const b200_matmul_params_t &p, const float (&y)[CH], char *drow, int64_t nvalid) {
+    if (nvalid <= 0) return;
+    store_row_at(p, y, drow, nvalid);
+    if (PEERS) {
+        const int64_t off = drow - (char *)p.dst;
+#pragma unroll 1
+        for (int i = 0; i < p.n_dst_peers; ++i) store_row_at(p, y, (char *)p.dst_peer[i] + off, nvalid);
+    }
+}
+
 // SUM: how the sum post-op's prior destination values are obtained
 //   0 no sum;  1 the sum type is s8 / u8: 16 bytes per chunk, kept packed in four registers;
 //   2 any other sum type: converted to f32 up front.
 enum { SUM_NONE = 0, SUM_8BIT = 1, SUM_OTHER = 2 };
 
-template <bool FP8, int EPI, int SUM>
+template <bool FP8, int EPI, int SUM, bool PEERS>
 __device__ __forceinline__ void epilogue_chunk(const b200_matmul_params_t &p, const uint32_t (&v)[CH], int64_t m,
         int64_t n0, const float *wscale, const float *bias, const int32_t *comp, const float *zp, const epi_consts_t &k,
         uint32_t taddr, int lane, uint4 old_raw, bool old_prefetched) {
@@ -540,14 +552,14 @@ __device__ __forceinline__ void epilogue_chunk(const b200_matmul_params_t &p, co
 #pragma unroll
         for (int j = 0; j < CH; ++j) y[j] = tail(y[j], j);
     }
-    store_row(p, y, drow, nvalid);
+    store_row<PEERS>(p, y, drow, nvalid);
 }
 
 // ---- the kernel -------------------------------------------------------------------------
 
 // 18 warps land 5 + 5 + 4 + 4 on the four schedulers, so a thread may use at most
 // 16384 / (5 * 32) = 102 registers; declaring 640 threads makes ptxas stay within that.
-template <bool FP8, int EPI, int SUM>
+template <bool FP8, int EPI, int SUM, bool PEERS = false>
 __global__ void __launch_bounds__(640, 1) matmul_tc8_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const __grid_constant__ CUtensorMap tmap_b, const __grid_constant__ tc8_args_t args) {
     extern __shared__ uint8_t smem_raw[];
@@ -697,7 +709,7 @@ __global__ void __launch_bounds__(640, 1) matmul_tc8_kernel(const __grid_constan
                 uint32_t v[CH];
                 tmem_ld16_issue(trow + c * CH, v);
                 tmem_ld_wait(v);
-                epilogue_chunk<FP8, EPI, SUM>(p, v, m, n0 + c * CH, wscale + c * CH, bias + c * CH, comp + c * CH, zpv + c * CH, k,
+                epilogue_chunk<FP8, EPI, SUM, PEERS>(p, v, m, n0 + c * CH, wscale + c * CH, bias + c * CH, comp + c * CH, zpv + c * CH, k,
                         trow + c * CH, lane, ob0, (ofbits & 1u) != 0);
                 ob0 = ob1;
                 ob1 = ob2;
@@ -783,6 +795,9 @@ extern "C" int b200_matmul_tc8_launch(const b200_matmul_params_t *p, b200_stream
             && (p->wei_dt == B200_DT_F8_E4M3 || p->wei_dt == B200_DT_F8_E5M2);
     if (!i8 && !f8) return B200_ERR_UNSUPPORTED;
     if (p->K % 16 != 0 || p->src_sk != 1 || p->dst_sn != 1) return B200_ERR_UNSUPPORTED;
+    if (p->n_dst_peers < 0 || p->n_dst_peers > B200_MAX_DST_PEERS) return B200_ERR_BAD_ARG;
+    for (int i = 0; i < p->n_dst_peers; ++i)
+        if (!p->dst_peer[i] || (((uintptr_t)p->dst_peer[i] ^ (uintptr_t)p->dst) & 15)) return B200_ERR_BAD_ARG; // same 16-byte phase as dst
     // weights: packed K-major, or plain with K contiguous
     int64_t wpitch;
     if (p->wei_layout == B200_WEI_KMAJOR) wpitch = p->K;
@@ -855,16 +870,26 @@ extern "C" int b200_matmul_tc8_launch(const b200_matmul_params_t *p, b200_stream
     static const kernel_t table[2][4][3] = {TC8_ROW(false), TC8_ROW(true)};
 #undef TC8_ROW
     kernel_t kern = table[f8 ? 1 : 0][epi][sum];
+    if (p->n_dst_peers) {
+        // mirrored destinations: built for the epilogues an N-split layer has (bias, simple eltwise), no sum
+        kern = nullptr;
+        if (sum == SUM_NONE && epi == EPI_NONE)
+            kern = f8 ? matmul_tc8_kernel<true, EPI_NONE, SUM_NONE, true> : matmul_tc8_kernel<false, EPI_NONE, SUM_NONE, true>;
+        if (sum == SUM_NONE && epi == EPI_SIMPLE)
+            kern = f8 ? matmul_tc8_kernel<true, EPI_SIMPLE, SUM_NONE, true> : matmul_tc8_kernel<false, EPI_SIMPLE, SUM_NONE, true>;
+    }
     if (!kern) return B200_ERR_UNSUPPORTED;
     // opt in to the large dynamic shared memory once per kernel and device
     static std::mutex attr_mu;
     static bool attr_done[64][2][4][3] = {};
     {
         std::lock_guard<std::mutex> g(attr_mu);
-        if (dev < 64 && !attr_done[dev][f8 ? 1 : 0][epi][sum]) {
+        static bool attr_done_peers[64][2][4] = {};
+        bool &done = p->n_dst_peers ? attr_done_peers[dev & 63][f8 ? 1 : 0][epi] : attr_done[dev & 63][f8 ? 1 : 0][epi][sum];
+        if (dev < 64 && !done) {
             cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
             if (e != cudaSuccess) return (int)e;
-            attr_done[dev][f8 ? 1 : 0][epi][sum] = true;
+            done = true;
         }
     }
     kern<<<grid, NUM_THREADS, SMEM_BYTES, (cudaStream_t)stream>>>(ta, tb, a);

@@ -543,7 +543,7 @@ static void wc_launch_variant(const wc_args_t &a, const b200_matmul_params_t &p,
 static int wc_validate(const b200_matmul_params_t *p, int64_t *gs_out, int64_t *gz_out, int64_t *fold_out) {
     if (p->wei_dt != B200_DT_U4 && p->wei_dt != B200_DT_S4) return B200_ERR_UNSUPPORTED;
     if (!p->apply_to_int) return B200_ERR_UNSUPPORTED;
-    if (p->N % WC_TILE_N != 0 || p->K % WC_TILE_K != 0 || p->src_sk != 1 || p->dst_sn != 1) return B200_ERR_UNSUPPORTED;
+    if (p->N % WC_TILE_N != 0 || p->K % WC_TILE_K != 0 || p->src_sk != 1 || p->dst_sn != 1 || p->n_dst_peers) return B200_ERR_UNSUPPORTED;
     if (p->K > (int64_t)1 << 30 || (p->N / WC_TILE_N) * (p->K / WC_TILE_K) >= ((int64_t)1 << 31)) return B200_ERR_TOO_LARGE;
     if (p->src_zp.ptr || p->dst_zp.ptr) return B200_ERR_UNSUPPORTED;
     if (p->src_scale.ptr && (p->src_scale.s0 || p->src_scale.s1)) return B200_ERR_UNSUPPORTED;

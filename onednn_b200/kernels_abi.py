@@ -39,6 +39,7 @@ class MatmulParams(C.Structure):
         ("status", C.c_void_p),
         ("scratch", C.c_void_p), ("scratch_bytes", C.c_size_t),
         ("scratch_zeroed", C.c_int32), ("reserved3", C.c_int32),
+        ("n_dst_peers", C.c_int32), ("reserved4", C.c_int32), ("dst_peer", C.c_void_p * 7),
     ]
 
 

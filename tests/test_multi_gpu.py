@@ -101,7 +101,7 @@ def test_gather_columns_kernel():
     assert kernels_abi.lib().b200_gather_columns_launch(st.data_ptr(), dst.data_ptr(), M, 4 * 10, 4, 1, 0) == -1
 
 
-def _nccl_rank(rank, world, port, q):
+def _nccl_rank(rank, world, port, q, mode="nccl"):
     import torch
     import torch.distributed as dist
     os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
@@ -109,8 +109,9 @@ def _nccl_rank(rank, world, port, q):
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
     try:
         case = W.config4(256, 512, 128, seed=9)
-        op = multi_gpu.NSplitMatmul(case, rank, world, rank)
-        op.execute()
+        op = multi_gpu.NSplitMatmul(case, rank, world, rank, mode=mode)
+        for _ in range(2):   # twice: the second run overwrites a destination that is already full
+            op.execute()
         got = op.result()
         want = ob.run_oracle(case, tanh_mode=1, exact_acc=1)
         a, b = dt.to_f32(got, case.dst_dt), dt.to_f32(want, case.dst_dt)
@@ -122,14 +123,16 @@ def _nccl_rank(rank, world, port, q):
 
 
 @pytest.mark.gpu
-def test_n_split_cuda():
-    """N-split through the library: on two GPUs when the box has them (NCCL all-gather),
-    else the same code path with a single rank."""
+@pytest.mark.parametrize("mode", ["nccl", "p2p"])
+def test_n_split_cuda(mode):
+    """N-split through the library: on two GPUs when the box has them (NCCL all-gather, or
+    slices stored into the peers' copies by the matmul's epilogue), else the same code path
+    with a single rank."""
     import torch
     world = 2 if torch.cuda.device_count() >= 2 else 1
     if world == 1:
         case = W.config4(256, 512, 128, seed=9)
-        op = multi_gpu.NSplitMatmul(case, 0, 1, 0)
+        op = multi_gpu.NSplitMatmul(case, 0, 1, 0, mode=mode)
         op.execute()
         got = op.result()
         want = ob.run_oracle(case, tanh_mode=1, exact_acc=1)
@@ -139,7 +142,7 @@ def test_n_split_cuda():
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_nccl_rank, args=(r, world, port, q)) for r in range(world)]
+    procs = [ctx.Process(target=_nccl_rank, args=(r, world, port, q, mode)) for r in range(world)]
     for p in procs:
         p.start()
     out = [q.get(timeout=150) for _ in procs]

@@ -121,7 +121,8 @@ typedef struct {
      * the same offset from each of these bases -- the same (M, N_full) destination in the
      * memory of the other GPUs, mapped into this process (peer / symmetric memory) -- so that
      * the exchange of column slices rides on the epilogue's stores instead of a collective
-     * afterwards.  Plain stores only; nothing is ever loaded from a peer.  Honoured by
+     * afterwards (each warp re-reads its finished block from the local L2 and sends whole row
+     * segments).  Plain stores only; nothing is ever loaded from a peer.  Honoured by
      * b200_matmul_tc8_launch; the other kernels return B200_ERR_UNSUPPORTED when it is set. */
     int32_t n_dst_peers; int32_t reserved4;
     void *dst_peer[B200_MAX_DST_PEERS];

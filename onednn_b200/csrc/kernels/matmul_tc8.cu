@@ -332,16 +332,43 @@ __device__ __forceinline__ void store_row_at(const b200_matmul_params_t &p, cons
     }
 }
 
-// the row goes to drow and, in the kernels built for a destination mirrored on other GPUs
-// (PEERS), to the same offset from every peer base
 template <bool PEERS>
 __device__ __forceinline__ void store_row(const b200_matmul_params_t &p, const float (&y)[CH], char *drow, int64_t nvalid) {
     if (nvalid <= 0) return;
     store_row_at(p, y, drow, nvalid);
-    if (PEERS) {
-        const int64_t off = drow - (char *)p.dst;
-#pragma unroll 1
-        for (int i = 0; i < p.n_dst_peers; ++i) store_row_at(p, y, (char *)p.dst_peer[i] + off, nvalid);
+}
+
+// Kernels built for a destination mirrored on other GPUs: once a warp has stored its block of
+// the tile (32 rows x EPI_COLS columns) locally, it reads the block back from L2 row by row
+// and stores it at the same offset from every peer base, 16 bytes per lane with the lanes
+// running along the row, so that what crosses NVLink are whole 64- to 256-byte row segments
+// (one row of the block per store instruction for f32, two for bf16, four for 8-bit types)
+// rather than the 16-byte pieces per row a lane holds after the epilogue.
+__device__ __forceinline__ void mirror_block(const b200_matmul_params_t &p, int64_t row0, int64_t n0, int cols_max, int lane) {
+    const int64_t rows = p.M - row0 < 32 ? p.M - row0 : 32;
+    const int64_t cols = p.N - n0 < cols_max ? p.N - n0 : cols_max;
+    if (rows <= 0 || cols <= 0) return;
+    const int eb = dt_bits(p.dst_dt) / 8;
+    const int64_t pitch = p.dst_sm * eb, row_bytes = cols * eb;
+    const int64_t off0 = (row0 * p.dst_sm + n0) * eb;
+    const char *base = (const char *)p.dst + off0;
+    __syncwarp(); // the lanes' stores of this block are ordered before the reads below
+    if ((((uintptr_t)base | (uintptr_t)pitch | (uintptr_t)row_bytes) & 15) == 0) {
+        const int vecs = (int)(row_bytes >> 4);
+        const int total = (int)rows * vecs;
+        for (int i = lane; i < total; i += 32) {
+            const int r = i / vecs, v = i - r * vecs;
+            const int64_t off = r * pitch + v * 16;
+            const uint4 val = __ldcg(reinterpret_cast<const uint4 *>(base + off));
+            for (int q = 0; q < p.n_dst_peers; ++q) *reinterpret_cast<uint4 *>((char *)p.dst_peer[q] + off0 + off) = val;
+        }
+    } else {
+        const int64_t total = rows * row_bytes;
+        for (int64_t i = lane; i < total; i += 32) {
+            const int64_t r = i / row_bytes, off = r * pitch + (i - r * row_bytes);
+            const unsigned char val = __ldcg(reinterpret_cast<const unsigned char *>(base + off));
+            for (int q = 0; q < p.n_dst_peers; ++q) ((unsigned char *)p.dst_peer[q])[off0 + off] = val;
+        }
     }
 }
 
@@ -719,6 +746,7 @@ __global__ void __launch_bounds__(640, 1) matmul_tc8_kernel(const __grid_constan
             tcgen05_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&ctrl->tmem_empty[a]);
+            if (PEERS) mirror_block(p, m0 + quarter * 32, n0, EPI_COLS, lane); // after the accumulator is handed back
         }
     }
 

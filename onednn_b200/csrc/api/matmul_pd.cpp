@@ -256,7 +256,8 @@ static bool accept_wc(dnnl_primitive_desc *pd) {
     if (dst.is_plain() && dst.strides[1] != 1) return reject(name, "dst must be row-major"), false;
     if (wei.is_plain() && !(wei.strides[1] == 1 && wei.strides[0] == N && wei.offset0 == 0))
         return reject(name, "weights must be dense ab"), false;
-    if (wei.format_kind == dnnl_format_kind_opaque && wei.packed_layout != B200_WEI_WC4_TILED)
+    if (wei.format_kind == dnnl_format_kind_opaque && wei.packed_layout != B200_WEI_WC4_TILED
+            && wei.packed_layout != B200_WEI_WC4_TC)
         return reject(name, "unknown packed weights layout"), false;
     if (!quant_simple(a.scale(DNNL_ARG_SRC), 0)) return reject(name, "src scales must be per-tensor"), false;
     if (!quant_simple(a.scale(DNNL_ARG_DST), 0)) return reject(name, "dst scales must be per-tensor"), false;
@@ -276,12 +277,26 @@ static bool accept_wc(dnnl_primitive_desc *pd) {
     if (src.is_any()) make_plain(pd->src);
     pd->dst = dst;
     if (dst.is_any()) make_plain(pd->dst);
+    // More activation rows than one pass of the decode kernel takes (32): the tensor-core kernel
+    // (weights converted to bf16 in shared memory; its time hardly depends on M, the decode
+    // kernel's grows with every pass), when it can take the problem: bf16 src, bf16 scales,
+    // 4-bit zero-points.
+    const quant_entry_t &ws = a.scale(DNNL_ARG_WEIGHTS), &wz = a.zp(DNNL_ARG_WEIGHTS);
+    bool tc = M > 32 && sdt == dnnl_bf16 && (!ws.set || ws.dt == dnnl_bf16) && (!wz.set || dt_is_int4(wz.dt))
+            && !(wz.set && wz.mask == 0); // a 4-bit zero-point needs a mask (the attribute check says so too)
+    if (const char *v = std::getenv("ONEDNN_CUDA_DISABLE_IMPL"))
+        if (std::string(v).find("wc_tc") != std::string::npos) tc = false;
+    if (wei.format_kind == dnnl_format_kind_opaque) {
+        // the layout was fixed when the weights were packed: it decides
+        if (wei.packed_layout == B200_WEI_WC4_TC && !tc) return reject(name, "weights packed for the tensor-core kernel"), false;
+        tc = wei.packed_layout == B200_WEI_WC4_TC;
+    }
     pd->wei = wei;
     if (wei.is_any()) {
         pd->wei.format_kind = dnnl_format_kind_opaque;
-        pd->wei.packed_layout = B200_WEI_WC4_TILED;
+        pd->wei.packed_layout = tc ? B200_WEI_WC4_TC : B200_WEI_WC4_TILED;
     }
-    pd->impl_str = "cuda:sm100:wc_gemv";
+    pd->impl_str = tc ? "cuda:sm100:wc_tcgen05" : "cuda:sm100:wc_gemv";
     return true;
 }
 
@@ -343,7 +358,10 @@ static size_t scratch_bytes_for(const dnnl_primitive_desc *pd) {
         q.K = pd->K();
         q.src_dt = pd->src.data_type;
         q.wei_layout = pd->wei.format_kind == dnnl_format_kind_opaque ? pd->wei.packed_layout : B200_WEI_PLAIN;
-        bytes = b200_matmul_scratch_bytes(&q, 2);
+        if (pd->impl_str.find("tcgen05") != std::string::npos)
+            bytes = q.wei_layout == B200_WEI_PLAIN ? b200_wc_tc_packed_bytes(q.K, q.N) : 0; // plain weights are packed per execution
+        else
+            bytes = b200_matmul_scratch_bytes(&q, 2);
     }
     return (bytes + 255) / 256 * 256;
 }
@@ -537,7 +555,9 @@ dnnl_status_t matmul_execute(const dnnl_primitive *prim, dnnl_stream *stream, co
     int rc = 0;
     switch (pd->impl) {
         case IMPL_GENERIC: rc = b200_matmul_generic_launch(&p, cs); break;
-        case IMPL_WC: rc = b200_matmul_wc_launch(&p, cs); break;
+        case IMPL_WC:
+            rc = pd->impl_str.find("tcgen05") != std::string::npos ? b200_matmul_wc_tc_launch(&p, cs) : b200_matmul_wc_launch(&p, cs);
+            break;
         case IMPL_TC8: {
             if (p.wei_layout == B200_WEI_KMAJOR) {
                 if (p.src_zp.ptr)

@@ -1,0 +1,594 @@
+// Weight-compressed matmul on the tensor cores: bf16 activations (9 .. 256 rows per
+// pass) times 4-bit weights with K-grouped scales and zero-points.
+// Semantics: the reference's weights-decompression matmul
+// (src/cpu/matmul/ref_matmul.cpp:130-233, with_wei_decompression) under fpmath bf16
+// with apply_to_int: every weight is decompressed to w' = (q - zp) * scale and rounded
+// to bf16 (exactly the bf16 rounding of the reference's f32 w', because (q - zp) * scale
+// with a bf16 scale is exact in f32), products are accumulated in f32.
+//
+// Where the decode kernel (matmul_wc.cu) spends its issue slots on register-level MMAs,
+// this one only converts: per stage of 64 k, sixteen warps turn 4 KiB of packed nibbles into
+// a 128-column x 64-k bf16 tile in shared memory, laid out as the 128-byte-swizzled K-major
+// operand tile a TMA load would have produced; the activations of the same 64 k arrive by
+// TMA; one thread issues tcgen05.mma (kind::f16, 128 x NB x 16) with the weights as the A
+// operand (128 output columns = the TMEM lanes) and the activations as B (NB = activation
+// rows rounded up to 16), accumulating in TMEM over the whole K.  The epilogue reads TMEM
+// with one output column per lane, so that stores of a dst row are coalesced.
+//
+//   warp 0        TMA producer (activations)           waits empty[s]   -> full_b[s] (tx bytes)
+//   warp 1        TMEM owner and MMA issuer            waits full_a/b   -> empty[s], acc_full
+//   warps 2..17   dequantisers, then epilogue          waits empty[s]   -> full_a[s]; acc_full -> acc_empty
+//
+// Weights are read in the B200_WEI_WC4_TC layout written by the pack kernel below:
+// blocks of 128 output columns x 64 k = 4 KiB, block (nt, kb) at ((nt * K/64) + kb) * 4096,
+// inside a block row-major [128 columns][64 k] nibbles, 32 bytes per column; inside each
+// 32-bit word (8 consecutive k) nibble i holds k 2i and nibble i + 4 holds k 2i + 1, so that
+// (w >> 4i) & 0x000f000f | 0x43004300 is the bf16 pair (128 + q[2i], 128 + q[2i + 1]).
+// Columns past N are stored as zeros.  s4 values are stored offset by 8.
+//
+// Every wait is bounded; a wait that runs out sets a bit in the stream's status word,
+// every role stops at its next wait, copies in flight are drained and TMEM is released.
+#include <cuda.h>
+#include <cuda_bf16.h>
+
+#include <mutex>
+
+#include "common.cuh"
+#include "launch.hpp"
+
+namespace b200 {
+namespace wctc {
+
+constexpr int TN = 128;              // output columns per tile (UMMA M, TMEM lanes)
+constexpr int TK = 64;               // k per stage: 128 bytes of bf16 = one swizzle row
+constexpr int MAX_STAGES = 4;        // operand stages (3 when the activation tile is 256 rows)
+constexpr int PF = 16;               // packed-weight blocks requested ahead (8 bytes per thread and block)
+constexpr int KPT = 16;               // k per dequantising thread and stage (16 or 32)
+constexpr int DQ_WARPS = TN * TK / KPT / 32; // 8 or 16 warps: one 16- or 8-byte load of packed weights each per stage
+constexpr int PF_BYTES = KPT / 2;    // bytes per thread and block in the prefetch ring
+constexpr int NUM_THREADS = 64 + DQ_WARPS * 32;
+constexpr int A_BYTES = TN * TK * 2; // dequantised weights tile, 16 KiB
+constexpr int BLOCK_BYTES = TN * TK / 2; // packed weights per stage, 4 KiB
+constexpr uint32_t WAIT_SPINS = 1u << 24; // polls of the drain loop
+constexpr uint32_t WAIT_TRIES = 1u << 19; // hardware-suspended waits of up to ~2 us each
+enum : uint32_t { ST_WAIT_FULL = 0x1000, ST_WAIT_EMPTY = 0x2000, ST_WAIT_ACC = 0x4000 };
+
+struct ctrl_t {
+    uint64_t full_a[MAX_STAGES];
+    uint64_t full_b[MAX_STAGES];
+    uint64_t empty[MAX_STAGES];
+    uint64_t acc_full, acc_empty;
+    uint32_t tmem_base;
+    volatile uint32_t abort;
+};
+
+struct args_t {
+    b200_matmul_params_t p;
+    const __nv_bfloat16 *x;  // activations (bf16, possibly a converted copy)
+    const uint8_t *wei;      // packed weights
+    int nb;                  // activation rows per pass, rounded up to 16 (UMMA N)
+    int m_passes, n_tiles, k_blocks;
+    int stages;
+    int64_t rows_per_pass;
+    uint32_t idesc;
+    uint32_t tmem_cols;
+    uint32_t gs_blocks, gz_blocks; // K-group sizes of scales and zero-points in k-blocks of 64 (K / 64 when not grouped)
+    uint32_t s_groups, z_groups;   // number of such groups along K
+    float nibble_offset;     // 128 (u4) or 136 (s4 stored offset by 8)
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_test(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(smem_u32(bar)), "r"(parity)
+            : "memory");
+    return ok != 0;
+}
+// one wait of at most about two microseconds, suspended in hardware
+__device__ __forceinline__ bool mbar_try(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(smem_u32(bar)), "r"(parity), "r"(2000u)
+            : "memory");
+    return ok != 0;
+}
+// bounded wait (about a second); false when it ran out or another role already gave up
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, ctrl_t *c, uint32_t *status, uint32_t code) {
+    for (uint32_t i = 0; i < WAIT_TRIES; ++i) {
+        if (mbar_try(bar, parity)) return true;
+        if (c->abort) return false;
+    }
+    c->abort = 1;
+    if (status) atomicOr(status, code);
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, int c0, int c1, uint64_t *bar) {
+    asm volatile(
+            "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+            :
+            : "r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
+            : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t *bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void tc_mma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
+    asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+            :
+            : "r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc)
+            : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
+    asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+            "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+            : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+            "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+            : "r"(taddr)
+            : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7]), "+r"(v[8]),
+                 "+r"(v[9]), "+r"(v[10]), "+r"(v[11]), "+r"(v[12]), "+r"(v[13]), "+r"(v[14]), "+r"(v[15])
+                 :
+                 : "memory");
+}
+// shared-memory matrix descriptor: K-major operand, 128-byte swizzle, rows of 128 bytes,
+// 8-row groups 1024 bytes apart (tile base 1024-byte aligned)
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3ffff) >> 4);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+
+// Epilogue of 16 activation rows of one output column: src scale, bias, post-ops, dst
+// scale, conversion, store.  Out of line and not unrolled: the interpreter behind
+// finish_element is large, and the conversion loop should keep the instruction cache.
+__device__ __noinline__ void finish_chunk(const b200_matmul_params_t &p, const uint32_t (&v)[16], int64_t m_first, int64_t m_end,
+        int64_t n) {
+    if (n >= p.N) return;
+    const float dst_inv = dst_scale_reciprocal(p);
+    const float src_scale = p.src_scale.ptr ? load_f32(p.src_scale.dt, p.src_scale.ptr, 0) : 1.f;
+#pragma unroll 1
+    for (int j = 0; j < 16; ++j) {
+        const int64_t m = m_first + j;
+        if (m >= m_end) break;
+        float dv = __uint_as_float(v[j]);
+        if (p.src_scale.ptr) dv = __fmul_rn(dv, src_scale);
+        finish_element(p, dv, m, n, false, dst_inv);
+    }
+}
+
+// ---- the kernel -------------------------------------------------------------------------
+
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+        wc_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ args_t args) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    const b200_matmul_params_t &p = args.p;
+    const int nb = args.nb;
+    const uint32_t b_bytes = (uint32_t)nb * (TK * 2);
+    const uint32_t stage_bytes = A_BYTES + b_bytes;
+    const uint32_t STAGES = (uint32_t)args.stages;
+    uint8_t *pf_ring = smem + (size_t)STAGES * stage_bytes;                    // [PF][threads][PF_BYTES] packed weights in flight
+    ctrl_t *ctrl = (ctrl_t *)(smem + (size_t)STAGES * stage_bytes + (size_t)PF * DQ_WARPS * 32 * PF_BYTES);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int num_tiles = args.n_tiles * args.m_passes;
+    const int KB = args.k_blocks;
+
+    if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < STAGES; ++s) {
+            mbar_init(&ctrl->full_a[s], DQ_WARPS);
+            mbar_init(&ctrl->full_b[s], 1);
+            mbar_init(&ctrl->empty[s], 1);
+        }
+        mbar_init(&ctrl->acc_full, 1);
+        mbar_init(&ctrl->acc_empty, DQ_WARPS);
+        ctrl->abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ctrl->tmem_base)),
+                     "r"(args.tmem_cols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = ctrl->tmem_base;
+
+    if (warp == 0) {
+        // ---------------- TMA producer: activations of each k-block ----------------
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                const int row0 = (int)((tile / args.n_tiles) * args.rows_per_pass);
+                for (int kb = 0; kb < KB; ++kb, ++it) {
+                    const uint32_t s = it % STAGES, r = it / STAGES;
+                    if (!(ok = mbar_wait(&ctrl->empty[s], (r & 1) ^ 1, ctrl, p.status, ST_WAIT_EMPTY))) break;
+                    mbar_expect_tx(&ctrl->full_b[s], b_bytes);
+                    tma_load_2d(smem + (size_t)s * stage_bytes + A_BYTES, &tmap_x, kb * (TK * 2), row0, &ctrl->full_b[s]); // byte coordinates
+                }
+            }
+            // drain: every copy this thread issued must have landed before the CTA may exit
+            const uint32_t issued = it;
+            for (uint32_t j = issued > STAGES ? issued - STAGES : 0; j < issued; ++j) {
+                const uint32_t s = j % STAGES, r = j / STAGES;
+                for (uint32_t i = 0; i < WAIT_SPINS; ++i) {
+                    if (mbar_test(&ctrl->full_b[s], r & 1)) break;
+                    __nanosleep(64);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            uint32_t it = 0, tile_i = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tile_i) {
+                if (!(ok = mbar_wait(&ctrl->acc_empty, (tile_i & 1) ^ 1, ctrl, p.status, ST_WAIT_ACC))) break;
+                tc_fence_after();
+                for (int kb = 0; kb < KB; ++kb, ++it) {
+                    const uint32_t s = it % STAGES, r = it / STAGES;
+                    if (!(ok = mbar_wait(&ctrl->full_a[s], r & 1, ctrl, p.status, ST_WAIT_FULL))) break;
+                    if (!(ok = mbar_wait(&ctrl->full_b[s], r & 1, ctrl, p.status, ST_WAIT_FULL))) break;
+                    tc_fence_after();
+                    const uint32_t sa = smem_u32(smem + (size_t)s * stage_bytes);
+                    const uint64_t adesc = make_smem_desc(sa), bdesc = make_smem_desc(sa + A_BYTES);
+#pragma unroll
+                    for (int k = 0; k < TK / 16; ++k) // 16 bf16 = 32 bytes of K per instruction: +2 in 16-byte units
+                        tc_mma_bf16(tmem_base, adesc + 2 * k, bdesc + 2 * k, args.idesc, (kb | k) != 0);
+                    tc_commit(&ctrl->empty[s]);
+                }
+                if (ok) tc_commit(&ctrl->acc_full);
+            }
+        }
+    } else {
+        // ---------------- dequantisers, then epilogue ----------------
+        const int d = threadIdx.x - 64;     // 0 .. DQ_WARPS * 32 - 1
+        constexpr int PARTS = TK / KPT;     // threads per column
+        const int r = d / PARTS, h = d % PARTS; // column of the tile, which part of the 64 k
+        const int quarter = warp & 3;       // TMEM lanes this warp may read: 32*quarter .. +31
+        const int which = (warp - 2) >> 2;  // four warps share a quarter and split the chunks of columns
+        const uint32_t row_off = (uint32_t)r * 128, sw = (uint32_t)(r & 7);
+        const bool zp_signed = p.wei_zp.ptr && p.wei_zp.dt == B200_DT_S4;
+        const bool simple_epilogue = p.npo == 0 && !p.dst_scale.ptr && (!p.bias || p.bias_sm == 0)
+                && (p.dst_dt == B200_DT_BF16 || p.dst_dt == B200_DT_F32);
+        const float src_scale = p.src_scale.ptr ? load_f32(p.src_scale.dt, p.src_scale.ptr, 0) : 1.f;
+        uint32_t st = 0, round = 0, tile_i = 0;
+        bool ok = true;
+
+        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tile_i) {
+            const int nt = tile % args.n_tiles;
+            const int64_t ncol = (int64_t)nt * TN + r;
+            const bool col_ok = ncol < p.N;
+            // packed nibbles of (column r, 16 k) of every k-block: 8 bytes per thread and block,
+            // copied asynchronously PF blocks ahead into a slot only this thread reads
+            const uint8_t *wsrc = args.wei + (size_t)nt * KB * BLOCK_BYTES + (size_t)d * PF_BYTES;
+            const uint32_t pf_s = smem_u32(pf_ring + (size_t)d * PF_BYTES);
+            auto request = [&](int kb) {
+                if (kb < KB)
+                    asm volatile("cp.async.ca.shared.global [%0], [%1], %2;" ::"r"(pf_s + (uint32_t)(kb % PF) * (DQ_WARPS * 32 * PF_BYTES)),
+                                 "l"(wsrc + (size_t)kb * BLOCK_BYTES), "n"(PF_BYTES)
+                                 : "memory");
+                asm volatile("cp.async.commit_group;" ::: "memory"); // also when empty: the waits count groups
+            };
+#pragma unroll 1
+            for (int kb = 0; kb < PF; ++kb) request(kb);
+            // scale / zero-point of the column: raw bits are requested one group ahead and
+            // decoded when the group starts, so that no load is waited for in the loop
+            const uint16_t *sp = col_ok && p.wei_scale.ptr ? (const uint16_t *)p.wei_scale.ptr + ncol * p.wei_scale.s1 : nullptr;
+            const int64_t zbase = ncol * p.wei_zp.s1;
+            const bool has_zp = col_ok && p.wei_zp.ptr;
+            uint32_t s_left = 1, z_left = 1, s_grp = 0, z_grp = 0; // k-blocks left in the current group, next group index
+            uint32_t sraw = col_ok ? 0x3f80u : 0u, zraw = 0, zshift = 0; // 1.0 (0 for padding columns), zero-point 0
+            auto load_scale = [&](uint32_t g) {
+                if (sp) sraw = sp[(int64_t)g * p.wei_scale.s0];
+            };
+            auto load_zp = [&](uint32_t g) {
+                if (has_zp) {
+                    const int64_t e = (int64_t)g * p.wei_zp.s0 + zbase;
+                    zraw = ((const uint8_t *)p.wei_zp.ptr)[e >> 1];
+                    zshift = (uint32_t)(e & 1) * 4;
+                }
+            };
+            load_scale(0);
+            load_zp(0);
+            __nv_bfloat162 sc, cc;
+            for (int kb = 0; kb < KB; ++kb) {
+                const uint32_t s = st, rd = round;
+                if (++st == STAGES) { // stage index and round without a division
+                    st = 0;
+                    ++round;
+                }
+                if (--s_left == 0) { // a scale group starts: decode what was requested, request the next
+                    const uint32_t sb = sraw | (sraw << 16);
+                    sc = *reinterpret_cast<const __nv_bfloat162 *>(&sb);
+                    s_left = args.gs_blocks;
+                    load_scale(++s_grp < args.s_groups ? s_grp : 0);
+                }
+                if (--z_left == 0) {
+                    int zp = (int)((zraw >> zshift) & 0xf);
+                    if (zp_signed) zp = (zp ^ 8) - 8;
+                    cc = __float2bfloat162_rn(args.nibble_offset + (float)zp); // exact: an integer below 256
+                    z_left = args.gz_blocks;
+                    load_zp(++z_grp < args.z_groups ? z_grp : 0);
+                }
+                asm volatile("cp.async.wait_group %0;" ::"n"(PF - 1) : "memory"); // block kb has landed
+                uint32_t words[KPT / 8];
+                {
+                    const uint8_t *slot = pf_ring + ((size_t)(kb % PF) * (DQ_WARPS * 32) + d) * PF_BYTES;
+                    if (KPT == 32) {
+                        const uint4 t4 = *reinterpret_cast<const uint4 *>(slot);
+                        words[0] = t4.x, words[1] = t4.y, words[KPT / 8 - 2] = t4.z, words[KPT / 8 - 1] = t4.w;
+                    } else {
+                        const uint2 t2 = *reinterpret_cast<const uint2 *>(slot);
+                        words[0] = t2.x, words[1] = t2.y;
+                    }
+                }
+                if (!(ok = mbar_wait(&ctrl->empty[s], (rd & 1) ^ 1, ctrl, p.status, ST_WAIT_EMPTY))) {
+                    asm volatile("cp.async.wait_group 0;" ::: "memory");
+                    break;
+                }
+                uint8_t *tile_a = smem + (size_t)s * stage_bytes + row_off;
+#pragma unroll
+                for (int j = 0; j < KPT / 8; ++j) {
+                    const uint32_t v = words[j];
+                    uint32_t o[4];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const uint32_t bits = ((v >> (4 * i)) & 0x000f000fu) | 0x43004300u; // (128 + q, 128 + q')
+                        __nv_bfloat162 x = *reinterpret_cast<const __nv_bfloat162 *>(&bits);
+                        x = __hmul2(__hsub2(x, cc), sc); // (q - zp) exactly, then one rounding of the product
+                        o[i] = *reinterpret_cast<const uint32_t *>(&x);
+                    }
+                    const uint32_t chunk = (uint32_t)((KPT / 8) * h + j) ^ sw;
+                    *reinterpret_cast<uint4 *>(tile_a + chunk * 16) = make_uint4(o[0], o[1], o[2], o[3]);
+                }
+                // generic-proxy writes -> visible to the tensor core's (async proxy) reads
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&ctrl->full_a[s]);
+                request(kb + PF); // the slot of block kb is free again
+            }
+            if (!ok) break;
+
+            // epilogue: lane = output column, TMEM columns = activation rows of this pass
+            ok = mbar_wait(&ctrl->acc_full, tile_i & 1, ctrl, p.status, ST_WAIT_ACC);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after();
+            const int64_t n = (int64_t)nt * TN + quarter * 32 + lane;
+            const int64_t m0 = (int64_t)(tile / args.n_tiles) * args.rows_per_pass;
+            const int64_t m_end = m0 + args.rows_per_pass < p.M ? m0 + args.rows_per_pass : p.M;
+            const uint32_t trow = tmem_base + ((uint32_t)(quarter * 32) << 16);
+            const float bias_n = simple_epilogue && p.bias && n < p.N ? load_f32(p.bias_dt, p.bias, n * p.bias_sn) : 0.f;
+            for (int c = which; c * 16 < nb; c += DQ_WARPS / 4) {
+                if (m0 + c * 16 >= m_end) break; // warp-uniform: nothing but padding from here on
+                uint32_t v[16];
+                tmem_ld16(trow + c * 16, v);
+                if (simple_epilogue) {
+                    // no post-ops, no dst scale, bias per column or none, bf16 / f32 dst: a handful of
+                    // instructions per element, lanes along a dst row
+                    if (n < p.N) {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            const int64_t m = m0 + c * 16 + j;
+                            if (m < m_end) {
+                                float dv = __uint_as_float(v[j]);
+                                if (p.src_scale.ptr) dv = __fmul_rn(dv, src_scale);
+                                if (p.bias) dv = __fadd_rn(dv, bias_n);
+                                if (p.dst_dt == B200_DT_BF16) ((uint16_t *)p.dst)[m * p.dst_sm + n] = f32_to_bf16_bits(dv);
+                                else ((float *)p.dst)[m * p.dst_sm + n] = dv;
+                            }
+                        }
+                    }
+                } else {
+                    finish_chunk(p, v, m0 + c * 16, m_end, n);
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&ctrl->acc_empty);
+        }
+    }
+
+    __syncwarp();
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(args.tmem_cols) : "memory");
+    }
+}
+
+// plain (K, N) 4-bit weights, two per byte along N -> B200_WEI_WC4_TC.  One thread per
+// 32-bit output word (8 consecutive k of one column).
+__global__ void __launch_bounds__(256) wc_tc_pack_kernel(const uint8_t *__restrict__ src, uint32_t *__restrict__ dst,
+        int64_t K, int64_t N, int is_signed) {
+    const int64_t KB = K / TK, n_tiles = (N + TN - 1) / TN;
+    const int64_t nwords = n_tiles * KB * (BLOCK_BYTES / 4);
+    for (int64_t wi = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; wi < nwords; wi += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t block = wi / (BLOCK_BYTES / 4);
+        const int in_block = (int)(wi % (BLOCK_BYTES / 4));
+        const int r = in_block >> 3, j = in_block & 7;
+        const int64_t nt = block / KB, kb = block % KB;
+        const int64_t n = nt * TN + r, k8 = kb * TK + j * 8;
+        uint32_t word = 0;
+        if (n < N) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int64_t k = k8 + (i < 4 ? 2 * i : 2 * (i - 4) + 1);
+                const int64_t e = k * N + n;
+                uint32_t q = (src[e >> 1] >> ((e & 1) * 4)) & 0xf;
+                if (is_signed) q ^= 8u; // two's complement nibble -> offset binary (value + 8)
+                word |= q << (4 * i);
+            }
+        }
+        dst[wi] = word;
+    }
+}
+
+} // namespace wctc
+} // namespace b200
+
+using namespace b200;
+using namespace b200::wctc;
+
+typedef CUresult (*wctc_encode_fn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+        const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+        CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static wctc_encode_fn wctc_get_encode_fn() {
+    static wctc_encode_fn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void *sym = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess
+                && q == cudaDriverEntryPointSuccess)
+            fn = (wctc_encode_fn)sym;
+    });
+    return fn;
+}
+
+static inline size_t wctc_align256(size_t x) { return (x + 255) / 256 * 256; }
+
+extern "C" size_t b200_wc_tc_packed_bytes(int64_t K, int64_t N) {
+    if (K <= 0 || N <= 0) return 0;
+    return (size_t)((N + TN - 1) / TN) * (size_t)(K / TK) * BLOCK_BYTES;
+}
+
+extern "C" int b200_wc_tc_pack_launch(const void *src, void *dst, int64_t K, int64_t N, int32_t dt, b200_stream_t stream) {
+    if (!src || !dst) return B200_ERR_BAD_ARG;
+    if ((dt != B200_DT_U4 && dt != B200_DT_S4) || K % TK != 0 || (N & 1)) return B200_ERR_UNSUPPORTED;
+    const int64_t nwords = (int64_t)(b200_wc_tc_packed_bytes(K, N) / 4);
+    if (nwords == 0) return 0;
+    int64_t blocks = (nwords + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    wc_tc_pack_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>((const uint8_t *)src, (uint32_t *)dst, K, N,
+            dt == B200_DT_S4);
+    return after_launch();
+}
+
+extern "C" int b200_matmul_wc_tc_launch(const b200_matmul_params_t *p, b200_stream_t stream) {
+    if (!p || !p->src || !p->wei || !p->dst) return B200_ERR_BAD_ARG;
+    if (p->M <= 0 || p->N <= 0 || p->K <= 0) return p->M < 0 || p->N < 0 || p->K < 0 ? B200_ERR_BAD_ARG : 0;
+    if (p->wei_dt != B200_DT_U4 && p->wei_dt != B200_DT_S4) return B200_ERR_UNSUPPORTED;
+    if (!p->apply_to_int || p->src_dt != B200_DT_BF16) return B200_ERR_UNSUPPORTED;
+    if (p->K % TK != 0 || (p->N & 1) || p->src_sk != 1 || p->dst_sn != 1 || p->n_dst_peers) return B200_ERR_UNSUPPORTED;
+    if (p->M > INT32_MAX || p->N > INT32_MAX || p->K > INT32_MAX) return B200_ERR_TOO_LARGE;
+    if (p->wei_layout == B200_WEI_PLAIN && !(p->wei_sn == 1 && p->wei_sk == p->N)) return B200_ERR_UNSUPPORTED;
+    if (p->wei_layout != B200_WEI_PLAIN && p->wei_layout != B200_WEI_WC4_TC) return B200_ERR_UNSUPPORTED;
+    if (p->src_zp.ptr || p->dst_zp.ptr) return B200_ERR_UNSUPPORTED;
+    if (p->src_scale.ptr && (p->src_scale.s0 || p->src_scale.s1)) return B200_ERR_UNSUPPORTED;
+    // the conversion multiplies in bf16: the scale must be bf16 to begin with, and 128 + zero-point
+    // must be exact in bf16, which 4-bit zero-points guarantee
+    int64_t gs = p->K, gz = p->K;
+    if (p->wei_scale.ptr) {
+        if (p->wei_scale.dt != B200_DT_BF16 || p->wei_scale.g1 != 1) return B200_ERR_UNSUPPORTED;
+        if (p->wei_scale.s0) gs = p->wei_scale.g0;
+    }
+    if (p->wei_zp.ptr) {
+        if ((p->wei_zp.dt != B200_DT_U4 && p->wei_zp.dt != B200_DT_S4) || p->wei_zp.g1 != 1) return B200_ERR_UNSUPPORTED;
+        if (p->wei_zp.s0) gz = p->wei_zp.g0;
+    }
+    if (gs % TK || gz % TK || p->K % gs || p->K % gz) return B200_ERR_UNSUPPORTED;
+    // activations arrive by TMA: 16-byte aligned base and row pitch
+    if (((uintptr_t)p->src & 15) || ((p->src_sm * 2) & 15)) return B200_ERR_BAD_ARG;
+
+    cudaStream_t cs = (cudaStream_t)stream;
+    const void *wei = p->wei;
+    if (p->wei_layout == B200_WEI_PLAIN) {
+        const size_t need = wctc_align256(b200_wc_tc_packed_bytes(p->K, p->N));
+        if (!p->scratch || p->scratch_bytes < need) return B200_ERR_BAD_ARG;
+        int rc = b200_wc_tc_pack_launch(p->wei, p->scratch, p->K, p->N, p->wei_dt, stream);
+        if (rc) return rc;
+        wei = p->scratch;
+    }
+    if ((uintptr_t)wei & 15) return B200_ERR_BAD_ARG;
+
+    args_t a;
+    a.p = *p;
+    a.x = (const __nv_bfloat16 *)p->src;
+    a.wei = (const uint8_t *)wei;
+    a.rows_per_pass = p->M <= 256 ? p->M : 256;
+    a.nb = (int)((a.rows_per_pass + 15) / 16 * 16);
+    a.m_passes = (int)((p->M + a.rows_per_pass - 1) / a.rows_per_pass);
+    a.n_tiles = (int)((p->N + TN - 1) / TN);
+    a.k_blocks = (int)(p->K / TK);
+    a.gs_blocks = (uint32_t)(gs / TK);
+    a.gz_blocks = (uint32_t)(gz / TK);
+    a.s_groups = (uint32_t)(p->K / gs);
+    a.z_groups = (uint32_t)(p->K / gz);
+    a.nibble_offset = p->wei_dt == B200_DT_S4 ? 136.f : 128.f;
+    a.tmem_cols = 32;
+    while ((int)a.tmem_cols < a.nb) a.tmem_cols *= 2;
+    // instruction descriptor: D f32, A and B bf16, both K-major, N = nb, M = 128
+    a.idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(a.nb >> 3) << 17) | ((uint32_t)(TN >> 4) << 24);
+
+    wctc_encode_fn fn = wctc_get_encode_fn();
+    if (!fn) return (int)cudaErrorUnknown;
+    CUtensorMap tx;
+    {
+        // bytes: rows of K * 2 bytes; box = 128 bytes of K x nb rows, 128-byte swizzle; rows past M read as zero
+        const cuuint64_t gdim[2] = {(cuuint64_t)p->K * 2, (cuuint64_t)p->M};
+        const cuuint64_t gstride[1] = {(cuuint64_t)p->src_sm * 2};
+        const cuuint32_t box[2] = {(cuuint32_t)(TK * 2), (cuuint32_t)a.nb};
+        const cuuint32_t estr[2] = {1, 1};
+        if (fn(&tx, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(p->src), gdim, gstride, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE)
+                != CUDA_SUCCESS)
+            return (int)cudaErrorUnknown;
+    }
+
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int64_t tiles = (int64_t)a.n_tiles * a.m_passes;
+    const unsigned grid = (unsigned)(tiles < sms ? tiles : sms);
+    a.stages = a.nb > 128 ? 3 : MAX_STAGES;
+    const size_t smem = 1024 + (size_t)a.stages * (A_BYTES + (size_t)a.nb * TK * 2) + (size_t)PF * DQ_WARPS * 32 * PF_BYTES + sizeof(ctrl_t);
+    static std::mutex mu;
+    static bool attr_done[64] = {};
+    {
+        std::lock_guard<std::mutex> g(mu);
+        if (dev < 64 && !attr_done[dev]) {
+            const cudaError_t e = cudaFuncSetAttribute(wc_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+            if (e != cudaSuccess) return (int)e;
+            attr_done[dev] = true;
+        }
+    }
+    wc_tc_kernel<<<grid, NUM_THREADS, smem, cs>>>(tx, a);
+    return after_launch();
+}

@@ -175,6 +175,10 @@ CASES = {
     "wc_u4_g128_m1_deep": _wc_case(1, 64, 4096, 128, dt.U4, seed=15),
     "wc_u4_g64_m5_mid": _wc_case(5, 1040, 192, 64, dt.U4, seed=16),
     "wc_s4_perN_m2": _wc_case(2, 96, 384, 384, dt.S4, seed=17, zp="none"),
+    # tensor-core weight decompression (more than 32 rows): ragged N, two passes over M, no zero-points
+    "wc_tc_u4_g64_m33_ragged": _wc_case(33, 208, 128, 64, dt.U4, seed=18),
+    "wc_tc_u4_g128_m40_wide": _wc_case(40, 2560, 256, 128, dt.U4, seed=20),
+    "wc_tc_s4_perN_m300": _wc_case(300, 144, 192, 192, dt.S4, seed=19, zp="none"),
     "wc_s4_g32_m2_f32dst": _wc_case(2, 32, 128, 32, dt.S4, dst_dt=dt.F32),
     "wc_s8_perN_common_zp": _wc_case(5, 48, 96, 96, dt.S8, zp="common"),
     "wc_u8_g32_nozp": _wc_case(4, 40, 64, 32, dt.U8, zp="none"),

@@ -1,4 +1,4 @@
-// Weight-compressed matmul on the tensor cores: bf16 activations (9 .. 256 rows per
+// Weight-compressed matmul on the tensor cores: bf16 activations (up to 128 rows per
 // pass) times 4-bit weights with K-grouped scales and zero-points.
 // Semantics: the reference's weights-decompression matmul
 // (src/cpu/matmul/ref_matmul.cpp:130-233, with_wei_decompression) under fpmath bf16
@@ -7,8 +7,8 @@
 // with a bf16 scale is exact in f32), products are accumulated in f32.
 //
 // Where the decode kernel (matmul_wc.cu) spends its issue slots on register-level MMAs,
-// this one only converts: per stage of 64 k, sixteen warps turn 4 KiB of packed nibbles into
-// a 128-column x 64-k bf16 tile in shared memory, laid out as the 128-byte-swizzled K-major
+// this one only converts: per stage of 64 k, a group of four warps (one thread per output
+// column) turns 4 KiB of packed nibbles into a 128-column x 64-k bf16 tile in shared memory, laid out as the 128-byte-swizzled K-major
 // operand tile a TMA load would have produced; the activations of the same 64 k arrive by
 // TMA; one thread issues tcgen05.mma (kind::f16, 128 x NB x 16) with the weights as the A
 // operand (128 output columns = the TMEM lanes) and the activations as B (NB = activation
@@ -17,7 +17,8 @@
 //
 //   warp 0        TMA producer (activations)           waits empty[s]   -> full_b[s] (tx bytes)
 //   warp 1        TMEM owner and MMA issuer            waits full_a/b   -> empty[s], acc_full
-//   warps 2..17   dequantisers, then epilogue          waits empty[s]   -> full_a[s]; acc_full -> acc_empty
+//   warps 2..17   four dequantising groups (group g    waits empty[g]   -> full_a[g]; acc_full -> acc_empty
+//                 owns stage g), then the epilogue
 //
 // Weights are read in the B200_WEI_WC4_TC layout written by the pack kernel below:
 // blocks of 128 output columns x 64 k = 4 KiB, block (nt, kb) at ((nt * K/64) + kb) * 4096,
@@ -41,11 +42,12 @@ namespace wctc {
 
 constexpr int TN = 128;              // output columns per tile (UMMA M, TMEM lanes)
 constexpr int TK = 64;               // k per stage: 128 bytes of bf16 = one swizzle row
-constexpr int MAX_STAGES = 4;        // operand stages (3 when the activation tile is 256 rows)
-constexpr int PF = 16;               // packed-weight blocks requested ahead (8 bytes per thread and block)
-constexpr int KPT = 16;               // k per dequantising thread and stage (16 or 32)
-constexpr int DQ_WARPS = TN * TK / KPT / 32; // 8 or 16 warps: one 16- or 8-byte load of packed weights each per stage
-constexpr int PF_BYTES = KPT / 2;    // bytes per thread and block in the prefetch ring
+constexpr int STAGES = 4;            // operand stages; stage g belongs to warp group g
+constexpr int GROUPS = STAGES;       // dequantising warp groups, each converts every fourth k-block
+constexpr int GROUP_WARPS = TN / 32; // one thread per output column of the tile
+constexpr int DQ_WARPS = GROUPS * GROUP_WARPS;
+constexpr int PFS = 4;               // k-blocks of its own that a group requests ahead (32 bytes per thread each)
+constexpr int PF_BYTES = TK / 2;     // packed bytes of one column in one k-block
 constexpr int NUM_THREADS = 64 + DQ_WARPS * 32;
 constexpr int A_BYTES = TN * TK * 2; // dequantised weights tile, 16 KiB
 constexpr int BLOCK_BYTES = TN * TK / 2; // packed weights per stage, 4 KiB
@@ -54,9 +56,9 @@ constexpr uint32_t WAIT_TRIES = 1u << 19; // hardware-suspended waits of up to ~
 enum : uint32_t { ST_WAIT_FULL = 0x1000, ST_WAIT_EMPTY = 0x2000, ST_WAIT_ACC = 0x4000 };
 
 struct ctrl_t {
-    uint64_t full_a[MAX_STAGES];
-    uint64_t full_b[MAX_STAGES];
-    uint64_t empty[MAX_STAGES];
+    uint64_t full_a[STAGES];
+    uint64_t full_b[STAGES];
+    uint64_t empty[STAGES];
     uint64_t acc_full, acc_empty;
     uint32_t tmem_base;
     volatile uint32_t abort;
@@ -68,7 +70,6 @@ struct args_t {
     const uint8_t *wei;      // packed weights
     int nb;                  // activation rows per pass, rounded up to 16 (UMMA N)
     int m_passes, n_tiles, k_blocks;
-    int stages;
     int64_t rows_per_pass;
     uint32_t idesc;
     uint32_t tmem_cols;
@@ -195,16 +196,15 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     const int nb = args.nb;
     const uint32_t b_bytes = (uint32_t)nb * (TK * 2);
     const uint32_t stage_bytes = A_BYTES + b_bytes;
-    const uint32_t STAGES = (uint32_t)args.stages;
-    uint8_t *pf_ring = smem + (size_t)STAGES * stage_bytes;                    // [PF][threads][PF_BYTES] packed weights in flight
-    ctrl_t *ctrl = (ctrl_t *)(smem + (size_t)STAGES * stage_bytes + (size_t)PF * DQ_WARPS * 32 * PF_BYTES);
+    uint8_t *pf_ring = smem + (size_t)STAGES * stage_bytes;                    // [PFS][threads][PF_BYTES] packed weights in flight
+    ctrl_t *ctrl = (ctrl_t *)(smem + (size_t)STAGES * stage_bytes + (size_t)PFS * DQ_WARPS * 32 * PF_BYTES);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int num_tiles = args.n_tiles * args.m_passes;
     const int KB = args.k_blocks;
 
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < STAGES; ++s) {
-            mbar_init(&ctrl->full_a[s], DQ_WARPS);
+            mbar_init(&ctrl->full_a[s], GROUP_WARPS);
             mbar_init(&ctrl->full_b[s], 1);
             mbar_init(&ctrl->empty[s], 1);
         }
@@ -274,95 +274,81 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         }
     } else {
         // ---------------- dequantisers, then epilogue ----------------
-        const int d = threadIdx.x - 64;     // 0 .. DQ_WARPS * 32 - 1
-        constexpr int PARTS = TK / KPT;     // threads per column
-        const int r = d / PARTS, h = d % PARTS; // column of the tile, which part of the 64 k
+        // Warp group g (four warps, one thread per column of the tile) converts the k-blocks that
+        // land in operand stage g, i.e. every fourth one: a thread then has a quarter of the
+        // iterations, each with a whole 64-k row to convert, and the four groups work on four
+        // different stages at the same time.
+        const int dq = threadIdx.x - 64;    // 0 .. 511
+        const int grp = dq >> 7, r = dq & 127;
         const int quarter = warp & 3;       // TMEM lanes this warp may read: 32*quarter .. +31
         const int which = (warp - 2) >> 2;  // four warps share a quarter and split the chunks of columns
-        const uint32_t row_off = (uint32_t)r * 128, sw = (uint32_t)(r & 7);
+        const uint32_t sw = (uint32_t)(r & 7);
         const bool zp_signed = p.wei_zp.ptr && p.wei_zp.dt == B200_DT_S4;
         const bool simple_epilogue = p.npo == 0 && !p.dst_scale.ptr && (!p.bias || p.bias_sm == 0)
                 && (p.dst_dt == B200_DT_BF16 || p.dst_dt == B200_DT_F32);
         const float src_scale = p.src_scale.ptr ? load_f32(p.src_scale.dt, p.src_scale.ptr, 0) : 1.f;
-        uint32_t st = 0, round = 0, tile_i = 0;
+        uint8_t *tile_a = smem + (size_t)grp * stage_bytes + (uint32_t)r * 128;
+        uint8_t *my_ring = pf_ring + (size_t)dq * PF_BYTES;
+        const uint32_t my_ring_s = smem_u32(my_ring);
+        constexpr uint32_t RING_STRIDE = DQ_WARPS * 32 * PF_BYTES;
+        uint32_t uses = 0, tile_i = 0; // times this group has filled its stage
         bool ok = true;
 
         for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tile_i) {
             const int nt = tile % args.n_tiles;
             const int64_t ncol = (int64_t)nt * TN + r;
             const bool col_ok = ncol < p.N;
-            // packed nibbles of (column r, 16 k) of every k-block: 8 bytes per thread and block,
-            // copied asynchronously PF blocks ahead into a slot only this thread reads
-            const uint8_t *wsrc = args.wei + (size_t)nt * KB * BLOCK_BYTES + (size_t)d * PF_BYTES;
-            const uint32_t pf_s = smem_u32(pf_ring + (size_t)d * PF_BYTES);
-            auto request = [&](int kb) {
-                if (kb < KB)
-                    asm volatile("cp.async.ca.shared.global [%0], [%1], %2;" ::"r"(pf_s + (uint32_t)(kb % PF) * (DQ_WARPS * 32 * PF_BYTES)),
-                                 "l"(wsrc + (size_t)kb * BLOCK_BYTES), "n"(PF_BYTES)
-                                 : "memory");
+            // the k-blocks of this tile that fall into this group's stage
+            const int first_kb = (int)((grp + STAGES - (uint32_t)(((uint64_t)tile_i * KB) % STAGES)) % STAGES);
+            const int iters = first_kb < KB ? (KB - first_kb + STAGES - 1) / STAGES : 0;
+            const uint8_t *wsrc = args.wei + ((size_t)nt * KB + first_kb) * BLOCK_BYTES + (size_t)r * PF_BYTES;
+            auto request = [&](int j) { // packed row of this thread's j-th k-block, two 16-byte copies
+                if (j < iters) {
+                    const uint8_t *src = wsrc + (size_t)j * (STAGES * BLOCK_BYTES);
+                    const uint32_t dst = my_ring_s + (uint32_t)(j % PFS) * RING_STRIDE;
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + 16), "l"(src + 16) : "memory");
+                }
                 asm volatile("cp.async.commit_group;" ::: "memory"); // also when empty: the waits count groups
             };
 #pragma unroll 1
-            for (int kb = 0; kb < PF; ++kb) request(kb);
-            // scale / zero-point of the column: raw bits are requested one group ahead and
-            // decoded when the group starts, so that no load is waited for in the loop
+            for (int j = 0; j < PFS; ++j) request(j);
+            // scale / zero-point of the column: the raw bits for the next iteration are requested
+            // while this one is converted
             const uint16_t *sp = col_ok && p.wei_scale.ptr ? (const uint16_t *)p.wei_scale.ptr + ncol * p.wei_scale.s1 : nullptr;
-            const int64_t zbase = ncol * p.wei_zp.s1;
             const bool has_zp = col_ok && p.wei_zp.ptr;
-            uint32_t s_left = 1, z_left = 1, s_grp = 0, z_grp = 0; // k-blocks left in the current group, next group index
+            const int64_t zbase = ncol * p.wei_zp.s1;
             uint32_t sraw = col_ok ? 0x3f80u : 0u, zraw = 0, zshift = 0; // 1.0 (0 for padding columns), zero-point 0
-            auto load_scale = [&](uint32_t g) {
-                if (sp) sraw = sp[(int64_t)g * p.wei_scale.s0];
-            };
-            auto load_zp = [&](uint32_t g) {
+            auto load_q = [&](int kb) {
+                if (kb >= KB) return;
+                if (sp) sraw = sp[(int64_t)((uint32_t)kb / args.gs_blocks) * p.wei_scale.s0];
                 if (has_zp) {
-                    const int64_t e = (int64_t)g * p.wei_zp.s0 + zbase;
+                    const int64_t e = (int64_t)((uint32_t)kb / args.gz_blocks) * p.wei_zp.s0 + zbase;
                     zraw = ((const uint8_t *)p.wei_zp.ptr)[e >> 1];
                     zshift = (uint32_t)(e & 1) * 4;
                 }
             };
-            load_scale(0);
-            load_zp(0);
-            __nv_bfloat162 sc, cc;
-            for (int kb = 0; kb < KB; ++kb) {
-                const uint32_t s = st, rd = round;
-                if (++st == STAGES) { // stage index and round without a division
-                    st = 0;
-                    ++round;
-                }
-                if (--s_left == 0) { // a scale group starts: decode what was requested, request the next
-                    const uint32_t sb = sraw | (sraw << 16);
-                    sc = *reinterpret_cast<const __nv_bfloat162 *>(&sb);
-                    s_left = args.gs_blocks;
-                    load_scale(++s_grp < args.s_groups ? s_grp : 0);
-                }
-                if (--z_left == 0) {
-                    int zp = (int)((zraw >> zshift) & 0xf);
-                    if (zp_signed) zp = (zp ^ 8) - 8;
-                    cc = __float2bfloat162_rn(args.nibble_offset + (float)zp); // exact: an integer below 256
-                    z_left = args.gz_blocks;
-                    load_zp(++z_grp < args.z_groups ? z_grp : 0);
-                }
-                asm volatile("cp.async.wait_group %0;" ::"n"(PF - 1) : "memory"); // block kb has landed
-                uint32_t words[KPT / 8];
-                {
-                    const uint8_t *slot = pf_ring + ((size_t)(kb % PF) * (DQ_WARPS * 32) + d) * PF_BYTES;
-                    if (KPT == 32) {
-                        const uint4 t4 = *reinterpret_cast<const uint4 *>(slot);
-                        words[0] = t4.x, words[1] = t4.y, words[KPT / 8 - 2] = t4.z, words[KPT / 8 - 1] = t4.w;
-                    } else {
-                        const uint2 t2 = *reinterpret_cast<const uint2 *>(slot);
-                        words[0] = t2.x, words[1] = t2.y;
-                    }
-                }
-                if (!(ok = mbar_wait(&ctrl->empty[s], (rd & 1) ^ 1, ctrl, p.status, ST_WAIT_EMPTY))) {
+            load_q(first_kb);
+            for (int j = 0; j < iters; ++j, ++uses) {
+                const int kb = first_kb + j * STAGES;
+                // decode this block's scale and zero-point, then ask for the next block's
+                const uint32_t sb = sraw | (sraw << 16);
+                const __nv_bfloat162 sc = *reinterpret_cast<const __nv_bfloat162 *>(&sb);
+                int zp = (int)((zraw >> zshift) & 0xf);
+                if (zp_signed) zp = (zp ^ 8) - 8;
+                const __nv_bfloat162 cc = __float2bfloat162_rn(args.nibble_offset + (float)zp); // exact: an integer below 256
+                load_q(kb + STAGES);
+                asm volatile("cp.async.wait_group %0;" ::"n"(PFS - 1) : "memory"); // this thread's j-th row has landed
+                const uint4 w0 = *reinterpret_cast<const uint4 *>(my_ring + (size_t)(j % PFS) * RING_STRIDE);
+                const uint4 w1 = *reinterpret_cast<const uint4 *>(my_ring + (size_t)(j % PFS) * RING_STRIDE + 16);
+                if (!(ok = mbar_wait(&ctrl->empty[grp], (uses & 1) ^ 1, ctrl, p.status, ST_WAIT_EMPTY))) {
                     asm volatile("cp.async.wait_group 0;" ::: "memory");
                     break;
                 }
-                uint8_t *tile_a = smem + (size_t)s * stage_bytes + row_off;
+                const uint32_t words[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
 #pragma unroll
-                for (int j = 0; j < KPT / 8; ++j) {
-                    const uint32_t v = words[j];
+                for (int c = 0; c < 8; ++c) { // 16-byte chunk c of the row: k 8c .. 8c + 7
+                    const uint32_t v = words[c];
                     uint32_t o[4];
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
@@ -371,14 +357,13 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                         x = __hmul2(__hsub2(x, cc), sc); // (q - zp) exactly, then one rounding of the product
                         o[i] = *reinterpret_cast<const uint32_t *>(&x);
                     }
-                    const uint32_t chunk = (uint32_t)((KPT / 8) * h + j) ^ sw;
-                    *reinterpret_cast<uint4 *>(tile_a + chunk * 16) = make_uint4(o[0], o[1], o[2], o[3]);
+                    *reinterpret_cast<uint4 *>(tile_a + (((uint32_t)c ^ sw) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
                 }
                 // generic-proxy writes -> visible to the tensor core's (async proxy) reads
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&ctrl->full_a[s]);
-                request(kb + PF); // the slot of block kb is free again
+                if (lane == 0) mbar_arrive(&ctrl->full_a[grp]);
+                request(j + PFS); // the ring slot of iteration j is free again
             }
             if (!ok) break;
 
@@ -541,7 +526,7 @@ extern "C" int b200_matmul_wc_tc_launch(const b200_matmul_params_t *p, b200_stre
     a.p = *p;
     a.x = (const __nv_bfloat16 *)p->src;
     a.wei = (const uint8_t *)wei;
-    a.rows_per_pass = p->M <= 256 ? p->M : 256;
+    a.rows_per_pass = p->M <= 128 ? p->M : 128;
     a.nb = (int)((a.rows_per_pass + 15) / 16 * 16);
     a.m_passes = (int)((p->M + a.rows_per_pass - 1) / a.rows_per_pass);
     a.n_tiles = (int)((p->N + TN - 1) / TN);
@@ -577,8 +562,7 @@ extern "C" int b200_matmul_wc_tc_launch(const b200_matmul_params_t *p, b200_stre
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     const int64_t tiles = (int64_t)a.n_tiles * a.m_passes;
     const unsigned grid = (unsigned)(tiles < sms ? tiles : sms);
-    a.stages = a.nb > 128 ? 3 : MAX_STAGES;
-    const size_t smem = 1024 + (size_t)a.stages * (A_BYTES + (size_t)a.nb * TK * 2) + (size_t)PF * DQ_WARPS * 32 * PF_BYTES + sizeof(ctrl_t);
+    const size_t smem = 1024 + (size_t)STAGES * (A_BYTES + (size_t)a.nb * TK * 2) + (size_t)PFS * DQ_WARPS * 32 * PF_BYTES + sizeof(ctrl_t);
     static std::mutex mu;
     static bool attr_done[64] = {};
     {

@@ -68,6 +68,14 @@ def test_c2_decode_4096x14336(ctx, M):
     assert impl == ("cuda:sm100:wc_gemv" if M <= 32 else "cuda:sm100:wc_tcgen05")
     ns = 1 if M == 1 else (7 if M == 16 else 61)
     want = B.run_oracle(c, n_step=ns)
+    if "tcgen05" in impl:
+        # This kernel rounds every decompressed weight to bf16 (relative error up to 2^-9 each,
+        # which fpmath bf16 permits), so the error of a K = 4096 sum is about 1e-3 of the sum's
+        # typical size whatever the element's own value: the absolute part of the tolerance is
+        # 1e-2 of the root-mean-square output instead of a constant.
+        import copy
+        c = copy.copy(c)
+        c.atol = max(c.atol, 1e-2 * float(np.sqrt(np.mean(dt.to_f32(want[:, ::ns], c.dst_dt).astype(np.float64) ** 2))))
     _close(c, got[:, ::ns], want[:, ::ns], "c2 M=%d against the oracle" % M)
     if M > 1:
         # every row on its own is the M = 1 problem of that row (other kernel variant, other

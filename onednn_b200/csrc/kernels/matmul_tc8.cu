@@ -434,17 +434,18 @@ __device__ __forceinline__ void epilogue_chunk(const b200_matmul_params_t &p, co
 
     if (EPI == EPI_GELU_Q) {
         // gelu_tanh (then optionally sum) into an s8 / u8 destination, bit-exact.  The exact
-        // value needs a double-precision tanh; almost always it is not needed:
-        //  * |tanh argument| >= 9.02: the float tanh is exactly +-1, gelu(x) is x or -0;
-        //  * otherwise evaluate with a fast tanh (absolute error < 1e-6) and check how far the
-        //    value to be rounded is from a rounding boundary (k + 0.5).  The fast and the
-        //    exact value differ by less than tau (propagated error bound with a 4x margin),
-        //    so away from a boundary both round to the same integer; only elements within
-        //    tau of one are recomputed exactly (one warp vote per chunk).
+        // value needs a double-precision tanh; almost always it is not needed: evaluate with a
+        // fast tanh (ex2 / rcp, absolute error < 1e-6, saturating to +-1 by itself) and fused
+        // multiply-adds, bound the distance tau between this value and the exact one (propagated
+        // error bound with a 4x margin), and convert both o + tau and o - tau with the
+        // saturating round-to-nearest-even conversion.  If the two bytes agree, the exact value
+        // -- which lies between them -- converts to the same byte, saturation included; only
+        // elements where they differ are recomputed exactly (one warp vote per chunk).
         // The chunk is handled as two independent halves of eight columns, each a sequence
         // of passes of eight independent operations, ending in packed bytes: short live
         // ranges, no per-element control flow.
         const float sqrt_2_over_pi = 0.79788458347320556640625f, fitting_const = 0.044715f;
+        const float g_lin = sqrt_2_over_pi, g_cub = sqrt_2_over_pi * fitting_const;
         const float elt_scale = p.po[0].scale;
         const float sum_scale = SUM != SUM_NONE ? p.po[1].scale : 0.f;
         const float sum_zp = SUM != SUM_NONE ? (float)p.po[1].zero_point : 0.f;
@@ -465,39 +466,36 @@ __device__ __forceinline__ void epilogue_chunk(const b200_matmul_params_t &p, co
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     const float acc = FP8 ? __uint_as_float(v[hb + 4 * q + i]) : (float)((int)v[hb + 4 * q + i] - cs[i]);
-                    x[4 * q + i] = __fadd_rn(__fmul_rn(__fmul_rn(acc, k.src_scale), ws[i]), bs[i]);
+                    x[4 * q + i] = fmaf(acc * k.src_scale, ws[i], bs[i]); // within 2 ulp of the reference's unfused value
                 }
             }
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                g[j] = __fmul_rn(__fmul_rn(sqrt_2_over_pi, x[j]), __fadd_rn(1.f, __fmul_rn(__fmul_rn(fitting_const, x[j]), x[j])));
-            }
+            for (int j = 0; j < 8; ++j) g[j] = x[j] * fmaf(g_cub, x[j] * x[j], g_lin);
 #pragma unroll
             for (int j = 0; j < 8; ++j) t[j] = tanh_fast(g[j]);
             const float4 z0 = ((const float4 *)zp)[hb / 4], z1 = ((const float4 *)zp)[hb / 4 + 1];
             const float zs[8] = {z0.x, z0.y, z0.z, z0.w, z1.x, z1.y, z1.z, z1.w};
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
-                const bool sat_arg = fabsf(g[j]) >= 9.02f;
                 const float h = 0.5f * x[j];
-                const float gelu = sat_arg ? (g[j] > 0 ? x[j] : -0.f) : fmaf(h, t[j], h);
+                const float gelu = fmaf(h, t[j], h);
                 float r = __fmul_rn(gelu, elt_scale);
                 if (SUM != SUM_NONE) r = __fadd_rn(r, __fmul_rn(sum_scale, __fsub_rn(old_val(hb + j), sum_zp)));
                 r = __fmul_rn(r, k.dst_inv);
                 o[j] = FP8 ? r : __fadd_rn(r, zs[j]);
             }
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                // distance of o from the nearest rounding boundary: 0.5 - |o - rint(o)|
-                const float tau = fmaf(inv_abs, fabsf(x[j]) + 1.f, 4e-7f * fabsf(o[j]));
-                const bool rk = fabsf(g[j]) < 9.02f && fabsf(o[j] - rintf(o[j])) > 0.5f - tau;
-                risky |= (rk ? 1u : 0u) << (hb + j);
-            }
-#pragma unroll
             for (int q = 0; q < 2; ++q) {
                 uint32_t w = 0;
 #pragma unroll
-                for (int i = 0; i < 4; ++i) w |= (is_s8 ? cvt_sat_s8(o[4 * q + i]) : cvt_sat_u8(o[4 * q + i])) << (8 * i);
+                for (int i = 0; i < 4; ++i) {
+                    const int j = 4 * q + i;
+                    const float tau = fmaf(inv_abs, fabsf(x[j]) + 1.f, 4e-7f * fabsf(o[j]));
+                    const uint32_t up = is_s8 ? cvt_sat_s8(o[j] + tau) : cvt_sat_u8(o[j] + tau);
+                    const uint32_t dn = is_s8 ? cvt_sat_s8(o[j] - tau) : cvt_sat_u8(o[j] - tau);
+                    if (up != dn) risky |= 1u << (hb + j);
+                    w |= up << (8 * i);
+                }
                 packed[hb / 4 + q] = w;
             }
         }

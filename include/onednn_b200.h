@@ -217,6 +217,12 @@ dnnl_status_t DNNL_API dnnl_cuda_interop_stream_create(dnnl_stream_t *stream, dn
 dnnl_status_t DNNL_API dnnl_cuda_interop_stream_get(dnnl_stream_t stream, void **cuda_stream);
 dnnl_status_t DNNL_API dnnl_cuda_interop_engine_get_device(dnnl_engine_t engine, int *device);
 
+/* Extension, for tests of error reporting: enqueue on the stream a kernel whose (bounded) wait
+ * cannot succeed; it gives up after at most max_polls x 100 ns and flags the stream's status
+ * word, so that the next dnnl_stream_wait returns dnnl_runtime_error (and clears the flag).
+ * No counterpart in the reference. */
+dnnl_status_t DNNL_API dnnl_b200_stream_selftest_bounded_wait(dnnl_stream_t stream, unsigned max_polls);
+
 /* ---- memory descriptors (replaces dnnl.h:826-1200; reference implementation
  *      src/common/memory_desc.cpp, memory_desc_wrapper.hpp) ----------------------- */
 dnnl_status_t DNNL_API dnnl_memory_desc_destroy(dnnl_memory_desc_t memory_desc);

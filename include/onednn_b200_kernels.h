@@ -246,6 +246,12 @@ B200_API int b200_gather_columns_launch(const void *staged, void *dst, int64_t M
 
 /* ---- utilities ----------------------------------------------------------- */
 
+/* Test hook for the bounded-wait mechanism every kernel here uses: one warp polls an
+ * mbarrier that is never completed, at most max_polls (<= 2^20) times 100 ns, then ORs
+ * B200_STATUS_SELFTEST_WAIT into *status and returns.  The context stays usable. */
+#define B200_STATUS_SELFTEST_WAIT 0x80000000u
+B200_API int b200_selftest_bounded_wait_launch(uint32_t *status, uint32_t max_polls, b200_stream_t stream);
+
 /* number of kernel launches issued by this library since load (for benchmarks) */
 B200_API uint64_t b200_launch_count(void);
 

@@ -158,6 +158,13 @@ dnnl_status_t dnnl_stream_wait(dnnl_stream_t stream) {
     return dnnl_success;
 }
 
+dnnl_status_t dnnl_b200_stream_selftest_bounded_wait(dnnl_stream_t stream, unsigned max_polls) {
+    if (!stream || !stream->status) return dnnl_invalid_arguments;
+    if (set_device(stream->engine) != dnnl_success) return dnnl_runtime_error;
+    const int rc = b200_selftest_bounded_wait_launch(stream->status, max_polls, stream->cuda_stream);
+    return rc == 0 ? dnnl_success : (rc == B200_ERR_BAD_ARG ? dnnl_invalid_arguments : dnnl_runtime_error);
+}
+
 dnnl_status_t dnnl_stream_destroy(dnnl_stream_t stream) {
     if (!stream) return dnnl_invalid_arguments;
     if (stream->engine->usable()) {

@@ -180,6 +180,35 @@ extern "C" int b200_reorder_launch(const b200_reorder_params_t *p, b200_stream_t
     return after_launch();
 }
 
+// The kernels of this library never wait without a bound: a wait that runs out ORs a code
+// into the status word and the kernel winds down.  This kernel is that mechanism on its
+// own, for tests: one warp polls an mbarrier that nothing will ever complete, at most
+// max_polls times, then reports through the status word like the matmul kernels do.
+__global__ void bounded_wait_selftest_kernel(uint32_t *status, uint32_t max_polls) {
+    __shared__ uint64_t bar;
+    const uint32_t addr = (uint32_t)__cvta_generic_to_shared(&bar);
+    if (threadIdx.x == 0) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(addr));
+    __syncwarp();
+    bool done = false;
+    for (uint32_t i = 0; i < max_polls && !done; ++i) {
+        uint32_t ok;
+        asm volatile(
+                "{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], 0;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                : "=r"(ok)
+                : "r"(addr)
+                : "memory");
+        done = ok != 0;
+        if (!done) __nanosleep(100);
+    }
+    if (!done && threadIdx.x == 0 && status) atomicOr(status, B200_STATUS_SELFTEST_WAIT);
+}
+
+extern "C" int b200_selftest_bounded_wait_launch(uint32_t *status, uint32_t max_polls, b200_stream_t stream) {
+    if (!status || max_polls == 0 || max_polls > (1u << 20)) return B200_ERR_BAD_ARG; // at most ~0.1 s
+    bounded_wait_selftest_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(status, max_polls);
+    return after_launch();
+}
+
 extern "C" uint64_t b200_launch_count(void) {
     return g_launches.load();
 }

@@ -141,3 +141,20 @@ def test_reorder_plain_and_convert(ctx):
     got = dst.read(np.int8, (53, 37)).T
     want = np.clip(np.rint(a), -128, 127).astype(np.int8)
     assert np.array_equal(got, want)
+
+
+def test_bounded_wait_reports_and_context_survives(ctx):
+    """A wait that cannot succeed gives up after its bound, the stream reports
+    dnnl_runtime_error once, and the same stream and context keep working."""
+    eng, strm = ctx
+    L = api.lib()
+    L.dnnl_b200_stream_selftest_bounded_wait.argtypes = [api.C.c_void_p, api.C.c_uint]
+    assert L.dnnl_b200_stream_selftest_bounded_wait(strm.h, 2000) == 0      # about 0.2 ms of polling
+    with pytest.raises(api.Error) as e:
+        strm.wait()
+    assert e.value.status == 5                                               # dnnl_runtime_error
+    strm.wait()                                                              # the flag was cleared
+    c = cases.build("c1_small")
+    got, impl = api.run_case(c, eng, strm)
+    want = B.run_oracle(c, tanh_mode=1, exact_acc=1)
+    assert_close(c, got, want, "after a reported wait timeout")

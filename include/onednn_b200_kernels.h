@@ -89,6 +89,7 @@ enum {
     B200_WEI_KMAJOR = 1,     /* 8-bit weights transposed to [N][Kp] (K contiguous,
                                 Kp = K rounded up to 16) followed by the s32 column
                                 sums: the tcgen05 operand layout */
+    B200_WEI_WC8_TC = 4,     /* 8-bit weights, same blocks (8 KiB), one byte per weight */
     B200_WEI_WC4_TC = 3,     /* 4-bit weights in blocks of 128 n x 64 k (4 KiB), row-major inside,
                               * for the tensor-core weight-decompression kernel (matmul_wctc.cu) */
     B200_WEI_WC4_TILED = 2   /* 4-bit weights in tiles of 16 n x 64 k (512 bytes),
@@ -187,14 +188,18 @@ B200_API size_t b200_matmul_wc_noalloc_max_bytes(void);
  * converted to bf16 in shared memory and multiplied on the tensor cores (tcgen05, f32
  * accumulation in tensor memory).  bf16 activations, u4 / s4 weights in the
  * B200_WEI_WC4_TC layout (or plain dense ab, packed into the scratch first), bf16 scales
- * (per tensor, per column or K-grouped) or none, u4 / s4 zero-points or none, K groups
- * multiples of 64.  Same semantics as b200_matmul_wc_launch
+ * (per tensor, per column or K-grouped) or none, u4 / s4 zero-points or none; or s8 / u8
+ * weights in the B200_WEI_WC8_TC layout (or plain, any strides) with f32 / bf16 / f16 scales
+ * and s8 / u8 / s32 / 4-bit zero-points.  K groups multiples of 64.  Same semantics as b200_matmul_wc_launch
  * (ref_matmul.cpp:130-233 with_wei_decompression) with each decompressed weight rounded to
  * bf16, which fpmath mode bf16 with apply_to_int permits. */
 B200_API int b200_matmul_wc_tc_launch(const b200_matmul_params_t *p, b200_stream_t stream);
 /* plain dense (K, N) 4-bit weights -> B200_WEI_WC4_TC, and the size of the result */
 B200_API int b200_wc_tc_pack_launch(const void *src, void *dst, int64_t K, int64_t N, int32_t dt, b200_stream_t stream);
-B200_API size_t b200_wc_tc_packed_bytes(int64_t K, int64_t N);
+/* plain (K, N) s8 / u8 weights with element strides sk, sn -> B200_WEI_WC8_TC */
+B200_API int b200_wc_tc_pack8_launch(const void *src, int64_t sk, int64_t sn, void *dst, int64_t K, int64_t N, int32_t dt,
+        b200_stream_t stream);
+B200_API size_t b200_wc_tc_packed_bytes(int64_t K, int64_t N, int32_t dt);
 
 /* plain dense (K, N) 4-bit weights (two per byte along N) -> B200_WEI_WC4_TILED;
  * needs K % 64 == 0 and N % 16 == 0 */

@@ -246,18 +246,18 @@ static bool accept_wc(dnnl_primitive_desc *pd) {
     if (src.ndims != 2) return reject(name, "only 2-D problems"), false;
     const int sdt = src.data_type, wdt = wei.data_type;
     if (!(sdt == dnnl_bf16 || sdt == dnnl_f16 || sdt == dnnl_f32)) return reject(name, "src must be bf16/f16/f32"), false;
-    if (!dt_is_int4(wdt) || !a.apply_to_int) return reject(name, "needs 4-bit weights with fpmath apply_to_int"), false;
+    const bool w8 = wdt == dnnl_s8 || wdt == dnnl_u8;
+    if (!(dt_is_int4(wdt) || w8) || !a.apply_to_int) return reject(name, "needs 4- or 8-bit weights with fpmath apply_to_int"), false;
     const int64_t M = src.dims[0], K = src.dims[1], N = wei.dims[1];
     if (M == 0 || N == 0 || K == 0) return reject(name, "zero dim"), false;
-    if (M > 512) return reject(name, "M too large for the decode kernel"), false;
-    if (N % 16 != 0 || K % 64 != 0) return reject(name, "needs N % 16 == 0 and K % 64 == 0"), false;
+    if ((!w8 && N % 16 != 0) || K % 64 != 0) return reject(name, "needs N % 16 == 0 and K % 64 == 0"), false;
     if (src.is_plain() && !(src.strides[1] == 1 && src.strides[0] % 8 == 0 && src.offset0 % 8 == 0))
         return reject(name, "src must be row-major with 16-byte aligned rows"), false;
     if (dst.is_plain() && dst.strides[1] != 1) return reject(name, "dst must be row-major"), false;
-    if (wei.is_plain() && !(wei.strides[1] == 1 && wei.strides[0] == N && wei.offset0 == 0))
+    if (!w8 && wei.is_plain() && !(wei.strides[1] == 1 && wei.strides[0] == N && wei.offset0 == 0))
         return reject(name, "weights must be dense ab"), false;
     if (wei.format_kind == dnnl_format_kind_opaque && wei.packed_layout != B200_WEI_WC4_TILED
-            && wei.packed_layout != B200_WEI_WC4_TC)
+            && wei.packed_layout != B200_WEI_WC4_TC && wei.packed_layout != B200_WEI_WC8_TC)
         return reject(name, "unknown packed weights layout"), false;
     if (!quant_simple(a.scale(DNNL_ARG_SRC), 0)) return reject(name, "src scales must be per-tensor"), false;
     if (!quant_simple(a.scale(DNNL_ARG_DST), 0)) return reject(name, "dst scales must be per-tensor"), false;
@@ -284,17 +284,29 @@ static bool accept_wc(dnnl_primitive_desc *pd) {
     const quant_entry_t &ws = a.scale(DNNL_ARG_WEIGHTS), &wz = a.zp(DNNL_ARG_WEIGHTS);
     bool tc = M > 32 && sdt == dnnl_bf16 && (!ws.set || ws.dt == dnnl_bf16) && (!wz.set || dt_is_int4(wz.dt))
             && !(wz.set && wz.mask == 0); // a 4-bit zero-point needs a mask (the attribute check says so too)
+    if (w8) {
+        // 8-bit weights: the tensor-core kernel for any M (there is no 8-bit decode kernel); it converts
+        // in f32, so any float scale and any integer zero-point type will do
+        tc = sdt == dnnl_bf16 && (!ws.set || ws.dt == dnnl_bf16 || ws.dt == dnnl_f16 || ws.dt == dnnl_f32)
+                && (!wz.set || dt_is_int4(wz.dt) || wz.dt == dnnl_s8 || wz.dt == dnnl_u8 || wz.dt == dnnl_s32);
+        if (!tc) return reject(name, "8-bit weights need bf16 src and float scales"), false;
+    }
     if (const char *v = std::getenv("ONEDNN_CUDA_DISABLE_IMPL"))
         if (std::string(v).find("wc_tc") != std::string::npos) tc = false;
+    if (const char *v = std::getenv("ONEDNN_CUDA_DISABLE_IMPL"))
+        if (w8 && std::string(v).find("wc_tc") != std::string::npos) return reject(name, "disabled"), false;
+    if (!tc && M > 512) return reject(name, "M too large for the decode kernel"), false;
     if (wei.format_kind == dnnl_format_kind_opaque) {
         // the layout was fixed when the weights were packed: it decides
-        if (wei.packed_layout == B200_WEI_WC4_TC && !tc) return reject(name, "weights packed for the tensor-core kernel"), false;
-        tc = wei.packed_layout == B200_WEI_WC4_TC;
+        const bool packed_tc = wei.packed_layout == B200_WEI_WC4_TC || wei.packed_layout == B200_WEI_WC8_TC;
+        if (packed_tc && !tc) return reject(name, "weights packed for the tensor-core kernel"), false;
+        if ((wei.packed_layout == B200_WEI_WC8_TC) != w8) return reject(name, "packed layout of another weight width"), false;
+        tc = packed_tc;
     }
     pd->wei = wei;
     if (wei.is_any()) {
         pd->wei.format_kind = dnnl_format_kind_opaque;
-        pd->wei.packed_layout = tc ? B200_WEI_WC4_TC : B200_WEI_WC4_TILED;
+        pd->wei.packed_layout = w8 ? B200_WEI_WC8_TC : (tc ? B200_WEI_WC4_TC : B200_WEI_WC4_TILED);
     }
     pd->impl_str = tc ? "cuda:sm100:wc_tcgen05" : "cuda:sm100:wc_gemv";
     return true;
@@ -359,7 +371,7 @@ static size_t scratch_bytes_for(const dnnl_primitive_desc *pd) {
         q.src_dt = pd->src.data_type;
         q.wei_layout = pd->wei.format_kind == dnnl_format_kind_opaque ? pd->wei.packed_layout : B200_WEI_PLAIN;
         if (pd->impl_str.find("tcgen05") != std::string::npos)
-            bytes = q.wei_layout == B200_WEI_PLAIN ? b200_wc_tc_packed_bytes(q.K, q.N) : 0; // plain weights are packed per execution
+            bytes = q.wei_layout == B200_WEI_PLAIN ? b200_wc_tc_packed_bytes(q.K, q.N, pd->wei.data_type) : 0; // plain weights are packed per execution
         else
             bytes = b200_matmul_scratch_bytes(&q, 2);
     }

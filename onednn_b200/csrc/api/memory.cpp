@@ -74,7 +74,8 @@ std::string dnnl_memory_desc::layout_str() const {
     if (is_any()) return "any";
     if (format_kind == dnnl_format_kind_opaque)
         return packed_layout == B200_WEI_KMAJOR ? "packed:kmajor_colsum"
-                : packed_layout == B200_WEI_WC4_TC ? "packed:wc4_tc" : "packed:wc4_tiled";
+                : packed_layout == B200_WEI_WC4_TC ? "packed:wc4_tc"
+                : packed_layout == B200_WEI_WC8_TC ? "packed:wc8_tc" : "packed:wc4_tiled";
     // order dims by decreasing stride and print them as letters
     std::vector<int> idx(ndims);
     for (int i = 0; i < ndims; ++i) idx[i] = i;

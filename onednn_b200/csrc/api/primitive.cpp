@@ -44,6 +44,7 @@ dnnl_status_t dnnl_reorder_primitive_desc_create(dnnl_primitive_desc_t *reorder_
         if (d.packed_layout == B200_WEI_WC4_TC
                 && !(dt_is_int4(s.data_type) && s.is_dense_row_major() && s.dims[0] % 64 == 0 && s.dims[1] % 2 == 0))
             return dnnl_unimplemented;
+        if (d.packed_layout == B200_WEI_WC8_TC && !(dt_is_int8(s.data_type) && s.dims[0] % 64 == 0)) return dnnl_unimplemented;
     } else {
         if (s.ndims > 6) return dnnl_unimplemented;
         const int sb = dt_nbits(s.data_type), db = dt_nbits(d.data_type);

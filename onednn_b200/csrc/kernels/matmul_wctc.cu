@@ -46,11 +46,13 @@ constexpr int STAGES = 4;            // operand stages; stage g belongs to warp 
 constexpr int GROUPS = STAGES;       // dequantising warp groups, each converts every fourth k-block
 constexpr int GROUP_WARPS = TN / 32; // one thread per output column of the tile
 constexpr int DQ_WARPS = GROUPS * GROUP_WARPS;
-constexpr int PFS = 4;               // k-blocks of its own that a group requests ahead (32 bytes per thread each)
-constexpr int PF_BYTES = TK / 2;     // packed bytes of one column in one k-block
+// per weight width (4 or 8 bits): packed bytes of one column in one k-block, of a whole block,
+// and the number of its own k-blocks a group requests ahead (64 KiB of ring either way)
+__host__ __device__ constexpr int pf_bytes(int wbits) { return TK * wbits / 8; }
+__host__ __device__ constexpr int block_bytes(int wbits) { return TN * TK * wbits / 8; }
+__host__ __device__ constexpr int pfs(int wbits) { return wbits == 4 ? 4 : 2; }
 constexpr int NUM_THREADS = 64 + DQ_WARPS * 32;
 constexpr int A_BYTES = TN * TK * 2; // dequantised weights tile, 16 KiB
-constexpr int BLOCK_BYTES = TN * TK / 2; // packed weights per stage, 4 KiB
 constexpr uint32_t WAIT_SPINS = 1u << 24; // polls of the drain loop
 constexpr uint32_t WAIT_TRIES = 1u << 19; // hardware-suspended waits of up to ~2 us each
 enum : uint32_t { ST_WAIT_FULL = 0x1000, ST_WAIT_EMPTY = 0x2000, ST_WAIT_ACC = 0x4000 };
@@ -75,7 +77,8 @@ struct args_t {
     uint32_t tmem_cols;
     uint32_t gs_blocks, gz_blocks; // K-group sizes of scales and zero-points in k-blocks of 64 (K / 64 when not grouped)
     uint32_t s_groups, z_groups;   // number of such groups along K
-    float nibble_offset;     // 128 (u4) or 136 (s4 stored offset by 8)
+    float nibble_offset;     // 4-bit weights: 128 (u4) or 136 (s4 stored offset by 8)
+    uint32_t byte_xor;       // 8-bit weights: 0x80808080 for s8 (to offset binary), 0 for u8
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -188,8 +191,10 @@ __device__ __noinline__ void finish_chunk(const b200_matmul_params_t &p, const u
 
 // ---- the kernel -------------------------------------------------------------------------
 
+template <int WBITS>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
         wc_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ args_t args) {
+    constexpr int PFS = pfs(WBITS), PF_BYTES = pf_bytes(WBITS), BLOCK_BYTES = block_bytes(WBITS);
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     const b200_matmul_params_t &p = args.p;
@@ -283,7 +288,6 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         const int quarter = warp & 3;       // TMEM lanes this warp may read: 32*quarter .. +31
         const int which = (warp - 2) >> 2;  // four warps share a quarter and split the chunks of columns
         const uint32_t sw = (uint32_t)(r & 7);
-        const bool zp_signed = p.wei_zp.ptr && p.wei_zp.dt == B200_DT_S4;
         const bool simple_epilogue = p.npo == 0 && !p.dst_scale.ptr && (!p.bias || p.bias_sm == 0)
                 && (p.dst_dt == B200_DT_BF16 || p.dst_dt == B200_DT_F32);
         const float src_scale = p.src_scale.ptr ? load_f32(p.src_scale.dt, p.src_scale.ptr, 0) : 1.f;
@@ -302,12 +306,13 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             const int first_kb = (int)((grp + STAGES - (uint32_t)(((uint64_t)tile_i * KB) % STAGES)) % STAGES);
             const int iters = first_kb < KB ? (KB - first_kb + STAGES - 1) / STAGES : 0;
             const uint8_t *wsrc = args.wei + ((size_t)nt * KB + first_kb) * BLOCK_BYTES + (size_t)r * PF_BYTES;
-            auto request = [&](int j) { // packed row of this thread's j-th k-block, two 16-byte copies
+            auto request = [&](int j) { // packed row of this thread's j-th k-block, 16-byte copies
                 if (j < iters) {
                     const uint8_t *src = wsrc + (size_t)j * (STAGES * BLOCK_BYTES);
                     const uint32_t dst = my_ring_s + (uint32_t)(j % PFS) * RING_STRIDE;
-                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
-                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + 16), "l"(src + 16) : "memory");
+#pragma unroll
+                    for (int q = 0; q < PF_BYTES; q += 16)
+                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + q), "l"(src + q) : "memory");
                 }
                 asm volatile("cp.async.commit_group;" ::: "memory"); // also when empty: the waits count groups
             };
@@ -315,49 +320,100 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             for (int j = 0; j < PFS; ++j) request(j);
             // scale / zero-point of the column: the raw bits for the next iteration are requested
             // while this one is converted
-            const uint16_t *sp = col_ok && p.wei_scale.ptr ? (const uint16_t *)p.wei_scale.ptr + ncol * p.wei_scale.s1 : nullptr;
-            const bool has_zp = col_ok && p.wei_zp.ptr;
-            const int64_t zbase = ncol * p.wei_zp.s1;
-            uint32_t sraw = col_ok ? 0x3f80u : 0u, zraw = 0, zshift = 0; // 1.0 (0 for padding columns), zero-point 0
+            const bool has_s = col_ok && p.wei_scale.ptr, has_zp = col_ok && p.wei_zp.ptr;
+            const int64_t sbase = ncol * p.wei_scale.s1, zbase = ncol * p.wei_zp.s1;
+            uint32_t sraw = 0, zraw = 0, zshift = 0;
             auto load_q = [&](int kb) {
                 if (kb >= KB) return;
-                if (sp) sraw = sp[(int64_t)((uint32_t)kb / args.gs_blocks) * p.wei_scale.s0];
+                if (has_s) {
+                    const int64_t e = (int64_t)((uint32_t)kb / args.gs_blocks) * p.wei_scale.s0 + sbase;
+                    sraw = p.wei_scale.dt == B200_DT_F32 ? ((const uint32_t *)p.wei_scale.ptr)[e] : ((const uint16_t *)p.wei_scale.ptr)[e];
+                }
                 if (has_zp) {
                     const int64_t e = (int64_t)((uint32_t)kb / args.gz_blocks) * p.wei_zp.s0 + zbase;
-                    zraw = ((const uint8_t *)p.wei_zp.ptr)[e >> 1];
-                    zshift = (uint32_t)(e & 1) * 4;
+                    if (p.wei_zp.dt == B200_DT_S32) {
+                        zraw = ((const uint32_t *)p.wei_zp.ptr)[e];
+                    } else if (p.wei_zp.dt == B200_DT_S8 || p.wei_zp.dt == B200_DT_U8) {
+                        zraw = ((const uint8_t *)p.wei_zp.ptr)[e];
+                    } else { // u4 / s4: the byte that holds the nibble
+                        zraw = ((const uint8_t *)p.wei_zp.ptr)[e >> 1];
+                        zshift = (uint32_t)(e & 1) * 4;
+                    }
                 }
+            };
+            auto scale_f32 = [&]() -> float { // of the bits load_q fetched
+                if (!col_ok) return 0.f;      // padding columns convert to zeros
+                if (!has_s) return 1.f;
+                if (p.wei_scale.dt == B200_DT_F32) return __uint_as_float(sraw);
+                if (p.wei_scale.dt == B200_DT_BF16) return __uint_as_float(sraw << 16);
+                return __half2float(__ushort_as_half((unsigned short)sraw));
+            };
+            auto zp_int = [&]() -> int {
+                if (!has_zp) return 0;
+                if (p.wei_zp.dt == B200_DT_S32) return (int)zraw;
+                if (p.wei_zp.dt == B200_DT_S8) return (int)(int8_t)zraw;
+                if (p.wei_zp.dt == B200_DT_U8) return (int)zraw;
+                const int z = (int)((zraw >> zshift) & 0xf);
+                return p.wei_zp.dt == B200_DT_S4 ? (z ^ 8) - 8 : z;
             };
             load_q(first_kb);
             for (int j = 0; j < iters; ++j, ++uses) {
                 const int kb = first_kb + j * STAGES;
                 // decode this block's scale and zero-point, then ask for the next block's
-                const uint32_t sb = sraw | (sraw << 16);
-                const __nv_bfloat162 sc = *reinterpret_cast<const __nv_bfloat162 *>(&sb);
-                int zp = (int)((zraw >> zshift) & 0xf);
-                if (zp_signed) zp = (zp ^ 8) - 8;
-                const __nv_bfloat162 cc = __float2bfloat162_rn(args.nibble_offset + (float)zp); // exact: an integer below 256
+                const float sf = scale_f32();
+                const int zpi = zp_int();
                 load_q(kb + STAGES);
                 asm volatile("cp.async.wait_group %0;" ::"n"(PFS - 1) : "memory"); // this thread's j-th row has landed
-                const uint4 w0 = *reinterpret_cast<const uint4 *>(my_ring + (size_t)(j % PFS) * RING_STRIDE);
-                const uint4 w1 = *reinterpret_cast<const uint4 *>(my_ring + (size_t)(j % PFS) * RING_STRIDE + 16);
+                const uint4 *slot = reinterpret_cast<const uint4 *>(my_ring + (size_t)(j % PFS) * RING_STRIDE);
+                uint32_t words[PF_BYTES / 4];
+#pragma unroll
+                for (int q = 0; q < PF_BYTES / 16; ++q) {
+                    const uint4 t4 = slot[q];
+                    words[4 * q] = t4.x, words[4 * q + 1] = t4.y, words[4 * q + 2] = t4.z, words[4 * q + 3] = t4.w;
+                }
                 if (!(ok = mbar_wait(&ctrl->empty[grp], (uses & 1) ^ 1, ctrl, p.status, ST_WAIT_EMPTY))) {
                     asm volatile("cp.async.wait_group 0;" ::: "memory");
                     break;
                 }
-                const uint32_t words[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+                if (WBITS == 4) {
+                    // bf16 arithmetic: (128 + q) - (128 + zp) is exact, the product with the bf16 scale is
+                    // rounded once: the bf16 rounding of the reference's f32 (q - zp) * scale
+                    const __nv_bfloat162 sc = __float2bfloat162_rn(sf);                                // exact: the scale is bf16
+                    const __nv_bfloat162 cc = __float2bfloat162_rn(args.nibble_offset + (float)zpi);   // exact: an integer below 256
 #pragma unroll
-                for (int c = 0; c < 8; ++c) { // 16-byte chunk c of the row: k 8c .. 8c + 7
-                    const uint32_t v = words[c];
-                    uint32_t o[4];
+                    for (int c = 0; c < 8; ++c) { // 16-byte chunk c of the row: k 8c .. 8c + 7
+                        const uint32_t v = words[c];
+                        uint32_t o[4];
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const uint32_t bits = ((v >> (4 * i)) & 0x000f000fu) | 0x43004300u; // (128 + q, 128 + q')
-                        __nv_bfloat162 x = *reinterpret_cast<const __nv_bfloat162 *>(&bits);
-                        x = __hmul2(__hsub2(x, cc), sc); // (q - zp) exactly, then one rounding of the product
-                        o[i] = *reinterpret_cast<const uint32_t *>(&x);
+                        for (int i = 0; i < 4; ++i) {
+                            const uint32_t bits = ((v >> (4 * i)) & 0x000f000fu) | 0x43004300u; // (128 + q, 128 + q')
+                            __nv_bfloat162 x = *reinterpret_cast<const __nv_bfloat162 *>(&bits);
+                            x = __hmul2(__hsub2(x, cc), sc);
+                            o[i] = *reinterpret_cast<const uint32_t *>(&x);
+                        }
+                        *reinterpret_cast<uint4 *>(tile_a + (((uint32_t)c ^ sw) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
                     }
-                    *reinterpret_cast<uint4 *>(tile_a + (((uint32_t)c ^ sw) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+                } else {
+                    // f32 arithmetic: byte b (s8 as offset binary) inside the float 2^23 + b, minus
+                    // 2^23 + offset + zp is (q - zp) exactly; times the scale in f32 as the reference
+                    // does; then one rounding to bf16
+                    const float cf = 8388608.f + (args.byte_xor ? 128.f : 0.f) + (float)zpi;
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) { // 16-byte chunk c of the row: k 8c .. 8c + 7 = two words of four bytes
+                        uint32_t o[4];
+#pragma unroll
+                        for (int hw = 0; hw < 2; ++hw) {
+                            const uint32_t v = words[2 * c + hw] ^ args.byte_xor;
+                            float f[4];
+#pragma unroll
+                            for (int i = 0; i < 4; ++i)
+                                f[i] = (__uint_as_float(__byte_perm(v, 0x4B000000u, 0x7540u + i)) - cf) * sf;
+                            const __nv_bfloat162 lo = __floats2bfloat162_rn(f[0], f[1]), hi = __floats2bfloat162_rn(f[2], f[3]);
+                            o[2 * hw] = *reinterpret_cast<const uint32_t *>(&lo);
+                            o[2 * hw + 1] = *reinterpret_cast<const uint32_t *>(&hi);
+                        }
+                        *reinterpret_cast<uint4 *>(tile_a + (((uint32_t)c ^ sw) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+                    }
                 }
                 // generic-proxy writes -> visible to the tensor core's (async proxy) reads
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -420,6 +476,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 // 32-bit output word (8 consecutive k of one column).
 __global__ void __launch_bounds__(256) wc_tc_pack_kernel(const uint8_t *__restrict__ src, uint32_t *__restrict__ dst,
         int64_t K, int64_t N, int is_signed) {
+    constexpr int BLOCK_BYTES = block_bytes(4);
     const int64_t KB = K / TK, n_tiles = (N + TN - 1) / TN;
     const int64_t nwords = n_tiles * KB * (BLOCK_BYTES / 4);
     for (int64_t wi = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; wi < nwords; wi += (int64_t)gridDim.x * blockDim.x) {
@@ -440,6 +497,22 @@ __global__ void __launch_bounds__(256) wc_tc_pack_kernel(const uint8_t *__restri
             }
         }
         dst[wi] = word;
+    }
+}
+
+// plain (K, N) 8-bit weights, any strides -> B200_WEI_WC8_TC: blocks of 128 columns x 64 k,
+// row-major [128][64] bytes inside (k contiguous), columns past N zero.  One thread per byte.
+__global__ void __launch_bounds__(256) wc_tc_pack8_kernel(const uint8_t *__restrict__ src, int64_t sk, int64_t sn,
+        uint8_t *__restrict__ dst, int64_t K, int64_t N) {
+    constexpr int BLOCK_BYTES = block_bytes(8);
+    const int64_t KB = K / TK, n_tiles = (N + TN - 1) / TN;
+    const int64_t total = n_tiles * KB * BLOCK_BYTES;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t block = i / BLOCK_BYTES;
+        const int in_block = (int)(i % BLOCK_BYTES);
+        const int r = in_block / TK, kk = in_block % TK;
+        const int64_t n = (block / KB) * TN + r, k = (block % KB) * TK + kk;
+        dst[i] = n < N ? src[k * sk + n * sn] : (uint8_t)0;
     }
 }
 
@@ -468,15 +541,29 @@ static wctc_encode_fn wctc_get_encode_fn() {
 
 static inline size_t wctc_align256(size_t x) { return (x + 255) / 256 * 256; }
 
-extern "C" size_t b200_wc_tc_packed_bytes(int64_t K, int64_t N) {
+extern "C" size_t b200_wc_tc_packed_bytes(int64_t K, int64_t N, int32_t dt) {
     if (K <= 0 || N <= 0) return 0;
-    return (size_t)((N + TN - 1) / TN) * (size_t)(K / TK) * BLOCK_BYTES;
+    const int bits = dt_bits(dt);
+    if (bits != 4 && bits != 8) return 0;
+    return (size_t)((N + TN - 1) / TN) * (size_t)(K / TK) * (size_t)block_bytes(bits);
+}
+
+extern "C" int b200_wc_tc_pack8_launch(const void *src, int64_t sk, int64_t sn, void *dst, int64_t K, int64_t N, int32_t dt,
+        b200_stream_t stream) {
+    if (!src || !dst) return B200_ERR_BAD_ARG;
+    if ((dt != B200_DT_U8 && dt != B200_DT_S8) || K % TK != 0) return B200_ERR_UNSUPPORTED;
+    const int64_t total = (int64_t)b200_wc_tc_packed_bytes(K, N, dt);
+    if (total == 0) return 0;
+    int64_t blocks = (total + 255) / 256;
+    if (blocks > 148 * 32) blocks = 148 * 32;
+    wc_tc_pack8_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>((const uint8_t *)src, sk, sn, (uint8_t *)dst, K, N);
+    return after_launch();
 }
 
 extern "C" int b200_wc_tc_pack_launch(const void *src, void *dst, int64_t K, int64_t N, int32_t dt, b200_stream_t stream) {
     if (!src || !dst) return B200_ERR_BAD_ARG;
     if ((dt != B200_DT_U4 && dt != B200_DT_S4) || K % TK != 0 || (N & 1)) return B200_ERR_UNSUPPORTED;
-    const int64_t nwords = (int64_t)(b200_wc_tc_packed_bytes(K, N) / 4);
+    const int64_t nwords = (int64_t)(b200_wc_tc_packed_bytes(K, N, dt) / 4);
     if (nwords == 0) return 0;
     int64_t blocks = (nwords + 255) / 256;
     if (blocks > 148 * 16) blocks = 148 * 16;
@@ -488,23 +575,31 @@ extern "C" int b200_wc_tc_pack_launch(const void *src, void *dst, int64_t K, int
 extern "C" int b200_matmul_wc_tc_launch(const b200_matmul_params_t *p, b200_stream_t stream) {
     if (!p || !p->src || !p->wei || !p->dst) return B200_ERR_BAD_ARG;
     if (p->M <= 0 || p->N <= 0 || p->K <= 0) return p->M < 0 || p->N < 0 || p->K < 0 ? B200_ERR_BAD_ARG : 0;
-    if (p->wei_dt != B200_DT_U4 && p->wei_dt != B200_DT_S4) return B200_ERR_UNSUPPORTED;
+    const int wbits = dt_bits(p->wei_dt);
+    const bool w4 = p->wei_dt == B200_DT_U4 || p->wei_dt == B200_DT_S4, w8 = p->wei_dt == B200_DT_U8 || p->wei_dt == B200_DT_S8;
+    if (!w4 && !w8) return B200_ERR_UNSUPPORTED;
     if (!p->apply_to_int || p->src_dt != B200_DT_BF16) return B200_ERR_UNSUPPORTED;
-    if (p->K % TK != 0 || (p->N & 1) || p->src_sk != 1 || p->dst_sn != 1 || p->n_dst_peers) return B200_ERR_UNSUPPORTED;
+    if (p->K % TK != 0 || (w4 && (p->N & 1)) || p->src_sk != 1 || p->dst_sn != 1 || p->n_dst_peers) return B200_ERR_UNSUPPORTED;
     if (p->M > INT32_MAX || p->N > INT32_MAX || p->K > INT32_MAX) return B200_ERR_TOO_LARGE;
-    if (p->wei_layout == B200_WEI_PLAIN && !(p->wei_sn == 1 && p->wei_sk == p->N)) return B200_ERR_UNSUPPORTED;
-    if (p->wei_layout != B200_WEI_PLAIN && p->wei_layout != B200_WEI_WC4_TC) return B200_ERR_UNSUPPORTED;
+    if (w4 && p->wei_layout == B200_WEI_PLAIN && !(p->wei_sn == 1 && p->wei_sk == p->N)) return B200_ERR_UNSUPPORTED;
+    if (p->wei_layout != B200_WEI_PLAIN && p->wei_layout != (w4 ? B200_WEI_WC4_TC : B200_WEI_WC8_TC)) return B200_ERR_UNSUPPORTED;
     if (p->src_zp.ptr || p->dst_zp.ptr) return B200_ERR_UNSUPPORTED;
     if (p->src_scale.ptr && (p->src_scale.s0 || p->src_scale.s1)) return B200_ERR_UNSUPPORTED;
-    // the conversion multiplies in bf16: the scale must be bf16 to begin with, and 128 + zero-point
-    // must be exact in bf16, which 4-bit zero-points guarantee
+    // 4-bit weights are converted with bf16 arithmetic: the scale must be bf16 to begin with, and
+    // 128 + zero-point must be exact in bf16, which 4-bit zero-points guarantee.  8-bit weights
+    // are converted in f32: any float scale, any integer zero-point.
     int64_t gs = p->K, gz = p->K;
     if (p->wei_scale.ptr) {
-        if (p->wei_scale.dt != B200_DT_BF16 || p->wei_scale.g1 != 1) return B200_ERR_UNSUPPORTED;
+        const int sdt = p->wei_scale.dt;
+        if (w4 ? sdt != B200_DT_BF16 : (sdt != B200_DT_BF16 && sdt != B200_DT_F16 && sdt != B200_DT_F32)) return B200_ERR_UNSUPPORTED;
+        if (p->wei_scale.g1 != 1) return B200_ERR_UNSUPPORTED;
         if (p->wei_scale.s0) gs = p->wei_scale.g0;
     }
     if (p->wei_zp.ptr) {
-        if ((p->wei_zp.dt != B200_DT_U4 && p->wei_zp.dt != B200_DT_S4) || p->wei_zp.g1 != 1) return B200_ERR_UNSUPPORTED;
+        const int zdt = p->wei_zp.dt;
+        const bool z4 = zdt == B200_DT_U4 || zdt == B200_DT_S4;
+        if (w4 ? !z4 : !(z4 || zdt == B200_DT_S8 || zdt == B200_DT_U8 || zdt == B200_DT_S32)) return B200_ERR_UNSUPPORTED;
+        if (p->wei_zp.g1 != 1) return B200_ERR_UNSUPPORTED;
         if (p->wei_zp.s0) gz = p->wei_zp.g0;
     }
     if (gs % TK || gz % TK || p->K % gs || p->K % gz) return B200_ERR_UNSUPPORTED;
@@ -514,9 +609,10 @@ extern "C" int b200_matmul_wc_tc_launch(const b200_matmul_params_t *p, b200_stre
     cudaStream_t cs = (cudaStream_t)stream;
     const void *wei = p->wei;
     if (p->wei_layout == B200_WEI_PLAIN) {
-        const size_t need = wctc_align256(b200_wc_tc_packed_bytes(p->K, p->N));
+        const size_t need = wctc_align256(b200_wc_tc_packed_bytes(p->K, p->N, p->wei_dt));
         if (!p->scratch || p->scratch_bytes < need) return B200_ERR_BAD_ARG;
-        int rc = b200_wc_tc_pack_launch(p->wei, p->scratch, p->K, p->N, p->wei_dt, stream);
+        int rc = w4 ? b200_wc_tc_pack_launch(p->wei, p->scratch, p->K, p->N, p->wei_dt, stream)
+                    : b200_wc_tc_pack8_launch(p->wei, p->wei_sk, p->wei_sn, p->scratch, p->K, p->N, p->wei_dt, stream);
         if (rc) return rc;
         wei = p->scratch;
     }
@@ -536,6 +632,7 @@ extern "C" int b200_matmul_wc_tc_launch(const b200_matmul_params_t *p, b200_stre
     a.s_groups = (uint32_t)(p->K / gs);
     a.z_groups = (uint32_t)(p->K / gz);
     a.nibble_offset = p->wei_dt == B200_DT_S4 ? 136.f : 128.f;
+    a.byte_xor = p->wei_dt == B200_DT_S8 ? 0x80808080u : 0u;
     a.tmem_cols = 32;
     while ((int)a.tmem_cols < a.nb) a.tmem_cols *= 2;
     // instruction descriptor: D f32, A and B bf16, both K-major, N = nb, M = 128
@@ -562,17 +659,20 @@ extern "C" int b200_matmul_wc_tc_launch(const b200_matmul_params_t *p, b200_stre
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     const int64_t tiles = (int64_t)a.n_tiles * a.m_passes;
     const unsigned grid = (unsigned)(tiles < sms ? tiles : sms);
-    const size_t smem = 1024 + (size_t)STAGES * (A_BYTES + (size_t)a.nb * TK * 2) + (size_t)PFS * DQ_WARPS * 32 * PF_BYTES + sizeof(ctrl_t);
+    const size_t smem = 1024 + (size_t)STAGES * (A_BYTES + (size_t)a.nb * TK * 2)
+            + (size_t)pfs(wbits) * DQ_WARPS * 32 * pf_bytes(wbits) + sizeof(ctrl_t);
     static std::mutex mu;
     static bool attr_done[64] = {};
     {
         std::lock_guard<std::mutex> g(mu);
         if (dev < 64 && !attr_done[dev]) {
-            const cudaError_t e = cudaFuncSetAttribute(wc_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+            cudaError_t e = cudaFuncSetAttribute(wc_tc_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+            if (e == cudaSuccess) e = cudaFuncSetAttribute(wc_tc_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
             if (e != cudaSuccess) return (int)e;
             attr_done[dev] = true;
         }
     }
-    wc_tc_kernel<<<grid, NUM_THREADS, smem, cs>>>(tx, a);
+    if (w4) wc_tc_kernel<4><<<grid, NUM_THREADS, smem, cs>>>(tx, a);
+    else wc_tc_kernel<8><<<grid, NUM_THREADS, smem, cs>>>(tx, a);
     return after_launch();
 }

@@ -110,7 +110,7 @@ extern "C" size_t b200_packed_colsum_offset(int64_t K, int64_t N, int32_t dt) {
 
 extern "C" size_t b200_packed_weights_bytes(int64_t K, int64_t N, int32_t dt, int32_t layout) {
     if (layout == B200_WEI_KMAJOR) return b200_packed_colsum_offset(K, N, dt) + align256((size_t)N * sizeof(int32_t));
-    if (layout == B200_WEI_WC4_TC) return b200_wc_tc_packed_bytes(K, N);
+    if (layout == B200_WEI_WC4_TC || layout == B200_WEI_WC8_TC) return b200_wc_tc_packed_bytes(K, N, dt);
     return (size_t)((K * N * dt_bits(dt) + 7) / 8);
 }
 
@@ -153,6 +153,10 @@ extern "C" int b200_reorder_launch(const b200_reorder_params_t *p, b200_stream_t
         if (p->src_dt == B200_DT_S8 || p->src_dt == B200_DT_U8)
             return b200_colsum_launch(p->src, p->src_dt, p->K, p->N, p->src_sk, p->src_sn, colsum, stream);
         return cudaMemsetAsync(colsum, 0, (size_t)p->N * sizeof(int32_t), cs) == cudaSuccess ? 0 : (int)cudaGetLastError();
+    }
+    if (p->dst_layout == B200_WEI_WC8_TC) {
+        if (p->src_dt != p->dst_dt) return B200_ERR_UNSUPPORTED;
+        return b200_wc_tc_pack8_launch(p->src, p->src_sk, p->src_sn, p->dst, p->K, p->N, p->src_dt, stream);
     }
     if (p->dst_layout == B200_WEI_WC4_TC) {
         if (p->src_dt != p->dst_dt || p->src_sn != 1 || p->src_sk != p->N) return B200_ERR_UNSUPPORTED;

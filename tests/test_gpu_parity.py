@@ -66,6 +66,11 @@ def test_dispatched_kernel(ctx, name, weights):
     got = plan.result()
     # the tensor-core kernel sums the products exactly in s32 and scales once
     want = B.run_oracle(c, tanh_mode=1, exact_acc=1 if "tcgen05_i8" in plan.impl else 0)
+    if "wc_tcgen05" in plan.impl:
+        # this kernel rounds every decompressed weight to bf16 (fpmath bf16 permits it): the error
+        # of a sum is about 1e-3 of the sum's typical size whatever the element's own value, so the
+        # absolute part of the tolerance is 1e-2 of the root-mean-square output
+        c.atol = max(c.atol, 1e-2 * float(np.sqrt(np.mean(dt.to_f32(want, c.dst_dt).astype(np.float64) ** 2))))
     assert_close(c, got, want, "%s via %s" % (name, plan.impl))
 
 

@@ -15,7 +15,7 @@
 // rows rounded up to 16), accumulating in TMEM over the whole K.  The epilogue reads TMEM
 // with one output column per lane, so that stores of a dst row are coalesced.
 //
-//   warp 0        TMA producer (activations)           waits empty[s]   -> full_b[s] (tx bytes)
+//   warp 0        TMA producer (activations)           waits empty[s]   -> full_a[s] (tx bytes)
 //   warp 1        TMEM owner and MMA issuer            waits full_a/b   -> empty[s], acc_full
 //   warps 2..17   four dequantising groups (group g    waits empty[g]   -> full_a[g]; acc_full -> acc_empty
 //                 owns stage g), then the epilogue
@@ -209,8 +209,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < STAGES; ++s) {
-            mbar_init(&ctrl->full_a[s], GROUP_WARPS);
-            mbar_init(&ctrl->full_b[s], 1);
+            mbar_init(&ctrl->full_a[s], GROUP_WARPS + 1); // the group's warps and the activations' copy
+            mbar_init(&ctrl->full_b[s], 1);                // unused
             mbar_init(&ctrl->empty[s], 1);
         }
         mbar_init(&ctrl->acc_full, 1);
@@ -240,8 +240,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                 for (int kb = 0; kb < KB; ++kb, ++it) {
                     const uint32_t s = it % STAGES, r = it / STAGES;
                     if (!(ok = mbar_wait(&ctrl->empty[s], (r & 1) ^ 1, ctrl, p.status, ST_WAIT_EMPTY))) break;
-                    mbar_expect_tx(&ctrl->full_b[s], b_bytes);
-                    tma_load_2d(smem + (size_t)s * stage_bytes + A_BYTES, &tmap_x, kb * (TK * 2), row0, &ctrl->full_b[s]); // byte coordinates
+                    mbar_expect_tx(&ctrl->full_a[s], b_bytes);
+                    tma_load_2d(smem + (size_t)s * stage_bytes + A_BYTES, &tmap_x, kb * (TK * 2), row0, &ctrl->full_a[s]); // byte coordinates
                 }
             }
             // drain: every copy this thread issued must have landed before the CTA may exit
@@ -249,7 +249,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             for (uint32_t j = issued > STAGES ? issued - STAGES : 0; j < issued; ++j) {
                 const uint32_t s = j % STAGES, r = j / STAGES;
                 for (uint32_t i = 0; i < WAIT_SPINS; ++i) {
-                    if (mbar_test(&ctrl->full_b[s], r & 1)) break;
+                    if (mbar_test(&ctrl->full_a[s], r & 1)) break;
                     __nanosleep(64);
                 }
             }
@@ -259,16 +259,17 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         if (lane == 0) {
             uint32_t it = 0, tile_i = 0;
             bool ok = true;
+            // descriptors of stage 0; a stage further on is stage_bytes / 16 more in the address field
+            const uint64_t adesc0 = make_smem_desc(smem_u32(smem)), bdesc0 = make_smem_desc(smem_u32(smem) + A_BYTES);
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tile_i) {
                 if (!(ok = mbar_wait(&ctrl->acc_empty, (tile_i & 1) ^ 1, ctrl, p.status, ST_WAIT_ACC))) break;
                 tc_fence_after();
                 for (int kb = 0; kb < KB; ++kb, ++it) {
                     const uint32_t s = it % STAGES, r = it / STAGES;
+                    // one barrier per stage: converted weights (four warps) and activations (copy bytes)
                     if (!(ok = mbar_wait(&ctrl->full_a[s], r & 1, ctrl, p.status, ST_WAIT_FULL))) break;
-                    if (!(ok = mbar_wait(&ctrl->full_b[s], r & 1, ctrl, p.status, ST_WAIT_FULL))) break;
                     tc_fence_after();
-                    const uint32_t sa = smem_u32(smem + (size_t)s * stage_bytes);
-                    const uint64_t adesc = make_smem_desc(sa), bdesc = make_smem_desc(sa + A_BYTES);
+                    const uint64_t adesc = adesc0 + (uint64_t)(s * (stage_bytes >> 4)), bdesc = bdesc0 + (uint64_t)(s * (stage_bytes >> 4));
 #pragma unroll
                     for (int k = 0; k < TK / 16; ++k) // 16 bf16 = 32 bytes of K per instruction: +2 in 16-byte units
                         tc_mma_bf16(tmem_base, adesc + 2 * k, bdesc + 2 * k, args.idesc, (kb | k) != 0);

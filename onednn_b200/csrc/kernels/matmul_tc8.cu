@@ -650,6 +650,8 @@ __global__ void __launch_bounds__(640, 1) matmul_tc8_kernel(const __grid_constan
         if (lane == 0) {
             uint32_t it = 0, tile_i = 0;
             bool ok = true;
+            // descriptors of stage 0; a stage further on is STAGE_BYTES / 16 more in the address field
+            const uint64_t adesc0 = make_smem_desc(smem_u32(smem)), bdesc0 = make_smem_desc(smem_u32(smem) + A_BYTES);
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tile_i) {
                 const uint32_t a = tile_i & 1, use = tile_i >> 1;
                 if (!(ok = mbar_wait(&ctrl->tmem_empty[a], (use & 1) ^ 1, ctrl, p.status, ST_WAIT_TMEM_EMPTY))) break;
@@ -659,8 +661,7 @@ __global__ void __launch_bounds__(640, 1) matmul_tc8_kernel(const __grid_constan
                     const uint32_t s = it % STAGES, r = it / STAGES;
                     if (!(ok = mbar_wait(&ctrl->full[s], r & 1, ctrl, p.status, ST_WAIT_FULL))) break;
                     tcgen05_fence_after();
-                    const uint32_t sa = smem_u32(smem + (size_t)s * STAGE_BYTES);
-                    const uint64_t adesc = make_smem_desc(sa), bdesc = make_smem_desc(sa + A_BYTES);
+                    const uint64_t adesc = adesc0 + (uint64_t)(s * (STAGE_BYTES >> 4)), bdesc = bdesc0 + (uint64_t)(s * (STAGE_BYTES >> 4));
 #pragma unroll
                     for (int k = 0; k < BK / 32; ++k) // 32 bytes of K per instruction: +2 in 16-byte units
                         tcgen05_mma<FP8>(tmem_d, adesc + 2 * k, bdesc + 2 * k, args.idesc, (kb | k) != 0);

@@ -67,12 +67,13 @@ struct smem_ctrl_t {
     // per epilogue warp: per-column vectors of its half of the current tile
     // (16-byte aligned: the epilogue reads these four columns at a time)
     alignas(16) float wscale[EPI_WARPS][EPI_COLS];   // weights scale, 1 when unset
+    alignas(16) float wsx[EPI_WARPS][EPI_COLS];      // src scale x weights scale (approximate paths only)
     alignas(16) float bias[EPI_WARPS][EPI_COLS];     // bias, -0 when unset (x + -0 == x for every x)
     alignas(16) int32_t comp[EPI_WARPS][EPI_COLS];   // zp_src * colsum_W[n], 0 when unset
     alignas(16) float zp[EPI_WARPS][EPI_COLS];       // destination zero-point addend
 };
 
-static_assert(offsetof(smem_ctrl_t, wscale) % 16 == 0 && offsetof(smem_ctrl_t, bias) % 16 == 0
+static_assert(offsetof(smem_ctrl_t, wscale) % 16 == 0 && offsetof(smem_ctrl_t, wsx) % 16 == 0 && offsetof(smem_ctrl_t, bias) % 16 == 0
                 && offsetof(smem_ctrl_t, comp) % 16 == 0 && offsetof(smem_ctrl_t, zp) % 16 == 0,
         "per-column vectors are read with 128-bit loads");
 static_assert((EPI_COLS * sizeof(float)) % 16 == 0 && (CH * sizeof(float)) % 16 == 0, "chunk offsets keep the alignment");
@@ -222,6 +223,15 @@ struct epi_consts_t {
 // the exact gelu_tanh, kept out of line: it is needed for about one element in ten thousand
 // and would otherwise sit in the middle of the hot epilogue code
 __device__ __noinline__ float gelu_tanh_exact(float x) { return gelu_tanh_f32(x); }
+
+// 1 / (exp(2a) + 1) by ex2.approx / rcp.approx: tanh(a) = 1 - 2r with absolute error below 1e-6
+// on the whole range, 0 and 1 at the far ends
+__device__ __forceinline__ float sigmoid_neg2_fast(float a) {
+    float e, r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(a * 2.885390081777927f));
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(e + 1.f));
+    return r;
+}
 
 // tanh by ex2.approx / rcp.approx: absolute error below 1e-6 on the whole range
 __device__ __forceinline__ float tanh_fast(float a) {
@@ -379,7 +389,7 @@ enum { SUM_NONE = 0, SUM_8BIT = 1, SUM_OTHER = 2 };
 
 template <bool FP8, int EPI, int SUM, bool PEERS>
 __device__ __forceinline__ void epilogue_chunk(const b200_matmul_params_t &p, const uint32_t (&v)[CH], int64_t m,
-        int64_t n0, const float *wscale, const float *bias, const int32_t *comp, const float *zp, const epi_consts_t &k,
+        int64_t n0, const float *wscale, const float *wsx, const float *bias, const int32_t *comp, const float *zp, const epi_consts_t &k,
         uint32_t taddr, int lane, uint4 old_raw, bool old_prefetched) {
     const int64_t nvalid = m < p.M ? (p.N - n0 < CH ? p.N - n0 : CH) : 0;
     char *drow = (char *)p.dst + (size_t)((m < p.M ? m : 0) * p.dst_sm + n0) * (dt_bits(p.dst_dt) / 8);
@@ -451,6 +461,7 @@ __device__ __forceinline__ void epilogue_chunk(const b200_matmul_params_t &p, co
         const float sum_zp = SUM != SUM_NONE ? (float)p.po[1].zero_point : 0.f;
         const float inv_abs = 2e-6f * fabsf(k.dst_inv) * fabsf(elt_scale);
         const bool is_s8 = p.dst_dt == B200_DT_S8;
+        const float tau0 = inv_abs + 4e-7f * (is_s8 ? 130.f : 258.f);
         static_assert(CH == 16, "four packed words per chunk");
         uint32_t packed[4];
         uint32_t risky = 0;
@@ -459,26 +470,25 @@ __device__ __forceinline__ void epilogue_chunk(const b200_matmul_params_t &p, co
             float x[8], g[8], t[8], o[8];
 #pragma unroll
             for (int q = 0; q < 2; ++q) {
-                const float4 a = ((const float4 *)wscale)[hb / 4 + q], b = ((const float4 *)bias)[hb / 4 + q];
+                const float4 a = ((const float4 *)wsx)[hb / 4 + q], b = ((const float4 *)bias)[hb / 4 + q];
                 const int4 c = ((const int4 *)comp)[hb / 4 + q];
                 const float ws[4] = {a.x, a.y, a.z, a.w}, bs[4] = {b.x, b.y, b.z, b.w};
                 const int cs[4] = {c.x, c.y, c.z, c.w};
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     const float acc = FP8 ? __uint_as_float(v[hb + 4 * q + i]) : (float)((int)v[hb + 4 * q + i] - cs[i]);
-                    x[4 * q + i] = fmaf(acc * k.src_scale, ws[i], bs[i]); // within 2 ulp of the reference's unfused value
+                    x[4 * q + i] = fmaf(acc, ws[i], bs[i]); // within 2 ulp of the reference's unfused value
                 }
             }
 #pragma unroll
             for (int j = 0; j < 8; ++j) g[j] = x[j] * fmaf(g_cub, x[j] * x[j], g_lin);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) t[j] = tanh_fast(g[j]);
+            for (int j = 0; j < 8; ++j) t[j] = sigmoid_neg2_fast(g[j]); // r = 1 / (exp(2g) + 1): tanh(g) = 1 - 2r
             const float4 z0 = ((const float4 *)zp)[hb / 4], z1 = ((const float4 *)zp)[hb / 4 + 1];
             const float zs[8] = {z0.x, z0.y, z0.z, z0.w, z1.x, z1.y, z1.z, z1.w};
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
-                const float h = 0.5f * x[j];
-                const float gelu = fmaf(h, t[j], h);
+                const float gelu = fmaf(-x[j], t[j], x[j]); // 0.5 x (1 + tanh) = x - x r
                 float r = __fmul_rn(gelu, elt_scale);
                 if (SUM != SUM_NONE) r = __fadd_rn(r, __fmul_rn(sum_scale, __fsub_rn(old_val(hb + j), sum_zp)));
                 r = __fmul_rn(r, k.dst_inv);
@@ -490,7 +500,9 @@ __device__ __forceinline__ void epilogue_chunk(const b200_matmul_params_t &p, co
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     const int j = 4 * q + i;
-                    const float tau = fmaf(inv_abs, fabsf(x[j]) + 1.f, 4e-7f * fabsf(o[j]));
+                    // the part of the bound that grows with |o| is taken at the edge of the destination
+                    // type's range: beyond it both conversions saturate whatever tau is
+                    const float tau = fmaf(inv_abs, fabsf(x[j]), tau0);
                     const uint32_t up = is_s8 ? cvt_sat_s8(o[j] + tau) : cvt_sat_u8(o[j] + tau);
                     const uint32_t dn = is_s8 ? cvt_sat_s8(o[j] - tau) : cvt_sat_u8(o[j] - tau);
                     if (up != dn) risky |= 1u << (hb + j);
@@ -675,7 +687,7 @@ __global__ void __launch_bounds__(640, 1) matmul_tc8_kernel(const __grid_constan
         const int ew = warp - 2;           // 0..15
         const int quarter = warp & 3;      // TMEM lanes this warp may read: 32*quarter .. +31
         const int half = ew >> 2;          // which quarter of the tile's columns this warp converts
-        float *wscale = ctrl->wscale[ew], *bias = ctrl->bias[ew], *zpv = ctrl->zp[ew];
+        float *wscale = ctrl->wscale[ew], *wsx = ctrl->wsx[ew], *bias = ctrl->bias[ew], *zpv = ctrl->zp[ew];
         int32_t *comp = ctrl->comp[ew];
         const bool has_comp = !FP8 && p.src_zp.ptr && p.wei_colsum;
         const int zp_src = has_comp ? load_int(p.src_zp.dt, p.src_zp.ptr, 0) : 0;
@@ -700,6 +712,7 @@ __global__ void __launch_bounds__(640, 1) matmul_tc8_kernel(const __grid_constan
                 const int64_t n = n0 + j;
                 const bool in = n < p.N;
                 wscale[j] = (in && p.wei_scale.ptr) ? load_f32(p.wei_scale.dt, p.wei_scale.ptr, n * p.wei_scale.s1) : 1.f;
+                wsx[j] = wscale[j] * k.src_scale;
                 bias[j] = (in && bias_per_col) ? load_f32(p.bias_dt, p.bias, n * p.bias_sn) : -0.f;
                 comp[j] = (in && has_comp) ? zp_src * p.wei_colsum[n] : 0;
                 // the int8 path adds the zero-point (+0 when unset) whenever any attribute is set; -0 adds nothing
@@ -735,7 +748,7 @@ __global__ void __launch_bounds__(640, 1) matmul_tc8_kernel(const __grid_constan
                 uint32_t v[CH];
                 tmem_ld16_issue(trow + c * CH, v);
                 tmem_ld_wait(v);
-                epilogue_chunk<FP8, EPI, SUM, PEERS>(p, v, m, n0 + c * CH, wscale + c * CH, bias + c * CH, comp + c * CH, zpv + c * CH, k,
+                epilogue_chunk<FP8, EPI, SUM, PEERS>(p, v, m, n0 + c * CH, wscale + c * CH, wsx + c * CH, bias + c * CH, comp + c * CH, zpv + c * CH, k,
                         trow + c * CH, lane, ob0, (ofbits & 1u) != 0);
                 ob0 = ob1;
                 ob1 = ob2;

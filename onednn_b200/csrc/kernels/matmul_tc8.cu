@@ -233,13 +233,6 @@ __device__ __forceinline__ float sigmoid_neg2_fast(float a) {
     return r;
 }
 
-// tanh by ex2.approx / rcp.approx: absolute error below 1e-6 on the whole range
-__device__ __forceinline__ float tanh_fast(float a) {
-    float e, r;
-    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(a * 2.885390081777927f));
-    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(e + 1.f));
-    return fmaf(-2.f, r, 1.f);
-}
 
 // one non-transcendental eltwise kind applied to the CH values in registers
 __device__ __forceinline__ void eltwise_simple_chunk(const b200_postop_t &e, float (&y)[CH]) {

@@ -1,31 +1,35 @@
 // Weight-compressed matmul on the tensor cores: bf16 activations (up to 128 rows per
-// pass) times 4-bit weights with K-grouped scales and zero-points.
+// pass) times 4-bit or 8-bit integer weights with K-grouped scales and zero-points.
 // Semantics: the reference's weights-decompression matmul
 // (src/cpu/matmul/ref_matmul.cpp:130-233, with_wei_decompression) under fpmath bf16
 // with apply_to_int: every weight is decompressed to w' = (q - zp) * scale and rounded
-// to bf16 (exactly the bf16 rounding of the reference's f32 w', because (q - zp) * scale
-// with a bf16 scale is exact in f32), products are accumulated in f32.
+// to bf16 -- exactly the bf16 rounding of the reference's f32 w' (4-bit weights: (q - zp) is
+// formed exactly in bf16 and multiplied by the bf16 scale with one rounding; 8-bit weights:
+// the reference's own f32 arithmetic, then one rounding) -- and products are accumulated
+// in f32.
 //
 // Where the decode kernel (matmul_wc.cu) spends its issue slots on register-level MMAs,
 // this one only converts: per stage of 64 k, a group of four warps (one thread per output
-// column) turns 4 KiB of packed nibbles into a 128-column x 64-k bf16 tile in shared memory, laid out as the 128-byte-swizzled K-major
-// operand tile a TMA load would have produced; the activations of the same 64 k arrive by
-// TMA; one thread issues tcgen05.mma (kind::f16, 128 x NB x 16) with the weights as the A
-// operand (128 output columns = the TMEM lanes) and the activations as B (NB = activation
-// rows rounded up to 16), accumulating in TMEM over the whole K.  The epilogue reads TMEM
-// with one output column per lane, so that stores of a dst row are coalesced.
+// column) turns the packed weights of 128 columns into a 128-column x 64-k bf16 tile in
+// shared memory, laid out as the 128-byte-swizzled K-major operand tile a TMA load would
+// have produced; the activations of the same 64 k arrive by TMA; one thread issues
+// tcgen05.mma (kind::f16, 128 x NB x 16) with the weights as the A operand (128 output
+// columns = the TMEM lanes) and the activations as B (NB = activation rows rounded up to
+// 16), accumulating in TMEM over the whole K.  The epilogue reads TMEM with one output
+// column per lane, so that stores of a dst row are coalesced.
 //
 //   warp 0        TMA producer (activations)           waits empty[s]   -> full_a[s] (tx bytes)
-//   warp 1        TMEM owner and MMA issuer            waits full_a/b   -> empty[s], acc_full
+//   warp 1        TMEM owner and MMA issuer            waits full_a[s]  -> empty[s], acc_full
 //   warps 2..17   four dequantising groups (group g    waits empty[g]   -> full_a[g]; acc_full -> acc_empty
 //                 owns stage g), then the epilogue
 //
-// Weights are read in the B200_WEI_WC4_TC layout written by the pack kernel below:
+// Weights are read in the layouts written by the pack kernels below.  B200_WEI_WC4_TC:
 // blocks of 128 output columns x 64 k = 4 KiB, block (nt, kb) at ((nt * K/64) + kb) * 4096,
 // inside a block row-major [128 columns][64 k] nibbles, 32 bytes per column; inside each
 // 32-bit word (8 consecutive k) nibble i holds k 2i and nibble i + 4 holds k 2i + 1, so that
-// (w >> 4i) & 0x000f000f | 0x43004300 is the bf16 pair (128 + q[2i], 128 + q[2i + 1]).
-// Columns past N are stored as zeros.  s4 values are stored offset by 8.
+// (w >> 4i) & 0x000f000f | 0x43004300 is the bf16 pair (128 + q[2i], 128 + q[2i + 1]);
+// s4 values are stored offset by 8.  B200_WEI_WC8_TC: the same blocks with one byte per
+// weight (8 KiB, 64 bytes per column, k ascending).  Columns past N are stored as zeros.
 //
 // Every wait is bounded; a wait that runs out sets a bit in the stream's status word,
 // every role stops at its next wait, copies in flight are drained and TMEM is released.
@@ -58,8 +62,7 @@ constexpr uint32_t WAIT_TRIES = 1u << 19; // hardware-suspended waits of up to ~
 enum : uint32_t { ST_WAIT_FULL = 0x1000, ST_WAIT_EMPTY = 0x2000, ST_WAIT_ACC = 0x4000 };
 
 struct ctrl_t {
-    uint64_t full_a[STAGES];
-    uint64_t full_b[STAGES];
+    uint64_t full_a[STAGES]; // converted weights (four warp arrivals) and activations (copy bytes) of a stage
     uint64_t empty[STAGES];
     uint64_t acc_full, acc_empty;
     uint32_t tmem_base;
@@ -68,7 +71,6 @@ struct ctrl_t {
 
 struct args_t {
     b200_matmul_params_t p;
-    const __nv_bfloat16 *x;  // activations (bf16, possibly a converted copy)
     const uint8_t *wei;      // packed weights
     int nb;                  // activation rows per pass, rounded up to 16 (UMMA N)
     int m_passes, n_tiles, k_blocks;
@@ -76,7 +78,6 @@ struct args_t {
     uint32_t idesc;
     uint32_t tmem_cols;
     uint32_t gs_blocks, gz_blocks; // K-group sizes of scales and zero-points in k-blocks of 64 (K / 64 when not grouped)
-    uint32_t s_groups, z_groups;   // number of such groups along K
     float nibble_offset;     // 4-bit weights: 128 (u4) or 136 (s4 stored offset by 8)
     uint32_t byte_xor;       // 8-bit weights: 0x80808080 for s8 (to offset binary), 0 for u8
 };
@@ -210,7 +211,6 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < STAGES; ++s) {
             mbar_init(&ctrl->full_a[s], GROUP_WARPS + 1); // the group's warps and the activations' copy
-            mbar_init(&ctrl->full_b[s], 1);                // unused
             mbar_init(&ctrl->empty[s], 1);
         }
         mbar_init(&ctrl->acc_full, 1);
@@ -621,7 +621,6 @@ extern "C" int b200_matmul_wc_tc_launch(const b200_matmul_params_t *p, b200_stre
 
     args_t a;
     a.p = *p;
-    a.x = (const __nv_bfloat16 *)p->src;
     a.wei = (const uint8_t *)wei;
     a.rows_per_pass = p->M <= 128 ? p->M : 128;
     a.nb = (int)((a.rows_per_pass + 15) / 16 * 16);
@@ -630,8 +629,6 @@ extern "C" int b200_matmul_wc_tc_launch(const b200_matmul_params_t *p, b200_stre
     a.k_blocks = (int)(p->K / TK);
     a.gs_blocks = (uint32_t)(gs / TK);
     a.gz_blocks = (uint32_t)(gz / TK);
-    a.s_groups = (uint32_t)(p->K / gs);
-    a.z_groups = (uint32_t)(p->K / gz);
     a.nibble_offset = p->wei_dt == B200_DT_S4 ? 136.f : 128.f;
     a.byte_xor = p->wei_dt == B200_DT_S8 ? 0x80808080u : 0u;
     a.tmem_cols = 32;

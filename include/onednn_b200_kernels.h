@@ -232,6 +232,28 @@ B200_API size_t b200_packed_colsum_offset(int64_t K, int64_t N, int32_t dt);
  * (src/common/reorder.cpp:63-220, src/cpu/reorder/simple_reorder.hpp). */
 B200_API int b200_reorder_launch(const b200_reorder_params_t *p, b200_stream_t stream);
 
+/* Quantising reorder of a plain 2-D tensor (any element strides):
+ *   d = src_scale * (src - src_zp);  d += beta * dst (sum post-op);
+ *   d = d * (1 / dst_scale) + dst_zp;  dst = saturate + round-to-nearest-even (integer
+ *   destinations) or a plain conversion of d
+ * with every step a separate f32 operation and the subtraction done in s32 for integer
+ * sources -- the arithmetic of the reference's generic reorder
+ * (src/cpu/reorder/simple_reorder.hpp:2551-2635, destination scale inverted up front as in
+ * src/cpu/reorder/cpu_reorder_pd.hpp:83-109).  Scale / zero-point elements are addressed as
+ * b200_quant_t describes with (i0, i1) = (row, column); the destination zero-point is one
+ * s32 value.  8 / 16 / 32-bit element types.  Replaces dnnl_reorder with scales and
+ * zero-points attributes (src/common/reorder.cpp:63-160) for the tensors of this path:
+ * quantising activations before an int8 matmul, dequantising its result. */
+typedef struct {
+    int64_t rows, cols;
+    const void *src; int32_t src_dt; int32_t reserved0; int64_t src_s0, src_s1;
+    void *dst; int32_t dst_dt; int32_t reserved1; int64_t dst_s0, dst_s1;
+    b200_quant_t src_scale, dst_scale, src_zp, dst_zp;
+    float beta; int32_t reserved2;
+} b200_reorder_quant_params_t;
+
+B200_API int b200_reorder_quant_launch(const b200_reorder_quant_params_t *p, b200_stream_t stream);
+
 /* s32 column sums of plain 8-bit weights: out[n] = sum_k w[k][n]
  * (the zero-point compensation the reference computes at reorder time,
  * src/cpu/x64/matmul/brgemm_matmul.cpp:1184-1200) */

@@ -473,6 +473,59 @@ class CasePlan:
         return self.mem["dst"].read(dt.RAW[c.dst_dt], (c.M, c.N))
 
 
+class ReorderPlan:
+    """A :class:`onednn_b200.workloads.ReorderCase` lowered onto the engine through
+    ``dnnl_reorder_primitive_desc_create`` with a scales / zero-points attribute."""
+
+    def __init__(self, case, engine, stream):
+        self.case, self.engine, self.stream = case, engine, stream
+        c = case
+        shape = (c.rows, c.cols)
+        self.src_md = MemoryDesc(shape, c.src_dt, TAG_AB if c.src_tag == "ab" else TAG_BA)
+        self.dst_md = MemoryDesc(shape, c.dst_dt, TAG_AB if c.dst_tag == "ab" else TAG_BA)
+        attr = PrimitiveAttr()
+        for q, arg, is_zp in ((c.src_scale, ARG_SRC, False), (c.dst_scale, ARG_DST, False),
+                              (c.src_zp, ARG_SRC, True), (c.dst_zp, ARG_DST, True)):
+            if q is None:
+                continue
+            groups = tuple(q.groups) if tuple(q.groups) != (1, 1) else ()
+            (attr.set_zero_points if is_zp else attr.set_scales)(arg, q.mask, groups, q.dt)
+        if c.beta != 0.0:
+            po = PostOps()
+            po.append_sum(c.beta, 0, dt.UNDEF)
+            attr.set_post_ops(po)
+        self.attr = attr
+        self.pd = reorder_primitive_desc(engine, self.src_md, engine, self.dst_md, attr)
+        self.impl = self.pd.impl_info_str()
+        self.prim = Primitive(self.pd)
+        self.mem = {}
+        self.args = {ARG_FROM: self._mem("src", self.src_md, c.src),
+                     ARG_TO: self._mem("dst", self.dst_md, c.dst_init)}
+        for name, q, arg in (("src_scale", c.src_scale, ARG_ATTR_SCALES | ARG_SRC),
+                             ("dst_scale", c.dst_scale, ARG_ATTR_SCALES | ARG_DST),
+                             ("src_zp", c.src_zp, ARG_ATTR_ZERO_POINTS | ARG_SRC),
+                             ("dst_zp", c.dst_zp, ARG_ATTR_ZERO_POINTS | ARG_DST)):
+            if q is not None:
+                self.args[arg] = self._mem(name, MemoryDesc((q.data.size,), q.dt, TAG_A), q.data)
+
+    def _mem(self, name, md, array):
+        m = Memory(md, self.engine)
+        if array is not None:
+            m.write(array)
+        self.mem[name] = m
+        return m
+
+    def execute(self):
+        self.prim.execute(self.stream, self.args)
+
+    def result(self):
+        """Raw destination in its physical order: (rows, cols) for tag ab, (cols, rows) for ba."""
+        self.stream.wait()
+        c = self.case
+        shape = (c.rows, c.cols) if c.dst_tag == "ab" else (c.cols, c.rows)
+        return self.mem["dst"].read(dt.RAW[c.dst_dt], shape)
+
+
 def run_case(case, engine=None, stream=None, weights="any", impl=None):
     """Execute ``case`` once on the engine; returns (raw dst array, implementation name)."""
     engine = engine or Engine()

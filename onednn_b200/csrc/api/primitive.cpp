@@ -20,6 +20,46 @@ dnnl_primitive::~dnnl_primitive() {
 
 // ---- reorder primitive descriptor -----------------------------------------------
 
+// Attributes of a quantising reorder: what src/common/reorder.cpp:96-146 and the generic
+// implementation's own check (src/cpu/reorder/simple_reorder.hpp:2498-2547) admit, for the
+// plain 1-D / 2-D tensors this engine reorders with scales.
+static dnnl_status_t reorder_quant_validate(const dnnl_memory_desc &s, const dnnl_memory_desc &d,
+        const dnnl_primitive_attr &attr) {
+    if (!s.is_plain() || !d.is_plain()) return dnnl_unimplemented;
+    if (s.ndims < 1 || s.ndims > 2) return dnnl_unimplemented;
+    if (dt_nbits(s.data_type) == 4 || dt_nbits(d.data_type) == 4) return dnnl_unimplemented;
+    const int full = (1 << s.ndims) - 1;
+    for (const auto &kv : attr.scales) {
+        if (!kv.second.set) continue;
+        if (kv.first != DNNL_ARG_SRC && kv.first != DNNL_ARG_DST) return dnnl_unimplemented;
+        if (kv.second.mask & ~full) return dnnl_invalid_arguments;
+    }
+    for (const auto &kv : attr.zero_points) {
+        if (!kv.second.set) continue;
+        if (kv.first != DNNL_ARG_SRC && kv.first != DNNL_ARG_DST) return dnnl_unimplemented;
+        if (kv.second.mask & ~full) return dnnl_invalid_arguments;
+    }
+    // zero-points go with integer tensors only
+    auto is_int = [](int dt) { return dt == dnnl_s32 || dt == dnnl_s8 || dt == dnnl_u8; };
+    if (attr.zp(DNNL_ARG_SRC).set && !is_int(s.data_type)) return dnnl_invalid_arguments;
+    if (attr.zp(DNNL_ARG_DST).set && !is_int(d.data_type)) return dnnl_invalid_arguments;
+    if (attr.zp(DNNL_ARG_DST).set && (attr.zp(DNNL_ARG_DST).mask != 0 || attr.zp(DNNL_ARG_DST).dt != dnnl_s32))
+        return dnnl_unimplemented;
+    const b200::quant_entry_t &ss = attr.scale(DNNL_ARG_SRC), &ds = attr.scale(DNNL_ARG_DST);
+    if (ds.set && (ds.group_ndims != 0 || ds.dt != dnnl_f32)) return dnnl_unimplemented;
+    if (ss.set && ds.set && ss.mask > 0 && ds.mask > 0 && ss.mask != ds.mask) return dnnl_invalid_arguments;
+    for (const b200::quant_entry_t *q : {&ss, &attr.zp(DNNL_ARG_SRC)}) {
+        if (!q->set || q->group_ndims == 0) continue;
+        if (s.ndims != 2 || q->group_ndims != 2 || q->mask != 3) return dnnl_invalid_arguments;
+        for (int i = 0; i < 2; ++i)
+            if (q->groups[i] < 1 || s.dims[i] % q->groups[i] != 0) return dnnl_invalid_arguments;
+    }
+    const auto &po = attr.post_ops.entries;
+    if (po.size() > 1) return dnnl_unimplemented;
+    if (po.size() == 1 && !(po[0].kind == dnnl_sum && po[0].zero_point == 0)) return dnnl_unimplemented;
+    return dnnl_success;
+}
+
 dnnl_status_t dnnl_reorder_primitive_desc_create(dnnl_primitive_desc_t *reorder_primitive_desc,
         const_dnnl_memory_desc_t src_desc, dnnl_engine_t src_engine, const_dnnl_memory_desc_t dst_desc,
         dnnl_engine_t dst_engine, const_dnnl_primitive_attr_t attr) {
@@ -31,8 +71,11 @@ dnnl_status_t dnnl_reorder_primitive_desc_create(dnnl_primitive_desc_t *reorder_
     for (int i = 0; i < s.ndims; ++i)
         if (s.dims[i] != d.dims[i]) return dnnl_invalid_arguments;
     if (s.has_runtime_dims()) return dnnl_unimplemented;
-    if (attr && (!attr->scales.empty() || !attr->zero_points.empty() || !attr->post_ops.entries.empty()))
-        return dnnl_unimplemented; // quantising reorders are not part of this path yet
+    const bool quantising = attr && (!attr->scales.empty() || !attr->zero_points.empty() || !attr->post_ops.entries.empty());
+    if (quantising) {
+        const dnnl_status_t st = reorder_quant_validate(s, d, *attr);
+        if (st != dnnl_success) return st;
+    }
     if (!s.is_plain()) return dnnl_unimplemented; // unpacking is not needed by the matmul path
     if (d.format_kind == dnnl_format_kind_opaque) {
         if (s.ndims != 2 || s.data_type != d.data_type) return dnnl_unimplemented;
@@ -59,13 +102,63 @@ dnnl_status_t dnnl_reorder_primitive_desc_create(dnnl_primitive_desc_t *reorder_
     pd->user_src = pd->src = s;
     pd->user_dst = pd->dst = d;
     pd->impl = IMPL_REORDER;
-    pd->impl_str = d.format_kind == dnnl_format_kind_opaque ? "cuda:pack_weights" : "cuda:reorder";
+    pd->impl_str = d.format_kind == dnnl_format_kind_opaque ? "cuda:pack_weights"
+                                                            : (quantising ? "cuda:reorder_quant" : "cuda:reorder");
     dst_engine->refs.fetch_add(1);
     *reorder_primitive_desc = pd.release();
     return dnnl_success;
 }
 
 namespace b200 {
+
+static dnnl_status_t reorder_quant_execute(const dnnl_primitive_desc *pd, dnnl_stream *stream, const dnnl_memory *from,
+        const dnnl_memory *to, const std::map<int, dnnl_memory *> &args) {
+    const dnnl_memory_desc &s = pd->src, &d = pd->dst;
+    b200_reorder_quant_params_t r;
+    std::memset(&r, 0, sizeof(r));
+    r.src = (const char *)from->handle + s.offset0 * dt_nbits(s.data_type) / 8;
+    r.dst = (char *)to->handle + d.offset0 * dt_nbits(d.data_type) / 8;
+    r.src_dt = s.data_type;
+    r.dst_dt = d.data_type;
+    // a 1-D tensor is one row; its only dim then is mask bit 1 below
+    const int sh = s.ndims == 1 ? 1 : 0;
+    r.rows = sh ? 1 : s.dims[0];
+    r.cols = s.dims[s.ndims - 1];
+    r.src_s0 = sh ? 0 : s.strides[0];
+    r.dst_s0 = sh ? 0 : d.strides[0];
+    r.src_s1 = s.strides[s.ndims - 1];
+    r.dst_s1 = d.strides[s.ndims - 1];
+    const dnnl_primitive_attr &a = pd->attr;
+    struct { const quant_entry_t *q; int arg; b200_quant_t *out; } qs[4] = {
+            {&a.scale(DNNL_ARG_SRC), DNNL_ARG_ATTR_SCALES | DNNL_ARG_SRC, &r.src_scale},
+            {&a.scale(DNNL_ARG_DST), DNNL_ARG_ATTR_SCALES | DNNL_ARG_DST, &r.dst_scale},
+            {&a.zp(DNNL_ARG_SRC), DNNL_ARG_ATTR_ZERO_POINTS | DNNL_ARG_SRC, &r.src_zp},
+            {&a.zp(DNNL_ARG_DST), DNNL_ARG_ATTR_ZERO_POINTS | DNNL_ARG_DST, &r.dst_zp}};
+    for (auto &e : qs) {
+        b200_quant_t &o = *e.out;
+        o.g0 = o.g1 = 1;
+        if (!e.q->set) continue;
+        auto it = args.find(e.arg);
+        if (it == args.end() || !it->second->handle) return dnnl_invalid_arguments; // runtime argument missing
+        const dnnl_memory *m = it->second;
+        const int mask = e.q->mask << sh;
+        o.ptr = (const char *)m->handle + m->md.offset0 * dt_nbits(m->md.data_type) / 8;
+        o.dt = m->md.data_type;
+        if (o.dt != e.q->dt) return dnnl_invalid_arguments;
+        o.g0 = (mask & 1) && e.q->group_ndims ? e.q->groups[0] : 1;
+        o.g1 = (mask & 2) && e.q->group_ndims ? e.q->groups[1] : 1;
+        const int64_t n1 = (mask & 2) ? r.cols / o.g1 : 1, n0 = (mask & 1) ? r.rows / o.g0 : 1;
+        o.s0 = (mask & 1) ? n1 : 0;
+        o.s1 = (mask & 2) ? 1 : 0;
+        if (m->md.nelems() < n0 * n1) return dnnl_invalid_arguments;
+    }
+    if (!a.post_ops.entries.empty()) r.beta = a.post_ops.entries[0].scale;
+    const int rc = b200_reorder_quant_launch(&r, stream->cuda_stream);
+    if (rc == 0) return dnnl_success;
+    if (rc == B200_ERR_UNSUPPORTED) return dnnl_unimplemented;
+    if (rc == B200_ERR_BAD_ARG) return dnnl_invalid_arguments;
+    return dnnl_runtime_error;
+}
 
 dnnl_status_t reorder_execute(const dnnl_primitive *prim, dnnl_stream *stream, const std::map<int, dnnl_memory *> &args) {
     const dnnl_primitive_desc *pd = prim->pd.get();
@@ -75,6 +168,7 @@ dnnl_status_t reorder_execute(const dnnl_primitive *prim, dnnl_stream *stream, c
     if (pd->src.has_zero_dim()) return dnnl_success;
     if (!from->handle || !to->handle) return dnnl_invalid_arguments;
     const dnnl_memory_desc &s = pd->src, &d = pd->dst;
+    if (pd->impl_str == "cuda:reorder_quant") return reorder_quant_execute(pd, stream, from, to, args);
     b200_reorder_params_t r;
     std::memset(&r, 0, sizeof(r));
     r.src = (const char *)from->handle + s.offset0 * dt_nbits(s.data_type) / 8;
@@ -179,7 +273,7 @@ static const dnnl_memory_desc *arg_md(const dnnl_primitive_desc *pd, int arg) {
     if (pd->kind == dnnl_reorder) {
         if (arg == DNNL_ARG_FROM) return &pd->src;
         if (arg == DNNL_ARG_TO) return &pd->dst;
-        return &pd->zero_md;
+        if (!(arg & (DNNL_ARG_ATTR_SCALES | DNNL_ARG_ATTR_ZERO_POINTS))) return &pd->zero_md;
     }
     switch (arg) {
         case DNNL_ARG_SRC: return &pd->src;

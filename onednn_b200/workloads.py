@@ -100,6 +100,41 @@ class MatmulCase:
         return n
 
 
+@dataclass
+class ReorderCase:
+    """One quantising ``dnnl::reorder`` of a plain 2-D tensor: scales / zero-points on the
+    source and destination side (masks over (rows, cols)), optional sum post-op."""
+    name: str
+    rows: int
+    cols: int
+    src: np.ndarray
+    src_dt: int
+    dst_dt: int
+    src_tag: str = "ab"             # "ab": columns contiguous, "ba": rows contiguous
+    dst_tag: str = "ab"
+    src_scale: Optional[Quant] = None
+    dst_scale: Optional[Quant] = None
+    src_zp: Optional[Quant] = None
+    dst_zp: Optional[Quant] = None
+    beta: float = 0.0               # sum post-op scale (0 = none)
+    dst_init: Optional[np.ndarray] = None
+    exact: bool = True              # every destination type: the arithmetic is elementwise f32
+
+
+def quantize_case(rows=4096, cols=4096, src_dt=dt.F32, dst_dt=dt.S8, seed=20240620, per_row=False, name=None):
+    """Activations -> int8 in front of an int8 matmul: dst = sat_rne(src / scale + zp)."""
+    rng = np.random.default_rng(seed)
+    x = (rng.standard_normal((rows, cols)) * 1.5).astype(np.float32)
+    src = x if src_dt == dt.F32 else dt.from_f32(x, src_dt)
+    if per_row:
+        sc = (np.abs(x).max(axis=1) / 127.0).astype(np.float32)
+        dscale = Quant(sc, dt.F32, 1)
+    else:
+        dscale = Quant(np.float32([0.043]), dt.F32, 0)
+    zp = None if dst_dt == dt.S8 else Quant(np.int32([128]), dt.S32, 0)
+    return ReorderCase(name or "quantize_%dx%d" % (rows, cols), rows, cols, src, src_dt, dst_dt, dst_scale=dscale, dst_zp=zp)
+
+
 def eltwise(name, alpha=0.0, beta=0.0):
     return PostOp(PO_ELTWISE, alg=ELTWISE[name], alpha=alpha, beta=beta, scale=1.0)
 

@@ -44,6 +44,16 @@ class Problem(C.Structure):
     ]
 
 
+class Reorder(C.Structure):
+    _fields_ = [
+        ("rows", C.c_int64), ("cols", C.c_int64),
+        ("src", C.c_void_p), ("src_dt", C.c_int32), ("pad0", C.c_int32), ("src_s0", C.c_int64), ("src_s1", C.c_int64),
+        ("dst", C.c_void_p), ("dst_dt", C.c_int32), ("pad1", C.c_int32), ("dst_s0", C.c_int64), ("dst_s1", C.c_int64),
+        ("src_scale", Quant), ("dst_scale", Quant), ("src_zp", Quant), ("dst_zp", Quant),
+        ("beta", C.c_float), ("nthreads", C.c_int32),
+    ]
+
+
 _lib = None
 _ref = None
 
@@ -58,6 +68,8 @@ def lib():
         _lib = C.CDLL(str(so))
         _lib.orc_matmul.argtypes = [C.POINTER(Problem)]
         _lib.orc_matmul.restype = C.c_int
+        _lib.orc_reorder.argtypes = [C.POINTER(Reorder)]
+        _lib.orc_reorder.restype = C.c_int
         _lib.orc_load_float.argtypes = [C.c_int32, C.c_void_p, C.c_int64]
         _lib.orc_load_float.restype = C.c_float
         _lib.orc_store_float.argtypes = [C.c_int32, C.c_float, C.c_void_p, C.c_int64]
@@ -80,6 +92,8 @@ def ref():
         _ref.refrun_matmul.argtypes = [C.POINTER(Problem), C.c_char_p, C.c_int, C.c_int,
                                        C.POINTER(C.c_double), C.POINTER(C.c_double), C.c_char_p, C.c_int]
         _ref.refrun_matmul.restype = C.c_int
+        _ref.refrun_reorder.argtypes = [C.POINTER(Reorder), C.c_char_p, C.c_char_p, C.c_int]
+        _ref.refrun_reorder.restype = C.c_int
     return _ref
 
 
@@ -185,3 +199,65 @@ def run_reference(case, impl="", weights_any=False, iters=0):
     if rc != 0:
         raise RuntimeError("refrun_matmul failed: %d" % rc)
     return dst, name.value.decode(), tmin.value, tavg.value
+
+
+# ---- quantising reorder ---------------------------------------------------------------------
+
+def _rquant(q, rows, cols):
+    out = Quant()
+    out.g0 = out.g1 = 1
+    if q is None:
+        return out
+    g0, g1 = q.groups
+    out.g0, out.g1 = (g0 if (q.mask & 1) else 1), (g1 if (q.mask & 2) else 1)
+    n1 = (cols // out.g1) if (q.mask & 2) else 1
+    n0 = (rows // out.g0) if (q.mask & 1) else 1
+    out.ptr, out.dt = _ptr(q.data), q.dt
+    out.s0 = n1 if (q.mask & 1) else 0
+    out.s1 = 1 if (q.mask & 2) else 0
+    out.nelems_is_one = 1 if n0 * n1 == 1 else 0
+    return out
+
+
+def make_reorder(case, dst, nthreads=0):
+    """Fill an orc_reorder_t; ``dst`` is the raw destination in its physical order."""
+    r = Reorder()
+    r.rows, r.cols = case.rows, case.cols
+    r.src, r.src_dt = _ptr(case.src), case.src_dt
+    r.src_s0, r.src_s1 = (case.cols, 1) if case.src_tag == "ab" else (1, case.rows)
+    r.dst, r.dst_dt = _ptr(dst), case.dst_dt
+    r.dst_s0, r.dst_s1 = (case.cols, 1) if case.dst_tag == "ab" else (1, case.rows)
+    r.src_scale = _rquant(case.src_scale, case.rows, case.cols)
+    r.dst_scale = _rquant(case.dst_scale, case.rows, case.cols)
+    r.src_zp = _rquant(case.src_zp, case.rows, case.cols)
+    r.dst_zp = _rquant(case.dst_zp, case.rows, case.cols)
+    r.beta, r.nthreads = case.beta, nthreads
+    return r
+
+
+def new_reorder_dst(case):
+    from onednn_b200 import dtypes as dt
+    shape = (case.rows, case.cols) if case.dst_tag == "ab" else (case.cols, case.rows)
+    if case.dst_init is not None:
+        return np.ascontiguousarray(case.dst_init).copy()
+    return np.zeros(shape, dtype=dt.RAW[case.dst_dt])
+
+
+def run_oracle_reorder(case, nthreads=0):
+    dst = new_reorder_dst(case)
+    r = make_reorder(case, dst, nthreads)
+    rc = lib().orc_reorder(C.byref(r))
+    if rc != 0:
+        raise RuntimeError("orc_reorder failed: %d" % rc)
+    return dst
+
+
+def run_reference_reorder(case, impl=""):
+    """Returns (dst, impl_name) from the reference library's CPU engine."""
+    dst = new_reorder_dst(case)
+    r = make_reorder(case, dst)
+    name = C.create_string_buffer(128)
+    rc = ref().refrun_reorder(C.byref(r), impl.encode(), name, 128)
+    if rc != 0:
+        raise RuntimeError("refrun_reorder failed: %d" % rc)
+    return dst, name.value.decode()

@@ -519,3 +519,48 @@ int orc_matmul(const orc_problem_t *p) {
 #endif
     return 0;
 }
+
+/* src/cpu/reorder/simple_reorder.hpp:2551-2635 (the generic "simple:any" reorder) with
+ * src/cpu/reorder/cpu_reorder_pd.hpp:83-109: the destination scale is inverted up front;
+ * an integer source minus its zero-point is an integer subtraction, converted to f32
+ * afterwards; scale, sum and zero-point are separate f32 operations (no fused
+ * multiply-add); the store saturates, then rounds to nearest even. */
+int orc_reorder(const orc_reorder_t *r) {
+    if (!r || !r->src || !r->dst) return 1;
+    if (r->rows <= 0 || r->cols <= 0) return 0;
+    const int int_src = r->src_dt == ORC_S32 || r->src_dt == ORC_S8 || r->src_dt == ORC_U8;
+    const int32_t dst_zp = r->dst_zp.ptr ? orc_load_int(r->dst_zp.dt, r->dst_zp.ptr, 0) : 0;
+#ifdef _OPENMP
+    int saved = omp_get_max_threads();
+    if (r->nthreads > 0) omp_set_num_threads(r->nthreads);
+#pragma omp parallel for schedule(static)
+#endif
+    for (int64_t i = 0; i < r->rows; ++i)
+        for (int64_t j = 0; j < r->cols; ++j) {
+            float ss = 1.f, ds = 1.f;
+            if (r->src_scale.ptr)
+                ss = r->src_scale.nelems_is_one ? single_scale(&r->src_scale)
+                                                : orc_load_float(r->src_scale.dt, r->src_scale.ptr, qoff(&r->src_scale, i, j));
+            if (r->dst_scale.ptr)
+                ds = 1.f / orc_load_float(r->dst_scale.dt, r->dst_scale.ptr,
+                                          r->dst_scale.nelems_is_one ? 0 : qoff(&r->dst_scale, i, j));
+            int zp = 0;
+            if (r->src_zp.ptr)
+                zp = (int)orc_load_float(r->src_zp.dt, r->src_zp.ptr, r->src_zp.nelems_is_one ? 0 : qoff(&r->src_zp, i, j));
+            const int64_t ioff = i * r->src_s0 + j * r->src_s1, ooff = i * r->dst_s0 + j * r->dst_s1;
+            float d; /* built with -ffp-contract=off: the steps below stay separate */
+            if (int_src)
+                d = ss * (float)(orc_load_int(r->src_dt, r->src, ioff) - zp);
+            else
+                d = ss * (orc_load_float(r->src_dt, r->src, ioff) - (float)zp);
+            if (r->beta != 0.f) {
+                d += r->beta * orc_load_float(r->dst_dt, r->dst, ooff);
+            }
+            d = d * ds + (float)dst_zp;
+            orc_store_float(r->dst_dt, d, r->dst, ooff);
+        }
+#ifdef _OPENMP
+    if (r->nthreads > 0) omp_set_num_threads(saved);
+#endif
+    return 0;
+}

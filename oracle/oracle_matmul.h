@@ -94,6 +94,22 @@ typedef struct {
 /* returns 0 on success, non-zero for an unsupported combination */
 int orc_matmul(const orc_problem_t *p);
 
+/* Quantising reorder of a 2-D tensor (plain layouts): the reference's generic reorder
+ * implementation "simple:any" (src/cpu/reorder/simple_reorder.hpp:2551-2635).
+ * Scale / zero-point elements are addressed as in orc_quant_t with (i0, i1) the
+ * element's (row, column). */
+typedef struct {
+    int64_t rows, cols;
+    const void *src; int32_t src_dt; int32_t pad0; int64_t src_s0, src_s1;
+    void *dst; int32_t dst_dt; int32_t pad1; int64_t dst_s0, dst_s1;
+    orc_quant_t src_scale, dst_scale; /* dst scale: f32 */
+    orc_quant_t src_zp, dst_zp;       /* dst zero-point: one s32 value */
+    float beta;                       /* scale of a sum post-op (0 = none): d += beta * dst */
+    int32_t nthreads;                 /* 0 = OpenMP default */
+} orc_reorder_t;
+
+int orc_reorder(const orc_reorder_t *r);
+
 /* scalar helpers, exported for the data-type tests */
 float orc_load_float(int32_t dt, const void *ptr, int64_t idx);
 int32_t orc_load_int(int32_t dt, const void *ptr, int64_t idx);

@@ -234,3 +234,91 @@ extern "C" __attribute__((visibility("default"))) int refrun_matmul(const orc_pr
     dnnl_engine_destroy(eng);
     return 0;
 }
+
+// refrun_reorder(problem, impl_filter, impl_out): one quantising reorder of a plain 2-D
+// tensor through dnnl_reorder_primitive_desc_create on the CPU engine, with the scales,
+// zero-points and the optional sum post-op of orc_reorder_t as attributes.
+extern "C" __attribute__((visibility("default"))) int refrun_reorder(const orc_reorder_t *r, const char *impl_filter,
+        char *impl_out, int impl_out_len) {
+    dnnl_engine_t eng;
+    CK(dnnl_engine_create(&eng, dnnl_cpu, 0));
+    dnnl_stream_t strm;
+    CK(dnnl_stream_create(&strm, eng, dnnl_stream_default_flags));
+    const int64_t dims[2] = {r->rows, r->cols};
+    const int64_t sstr[2] = {r->src_s0, r->src_s1}, dstr[2] = {r->dst_s0, r->dst_s1};
+    dnnl_memory_desc_t src_md, dst_md;
+    CK(make_md(&src_md, 2, dims, r->src_dt, sstr));
+    CK(make_md(&dst_md, 2, dims, r->dst_dt, dstr));
+
+    dnnl_primitive_attr_t attr;
+    CK(dnnl_primitive_attr_create(&attr));
+    struct qarg { const orc_quant_t *q; int arg; bool is_zp; };
+    const qarg qs[4] = {{&r->src_scale, DNNL_ARG_SRC, false}, {&r->dst_scale, DNNL_ARG_DST, false},
+            {&r->src_zp, DNNL_ARG_SRC, true}, {&r->dst_zp, DNNL_ARG_DST, true}};
+    for (const qarg &a : qs) {
+        if (!a.q->ptr) continue;
+        const int mask = quant_mask(*a.q);
+        const bool grouped = a.q->g0 > 1 || a.q->g1 > 1;
+        const int64_t groups[2] = {a.q->g0, a.q->g1};
+        if (a.is_zp)
+            CK(dnnl_primitive_attr_set_zero_points(attr, a.arg, mask, grouped ? 2 : 0, groups, (dnnl_data_type_t)a.q->dt));
+        else
+            CK(dnnl_primitive_attr_set_scales(attr, a.arg, mask, grouped ? 2 : 0, groups, (dnnl_data_type_t)a.q->dt));
+    }
+    if (r->beta != 0.f) {
+        dnnl_post_ops_t po;
+        CK(dnnl_post_ops_create(&po));
+        CK(dnnl_post_ops_append_sum(po, r->beta, 0, dnnl_data_type_undef));
+        CK(dnnl_primitive_attr_set_post_ops(attr, po));
+        CK(dnnl_post_ops_destroy(po));
+    }
+
+    dnnl_primitive_desc_t pd;
+    CK(dnnl_reorder_primitive_desc_create(&pd, src_md, eng, dst_md, eng, attr));
+    const char *impl = nullptr;
+    for (;;) {
+        CK(dnnl_primitive_desc_query(pd, dnnl_query_impl_info_str, 0, &impl));
+        if (!impl_filter || !impl_filter[0] || std::strstr(impl, impl_filter)) break;
+        if (dnnl_primitive_desc_next_impl(pd) != dnnl_success) {
+            std::fprintf(stderr, "refrun: no reorder implementation matching '%s'\n", impl_filter);
+            return 3;
+        }
+    }
+    if (impl_out && impl_out_len > 0) std::snprintf(impl_out, impl_out_len, "%s", impl);
+    dnnl_primitive_t prim;
+    CK(dnnl_primitive_create(&prim, pd));
+
+    std::vector<dnnl_exec_arg_t> args;
+    std::vector<dnnl_memory_t> mems;
+    auto add = [&](int arg, const_dnnl_memory_desc_t md, const void *ptr) -> dnnl_status_t {
+        dnnl_memory_t m;
+        dnnl_status_t s = dnnl_memory_create(&m, md, eng, const_cast<void *>(ptr));
+        if (s != dnnl_success) return s;
+        mems.push_back(m);
+        args.push_back({arg, m});
+        return dnnl_success;
+    };
+    CK(add(DNNL_ARG_FROM, src_md, r->src));
+    CK(add(DNNL_ARG_TO, dst_md, r->dst));
+    std::vector<md_guard> qmds(4);
+    for (int i = 0; i < 4; ++i) {
+        const qarg &a = qs[i];
+        if (!a.q->ptr) continue;
+        const int64_t n = quant_count(*a.q, r->rows, r->cols);
+        const int64_t one = 1;
+        CK(make_md(&qmds[i].md, 1, &n, a.q->dt, &one));
+        CK(add((a.is_zp ? DNNL_ARG_ATTR_ZERO_POINTS : DNNL_ARG_ATTR_SCALES) | a.arg, qmds[i].md, a.q->ptr));
+    }
+    CK(dnnl_primitive_execute(prim, strm, (int)args.size(), args.data()));
+    CK(dnnl_stream_wait(strm));
+
+    for (dnnl_memory_t m : mems) dnnl_memory_destroy(m);
+    dnnl_primitive_destroy(prim);
+    dnnl_primitive_desc_destroy(pd);
+    dnnl_primitive_attr_destroy(attr);
+    dnnl_memory_desc_destroy(src_md);
+    dnnl_memory_desc_destroy(dst_md);
+    dnnl_stream_destroy(strm);
+    dnnl_engine_destroy(eng);
+    return 0;
+}

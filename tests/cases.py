@@ -11,7 +11,7 @@ import numpy as np
 
 from onednn_b200 import dtypes as dt
 from onednn_b200 import workloads as W
-from onednn_b200.workloads import MatmulCase, Quant
+from onednn_b200.workloads import MatmulCase, Quant, ReorderCase
 
 
 def _f32(x):
@@ -201,5 +201,84 @@ def _two_elt():
 
 def build(name):
     c = CASES[name]()
+    c.name = name
+    return c
+
+
+# ---- quantising reorders -------------------------------------------------------------------
+# What surrounds the int8 matmul: activations quantised in front of it (per tensor, per row,
+# per column), its s32 / s8 results dequantised or requantised behind it.
+
+def _rsrc(r, rows, cols, src_dt, spread=40.0):
+    x = (r.standard_normal((rows, cols)) * spread).astype(np.float32)
+    if src_dt == dt.S8:
+        return np.clip(np.rint(x), -128, 127).astype(np.int8)
+    if src_dt == dt.U8:
+        return np.clip(np.rint(x + 128), 0, 255).astype(np.uint8)
+    if src_dt == dt.S32:
+        return np.rint(x * 1000).astype(np.int32)
+    return x if src_dt == dt.F32 else dt.from_f32(x, src_dt)
+
+
+def _rq(r, rows, cols, mask, lo, hi, qdt=dt.F32, groups=(1, 1)):
+    n0 = rows // groups[0] if mask & 1 else 1
+    n1 = cols // groups[1] if mask & 2 else 1
+    v = _f32(r.uniform(lo, hi, n0 * n1))
+    return Quant(v if qdt == dt.F32 else dt.from_f32(v, qdt), qdt, mask, groups)
+
+
+def _zp(v):
+    return Quant(np.array([v], dtype=np.int32), dt.S32, 0)
+
+
+def _reorder(seed, rows, cols, src_dt, dst_dt, **kw):
+    r = np.random.default_rng(seed)
+    c = ReorderCase("reorder", rows, cols, _rsrc(r, rows, cols, src_dt, kw.pop("spread", 40.0)), src_dt, dst_dt)
+    for k, v in kw.items():
+        setattr(c, k, v(r) if callable(v) else v)
+    if c.src_tag == "ba":
+        c.src = np.ascontiguousarray(c.src.T)
+    return c
+
+
+def _sum_init(r, rows=40, cols=64):
+    return r.integers(-60, 60, (rows, cols)).astype(np.int8)
+
+
+REORDER_CASES = {
+    "q_f32_s8_tensor": lambda: _reorder(101, 64, 128, dt.F32, dt.S8, dst_scale=lambda r: _rq(r, 64, 128, 0, 0.3, 0.4)),
+    "q_f32_u8_zp": lambda: _reorder(102, 64, 128, dt.F32, dt.U8, dst_scale=lambda r: _rq(r, 64, 128, 0, 0.3, 0.4),
+                                     dst_zp=_zp(128)),
+    "q_bf16_s8_per_row": lambda: _reorder(103, 48, 256, dt.BF16, dt.S8, dst_scale=lambda r: _rq(r, 48, 256, 1, 0.2, 0.9)),
+    "q_f32_s8_per_col": lambda: _reorder(104, 32, 96, dt.F32, dt.S8, dst_scale=lambda r: _rq(r, 32, 96, 2, 0.2, 0.9)),
+    "q_f32_s8_saturating": lambda: _reorder(105, 16, 64, dt.F32, dt.S8, spread=1e9,
+                                            dst_scale=lambda r: _rq(r, 16, 64, 0, 0.5, 0.6)),
+    "q_f32_s8_sum": lambda: _reorder(106, 40, 64, dt.F32, dt.S8, dst_scale=lambda r: _rq(r, 40, 64, 0, 0.5, 0.6),
+                                      beta=0.5, dst_init=_sum_init),
+    "q_f32_s8_transposed_src": lambda: _reorder(107, 64, 48, dt.F32, dt.S8, src_tag="ba",
+                                                dst_scale=lambda r: _rq(r, 64, 48, 0, 0.5, 0.6)),
+    "q_f32_u8_ragged": lambda: _reorder(108, 7, 13, dt.F32, dt.U8, dst_scale=lambda r: _rq(r, 7, 13, 2, 0.3, 0.9),
+                                         dst_zp=_zp(100)),
+    "q_f32_bf16_scaled": lambda: _reorder(109, 32, 64, dt.F32, dt.BF16, src_scale=lambda r: _rq(r, 32, 64, 0, 0.1, 0.2)),
+    "dq_s32_f32_per_col": lambda: _reorder(110, 64, 128, dt.S32, dt.F32, src_scale=lambda r: _rq(r, 64, 128, 2, 1e-4, 1e-3)),
+    "dq_s8_bf16_zp": lambda: _reorder(111, 64, 128, dt.S8, dt.BF16, src_scale=lambda r: _rq(r, 64, 128, 0, 0.01, 0.1),
+                                       src_zp=_zp(3)),
+    "dq_u8_f32_grouped_bf16_scales": lambda: _reorder(
+        112, 64, 128, dt.U8, dt.F32, src_scale=lambda r: _rq(r, 64, 128, 3, 0.01, 0.1, dt.BF16, (8, 32)), src_zp=_zp(128)),
+    "dq_u8_f32_grouped_narrow": lambda: _reorder(
+        113, 32, 66, dt.U8, dt.F32, src_scale=lambda r: _rq(r, 32, 66, 3, 0.01, 0.1, dt.F32, (4, 2)), src_zp=_zp(7)),
+    "rq_s8_u8_both_scales": lambda: _reorder(114, 64, 128, dt.S8, dt.U8, src_scale=lambda r: _rq(r, 64, 128, 0, 0.02, 0.03),
+                                             dst_scale=lambda r: _rq(r, 64, 128, 0, 0.04, 0.05), src_zp=_zp(-2),
+                                             dst_zp=_zp(120)),
+    "rq_s32_s8_per_col_both": lambda: _reorder(115, 32, 64, dt.S32, dt.S8,
+                                               src_scale=lambda r: _rq(r, 32, 64, 2, 1e-4, 1e-3),
+                                               dst_scale=lambda r: _rq(r, 32, 64, 2, 0.2, 0.5), dst_zp=_zp(-5)),
+    "rq_s8_s32_transposed_dst": lambda: _reorder(116, 24, 40, dt.S8, dt.S32, dst_tag="ba",
+                                                 src_scale=lambda r: _rq(r, 24, 40, 0, 3.0, 4.0)),
+}
+
+
+def build_reorder(name):
+    c = REORDER_CASES[name]()
     c.name = name
     return c

@@ -9,6 +9,10 @@ its public C API, and the raw destination bytes are stored: in full when they
 are at most 64 KiB, otherwise as a SHA-256 digest plus every 61st byte.
 A digest of the regenerated inputs is stored too, so that a change in numpy's
 random streams is detected instead of reported as a parity failure.
+
+tests/golden/reorder_outputs.npz is made the same way from the quantising
+reorders of ``cases.REORDER_CASES``, each run through the implementation the
+reference dispatches for it (its JIT reorder or the generic ``simple:any``).
 """
 import hashlib
 import sys
@@ -38,7 +42,32 @@ def input_digest(c):
     return h.hexdigest()
 
 
+def reorder_input_digest(c):
+    h = hashlib.sha256()
+    for a in (c.src, c.dst_init):
+        if a is not None:
+            h.update(np.ascontiguousarray(a).tobytes())
+    for q in (c.src_scale, c.dst_scale, c.src_zp, c.dst_zp):
+        if q is not None:
+            h.update(np.ascontiguousarray(q.data).tobytes())
+    return h.hexdigest()
+
+
+def make_reorders():
+    out = {}
+    for name in cases.REORDER_CASES:
+        c = cases.build_reorder(name)
+        dst, impl = B.run_reference_reorder(c)
+        raw = np.ascontiguousarray(dst).view(np.uint8).reshape(-1)
+        out[name + "/impl"] = np.array(impl)
+        out[name + "/inputs_sha256"] = np.array(reorder_input_digest(c))
+        out[name + "/bytes"] = raw
+        print("%-32s %-14s %8d bytes" % (name, impl, raw.size))
+    np.savez_compressed(Path(__file__).with_name("reorder_outputs.npz"), **out)
+
+
 def main():
+    make_reorders()
     out = {}
     for name in cases.CASES:
         c = cases.build(name)

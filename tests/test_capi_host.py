@@ -237,6 +237,40 @@ def test_reorder_pd(eng):
         api.reorder_primitive_desc(eng, plain, eng, api.MemoryDesc((256, 64), dt.S8, api.TAG_AB))
 
 
+def test_quantising_reorder_pd(eng):
+    """Attribute checks of src/common/reorder.cpp:96-146 and simple_reorder.hpp:2498-2547."""
+    f32 = api.MemoryDesc((8, 16), dt.F32, api.TAG_AB)
+    s8 = api.MemoryDesc((8, 16), dt.S8, api.TAG_AB)
+    a = api.PrimitiveAttr()
+    a.set_scales(api.ARG_DST, 1, (), dt.F32)
+    a.set_zero_points(api.ARG_DST, 0, (), dt.S32)
+    pd = api.reorder_primitive_desc(eng, f32, eng, s8, a)
+    assert pd.impl_info_str() == "cuda:reorder_quant"
+    md = pd.query_md(api.QUERY_EXEC_ARG_MD, api.ARG_ATTR_SCALES | api.ARG_DST)
+    assert md.dims == [8] and md.data_type == dt.F32
+    a = api.PrimitiveAttr()
+    a.set_scales(api.ARG_SRC, 3, (4, 8), dt.BF16)
+    a.set_zero_points(api.ARG_SRC, 0, (), dt.S32)
+    pd = api.reorder_primitive_desc(eng, s8, eng, f32, a)
+    md = pd.query_md(api.QUERY_EXEC_ARG_MD, api.ARG_ATTR_SCALES | api.ARG_SRC)
+    assert md.dims == [2 * 2] and md.data_type == dt.BF16
+
+    def rejected(src, dst, fill):
+        a = api.PrimitiveAttr()
+        fill(a)
+        with pytest.raises(api.Error):
+            api.reorder_primitive_desc(eng, src, eng, dst, a)
+    rejected(f32, s8, lambda a: a.set_zero_points(api.ARG_SRC, 0, (), dt.S32))   # zero-point on a float tensor
+    rejected(s8, f32, lambda a: a.set_zero_points(api.ARG_DST, 0, (), dt.S32))
+    rejected(f32, s8, lambda a: a.set_scales(api.ARG_WEIGHTS, 0, (), dt.F32))    # scales go with src / dst only
+    rejected(f32, s8, lambda a: a.set_scales(api.ARG_SRC, 3, (3, 4), dt.F32))    # groups must divide the dims
+    rejected(f32, s8, lambda a: a.set_scales(api.ARG_DST, 3, (2, 2), dt.F32))    # no groups on the dst side
+    rejected(f32, s8, lambda a: (a.set_scales(api.ARG_SRC, 1, (), dt.F32), a.set_scales(api.ARG_DST, 2, (), dt.F32)))
+    po = api.PostOps()
+    po.append_eltwise(0x20, 0.0, 0.0)
+    rejected(f32, s8, lambda a: a.set_post_ops(po))                               # sum is the only post-op
+
+
 @pytest.mark.skipif(_have_gpu(), reason="checks behaviour on a machine without a CUDA device")
 def test_no_device_means_no_execution(eng):
     md = api.MemoryDesc((4, 4), dt.F32, api.TAG_AB)

@@ -1,0 +1,103 @@
+"""Quantising reorder: the oracle against the reference (stored outputs and, where the
+reference library has been built, the library itself), and the CUDA engine against the oracle.
+
+Every step of this operation is one f32 operation on one element, so every destination
+type is compared bit for bit.
+"""
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+import cases
+from golden.make_golden import reorder_input_digest
+from onednn_b200 import dtypes as dt
+from onednn_b200.workloads import Quant
+from oracle import binding as B
+
+GOLD = np.load(Path(__file__).parent / "golden" / "reorder_outputs.npz")
+NAMES = list(cases.REORDER_CASES)
+
+
+def _bytes(a):
+    return np.ascontiguousarray(a).view(np.uint8).reshape(-1)
+
+
+@pytest.mark.parametrize("name", NAMES)
+def test_oracle_matches_reference_golden(name):
+    c = cases.build_reorder(name)
+    if str(GOLD[name + "/inputs_sha256"]) != reorder_input_digest(c):
+        pytest.skip("numpy produced different inputs than when the fixture was made")
+    got, want = _bytes(B.run_oracle_reorder(c)), GOLD[name + "/bytes"]
+    assert np.array_equal(got, want), "%d of %d bytes differ" % (int((got != want).sum()), want.size)
+
+
+def test_every_reorder_case_has_a_fixture_and_both_reference_implementations_are_covered():
+    impls = set()
+    for name in NAMES:
+        assert name + "/bytes" in GOLD.files
+        impls.add(str(GOLD[name + "/impl"]))
+    assert {"jit:uni", "simple:any"} <= impls
+
+
+@pytest.mark.skipif(not B.have_reference(), reason="reference library not built here")
+@pytest.mark.parametrize("name", NAMES)
+def test_oracle_matches_reference_library(name):
+    c = cases.build_reorder(name)
+    want, impl = B.run_reference_reorder(c)
+    assert np.array_equal(_bytes(B.run_oracle_reorder(c)), _bytes(want)), impl
+
+
+def test_oracle_formula_by_hand():
+    """dst = sat_rne(src_scale * (src - zp) * (1 / dst_scale) + dst_zp), ties to even."""
+    from onednn_b200.workloads import ReorderCase
+    src = np.array([[-128, -3, 0, 5, 7, 127, 9, 11]], dtype=np.int8)
+    c = ReorderCase("hand", 1, 8, src, dt.S8, dt.U8, src_scale=Quant(np.float32([0.5]), dt.F32, 0),
+                    dst_scale=Quant(np.float32([2.0]), dt.F32, 0), src_zp=Quant(np.int32([1]), dt.S32, 0),
+                    dst_zp=Quant(np.int32([10]), dt.S32, 0))
+    # (s - 1) / 4 + 10: -22.25 -> 0 (saturated), 9, 9.75 -> 10, 11, 11.5 -> 12 (tie to even), 41.5 -> 42, 12, 12.5 -> 12
+    assert B.run_oracle_reorder(c).tolist() == [[0, 9, 10, 11, 12, 42, 12, 12]]
+
+
+# ---- the CUDA engine ---------------------------------------------------------------------------
+
+@pytest.fixture(scope="module")
+def ctx():
+    from onednn_b200 import api
+    eng = api.Engine()
+    return eng, api.Stream(eng)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name", NAMES)
+def test_cuda_matches_oracle(name, ctx):
+    from onednn_b200 import api
+    c = cases.build_reorder(name)
+    plan = api.ReorderPlan(c, *ctx)
+    assert plan.impl == "cuda:reorder_quant"
+    plan.execute()
+    got, want = _bytes(plan.result()), _bytes(B.run_oracle_reorder(c))
+    assert np.array_equal(got, want), "%s: %d of %d bytes differ" % (name, int((got != want).sum()), want.size)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("src_dt,dst_dt,per_row", [(dt.F32, dt.S8, False), (dt.BF16, dt.U8, True), (dt.F32, dt.U8, True)])
+def test_cuda_quantize_activations_full_size(src_dt, dst_dt, per_row, ctx):
+    """The activations of the 4096 x 4096 int8 benchmark problem, quantised on the device."""
+    from onednn_b200 import api, workloads as W
+    c = W.quantize_case(4096, 4096, src_dt, dst_dt, per_row=per_row)
+    plan = api.ReorderPlan(c, *ctx)
+    plan.execute()
+    got, want = plan.result(), B.run_oracle_reorder(c)
+    assert np.array_equal(got, want)
+    # quantise -> dequantise returns every value to within half a quantisation step
+    back = W.ReorderCase("dq", c.rows, c.cols, got, dst_dt, dt.F32, src_scale=c.dst_scale, src_zp=c.dst_zp)
+    plan2 = api.ReorderPlan(back, *ctx)
+    plan2.execute()
+    x = dt.to_f32(c.src, src_dt)
+    step = c.dst_scale.data.reshape(-1, 1) if per_row else c.dst_scale.data[0]
+    lo, hi = (-128, 127) if dst_dt == dt.S8 else (0, 255)
+    zp = 0 if c.dst_zp is None else int(c.dst_zp.data[0])
+    inside = (x / step + zp > lo) & (x / step + zp < hi)
+    err = np.abs(plan2.result() - x)
+    assert (err[inside] <= (0.5 * step * np.ones_like(x))[inside] * 1.001 + 1e-6).all()

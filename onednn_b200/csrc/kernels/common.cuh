@@ -134,6 +134,20 @@ __device__ __forceinline__ int sat_rne_s32(float v) {
     return __float2int_rn(v);
 }
 
+// f32 -> s8 / u8: round to nearest even and saturate in one instruction.  Rounding and
+// clamping to integer bounds commute, so this equals the reference's clamp-then-round; NaN
+// gives 0 in both.  The result is the byte, zero-extended.
+__device__ __forceinline__ uint32_t cvt_sat_s8(float v) {
+    int r;
+    asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(r) : "f"(v));
+    return (uint32_t)r & 0xffu;
+}
+__device__ __forceinline__ uint32_t cvt_sat_u8(float v) {
+    uint32_t r;
+    asm("cvt.rni.sat.u8.f32 %0, %1;" : "=r"(r) : "f"(v));
+    return r & 0xffu;
+}
+
 __device__ __forceinline__ void store_f32(int dt, float v, void *ptr, int64_t idx) {
     switch (dt) {
         case B200_DT_F32: ((float *)ptr)[idx] = v; break;

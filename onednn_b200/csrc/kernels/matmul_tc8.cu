@@ -287,20 +287,6 @@ __device__ __forceinline__ void eltwise_simple_chunk(const b200_postop_t &e, flo
     }
 }
 
-// f32 -> s8 / u8: round to nearest even and saturate in one instruction.  Rounding and
-// clamping to integer bounds commute, so this equals the reference's clamp-then-round; NaN
-// gives 0 in both.  The result is the byte, zero-extended.
-__device__ __forceinline__ uint32_t cvt_sat_s8(float v) {
-    int r;
-    asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(r) : "f"(v));
-    return (uint32_t)r & 0xffu;
-}
-__device__ __forceinline__ uint32_t cvt_sat_u8(float v) {
-    uint32_t r;
-    asm("cvt.rni.sat.u8.f32 %0, %1;" : "=r"(r) : "f"(v));
-    return r & 0xffu;
-}
-
 // pack CH final f32 values of one row and store them (or the valid part of them)
 __device__ __forceinline__ void store_row_at(const b200_matmul_params_t &p, const float (&y)[CH], char *drow, int64_t nvalid) {
     const bool aligned = nvalid == CH && ((uintptr_t)drow & 15) == 0;

@@ -91,8 +91,8 @@ __device__ __forceinline__ uint32_t encode(float d) {
         case B200_DT_F32: return __float_as_uint(d);
         case B200_DT_BF16: return f32_to_bf16_bits(d);
         case B200_DT_S32: return (uint32_t)sat_rne_s32(d);
-        case B200_DT_S8: return (uint32_t)sat_rne_s8(d) & 0xffu;
-        default: return (uint32_t)sat_rne_u8(d); // u8: already 0..255
+        case B200_DT_S8: return cvt_sat_s8(d);
+        default: return cvt_sat_u8(d); // u8
     }
 }
 
@@ -155,7 +155,7 @@ __global__ void __launch_bounds__(256) reorder_quant_rows_kernel(const __grid_co
             if (a.kind_ss == K_ROW) s_ss = __uint_as_float(q_ss[u]);
             if (a.kind_ds == K_ROW) s_rds = __fdiv_rn(1.f, __uint_as_float(q_ds[u]));
             if (a.kind_sz == K_ROW) s_zp = (int)q_sz[u];
-            if (COLQ) {
+            if (COLQ && (a.kind_ss == K_ROW || a.kind_ds == K_ROW || a.kind_sz == K_ROW)) {
 #pragma unroll
                 for (int e = 0; e < V; ++e) {
                     if (a.kind_ss == K_ROW) v_ss[e] = s_ss;

@@ -34,6 +34,7 @@
 #include <cuda.h>
 
 #include <cstddef>
+#include <cstdlib>
 #include <mutex>
 
 #include "common.cuh"
@@ -48,18 +49,27 @@ constexpr int STAGES = 4;
 constexpr int A_BYTES = BM * BK; // 16 KiB
 constexpr int B_BYTES = BN * BK; // 32 KiB
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+// Pair kernel (two CTAs of a cluster on one 256 x 256 tile, tcgen05 cta_group::2): each CTA
+// stages its 128 rows of A and its half of the tile's weight rows, so a stage is 32 KiB and six
+// of them fit where the single-CTA kernel has four.
+constexpr int PAIR_STAGES = 6;
+constexpr int PAIR_B_BYTES = B_BYTES / 2;
+constexpr int PAIR_STAGE_BYTES = A_BYTES + PAIR_B_BYTES;
+constexpr int MAX_STAGES = 6;
+static_assert(PAIR_STAGES * PAIR_STAGE_BYTES == STAGES * STAGE_BYTES, "both kernels use the same shared memory");
 constexpr int EPI_WARPS = 16;                 // four per TMEM lane quarter, each takes a quarter of the columns
 constexpr int NUM_THREADS = 64 + 32 * EPI_WARPS;
 constexpr int EPI_COLS = BN / (EPI_WARPS / 4); // columns per epilogue warp
 constexpr int CH = 16;                        // columns per epilogue chunk (held in registers)
 constexpr uint32_t TMEM_COLS = 512;
-constexpr uint32_t WAIT_SPINS = 1u << 24; // bounded wait: of the order of a second with the back-off below
+constexpr uint32_t WAIT_TRIES = 1u << 20; // bounded wait: a million suspended waits of up to a microsecond
+constexpr uint32_t WAIT_SPINS = 1u << 22; // drain loop of the producer: polls 64 ns apart
 
 enum : uint32_t { ST_WAIT_FULL = 0x1, ST_WAIT_EMPTY = 0x2, ST_WAIT_TMEM_FULL = 0x4, ST_WAIT_TMEM_EMPTY = 0x8 };
 
 struct smem_ctrl_t {
-    uint64_t full[STAGES];
-    uint64_t empty[STAGES];
+    uint64_t full[MAX_STAGES];
+    uint64_t empty[MAX_STAGES];
     uint64_t tmem_full[2];
     uint64_t tmem_empty[2];
     uint32_t tmem_base;
@@ -104,12 +114,25 @@ __device__ __forceinline__ bool mbar_test(uint64_t *bar, uint32_t parity) {
             : "memory");
     return ok != 0;
 }
-// bounded wait; false when it ran out or another role already gave up
+// one wait of at most about a microsecond, suspended in hardware: a waiting thread issues
+// no instructions and makes no shared-memory accesses until the phase completes or the time
+// runs out
+__device__ __forceinline__ bool mbar_try(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(smem_u32(bar)), "r"(parity), "r"(1000u)
+            : "memory");
+    return ok != 0;
+}
+// bounded wait (of the order of a second); false when it ran out or another role already gave up
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, smem_ctrl_t *c, uint32_t *status, uint32_t code) {
-    for (uint32_t i = 0; i < WAIT_SPINS; ++i) {
-        if (mbar_test(bar, parity)) return true;
+    for (uint32_t i = 0; i < WAIT_TRIES; ++i) {
+        if (mbar_try(bar, parity)) return true;
         if (c->abort) return false;
-        if (i > 64) __nanosleep(32);
     }
     c->abort = 1;
     if (status) atomicOr(status, code);
@@ -130,6 +153,63 @@ __device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fe
 __device__ __forceinline__ void tcgen05_commit(uint64_t *bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
                  : "memory");
+}
+
+// ---- two-CTA (cluster) forms ---------------------------------------------------------------
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// address of the same shared-memory location in the CTA with the given rank of this cluster
+__device__ __forceinline__ uint32_t cluster_map(uint32_t saddr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// TMA load of the pair kernel: the bytes land in this CTA's shared memory, their count is
+// reported to the barrier at bar_cluster_addr (the leader CTA's)
+__device__ __forceinline__ void tma_load_2d_pair(void *dst, const CUtensorMap *map, int c0, int c1, uint32_t bar_cluster_addr) {
+    asm volatile(
+            "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+            :
+            : "r"(smem_u32(dst)), "l"(map), "r"(bar_cluster_addr), "r"(c0), "r"(c1)
+            : "memory");
+}
+// completion of the leader's earlier MMAs arrives on the barrier at this offset in both CTAs
+__device__ __forceinline__ void tcgen05_commit_pair(uint64_t *bar) {
+    const uint16_t both = 3;
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
+                         smem_u32(bar)),
+                 "h"(both)
+                 : "memory");
+}
+template <bool FP8>
+__device__ __forceinline__ void tcgen05_mma_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
+    const uint32_t z = 0;
+    if (FP8) {
+        asm volatile(
+                "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t}"
+                :
+                : "r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc), "r"(z)
+                : "memory");
+    } else {
+        asm volatile(
+                "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t}"
+                :
+                : "r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc), "r"(z)
+                : "memory");
+    }
 }
 
 template <bool FP8>
@@ -194,8 +274,32 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
 struct tc8_args_t {
     b200_matmul_params_t p;
     int m_tiles, n_tiles, k_blocks;
-    uint32_t idesc;
+    // Work units: unit u < full_units is tile u (BM x BN); the tiles after that -- those of a
+    // last, less than half full wave -- are each cut into two units of BN / 2 columns, so that
+    // the wave's work spreads over twice as many CTAs.
+    int full_units, units;
+    uint32_t idesc, idesc_half; // instruction descriptors for N = BN and N = BN / 2
 };
+
+struct unit_t {
+    int m0, n0;   // origin of the unit in dst
+    bool wide;    // BN columns (else BN / 2)
+};
+
+// rows: dst rows per tile (BM, or 2 * BM in the pair kernel)
+__device__ __forceinline__ unit_t decode_unit(const tc8_args_t &a, int u, int rows) {
+    unit_t r;
+    int tile = u, off = 0;
+    r.wide = u < a.full_units;
+    if (!r.wide) {
+        const int h = u - a.full_units;
+        tile = a.full_units + (h >> 1);
+        off = (h & 1) * (BN / 2);
+    }
+    r.m0 = (tile % a.m_tiles) * rows; // m fastest
+    r.n0 = (tile / a.m_tiles) * BN + off;
+    return r;
+}
 
 // ---- epilogue on CH columns of one row ---------------------------------------------------
 //
@@ -575,7 +679,15 @@ __device__ __forceinline__ void epilogue_chunk(const b200_matmul_params_t &p, co
 
 // 18 warps land 5 + 5 + 4 + 4 on the four schedulers, so a thread may use at most
 // 16384 / (5 * 32) = 102 registers; declaring 640 threads makes ptxas stay within that.
-template <bool FP8, int EPI, int SUM, bool PEERS = false>
+//
+// PAIR: the two CTAs of a cluster compute one tile of 2 * BM rows together (tcgen05
+// cta_group::2).  CTA r stages rows [r * BM, +BM) of the tile's activations and half r of its
+// weight rows; all copies report to the leader's (rank 0) full barriers; the leader's thread
+// issues the MMAs, which read both CTAs' shared memory and write each CTA's rows into that
+// CTA's tensor memory; its commits arrive on the empty / accumulator-ready barriers of both
+// CTAs; each CTA's epilogue warps convert its own rows and arrive on the leader's
+// accumulator-free barrier.  Per tile this moves 2/3 of the bytes from L2 to shared memory.
+template <bool FP8, int EPI, int SUM, bool PEERS = false, bool PAIR = false>
 __global__ void __launch_bounds__(640, 1) matmul_tc8_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const __grid_constant__ CUtensorMap tmap_b, const __grid_constant__ tc8_args_t args) {
     extern __shared__ uint8_t smem_raw[];
@@ -583,30 +695,44 @@ __global__ void __launch_bounds__(640, 1) matmul_tc8_kernel(const __grid_constan
     smem_ctrl_t *ctrl = (smem_ctrl_t *)(smem + (size_t)STAGES * STAGE_BYTES);
     const b200_matmul_params_t &p = args.p;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int num_tiles = args.m_tiles * args.n_tiles;
     const int KB = args.k_blocks;
+    constexpr int NST = PAIR ? PAIR_STAGES : STAGES;
+    constexpr int SBYTES = PAIR ? PAIR_STAGE_BYTES : STAGE_BYTES;   // one stage
+    constexpr int BBYTES = PAIR ? PAIR_B_BYTES : B_BYTES;           // its weights part (wide unit)
+    const uint32_t rank = PAIR ? cluster_ctarank() : 0;             // 0: leader
+    // this CTA's (pair's) first unit and the stride over units
+    const int unit0 = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x, ustep = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
+    constexpr int TILE_ROWS = PAIR ? 2 * BM : BM;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES; ++s) {
+        for (int s = 0; s < NST; ++s) {
             mbar_init(&ctrl->full[s], 1);
             mbar_init(&ctrl->empty[s], 1);
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(&ctrl->tmem_full[a], 1);
-            mbar_init(&ctrl->tmem_empty[a], EPI_WARPS);
+            mbar_init(&ctrl->tmem_empty[a], PAIR ? 2 * EPI_WARPS : EPI_WARPS); // the pair's leader hears from both CTAs
         }
         ctrl->abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ctrl->tmem_base)),
-                     "r"(TMEM_COLS)
-                     : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        if (PAIR) { // the same warp of both CTAs, together
+            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ctrl->tmem_base)),
+                         "r"(TMEM_COLS)
+                         : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+        } else {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ctrl->tmem_base)),
+                         "r"(TMEM_COLS)
+                         : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        }
     }
     tcgen05_fence_before();
     __syncthreads();
+    if (PAIR) cluster_sync_all(); // both CTAs' barriers exist before either signals the other's
     tcgen05_fence_after();
     const uint32_t tmem_base = ctrl->tmem_base;
 
@@ -615,21 +741,36 @@ __global__ void __launch_bounds__(640, 1) matmul_tc8_kernel(const __grid_constan
         if (lane == 0) {
             uint32_t it = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-                const int m0 = (tile % args.m_tiles) * BM, n0 = (tile / args.m_tiles) * BN;
+            for (int u = unit0; u < args.units && ok; u += ustep) {
+                const unit_t un = decode_unit(args, u, TILE_ROWS);
                 for (int kb = 0; kb < KB; ++kb, ++it) {
-                    const uint32_t s = it % STAGES, r = it / STAGES;
+                    const uint32_t s = it % NST, r = it / NST;
                     if (!(ok = mbar_wait(&ctrl->empty[s], (r & 1) ^ 1, ctrl, p.status, ST_WAIT_EMPTY))) break;
-                    mbar_expect_tx(&ctrl->full[s], STAGE_BYTES);
-                    uint8_t *sa = smem + (size_t)s * STAGE_BYTES;
-                    tma_load_2d(sa, &tmap_a, kb * BK, m0, &ctrl->full[s]);
-                    tma_load_2d(sa + A_BYTES, &tmap_b, kb * BK, n0, &ctrl->full[s]);
+                    uint8_t *sa = smem + (size_t)s * SBYTES;
+                    if (PAIR) {
+                        // the leader's barrier counts the bytes of both CTAs
+                        const uint32_t bar = cluster_map(smem_u32(&ctrl->full[s]), 0);
+                        if (rank == 0) mbar_expect_tx(&ctrl->full[s], 2 * (un.wide ? SBYTES : A_BYTES + BBYTES / 2));
+                        tma_load_2d_pair(sa, &tmap_a, kb * BK, un.m0 + (int)rank * BM, bar);
+                        // the weights map's box is BN / 4 rows; this CTA's half of the unit's columns
+                        const int nb = un.n0 + (int)rank * (un.wide ? BN / 2 : BN / 4);
+                        tma_load_2d_pair(sa + A_BYTES, &tmap_b, kb * BK, nb, bar);
+                        if (un.wide) tma_load_2d_pair(sa + A_BYTES + BBYTES / 2, &tmap_b, kb * BK, nb + BN / 4, bar);
+                    } else {
+                        mbar_expect_tx(&ctrl->full[s], un.wide ? STAGE_BYTES : A_BYTES + B_BYTES / 2);
+                        tma_load_2d(sa, &tmap_a, kb * BK, un.m0, &ctrl->full[s]);
+                        // the weights map's box is BN / 2 rows: a wide unit takes two of them, one after the other
+                        tma_load_2d(sa + A_BYTES, &tmap_b, kb * BK, un.n0, &ctrl->full[s]);
+                        if (un.wide) tma_load_2d(sa + A_BYTES + B_BYTES / 2, &tmap_b, kb * BK, un.n0 + BN / 2, &ctrl->full[s]);
+                    }
                 }
             }
-            // drain: every copy this thread issued must have landed before the CTA may exit
+            // drain: every copy issued must have landed before the CTA may exit.  In the pair
+            // kernel the leader's barriers cover both CTAs' copies, and the other CTA stays
+            // until the leader has passed the cluster barrier at the end.
             const uint32_t issued = it;
-            for (uint32_t j = issued > STAGES ? issued - STAGES : 0; j < issued; ++j) {
-                const uint32_t s = j % STAGES, r = j / STAGES;
+            for (uint32_t j = issued > NST ? issued - NST : 0; j < issued && rank == 0; ++j) {
+                const uint32_t s = j % NST, r = j / NST;
                 for (uint32_t i = 0; i < WAIT_SPINS; ++i) {
                     if (mbar_test(&ctrl->full[s], r & 1)) break;
                     __nanosleep(64);
@@ -638,27 +779,37 @@ __global__ void __launch_bounds__(640, 1) matmul_tc8_kernel(const __grid_constan
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
-        if (lane == 0) {
+        if (lane == 0 && rank == 0) {
             uint32_t it = 0, tile_i = 0;
             bool ok = true;
             // descriptors of stage 0; a stage further on is STAGE_BYTES / 16 more in the address field
             const uint64_t adesc0 = make_smem_desc(smem_u32(smem)), bdesc0 = make_smem_desc(smem_u32(smem) + A_BYTES);
-            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tile_i) {
+            for (int u = unit0; u < args.units && ok; u += ustep, ++tile_i) {
                 const uint32_t a = tile_i & 1, use = tile_i >> 1;
+                const uint32_t idesc = u < args.full_units ? args.idesc : args.idesc_half;
                 if (!(ok = mbar_wait(&ctrl->tmem_empty[a], (use & 1) ^ 1, ctrl, p.status, ST_WAIT_TMEM_EMPTY))) break;
                 tcgen05_fence_after();
                 const uint32_t tmem_d = tmem_base + a * BN;
                 for (int kb = 0; kb < KB; ++kb, ++it) {
-                    const uint32_t s = it % STAGES, r = it / STAGES;
+                    const uint32_t s = it % NST, r = it / NST;
                     if (!(ok = mbar_wait(&ctrl->full[s], r & 1, ctrl, p.status, ST_WAIT_FULL))) break;
                     tcgen05_fence_after();
-                    const uint64_t adesc = adesc0 + (uint64_t)(s * (STAGE_BYTES >> 4)), bdesc = bdesc0 + (uint64_t)(s * (STAGE_BYTES >> 4));
+                    const uint64_t adesc = adesc0 + (uint64_t)(s * (SBYTES >> 4)), bdesc = bdesc0 + (uint64_t)(s * (SBYTES >> 4));
+#ifndef TC8_ABL_NOMMA
 #pragma unroll
                     for (int k = 0; k < BK / 32; ++k) // 32 bytes of K per instruction: +2 in 16-byte units
-                        tcgen05_mma<FP8>(tmem_d, adesc + 2 * k, bdesc + 2 * k, args.idesc, (kb | k) != 0);
-                    tcgen05_commit(&ctrl->empty[s]);
+                        if (PAIR)
+                            tcgen05_mma_pair<FP8>(tmem_d, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0);
+                        else
+                            tcgen05_mma<FP8>(tmem_d, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0);
+#endif
+                    if (PAIR) tcgen05_commit_pair(&ctrl->empty[s]);
+                    else tcgen05_commit(&ctrl->empty[s]);
                 }
-                if (ok) tcgen05_commit(&ctrl->tmem_full[a]);
+                if (ok) {
+                    if (PAIR) tcgen05_commit_pair(&ctrl->tmem_full[a]);
+                    else tcgen05_commit(&ctrl->tmem_full[a]);
+                }
             }
         }
     } else {
@@ -681,13 +832,16 @@ __global__ void __launch_bounds__(640, 1) matmul_tc8_kernel(const __grid_constan
         const bool bias_per_col = p.bias && !p.bias_sm;
         uint32_t tile_i = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tile_i) {
-            const int64_t m0 = (int64_t)(tile % args.m_tiles) * BM;
-            const int64_t n0 = (int64_t)(tile / args.m_tiles) * BN + half * EPI_COLS;
+        for (int u = unit0; u < args.units && ok; u += ustep, ++tile_i) {
+            const unit_t un = decode_unit(args, u, TILE_ROWS);
+            // this warp's share of the unit's columns: a quarter of them, in chunks of CH
+            const int ecols = un.wide ? EPI_COLS : EPI_COLS / 2, nch = ecols / CH;
+            const int64_t m0 = un.m0 + (int64_t)rank * BM;
+            const int64_t n0 = (int64_t)un.n0 + half * ecols;
             const uint32_t a = tile_i & 1, use = tile_i >> 1;
-            // per-column vectors of this warp's columns (4 per lane)
+            // per-column vectors of this warp's columns
             __syncwarp();
-            for (int j = lane; j < EPI_COLS; j += 32) {
+            for (int j = lane; j < ecols; j += 32) {
                 const int64_t n = n0 + j;
                 const bool in = n < p.N;
                 wscale[j] = (in && p.wei_scale.ptr) ? load_f32(p.wei_scale.dt, p.wei_scale.ptr, n * p.wei_scale.s1) : 1.f;
@@ -700,7 +854,7 @@ __global__ void __launch_bounds__(640, 1) matmul_tc8_kernel(const __grid_constan
             }
             __syncwarp();
             const int64_t m = m0 + quarter * 32 + lane;
-            const uint32_t trow = tmem_base + ((uint32_t)(quarter * 32) << 16) + a * BN + half * EPI_COLS;
+            const uint32_t trow = tmem_base + ((uint32_t)(quarter * 32) << 16) + a * BN + half * ecols;
             // Prior destination bytes of this warp's columns (sum post-op): requested now, for
             // the whole tile, so that the DRAM latency passes while the accumulator is still
             // being computed.  One aligned 16-byte read per chunk where that is possible.
@@ -710,7 +864,7 @@ __global__ void __launch_bounds__(640, 1) matmul_tc8_kernel(const __grid_constan
             static_assert(NCH == 4, "the prefetch registers below are named for four chunks");
             uint4 ob0 = make_uint4(0, 0, 0, 0), ob1 = ob0, ob2 = ob0, ob3 = ob0;
             const bool of0 = sum8 && n0 + 1 * CH <= p.N, of1 = sum8 && n0 + 2 * CH <= p.N;
-            const bool of2 = sum8 && n0 + 3 * CH <= p.N, of3 = sum8 && n0 + 4 * CH <= p.N;
+            const bool of2 = sum8 && nch > 2 && n0 + 3 * CH <= p.N, of3 = sum8 && nch > 2 && n0 + 4 * CH <= p.N;
             if (of0) ob0 = *(const uint4 *)(drow0);
             if (of1) ob1 = *(const uint4 *)(drow0 + CH);
             if (of2) ob2 = *(const uint4 *)(drow0 + 2 * CH);
@@ -720,10 +874,14 @@ __global__ void __launch_bounds__(640, 1) matmul_tc8_kernel(const __grid_constan
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tcgen05_fence_after();
-            // one copy of the chunk code, executed four times (the unrolled form does not fit
+            // one copy of the chunk code, executed once per chunk (the unrolled form does not fit
             // the instruction cache); the prefetched bytes rotate through named registers
 #pragma unroll 1
-            for (int c = 0; c < NCH; ++c) {
+#ifdef TC8_ABL_NOEPI
+            for (int c = 0; c < 0; ++c) {
+#else
+            for (int c = 0; c < nch; ++c) {
+#endif
                 uint32_t v[CH];
                 tmem_ld16_issue(trow + c * CH, v);
                 tmem_ld_wait(v);
@@ -736,17 +894,24 @@ __global__ void __launch_bounds__(640, 1) matmul_tc8_kernel(const __grid_constan
             }
             tcgen05_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&ctrl->tmem_empty[a]);
-            if (PEERS) mirror_block(p, m0 + quarter * 32, n0, EPI_COLS, lane); // after the accumulator is handed back
+            if (lane == 0) {
+                if (PAIR && rank != 0) mbar_arrive_cluster(cluster_map(smem_u32(&ctrl->tmem_empty[a]), 0));
+                else mbar_arrive(&ctrl->tmem_empty[a]);
+            }
+            if (PEERS) mirror_block(p, m0 + quarter * 32, n0, ecols, lane); // after the accumulator is handed back
         }
     }
 
     __syncwarp();
     tcgen05_fence_before();
     __syncthreads();
+    if (PAIR) cluster_sync_all(); // neither CTA leaves (or frees tensor memory) while the other may still reach into it
     if (warp == 1) {
         tcgen05_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+        if (PAIR)
+            asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+        else
+            asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
     }
 }
 
@@ -784,7 +949,7 @@ static bool make_tmap(CUtensorMap *map, const void *base, int64_t rows, int64_t 
             == CUDA_SUCCESS;
 }
 
-static uint32_t make_idesc(bool fp8, int a_dt, int b_dt) {
+static uint32_t make_idesc(bool fp8, int a_dt, int b_dt, int n, int m) {
     uint32_t d = 0;
     if (fp8) {
         d |= 1u << 4;                                       // accumulator f32
@@ -796,8 +961,8 @@ static uint32_t make_idesc(bool fp8, int a_dt, int b_dt) {
         d |= (b_dt == B200_DT_S8 ? 1u : 0u) << 10;          // B format
     }
     // bits 15 / 16: A and B are K-major (0)
-    d |= (uint32_t)(BN >> 3) << 17;
-    d |= (uint32_t)(BM >> 4) << 24;
+    d |= (uint32_t)(n >> 3) << 17;
+    d |= (uint32_t)(m >> 4) << 24;
     return d;
 }
 
@@ -831,22 +996,43 @@ extern "C" int b200_matmul_tc8_launch(const b200_matmul_params_t *p, b200_stream
     if (((uintptr_t)p->src & 15) || ((uintptr_t)p->wei & 15) || (p->src_sm & 15) || (wpitch & 15)) return B200_ERR_BAD_ARG;
     if (p->M > INT32_MAX || p->N > INT32_MAX || p->K > INT32_MAX) return B200_ERR_TOO_LARGE;
 
-    CUtensorMap ta, tb;
-    if (!make_tmap(&ta, p->src, p->M, p->K, p->src_sm, BM)) return (int)cudaErrorUnknown;
-    if (!make_tmap(&tb, p->wei, p->N, p->K, wpitch, BN)) return (int)cudaErrorUnknown;
-
-    tc8_args_t a;
-    a.p = *p;
-    a.m_tiles = (int)((p->M + BM - 1) / BM);
-    a.n_tiles = (int)((p->N + BN - 1) / BN);
-    a.k_blocks = (int)((p->K + BK - 1) / BK);
-    a.idesc = make_idesc(f8, p->src_dt, p->wei_dt);
-
     int dev = 0, sms = 148;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    // Two CTAs per tile of 2 * BM rows (cta_group::2): a third fewer bytes from L2 per tile, but
+    // a longer round trip per pipeline stage (both CTAs' copies report to the leader, its
+    // commits travel back to both) and work units twice as large.  Measured on 148 SMs it wins
+    // from about eight waves of single-CTA tiles upwards (8192^3: +4 %, 16384 x 28672 x 8192:
+    // +8 %) and loses below (4096^3: -3 %).  ONEDNN_B200_TC8_PAIR=0 / 1 forces the choice.
+    // Mirrored destinations (N-split over GPUs) use the single-CTA kernel.
+    const char *pe = std::getenv("ONEDNN_B200_TC8_PAIR");
+    const int64_t single_tiles = ((p->M + BM - 1) / BM) * ((p->N + BN - 1) / BN);
+    const bool pair_wanted = pe && (pe[0] == '0' || pe[0] == '1') ? pe[0] == '1' : single_tiles >= (int64_t)8 * sms;
+    const bool pair = pair_wanted && p->M > BM && p->n_dst_peers == 0 && sms >= 2;
+    const int tile_rows = pair ? 2 * BM : BM;
+    const int workers = pair ? sms / 2 : sms; // CTAs or CTA pairs working at the same time
+
+    CUtensorMap ta, tb;
+    if (!make_tmap(&ta, p->src, p->M, p->K, p->src_sm, BM)) return (int)cudaErrorUnknown;
+    // weights box: half of a CTA's share of a full-width unit (two boxes per wide unit, one per half-width unit)
+    if (!make_tmap(&tb, p->wei, p->N, p->K, wpitch, pair ? BN / 4 : BN / 2)) return (int)cudaErrorUnknown;
+
+    tc8_args_t a;
+    a.p = *p;
+    a.m_tiles = (int)((p->M + tile_rows - 1) / tile_rows);
+    a.n_tiles = (int)((p->N + BN - 1) / BN);
+    a.k_blocks = (int)((p->K + BK - 1) / BK);
+    a.idesc = make_idesc(f8, p->src_dt, p->wei_dt, BN, tile_rows);
+    a.idesc_half = make_idesc(f8, p->src_dt, p->wei_dt, BN / 2, tile_rows);
+
     const int64_t tiles = (int64_t)a.m_tiles * a.n_tiles;
-    const unsigned grid = (unsigned)(tiles < sms ? tiles : sms);
+    if (tiles > INT32_MAX / 2) return B200_ERR_TOO_LARGE;
+    // a last wave that fills at most half of the workers is cut into half-width units
+    const int64_t tail = tiles > workers ? tiles % workers : 0;
+    const bool split = tail > 0 && 2 * tail <= workers;
+    a.full_units = (int)(split ? tiles - tail : tiles);
+    a.units = (int)(split ? tiles + tail : tiles);
+    const unsigned grid = (unsigned)(a.units < workers ? a.units : workers) * (pair ? 2u : 1u);
 
     // epilogue evaluation mode
     int epi = EPI_NONE;
@@ -880,15 +1066,15 @@ extern "C" int b200_matmul_tc8_launch(const b200_matmul_params_t *p, b200_stream
     }
 
     typedef void (*kernel_t)(const CUtensorMap, const CUtensorMap, const tc8_args_t);
-#define TC8_ROW(F) \
-    {{matmul_tc8_kernel<F, EPI_NONE, SUM_NONE>, nullptr, nullptr}, \
-            {matmul_tc8_kernel<F, EPI_SIMPLE, SUM_NONE>, matmul_tc8_kernel<F, EPI_SIMPLE, SUM_8BIT>, \
-                    matmul_tc8_kernel<F, EPI_SIMPLE, SUM_OTHER>}, \
-            {matmul_tc8_kernel<F, EPI_GELU_Q, SUM_NONE>, matmul_tc8_kernel<F, EPI_GELU_Q, SUM_8BIT>, nullptr}, \
-            {matmul_tc8_kernel<F, EPI_GENERIC, SUM_NONE>, nullptr, nullptr}}
-    static const kernel_t table[2][4][3] = {TC8_ROW(false), TC8_ROW(true)};
+#define TC8_ROW(F, P) \
+    {{matmul_tc8_kernel<F, EPI_NONE, SUM_NONE, false, P>, nullptr, nullptr}, \
+            {matmul_tc8_kernel<F, EPI_SIMPLE, SUM_NONE, false, P>, matmul_tc8_kernel<F, EPI_SIMPLE, SUM_8BIT, false, P>, \
+                    matmul_tc8_kernel<F, EPI_SIMPLE, SUM_OTHER, false, P>}, \
+            {matmul_tc8_kernel<F, EPI_GELU_Q, SUM_NONE, false, P>, matmul_tc8_kernel<F, EPI_GELU_Q, SUM_8BIT, false, P>, nullptr}, \
+            {matmul_tc8_kernel<F, EPI_GENERIC, SUM_NONE, false, P>, nullptr, nullptr}}
+    static const kernel_t table[2][2][4][3] = {{TC8_ROW(false, false), TC8_ROW(true, false)}, {TC8_ROW(false, true), TC8_ROW(true, true)}};
 #undef TC8_ROW
-    kernel_t kern = table[f8 ? 1 : 0][epi][sum];
+    kernel_t kern = table[pair ? 1 : 0][f8 ? 1 : 0][epi][sum];
     if (p->n_dst_peers) {
         // mirrored destinations: built for the epilogues an N-split layer has (bias, simple eltwise), no sum
         kern = nullptr;
@@ -900,17 +1086,38 @@ extern "C" int b200_matmul_tc8_launch(const b200_matmul_params_t *p, b200_stream
     if (!kern) return B200_ERR_UNSUPPORTED;
     // opt in to the large dynamic shared memory once per kernel and device
     static std::mutex attr_mu;
-    static bool attr_done[64][2][4][3] = {};
+    static bool attr_done[64][2][2][4][3] = {};
     {
         std::lock_guard<std::mutex> g(attr_mu);
         static bool attr_done_peers[64][2][4] = {};
-        bool &done = p->n_dst_peers ? attr_done_peers[dev & 63][f8 ? 1 : 0][epi] : attr_done[dev & 63][f8 ? 1 : 0][epi][sum];
+        bool &done = p->n_dst_peers ? attr_done_peers[dev & 63][f8 ? 1 : 0][epi] : attr_done[dev & 63][pair ? 1 : 0][f8 ? 1 : 0][epi][sum];
         if (dev < 64 && !done) {
             cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
             if (e != cudaSuccess) return (int)e;
             done = true;
         }
     }
-    kern<<<grid, NUM_THREADS, SMEM_BYTES, (cudaStream_t)stream>>>(ta, tb, a);
-    return after_launch();
+    if (!pair) {
+        kern<<<grid, NUM_THREADS, SMEM_BYTES, (cudaStream_t)stream>>>(ta, tb, a);
+        return after_launch();
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(NUM_THREADS);
+    cfg.dynamicSmemBytes = SMEM_BYTES;
+    cfg.stream = (cudaStream_t)stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t le = cudaLaunchKernelEx(&cfg, kern, ta, tb, a);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    if (le != cudaSuccess) {
+        (void)cudaGetLastError();
+        return (int)le;
+    }
+    return 0;
 }

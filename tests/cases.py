@@ -139,6 +139,30 @@ def fp8_swish_f32():
     return c
 
 
+def int8_rows300_ragged_zp():
+    """More than two row tiles, ragged in every dim, source zero-point, relu, s8 out."""
+    r, c = _int8_base(300, 200, 144, 31, src_dt=dt.U8, dst_dt=dt.S8)
+    c.src_scale = Quant(_f32([0.02]), dt.F32, 0)
+    c.wei_scale = Quant(_f32(r.uniform(1e-3, 4e-3, 200)), dt.F32, 2)
+    c.src_zp = Quant(np.array([120], dtype=np.int32), dt.S32, 0)
+    c.dst_scale = Quant(_f32([0.4]), dt.F32, 0)
+    c.dst_zp = Quant(np.array([-7], dtype=np.int32), dt.S32, 0)
+    c.bias, c.bias_dt = _f32(r.uniform(-2, 2, (1, 200))), dt.F32
+    c.post_ops = [W.eltwise("relu", 0.1)]
+    return c
+
+
+def int8_rows513_gelu_sum():
+    """Five row tiles (an odd number: the last tile of a CTA pair is half empty), gelu + sum into s8."""
+    c = W.config1(513, 272, 272, seed=32, dst_scale=0.9)
+    return c
+
+
+def fp8_rows260_bf16():
+    c = W.config3(260, 520, 256, seed=33)
+    return c
+
+
 CASES = {
     # the benchmark's configurations at reduced size
     "c0_small": lambda: W.config0(64, 96, 128),
@@ -187,6 +211,9 @@ CASES = {
     "wc_s4_g32_m2_f32dst": _wc_case(2, 32, 128, 32, dt.S4, dst_dt=dt.F32),
     "wc_s8_perN_common_zp": _wc_case(5, 48, 96, 96, dt.S8, zp="common"),
     "wc_u8_g32_nozp": _wc_case(4, 40, 64, 32, dt.U8, zp="none"),
+    "int8_rows300_ragged_zp": int8_rows300_ragged_zp,
+    "int8_rows513_gelu_sum": int8_rows513_gelu_sum,
+    "fp8_rows260_bf16": fp8_rows260_bf16,
     "fp8_f8dst": fp8_f8dst,
     "fp8_swish_f32": fp8_swish_f32,
 }

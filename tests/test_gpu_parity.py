@@ -74,6 +74,29 @@ def test_dispatched_kernel(ctx, name, weights):
     assert_close(c, got, want, "%s via %s" % (name, plan.impl))
 
 
+@pytest.mark.parametrize("name", [n for n in cases.CASES])
+def test_tensor_core_kernel_as_cta_pair(ctx, name, monkeypatch):
+    """The two-CTA form of the int8 / fp8 kernel (tcgen05 cta_group::2), which the dispatcher
+    picks by itself only for large problems, forced on every case with more than 128 rows:
+    same result as the oracle, and bit for bit the single-CTA kernel's."""
+    c = cases.build(name)
+    if c.M <= 128:
+        pytest.skip("one row tile: nothing to pair")
+    monkeypatch.setenv("ONEDNN_B200_TC8_PAIR", "0")
+    plan = api.CasePlan(c, *ctx, weights="any")
+    if "tcgen05_i8" not in plan.impl and "tcgen05_f8" not in plan.impl:
+        pytest.skip("not a case of this kernel")
+    plan.execute()
+    single = plan.result()
+    monkeypatch.setenv("ONEDNN_B200_TC8_PAIR", "1")
+    plan.reset_dst()
+    plan.execute()
+    paired = plan.result()
+    assert np.array_equal(np.ascontiguousarray(single).view(np.uint8), np.ascontiguousarray(paired).view(np.uint8))
+    want = B.run_oracle(c, tanh_mode=1, exact_acc=1 if "tcgen05_i8" in plan.impl else 0)
+    assert_close(c, paired, want, "%s via the CTA-pair kernel" % name)
+
+
 def test_fast_kernels_are_dispatched(ctx):
     eng, strm = ctx
     assert api.CasePlan(cases.build("c1_small"), eng, strm, upload=False).impl == "cuda:sm100:tcgen05_i8"

@@ -217,7 +217,12 @@ static bool accept_tc8(dnnl_primitive_desc *pd) {
         const bool nmajor = wei.strides[1] == 1;
         if (!kmajor && !nmajor) return reject(name, "weights strides not supported"), false;
     }
-    if (!quant_simple(a.scale(DNNL_ARG_SRC), 0)) return reject(name, "src scales must be per-tensor"), false;
+    // source scales: one per tensor, or one per row -- what dynamic (per-token) quantisation of the
+    // activations produces; the API spells it mask M+K with one group spanning all of K
+    const quant_entry_t &ssc = a.scale(DNNL_ARG_SRC);
+    const bool src_per_row = i8 && ssc.set && ssc.mask == 3 && ssc.group_ndims == 2 && ssc.groups[0] == 1 && ssc.groups[1] == K
+            && ssc.dt == dnnl_f32;
+    if (!src_per_row && !quant_simple(ssc, 0)) return reject(name, "src scales must be per-tensor or per-row"), false;
     if (!quant_simple(a.scale(DNNL_ARG_WEIGHTS), 2)) return reject(name, "weights scales must be per-tensor or per-N"), false;
     if (!quant_simple(a.scale(DNNL_ARG_DST), 0)) return reject(name, "dst scales must be per-tensor"), false;
     if (!quant_simple(a.zp(DNNL_ARG_SRC), 0)) return reject(name, "src zero-point must be per-tensor"), false;

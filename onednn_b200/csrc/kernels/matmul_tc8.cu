@@ -317,7 +317,8 @@ __device__ __forceinline__ unit_t decode_unit(const tc8_args_t &a, int u, int ro
 enum { EPI_NONE = 0, EPI_SIMPLE = 1, EPI_GELU_Q = 2, EPI_GENERIC = 3 };
 
 struct epi_consts_t {
-    float src_scale;   // 1 when unset
+    float src_scale;   // 1 when unset; with per-row scales: this lane's row's
+    bool src_per_row;  // the combined scale vector then holds the weights scales alone
     float dst_inv;     // 1 when unset
     bool any_sum;
     int sum_dt;
@@ -558,10 +559,15 @@ __device__ __forceinline__ void epilogue_chunk(const b200_matmul_params_t &p, co
                 const float ws[4] = {a.x, a.y, a.z, a.w}, bs[4] = {b.x, b.y, b.z, b.w};
                 const int cs[4] = {c.x, c.y, c.z, c.w};
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const float acc = FP8 ? __uint_as_float(v[hb + 4 * q + i]) : (float)((int)v[hb + 4 * q + i] - cs[i]);
-                    x[4 * q + i] = fmaf(acc, ws[i], bs[i]); // within 2 ulp of the reference's unfused value
+                float accf[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) accf[i] = FP8 ? __uint_as_float(v[hb + 4 * q + i]) : (float)((int)v[hb + 4 * q + i] - cs[i]);
+                if (k.src_per_row) { // the row's scale is not part of the combined vector
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) accf[i] *= k.src_scale;
                 }
+#pragma unroll
+                for (int i = 0; i < 4; ++i) x[4 * q + i] = fmaf(accf[i], ws[i], bs[i]); // within 3 ulp of the reference's unfused value
             }
 #pragma unroll
             for (int j = 0; j < 8; ++j) g[j] = x[j] * fmaf(g_cub, x[j] * x[j], g_lin);
@@ -822,7 +828,9 @@ __global__ void __launch_bounds__(640, 1) matmul_tc8_kernel(const __grid_constan
         const bool has_comp = !FP8 && p.src_zp.ptr && p.wei_colsum;
         const int zp_src = has_comp ? load_int(p.src_zp.dt, p.src_zp.ptr, 0) : 0;
         epi_consts_t k;
-        k.src_scale = p.src_scale.ptr ? load_f32(p.src_scale.dt, p.src_scale.ptr, 0) : 1.f;
+        k.src_per_row = p.src_scale.ptr && p.src_scale.s0 != 0;
+        const float src_scale_all = (p.src_scale.ptr && !k.src_per_row) ? load_f32(p.src_scale.dt, p.src_scale.ptr, 0) : 1.f;
+        k.src_scale = src_scale_all;
         k.dst_inv = dst_scale_reciprocal(p);
         k.any_sum = has_sum(p);
         k.sum_dt = sum_dt_of(p);
@@ -845,7 +853,7 @@ __global__ void __launch_bounds__(640, 1) matmul_tc8_kernel(const __grid_constan
                 const int64_t n = n0 + j;
                 const bool in = n < p.N;
                 wscale[j] = (in && p.wei_scale.ptr) ? load_f32(p.wei_scale.dt, p.wei_scale.ptr, n * p.wei_scale.s1) : 1.f;
-                wsx[j] = wscale[j] * k.src_scale;
+                wsx[j] = wscale[j] * src_scale_all;
                 bias[j] = (in && bias_per_col) ? load_f32(p.bias_dt, p.bias, n * p.bias_sn) : -0.f;
                 comp[j] = (in && has_comp) ? zp_src * p.wei_colsum[n] : 0;
                 // the int8 path adds the zero-point (+0 when unset) whenever any attribute is set; -0 adds nothing
@@ -854,6 +862,7 @@ __global__ void __launch_bounds__(640, 1) matmul_tc8_kernel(const __grid_constan
             }
             __syncwarp();
             const int64_t m = m0 + quarter * 32 + lane;
+            if (k.src_per_row) k.src_scale = m < p.M ? ((const float *)p.src_scale.ptr)[m] : 1.f;
             const uint32_t trow = tmem_base + ((uint32_t)(quarter * 32) << 16) + a * BN + half * ecols;
             // Prior destination bytes of this warp's columns (sum post-op): requested now, for
             // the whole tile, so that the DRAM latency passes while the accumulator is still
@@ -987,7 +996,10 @@ extern "C" int b200_matmul_tc8_launch(const b200_matmul_params_t *p, b200_stream
     if (p->wei_layout == B200_WEI_KMAJOR) wpitch = p->K;
     else if (p->wei_layout == B200_WEI_PLAIN && p->wei_sk == 1) wpitch = p->wei_sn;
     else return B200_ERR_UNSUPPORTED;
-    if (p->src_scale.ptr && (p->src_scale.s0 || p->src_scale.s1)) return B200_ERR_UNSUPPORTED;
+    // source scales: per tensor, or per row (one K group covering all of K; f32)
+    if (p->src_scale.ptr && (p->src_scale.s0 || p->src_scale.s1)
+            && !(i8 && p->src_scale.s0 == 1 && p->src_scale.g0 == 1 && p->src_scale.g1 >= p->K && p->src_scale.dt == B200_DT_F32))
+        return B200_ERR_UNSUPPORTED;
     if (p->wei_scale.ptr && (p->wei_scale.s0 || p->wei_scale.g1 != 1)) return B200_ERR_UNSUPPORTED;
     if (p->dst_scale.ptr && (p->dst_scale.s0 || p->dst_scale.s1)) return B200_ERR_UNSUPPORTED;
     if (p->src_zp.ptr && (p->src_zp.s0 || p->src_zp.s1 || !p->wei_colsum || f8)) return B200_ERR_UNSUPPORTED;

@@ -163,6 +163,23 @@ def fp8_rows260_bf16():
     return c
 
 
+def int8_per_row_src_scales_bf16():
+    """Dynamic (per-token) quantisation: one source scale per row (mask M+K, one group over K)."""
+    r, c = _int8_base(200, 96, 128, 34, dst_dt=dt.BF16)
+    c.src_scale = Quant(_f32(r.uniform(0.005, 0.05, 200)), dt.F32, 3, (1, 128))
+    c.wei_scale = Quant(_f32(r.uniform(1e-3, 4e-3, 96)), dt.F32, 2)
+    c.bias, c.bias_dt = dt.f32_to_bf16(_f32(r.uniform(-1, 1, (1, 96)))), dt.BF16
+    c.exact, c.rtol, c.atol = False, 1e-2, 1e-2
+    return c
+
+
+def int8_per_row_src_scales_gelu_s8():
+    c = W.config1(160, 64, 96, seed=35, dst_scale=0.7)
+    r = np.random.default_rng(36)
+    c.src_scale = Quant(_f32(r.uniform(0.02, 0.08, 160)), dt.F32, 3, (1, 96))
+    return c
+
+
 CASES = {
     # the benchmark's configurations at reduced size
     "c0_small": lambda: W.config0(64, 96, 128),
@@ -214,6 +231,8 @@ CASES = {
     "int8_rows300_ragged_zp": int8_rows300_ragged_zp,
     "int8_rows513_gelu_sum": int8_rows513_gelu_sum,
     "fp8_rows260_bf16": fp8_rows260_bf16,
+    "int8_per_row_src_scales_bf16": int8_per_row_src_scales_bf16,
+    "int8_per_row_src_scales_gelu_s8": int8_per_row_src_scales_gelu_s8,
     "fp8_f8dst": fp8_f8dst,
     "fp8_swish_f32": fp8_swish_f32,
 }

@@ -101,3 +101,40 @@ def test_cuda_quantize_activations_full_size(src_dt, dst_dt, per_row, ctx):
     inside = (x / step + zp > lo) & (x / step + zp < hi)
     err = np.abs(plan2.result() - x)
     assert (err[inside] <= (0.5 * step * np.ones_like(x))[inside] * 1.001 + 1e-6).all()
+
+
+@pytest.mark.gpu
+def test_dynamic_quantisation_pipeline(ctx):
+    """f32 activations -> (reorder with per-row scales) -> s8 -> int8 matmul with the same per-row
+    source scales and per-column weights scales -> bf16: both primitives on the device, each
+    checked against the oracle, the s8 tensor handed from one to the other without leaving HBM."""
+    from onednn_b200 import api, workloads as W
+    from onednn_b200.workloads import MatmulCase, ReorderCase
+    eng, strm = ctx
+    M, K, N = 384, 512, 256
+    rng = np.random.default_rng(77)
+    x = (rng.standard_normal((M, K)) * rng.uniform(0.2, 3.0, (M, 1))).astype(np.float32)
+    row_scale = (np.abs(x).max(axis=1) / 127.0).astype(np.float32)
+    q = ReorderCase("quantize", M, K, x, dt.F32, dt.S8, dst_scale=Quant(row_scale, dt.F32, 1))
+    rplan = api.ReorderPlan(q, eng, strm)
+    rplan.execute()
+    xq = rplan.result()
+    assert np.array_equal(xq, B.run_oracle_reorder(q))
+
+    wei = rng.integers(-127, 128, (K, N), dtype=np.int8)
+    c = MatmulCase("dynq", M, N, K, src=xq, src_dt=dt.S8, wei=wei, wei_dt=dt.S8, dst_dt=dt.BF16,
+                   src_scale=Quant(row_scale, dt.F32, 3, (1, K)),
+                   wei_scale=Quant(rng.uniform(1e-3, 3e-3, N).astype(np.float32), dt.F32, 2),
+                   exact=False, rtol=1e-2, atol=1e-2)
+    mplan = api.CasePlan(c, eng, strm, weights="any")
+    assert mplan.impl == "cuda:sm100:tcgen05_i8"
+    # the matmul reads the reorder's destination buffer itself
+    mplan.args[api.ARG_SRC] = rplan.mem["dst"]
+    mplan.execute()
+    got = dt.to_f32(mplan.result(), dt.BF16)
+    want = dt.to_f32(B.run_oracle(c, exact_acc=1), dt.BF16)
+    assert np.allclose(got, want, rtol=1e-2, atol=1e-2)
+    # and the whole thing approximates the f32 product it stands for
+    ref = x @ (wei.astype(np.float32) * c.wei_scale.data)
+    err = np.abs(got - ref).max() / np.abs(ref).max()
+    assert err < 0.02, err

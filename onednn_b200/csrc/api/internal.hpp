@@ -176,6 +176,9 @@ struct dnnl_primitive_desc {
     std::string impl_str;
     // scratch md returned for DNNL_ARG_ATTR_* queries
     mutable std::map<int, dnnl_memory_desc> arg_mds;
+    // batched problems (more than two dims): the descriptor of one 2-D slice, which the
+    // selected implementation runs once per batch index
+    std::shared_ptr<dnnl_primitive_desc> inner;
 
     int64_t M() const { return dst.dims[dst.ndims - 2]; }
     int64_t N() const { return dst.dims[dst.ndims - 1]; }

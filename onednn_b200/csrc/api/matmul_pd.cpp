@@ -391,7 +391,153 @@ static bool impl_disabled(int id) {
     return (id == IMPL_TC8 && s.find("tc8") != std::string::npos) || (id == IMPL_WC && s.find("wc") != std::string::npos);
 }
 
+// ---- batched problems -------------------------------------------------------------------
+// The reference's matmul takes any number of leading batch dims, each equal in src, weights
+// and dst or 1 (broadcast) in src or weights (src/common/matmul.cpp:374-401); every batch
+// index is an independent 2-D problem (ref_matmul_int8.cpp:154-170 loops over it).  Here the
+// descriptor of one 2-D slice goes through the ordinary dispatch, and execution runs it once
+// per batch index on the same stream.
+
+// the last two dims of md as a 2-D descriptor
+static dnnl_memory_desc slice_2d(const dnnl_memory_desc &md) {
+    dnnl_memory_desc r = md;
+    if (r.is_any()) make_plain(r);
+    dnnl_memory_desc o;
+    o.ndims = 2;
+    o.data_type = r.data_type;
+    o.format_kind = r.format_kind;
+    o.packed_layout = r.packed_layout;
+    for (int i = 0; i < 2; ++i) {
+        o.dims[i] = r.dims[r.ndims - 2 + i];
+        o.strides[i] = r.strides[r.ndims - 2 + i];
+    }
+    return o;
+}
+
+static dnnl_status_t select_batched(dnnl_primitive_desc *pd, int first) {
+    const int nd = pd->user_dst.ndims, nb = nd - 2;
+    if (pd->user_src.format_kind == dnnl_format_kind_opaque || pd->user_wei.format_kind == dnnl_format_kind_opaque
+            || pd->user_dst.format_kind == dnnl_format_kind_opaque)
+        return first == 0 ? dnnl_unimplemented : dnnl_last_impl_reached; // packed layouts are 2-D
+    auto in = std::make_shared<dnnl_primitive_desc>();
+    in->kind = dnnl_matmul;
+    in->engine = pd->engine; // not counted: the slice descriptor lives and dies with this one
+    in->attr = pd->attr;
+    // scales / zero-points may vary over the last two dims only; their masks move down with them
+    for (auto *m : {&in->attr.scales, &in->attr.zero_points})
+        for (auto &kv : *m) {
+            if (!kv.second.set) continue;
+            if (kv.second.mask & ((1 << nb) - 1)) return first == 0 ? dnnl_unimplemented : dnnl_last_impl_reached;
+            kv.second.mask >>= nb;
+        }
+    for (auto &e : in->attr.post_ops.entries) {
+        if (e.kind == dnnl_binary) {
+            if (e.src1.ndims != nd) return dnnl_invalid_arguments;
+            e.src1 = slice_2d(e.src1);
+        } else if (e.kind == dnnl_prelu) {
+            if (e.mask & ((1 << nb) - 1)) return first == 0 ? dnnl_unimplemented : dnnl_last_impl_reached;
+            e.mask >>= nb;
+        }
+    }
+    in->user_src = slice_2d(pd->user_src);
+    in->user_wei = slice_2d(pd->user_wei); // weights given as `any` stay plain: packing is per 2-D matrix
+    in->user_dst = slice_2d(pd->user_dst);
+    if (pd->user_bias.ndims) in->user_bias = slice_2d(pd->user_bias);
+    const dnnl_status_t st = matmul_select_impl(in.get(), first);
+    if (st != dnnl_success) return st;
+    pd->src = pd->user_src;
+    if (pd->src.is_any()) make_plain(pd->src);
+    pd->wei = pd->user_wei;
+    if (pd->wei.is_any()) make_plain(pd->wei);
+    pd->dst = pd->user_dst;
+    if (pd->dst.is_any()) make_plain(pd->dst);
+    pd->bias = pd->user_bias;
+    if (pd->bias.ndims && pd->bias.is_any()) make_plain(pd->bias);
+    pd->impl = in->impl;
+    pd->impl_str = in->impl_str;
+    pd->scratchpad = in->scratchpad;
+    pd->inner = in;
+    return dnnl_success;
+}
+
+// element offset of batch index `idx` (over dst's batch dims) in a tensor whose batch dims are 1 or dst's
+static int64_t batch_offset(const dnnl_memory_desc &md, const int64_t *idx, int nb) {
+    int64_t off = 0;
+    for (int d = 0; d < nb; ++d)
+        if (md.dims[d] != 1) off += idx[d] * md.strides[d];
+    return off;
+}
+
+static dnnl_status_t batched_execute(const dnnl_primitive *prim, dnnl_stream *stream, const std::map<int, dnnl_memory *> &args) {
+    const dnnl_primitive_desc *pd = prim->pd.get();
+    const dnnl_primitive_desc *in = pd->inner.get();
+    const int nb = pd->dst.ndims - 2;
+    int64_t total = 1;
+    for (int d = 0; d < nb; ++d) total *= pd->dst.dims[d];
+    if (total == 0 || pd->dst.has_zero_dim() || pd->src.has_zero_dim() || pd->wei.has_zero_dim()) return dnnl_success;
+    // the tensors that move with the batch index, their N-D descriptors and their 2-D slices
+    struct moving_t { int arg; const dnnl_memory_desc *full; dnnl_memory_desc slice; dnnl_memory mem; };
+    std::vector<moving_t> mv;
+    auto add = [&](int arg, const dnnl_memory_desc &full, const dnnl_memory_desc &slice) -> bool {
+        auto it = args.find(arg);
+        if (it == args.end() || !it->second->handle) return false;
+        moving_t m;
+        m.arg = arg;
+        m.full = &full;
+        m.slice = slice;
+        m.mem = *it->second;
+        mv.push_back(m);
+        return true;
+    };
+    if (!add(DNNL_ARG_SRC, pd->src, in->src) || !add(DNNL_ARG_WEIGHTS, pd->wei, in->wei) || !add(DNNL_ARG_DST, pd->dst, in->dst))
+        return dnnl_invalid_arguments;
+    if (pd->bias.ndims && !add(DNNL_ARG_BIAS, pd->bias, in->bias)) return dnnl_invalid_arguments;
+    const auto &po = pd->attr.post_ops.entries;
+    std::vector<dnnl_memory_desc> po_full(po.size());
+    for (size_t i = 0; i < po.size(); ++i)
+        if (po[i].kind == dnnl_binary) {
+            po_full[i] = po[i].src1;
+            if (po_full[i].is_any()) make_plain(po_full[i]);
+            if (!add(DNNL_ARG_ATTR_MULTIPLE_POST_OP((int)i) | DNNL_ARG_SRC_1, po_full[i], in->attr.post_ops.entries[i].src1))
+                return dnnl_invalid_arguments;
+        }
+    std::vector<void *> base(mv.size());
+    for (size_t i = 0; i < mv.size(); ++i) {
+        base[i] = (char *)mv[i].mem.handle + mv[i].full->offset0 * dt_nbits(mv[i].full->data_type) / 8;
+        mv[i].mem.md = mv[i].slice;
+        mv[i].mem.owned = false;
+        mv[i].mem.mapped = nullptr;
+    }
+    // a primitive of the slice descriptor that borrows this primitive's scratchpad
+    dnnl_primitive tmp;
+    tmp.pd = pd->inner;
+    tmp.lib_scratch = prim->lib_scratch;
+    tmp.lib_scratch_bytes = prim->lib_scratch_bytes;
+    std::map<int, dnnl_memory *> a2 = args;
+    for (size_t i = 0; i < mv.size(); ++i) a2[mv[i].arg] = &mv[i].mem;
+    dnnl_status_t st = dnnl_success;
+    int64_t idx[DNNL_MAX_NDIMS] = {0};
+    for (int64_t b = 0; b < total && st == dnnl_success; ++b) {
+        int64_t rem = b;
+        for (int d = nb - 1; d >= 0; --d) {
+            idx[d] = rem % pd->dst.dims[d];
+            rem /= pd->dst.dims[d];
+        }
+        for (size_t i = 0; i < mv.size(); ++i) {
+            const int64_t off = batch_offset(*mv[i].full, idx, nb);
+            const int bits = dt_nbits(mv[i].full->data_type);
+            if ((off * bits) % 8 != 0) { st = dnnl_unimplemented; break; } // a 4-bit slice starting inside a byte
+            mv[i].mem.handle = (char *)base[i] + off * bits / 8;
+        }
+        if (st == dnnl_success) st = matmul_execute(&tmp, stream, a2);
+    }
+    tmp.lib_scratch = nullptr; // borrowed
+    tmp.pd.reset();
+    return st;
+}
+
 dnnl_status_t matmul_select_impl(dnnl_primitive_desc *pd, int first) {
+    if (pd->user_dst.ndims > 2) return select_batched(pd, first);
     for (int id = first; id <= IMPL_GENERIC; ++id) {
         bool ok = false;
         if (impl_disabled(id)) continue;
@@ -452,6 +598,7 @@ dnnl_status_t matmul_execute(const dnnl_primitive *prim, dnnl_stream *stream, co
         auto it = args.find(a);
         return it == args.end() ? nullptr : it->second;
     };
+    if (pd->inner) return batched_execute(prim, stream, args);
     dnnl_memory *src = get(DNNL_ARG_SRC), *wei = get(DNNL_ARG_WEIGHTS), *dst = get(DNNL_ARG_DST), *bias = get(DNNL_ARG_BIAS);
     if (!src || !wei || !dst) return dnnl_invalid_arguments;
     if (pd->bias.ndims && !bias) return dnnl_invalid_arguments;

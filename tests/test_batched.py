@@ -1,0 +1,127 @@
+"""Batched matmul (leading batch dims, equal or broadcast): every batch index must equal the
+2-D problem of its slices, which the oracle computes (src/common/matmul.cpp:374-401)."""
+import os
+
+import numpy as np
+import pytest
+
+os.environ["ONEDNN_B200_ALLOW_NO_DEVICE"] = "1"  # descriptor-only engine where there is no GPU
+
+from onednn_b200 import api, dtypes as dt, workloads as W
+from onednn_b200.workloads import MatmulCase, Quant
+from oracle import binding as B
+
+
+def _md(shape, dtype):
+    return api.MemoryDesc(tuple(shape), dtype, strides=tuple(int(np.prod(shape[i + 1:])) for i in range(len(shape))))
+
+
+def test_batched_descriptor_host():
+    """Dispatch of the 2-D slice, masks moved down with the dims, queries keep the batch dims."""
+    eng = api.Engine()
+    a = api.PrimitiveAttr()
+    a.set_scales(api.ARG_WEIGHTS, 1 << 2, (), dt.F32)          # per-N of a 3-D weights tensor
+    pd = api.matmul_primitive_desc(eng, _md((3, 70, 64), dt.S8), _md((3, 64, 48), dt.S8), _md((3, 70, 48), dt.F32), attr=a)
+    assert pd.impl_info_str() == "cuda:sm100:tcgen05_i8"
+    assert pd.query_md(api.QUERY_EXEC_ARG_MD, api.ARG_ATTR_SCALES | api.ARG_WEIGHTS).dims == [48]
+    assert pd.weights_desc().dims == [3, 64, 48]
+    # `any` weights of a batched problem stay plain
+    any_w = api.MemoryDesc((3, 64, 48), dt.S8, api.TAG_ANY)
+    pd = api.matmul_primitive_desc(eng, _md((3, 70, 64), dt.S8), any_w, _md((3, 70, 48), dt.F32))
+    assert pd.weights_desc() == _md((3, 64, 48), dt.S8)
+    # broadcast weights are fine, mismatched batch dims are not, scales over a batch dim are not implemented
+    api.matmul_primitive_desc(eng, _md((3, 70, 64), dt.S8), _md((1, 64, 48), dt.S8), _md((3, 70, 48), dt.F32))
+    with pytest.raises(api.Error):
+        api.matmul_primitive_desc(eng, _md((3, 70, 64), dt.S8), _md((2, 64, 48), dt.S8), _md((3, 70, 48), dt.F32))
+    a = api.PrimitiveAttr()
+    a.set_scales(api.ARG_WEIGHTS, 1, (), dt.F32)
+    with pytest.raises(api.Error):
+        api.matmul_primitive_desc(eng, _md((3, 70, 64), dt.S8), _md((3, 64, 48), dt.S8), _md((3, 70, 48), dt.F32), attr=a)
+
+
+def _run_batched(eng, strm, batch, wbatch, base: MatmulCase, binary=None):
+    """``base`` holds the tensors with leading batch dims; returns (result, impl)."""
+    nd = len(batch)
+    M, N, K = base.M, base.N, base.K
+    attr = api.PrimitiveAttr()
+    for q, arg, is_zp in ((base.src_scale, api.ARG_SRC, False), (base.wei_scale, api.ARG_WEIGHTS, False),
+                          (base.dst_scale, api.ARG_DST, False), (base.src_zp, api.ARG_SRC, True), (base.dst_zp, api.ARG_DST, True)):
+        if q is not None:
+            (attr.set_zero_points if is_zp else attr.set_scales)(arg, q.mask << nd, (), q.dt)
+    po = api.PostOps()
+    for e in base.post_ops:
+        if e.kind == W.PO_ELTWISE:
+            po.append_eltwise(e.alg, e.alpha, e.beta)
+    src1_md = None
+    if binary is not None:
+        src1_md = _md(binary.shape, dt.F32)
+        po.append_binary(W.BINARY["add"], src1_md)
+    attr.set_post_ops(po)
+    src_md, wei_md = _md(batch + (M, K), base.src_dt), _md(wbatch + (K, N), base.wei_dt)
+    dst_md = _md(batch + (M, N), base.dst_dt)
+    bias_md = _md((1,) * nd + (1, N), base.bias_dt) if base.bias is not None else None
+    pd = api.matmul_primitive_desc(eng, src_md, wei_md, dst_md, bias_md, attr)
+    prim = api.Primitive(pd)
+    mems = []
+
+    def mem(md, arr):
+        m = api.Memory(md, eng)
+        m.write(np.ascontiguousarray(arr))
+        mems.append(m)
+        return m
+    args = {api.ARG_SRC: mem(src_md, base.src), api.ARG_WEIGHTS: mem(wei_md, base.wei),
+            api.ARG_DST: mem(dst_md, np.zeros(batch + (M, N), dt.RAW[base.dst_dt]))}
+    if base.bias is not None:
+        args[api.ARG_BIAS] = mem(bias_md, base.bias)
+    for q, arg in ((base.src_scale, api.ARG_ATTR_SCALES | api.ARG_SRC), (base.wei_scale, api.ARG_ATTR_SCALES | api.ARG_WEIGHTS),
+                   (base.dst_scale, api.ARG_ATTR_SCALES | api.ARG_DST), (base.src_zp, api.ARG_ATTR_ZERO_POINTS | api.ARG_SRC),
+                   (base.dst_zp, api.ARG_ATTR_ZERO_POINTS | api.ARG_DST)):
+        if q is not None:
+            args[arg] = mem(api.MemoryDesc((q.data.size,), q.dt, api.TAG_A), q.data)
+    if binary is not None:
+        args[api.arg_post_op(len(base.post_ops)) | api.ARG_SRC_1] = mem(src1_md, binary)
+    prim.execute(strm, args)
+    strm.wait()
+    return args[api.ARG_DST].read(dt.RAW[base.dst_dt], batch + (M, N)), pd.impl_info_str()
+
+
+def _slice_case(base, b, wb, binary=None):
+    import copy
+    c = copy.copy(base)
+    c.src, c.wei = np.ascontiguousarray(base.src[b]), np.ascontiguousarray(base.wei[wb])
+    c.post_ops = list(base.post_ops)
+    if binary is not None:
+        sl = binary[tuple(0 if binary.shape[d] == 1 else b[d] for d in range(len(b)))]
+        c.post_ops.append(W.binary("add", np.ascontiguousarray(sl), dt.F32, sl.shape))
+    return c
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("kind", ["int8_3d", "int8_bcast_weights_binary", "fp8_4d"])
+def test_batched_matches_oracle_per_slice(kind):
+    eng = api.Engine()
+    strm = api.Stream(eng)
+    r = np.random.default_rng(91)
+    if kind == "fp8_4d":
+        batch, wbatch, (M, N, K) = (2, 2), (2, 2), (40, 64, 96)
+        base = W.config3(M, N, K, seed=92)
+        base.src = dt.from_f32(r.uniform(-2, 2, batch + (M, K)).astype(np.float32), dt.F8_E4M3)
+        base.wei = dt.from_f32(r.uniform(-2, 2, wbatch + (K, N)).astype(np.float32), dt.F8_E4M3)
+    else:
+        batch, (M, N, K) = (3,), (70, 48, 64)
+        wbatch = (3,) if kind == "int8_3d" else (1,)
+        base = MatmulCase(kind, M, N, K, src=r.integers(-128, 128, batch + (M, K), dtype=np.int8), src_dt=dt.S8,
+                          wei=r.integers(-127, 128, wbatch + (K, N), dtype=np.int8), wei_dt=dt.S8, dst_dt=dt.F32,
+                          src_scale=Quant(np.float32([0.02]), dt.F32, 0),
+                          wei_scale=Quant(r.uniform(1e-3, 4e-3, N).astype(np.float32), dt.F32, 2),
+                          bias=r.uniform(-1, 1, (1, N)).astype(np.float32), bias_dt=dt.F32,
+                          post_ops=[W.eltwise("relu", 0.0)], exact=False, rtol=1e-5, atol=1e-5)
+    binary = r.uniform(-1, 1, batch + (M, 1)).astype(np.float32) if kind == "int8_bcast_weights_binary" else None
+    got, impl = _run_batched(eng, strm, batch, wbatch, base, binary)
+    assert "tcgen05" in impl
+    for b in np.ndindex(*batch):
+        wb = tuple(0 if wbatch[d] == 1 else b[d] for d in range(len(b)))
+        c = _slice_case(base, b, wb, binary)
+        want = B.run_oracle(c, exact_acc=1 if "i8" in impl else 0)
+        g, w = dt.to_f32(got[b], c.dst_dt).astype(np.float64), dt.to_f32(want, c.dst_dt).astype(np.float64)
+        assert (np.abs(g - w) <= c.atol + c.rtol * np.abs(w)).all(), "%s batch %s" % (kind, b)

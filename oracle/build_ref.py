@@ -4,7 +4,9 @@
 TEST INFRASTRUCTURE ONLY.  Nothing here is part of the shipped product: the
 result (``oracle/_ref/libdnnl_ref.so`` and ``oracle/_ref/librefrun.so``) is
 used to pin the CPU restatement in ``oracle/oracle_matmul.c`` and as the timed
-CPU baseline of ``bench.py --impl reference``.
+CPU baseline of ``bench.py --impl reference``.  It also compiles the programs of
+``tests/consumer/`` against the reference's own ``dnnl.hpp`` and links them with the CUDA
+engine's library (``oracle/_ref/consumer_*``).
 
 The reference's own build system is not run.  This script plays the part of a
 short Makefile: it lists the translation units of the reference's common
@@ -164,6 +166,23 @@ def main():
             print(p.stderr[-6000:])
             return 1
         print("built", rlib)
+    # user programs written against the reference's own C++ header, linked against the CUDA
+    # engine instead of the reference library (the drop-in claim, checked by tests/test_consumer.py)
+    eng_lib = HERE.parent / "onednn_b200" / "libonednn_b200.so"
+    consumer = HERE.parent / "tests" / "consumer"
+    for prog in sorted(list(consumer.glob("*.cpp")) + list(consumer.glob("*.c"))):
+        if not eng_lib.exists():
+            print("skipped %s: %s not built yet" % (prog.name, eng_lib.name))
+            continue
+        out = OUT / ("consumer_" + prog.stem)
+        comp = [args.cxx, "-std=c++11"] if prog.suffix == ".cpp" else ["/usr/bin/gcc", "-std=c99"]
+        cmd = comp + ["-O1", str(prog), "-I", str(ref / "include"), "-I", str(inc), "-L", str(eng_lib.parent),
+                      "-lonednn_b200", "-lm", "-Wl,-rpath,$ORIGIN/../../onednn_b200", "-o", str(out)]
+        p = subprocess.run(cmd, capture_output=True, text=True)
+        if p.returncode != 0:
+            print(p.stderr[-6000:])
+            return 1
+        print("built", out)
     return 0
 
 

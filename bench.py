@@ -570,6 +570,20 @@ def run_extras(api, W, dt, eng, strm, tstream, torch, np, peaks):
         del plans
     except Exception as ex:
         out["c4_error"] = repr(ex)
+    try:
+        # the caller in front of the int8 matmul: activations quantised on the device (dnnl_reorder with scales)
+        for name, src_dt, per_row in (("reorder_quant_f32_s8_8192", dt.F32, False), ("reorder_quant_bf16_s8_per_row_8192", dt.BF16, True)):
+            c = W.quantize_case(8192, 8192, src_dt, dt.S8, per_row=per_row)
+            plans = [api.ReorderPlan(c, eng, gstrm) for _ in range(3)]  # 3 x (268 or 134) + 67 MB > L2
+            med, best = graph_time(plans)
+            nbytes = c.rows * c.cols * (np.dtype(dt.RAW[src_dt]).itemsize + 1)
+            gbs = nbytes / (med * 1e-3) / 1e9
+            out[name] = {"impl": plans[0].impl, "us": med * 1e3, "us_min": best * 1e3, "algorithmic_bytes": nbytes, "GB/s": gbs,
+                         "frac_of_hbm_%s" % peaks["source"]: gbs / peaks["hbm"],
+                         "timing": "CUDA graph of 3 executions over 3 buffer sets, median of 5 replays"}
+            del plans
+    except Exception as ex:
+        out["reorder_quant_error"] = repr(ex)
     return out
 
 

@@ -56,6 +56,8 @@ constexpr int PAIR_STAGES = 6;
 constexpr int PAIR_B_BYTES = B_BYTES / 2;
 constexpr int PAIR_STAGE_BYTES = A_BYTES + PAIR_B_BYTES;
 constexpr int MAX_STAGES = 6;
+constexpr int B_BOX_ROWS = 128;     // rows of one weights copy (TMA box) of the single-CTA kernel; a second map has 64-row boxes
+constexpr int B_BOX_ROWS_SMALL = 64; // ... for units of BN / 4 columns and for the pair kernel (a CTA's share is half of the unit)
 static_assert(PAIR_STAGES * PAIR_STAGE_BYTES == STAGES * STAGE_BYTES, "both kernels use the same shared memory");
 constexpr int EPI_WARPS = 16;                 // four per TMEM lane quarter, each takes a quarter of the columns
 constexpr int NUM_THREADS = 64 + 32 * EPI_WARPS;
@@ -275,26 +277,28 @@ struct tc8_args_t {
     b200_matmul_params_t p;
     int m_tiles, n_tiles, k_blocks;
     // Work units: unit u < full_units is tile u (BM x BN); the tiles after that -- those of a
-    // last, less than half full wave -- are each cut into two units of BN / 2 columns, so that
-    // the wave's work spreads over twice as many CTAs.
-    int full_units, units;
-    uint32_t idesc, idesc_half; // instruction descriptors for N = BN and N = BN / 2
+    // last wave that fills at most half of the SMs, or all tiles of a problem that small -- are
+    // each cut into `split` (2 or 4) units of BN / split columns, so that the work spreads
+    // over that many more CTAs.
+    int full_units, units, split;
+    uint32_t idesc, idesc_tail; // instruction descriptors for N = BN and N = BN / split
 };
 
 struct unit_t {
     int m0, n0;   // origin of the unit in dst
-    bool wide;    // BN columns (else BN / 2)
+    int width;    // columns: BN, BN / 2 or BN / 4
 };
 
 // rows: dst rows per tile (BM, or 2 * BM in the pair kernel)
 __device__ __forceinline__ unit_t decode_unit(const tc8_args_t &a, int u, int rows) {
     unit_t r;
     int tile = u, off = 0;
-    r.wide = u < a.full_units;
-    if (!r.wide) {
+    r.width = BN;
+    if (u >= a.full_units) {
         const int h = u - a.full_units;
-        tile = a.full_units + (h >> 1);
-        off = (h & 1) * (BN / 2);
+        r.width = BN / a.split;
+        tile = a.full_units + h / a.split;
+        off = (h % a.split) * r.width;
     }
     r.m0 = (tile % a.m_tiles) * rows; // m fastest
     r.n0 = (tile / a.m_tiles) * BN + off;
@@ -695,7 +699,8 @@ __device__ __forceinline__ void epilogue_chunk(const b200_matmul_params_t &p, co
 // accumulator-free barrier.  Per tile this moves 2/3 of the bytes from L2 to shared memory.
 template <bool FP8, int EPI, int SUM, bool PEERS = false, bool PAIR = false>
 __global__ void __launch_bounds__(640, 1) matmul_tc8_kernel(const __grid_constant__ CUtensorMap tmap_a,
-        const __grid_constant__ CUtensorMap tmap_b, const __grid_constant__ tc8_args_t args) {
+        const __grid_constant__ CUtensorMap tmap_b, const __grid_constant__ CUtensorMap tmap_b_small,
+        const __grid_constant__ tc8_args_t args) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     smem_ctrl_t *ctrl = (smem_ctrl_t *)(smem + (size_t)STAGES * STAGE_BYTES);
@@ -753,21 +758,28 @@ __global__ void __launch_bounds__(640, 1) matmul_tc8_kernel(const __grid_constan
                     const uint32_t s = it % NST, r = it / NST;
                     if (!(ok = mbar_wait(&ctrl->empty[s], (r & 1) ^ 1, ctrl, p.status, ST_WAIT_EMPTY))) break;
                     uint8_t *sa = smem + (size_t)s * SBYTES;
+                    // This CTA's share of the unit's weight rows (all of them, or half in the pair
+                    // kernel) is one or two boxes: of 128 rows, or of 64 (second map) where the share
+                    // is 64 rows and in the pair kernel.  Straight-line code: in the pair kernel the
+                    // time this thread takes per stage is part of the stage's round trip.
                     if (PAIR) {
                         // the leader's barrier counts the bytes of both CTAs
                         const uint32_t bar = cluster_map(smem_u32(&ctrl->full[s]), 0);
-                        if (rank == 0) mbar_expect_tx(&ctrl->full[s], 2 * (un.wide ? SBYTES : A_BYTES + BBYTES / 2));
+                        const bool two = un.width == BN; // 128 rows per CTA: two boxes of 64
+                        if (rank == 0) mbar_expect_tx(&ctrl->full[s], 2 * (A_BYTES + (two ? 2 : 1) * B_BOX_ROWS_SMALL * BK));
                         tma_load_2d_pair(sa, &tmap_a, kb * BK, un.m0 + (int)rank * BM, bar);
-                        // the weights map's box is BN / 4 rows; this CTA's half of the unit's columns
-                        const int nb = un.n0 + (int)rank * (un.wide ? BN / 2 : BN / 4);
-                        tma_load_2d_pair(sa + A_BYTES, &tmap_b, kb * BK, nb, bar);
-                        if (un.wide) tma_load_2d_pair(sa + A_BYTES + BBYTES / 2, &tmap_b, kb * BK, nb + BN / 4, bar);
+                        const int nb = un.n0 + (int)rank * (un.width / 2);
+                        tma_load_2d_pair(sa + A_BYTES, &tmap_b_small, kb * BK, nb, bar);
+                        if (two) tma_load_2d_pair(sa + A_BYTES + B_BOX_ROWS_SMALL * BK, &tmap_b_small, kb * BK, nb + B_BOX_ROWS_SMALL, bar);
                     } else {
-                        mbar_expect_tx(&ctrl->full[s], un.wide ? STAGE_BYTES : A_BYTES + B_BYTES / 2);
+                        mbar_expect_tx(&ctrl->full[s], A_BYTES + (uint32_t)un.width * BK);
                         tma_load_2d(sa, &tmap_a, kb * BK, un.m0, &ctrl->full[s]);
-                        // the weights map's box is BN / 2 rows: a wide unit takes two of them, one after the other
-                        tma_load_2d(sa + A_BYTES, &tmap_b, kb * BK, un.n0, &ctrl->full[s]);
-                        if (un.wide) tma_load_2d(sa + A_BYTES + B_BYTES / 2, &tmap_b, kb * BK, un.n0 + BN / 2, &ctrl->full[s]);
+                        if (un.width >= B_BOX_ROWS) {
+                            tma_load_2d(sa + A_BYTES, &tmap_b, kb * BK, un.n0, &ctrl->full[s]);
+                            if (un.width == BN) tma_load_2d(sa + A_BYTES + B_BOX_ROWS * BK, &tmap_b, kb * BK, un.n0 + B_BOX_ROWS, &ctrl->full[s]);
+                        } else {
+                            tma_load_2d(sa + A_BYTES, &tmap_b_small, kb * BK, un.n0, &ctrl->full[s]);
+                        }
                     }
                 }
             }
@@ -792,7 +804,7 @@ __global__ void __launch_bounds__(640, 1) matmul_tc8_kernel(const __grid_constan
             const uint64_t adesc0 = make_smem_desc(smem_u32(smem)), bdesc0 = make_smem_desc(smem_u32(smem) + A_BYTES);
             for (int u = unit0; u < args.units && ok; u += ustep, ++tile_i) {
                 const uint32_t a = tile_i & 1, use = tile_i >> 1;
-                const uint32_t idesc = u < args.full_units ? args.idesc : args.idesc_half;
+                const uint32_t idesc = u < args.full_units ? args.idesc : args.idesc_tail;
                 if (!(ok = mbar_wait(&ctrl->tmem_empty[a], (use & 1) ^ 1, ctrl, p.status, ST_WAIT_TMEM_EMPTY))) break;
                 tcgen05_fence_after();
                 const uint32_t tmem_d = tmem_base + a * BN;
@@ -843,7 +855,7 @@ __global__ void __launch_bounds__(640, 1) matmul_tc8_kernel(const __grid_constan
         for (int u = unit0; u < args.units && ok; u += ustep, ++tile_i) {
             const unit_t un = decode_unit(args, u, TILE_ROWS);
             // this warp's share of the unit's columns: a quarter of them, in chunks of CH
-            const int ecols = un.wide ? EPI_COLS : EPI_COLS / 2, nch = ecols / CH;
+            const int ecols = un.width / 4, nch = ecols / CH;
             const int64_t m0 = un.m0 + (int64_t)rank * BM;
             const int64_t n0 = (int64_t)un.n0 + half * ecols;
             const uint32_t a = tile_i & 1, use = tile_i >> 1;
@@ -1024,10 +1036,10 @@ extern "C" int b200_matmul_tc8_launch(const b200_matmul_params_t *p, b200_stream
     const int tile_rows = pair ? 2 * BM : BM;
     const int workers = pair ? sms / 2 : sms; // CTAs or CTA pairs working at the same time
 
-    CUtensorMap ta, tb;
+    CUtensorMap ta, tb, tbs;
     if (!make_tmap(&ta, p->src, p->M, p->K, p->src_sm, BM)) return (int)cudaErrorUnknown;
-    // weights box: half of a CTA's share of a full-width unit (two boxes per wide unit, one per half-width unit)
-    if (!make_tmap(&tb, p->wei, p->N, p->K, wpitch, pair ? BN / 4 : BN / 2)) return (int)cudaErrorUnknown;
+    if (!make_tmap(&tb, p->wei, p->N, p->K, wpitch, B_BOX_ROWS)) return (int)cudaErrorUnknown;
+    if (!make_tmap(&tbs, p->wei, p->N, p->K, wpitch, B_BOX_ROWS_SMALL)) return (int)cudaErrorUnknown;
 
     tc8_args_t a;
     a.p = *p;
@@ -1035,15 +1047,25 @@ extern "C" int b200_matmul_tc8_launch(const b200_matmul_params_t *p, b200_stream
     a.n_tiles = (int)((p->N + BN - 1) / BN);
     a.k_blocks = (int)((p->K + BK - 1) / BK);
     a.idesc = make_idesc(f8, p->src_dt, p->wei_dt, BN, tile_rows);
-    a.idesc_half = make_idesc(f8, p->src_dt, p->wei_dt, BN / 2, tile_rows);
 
     const int64_t tiles = (int64_t)a.m_tiles * a.n_tiles;
-    if (tiles > INT32_MAX / 2) return B200_ERR_TOO_LARGE;
-    // a last wave that fills at most half of the workers is cut into half-width units
-    const int64_t tail = tiles > workers ? tiles % workers : 0;
-    const bool split = tail > 0 && 2 * tail <= workers;
-    a.full_units = (int)(split ? tiles - tail : tiles);
-    a.units = (int)(split ? tiles + tail : tiles);
+    if (tiles > INT32_MAX / 4) return B200_ERR_TOO_LARGE;
+    // Narrower units where whole tiles would leave SMs idle: all tiles of a problem with at
+    // most half (a quarter) as many tiles as workers are cut in 2 (4); otherwise the tiles of a
+    // last wave that fills at most half of the workers are cut in 2.
+    const int max_split = pair ? 2 : 4; // a CTA of a pair holds half of the unit's weight rows: at least one box
+    int64_t tail = 0;
+    a.split = 1;
+    if (tiles * 2 <= workers) {
+        tail = tiles;
+        a.split = (tiles * 4 <= workers && max_split >= 4) ? 4 : 2;
+    } else if (tiles > workers && tiles % workers != 0 && 2 * (tiles % workers) <= workers) {
+        tail = tiles % workers;
+        a.split = 2;
+    }
+    a.full_units = (int)(tiles - tail);
+    a.units = (int)(tiles - tail + tail * a.split);
+    a.idesc_tail = make_idesc(f8, p->src_dt, p->wei_dt, BN / a.split, tile_rows);
     const unsigned grid = (unsigned)(a.units < workers ? a.units : workers) * (pair ? 2u : 1u);
 
     // epilogue evaluation mode
@@ -1077,7 +1099,7 @@ extern "C" int b200_matmul_tc8_launch(const b200_matmul_params_t *p, b200_stream
         if (epi == EPI_GELU_Q && sum == SUM_OTHER) epi = EPI_GENERIC, sum = SUM_NONE;
     }
 
-    typedef void (*kernel_t)(const CUtensorMap, const CUtensorMap, const tc8_args_t);
+    typedef void (*kernel_t)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const tc8_args_t);
 #define TC8_ROW(F, P) \
     {{matmul_tc8_kernel<F, EPI_NONE, SUM_NONE, false, P>, nullptr, nullptr}, \
             {matmul_tc8_kernel<F, EPI_SIMPLE, SUM_NONE, false, P>, matmul_tc8_kernel<F, EPI_SIMPLE, SUM_8BIT, false, P>, \
@@ -1110,7 +1132,7 @@ extern "C" int b200_matmul_tc8_launch(const b200_matmul_params_t *p, b200_stream
         }
     }
     if (!pair) {
-        kern<<<grid, NUM_THREADS, SMEM_BYTES, (cudaStream_t)stream>>>(ta, tb, a);
+        kern<<<grid, NUM_THREADS, SMEM_BYTES, (cudaStream_t)stream>>>(ta, tb, tbs, a);
         return after_launch();
     }
     cudaLaunchConfig_t cfg = {};
@@ -1125,7 +1147,7 @@ extern "C" int b200_matmul_tc8_launch(const b200_matmul_params_t *p, b200_stream
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    cudaError_t le = cudaLaunchKernelEx(&cfg, kern, ta, tb, a);
+    cudaError_t le = cudaLaunchKernelEx(&cfg, kern, ta, tb, tbs, a);
     g_launches.fetch_add(1, std::memory_order_relaxed);
     if (le != cudaSuccess) {
         (void)cudaGetLastError();

@@ -179,6 +179,9 @@ struct dnnl_primitive_desc {
     // batched problems (more than two dims): the descriptor of one 2-D slice, which the
     // selected implementation runs once per batch index
     std::shared_ptr<dnnl_primitive_desc> inner;
+    // some dims are DNNL_RUNTIME_DIM_VAL: the implementation is chosen at execution, from the
+    // descriptors of the memory arguments
+    bool runtime = false;
 
     int64_t M() const { return dst.dims[dst.ndims - 2]; }
     int64_t N() const { return dst.dims[dst.ndims - 1]; }

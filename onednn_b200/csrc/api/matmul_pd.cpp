@@ -536,7 +536,66 @@ static dnnl_status_t batched_execute(const dnnl_primitive *prim, dnnl_stream *st
     return st;
 }
 
+// a descriptor with runtime dims admits the concrete one of a memory argument
+static bool runtime_md_matches(const dnnl_memory_desc &decl, const dnnl_memory_desc &actual) {
+    if (decl.ndims != actual.ndims || decl.data_type != actual.data_type || actual.has_runtime_dims()) return false;
+    for (int i = 0; i < decl.ndims; ++i) {
+        if (decl.dims[i] != DNNL_RUNTIME_DIM_VAL && decl.dims[i] != actual.dims[i]) return false;
+        if (decl.is_plain() && actual.is_plain() && decl.strides[i] != DNNL_RUNTIME_DIM_VAL && decl.strides[i] != actual.strides[i])
+            return false;
+    }
+    return true;
+}
+
+// Execution of a primitive created with runtime dims: the sizes come from the memory
+// arguments; validation and dispatch run now, on a descriptor that lives for this call.
+static dnnl_status_t runtime_execute(const dnnl_primitive *prim, dnnl_stream *stream, const std::map<int, dnnl_memory *> &args) {
+    const dnnl_primitive_desc *pd = prim->pd.get();
+    auto get = [&](int a) -> dnnl_memory * {
+        auto it = args.find(a);
+        return it == args.end() ? nullptr : it->second;
+    };
+    dnnl_memory *src = get(DNNL_ARG_SRC), *wei = get(DNNL_ARG_WEIGHTS), *dst = get(DNNL_ARG_DST), *bias = get(DNNL_ARG_BIAS);
+    if (!src || !wei || !dst || (pd->bias.ndims && !bias)) return dnnl_invalid_arguments;
+    if (!runtime_md_matches(pd->src, src->md) || !runtime_md_matches(pd->wei, wei->md) || !runtime_md_matches(pd->dst, dst->md)
+            || (pd->bias.ndims && !runtime_md_matches(pd->bias, bias->md)))
+        return dnnl_invalid_arguments;
+    auto now = std::make_shared<dnnl_primitive_desc>();
+    now->kind = dnnl_matmul;
+    now->engine = pd->engine;
+    now->attr = pd->attr;
+    now->attr.scratchpad_mode = dnnl_scratchpad_mode_library;
+    now->user_src = src->md;
+    now->user_wei = wei->md;
+    now->user_dst = dst->md;
+    if (pd->bias.ndims) now->user_bias = bias->md;
+    dnnl_status_t st = matmul_validate(now->user_src, now->user_wei, pd->bias.ndims ? &now->user_bias : nullptr, now->user_dst, now->attr);
+    if (st != dnnl_success) return st;
+    st = matmul_select_impl(now.get(), 0);
+    if (st != dnnl_success) return st;
+    dnnl_primitive tmp;
+    tmp.pd = now;
+    const size_t sb = now->scratchpad.ndims ? (size_t)now->scratchpad.dims[0] : 0;
+    cudaStream_t cs = (cudaStream_t)stream->cuda_stream;
+    if (sb) { // stream-ordered: no synchronisation, released after the kernels queued below
+        if (cudaMallocAsync(&tmp.lib_scratch, sb, cs) != cudaSuccess) {
+            (void)cudaGetLastError();
+            tmp.lib_scratch = nullptr;
+            tmp.pd.reset();
+            return dnnl_out_of_memory;
+        }
+        if (cudaMemsetAsync(tmp.lib_scratch, 0, sb, cs) != cudaSuccess) st = dnnl_runtime_error;
+        tmp.lib_scratch_bytes = sb;
+    }
+    if (st == dnnl_success) st = matmul_execute(&tmp, stream, args);
+    if (tmp.lib_scratch) cudaFreeAsync(tmp.lib_scratch, cs);
+    tmp.lib_scratch = nullptr;
+    tmp.pd.reset();
+    return st;
+}
+
 dnnl_status_t matmul_select_impl(dnnl_primitive_desc *pd, int first) {
+    if (pd->runtime) return dnnl_last_impl_reached; // nothing to iterate over before the sizes are known
     if (pd->user_dst.ndims > 2) return select_batched(pd, first);
     for (int id = first; id <= IMPL_GENERIC; ++id) {
         bool ok = false;
@@ -598,6 +657,7 @@ dnnl_status_t matmul_execute(const dnnl_primitive *prim, dnnl_stream *stream, co
         auto it = args.find(a);
         return it == args.end() ? nullptr : it->second;
     };
+    if (pd->runtime) return runtime_execute(prim, stream, args);
     if (pd->inner) return batched_execute(prim, stream, args);
     dnnl_memory *src = get(DNNL_ARG_SRC), *wei = get(DNNL_ARG_WEIGHTS), *dst = get(DNNL_ARG_DST), *bias = get(DNNL_ARG_BIAS);
     if (!src || !wei || !dst) return dnnl_invalid_arguments;
@@ -774,8 +834,8 @@ dnnl_status_t dnnl_matmul_primitive_desc_create(dnnl_primitive_desc_t *primitive
     const dnnl_primitive_attr &a = attr ? *attr : default_attr;
     dnnl_status_t st = matmul_validate(*src_desc, *weights_desc, bias_desc, *dst_desc, a);
     if (st != dnnl_success) return st;
-    if (src_desc->has_runtime_dims() || weights_desc->has_runtime_dims() || dst_desc->has_runtime_dims())
-        return dnnl_unimplemented;
+    const bool runtime = src_desc->has_runtime_dims() || weights_desc->has_runtime_dims() || dst_desc->has_runtime_dims()
+            || (bias_desc && bias_desc->has_runtime_dims());
     auto pd = std::unique_ptr<dnnl_primitive_desc>(new dnnl_primitive_desc());
     pd->kind = dnnl_matmul;
     pd->engine = engine;
@@ -784,7 +844,24 @@ dnnl_status_t dnnl_matmul_primitive_desc_create(dnnl_primitive_desc_t *primitive
     pd->user_wei = *weights_desc;
     if (bias_desc) pd->user_bias = *bias_desc;
     pd->user_dst = *dst_desc;
-    st = matmul_select_impl(pd.get(), 0);
+    if (runtime) {
+        // Sizes known only at execution (DNNL_RUNTIME_DIM_VAL, src/common/matmul.cpp:374-401):
+        // nothing can be dispatched yet.  Layouts must be given (no format_tag::any); the
+        // implementation is selected per execution from the memory arguments' descriptors.
+        if (src_desc->is_any() || weights_desc->is_any() || dst_desc->is_any() || (bias_desc && bias_desc->is_any()))
+            return dnnl_unimplemented;
+        if (a.scratchpad_mode == dnnl_scratchpad_mode_user) return dnnl_unimplemented; // its size is not known here
+        pd->src = pd->user_src;
+        pd->wei = pd->user_wei;
+        pd->dst = pd->user_dst;
+        pd->bias = pd->user_bias;
+        pd->impl = IMPL_GENERIC;
+        pd->impl_str = "cuda:runtime_dims";
+        pd->runtime = true;
+        st = dnnl_success;
+    } else {
+        st = matmul_select_impl(pd.get(), 0);
+    }
     if (st != dnnl_success) return st;
     engine->refs.fetch_add(1);
     verbose_create(pd.get(), now_ms() - t0, false);

@@ -83,10 +83,15 @@ struct smem_ctrl_t {
     alignas(16) float bias[EPI_WARPS][EPI_COLS];     // bias, -0 when unset (x + -0 == x for every x)
     alignas(16) int32_t comp[EPI_WARPS][EPI_COLS];   // zp_src * colsum_W[n], 0 when unset
     alignas(16) float zp[EPI_WARPS][EPI_COLS];       // destination zero-point addend
+    // gelu-into-8-bit fast path: constant term of the fused output expression and the
+    // constant part of its error bound, per column
+    alignas(16) float cq[EPI_WARPS][EPI_COLS];
+    alignas(16) float hq[EPI_WARPS][EPI_COLS];
 };
 
 static_assert(offsetof(smem_ctrl_t, wscale) % 16 == 0 && offsetof(smem_ctrl_t, wsx) % 16 == 0 && offsetof(smem_ctrl_t, bias) % 16 == 0
-                && offsetof(smem_ctrl_t, comp) % 16 == 0 && offsetof(smem_ctrl_t, zp) % 16 == 0,
+                && offsetof(smem_ctrl_t, comp) % 16 == 0 && offsetof(smem_ctrl_t, zp) % 16 == 0
+                && offsetof(smem_ctrl_t, cq) % 16 == 0 && offsetof(smem_ctrl_t, hq) % 16 == 0,
         "per-column vectors are read with 128-bit loads");
 static_assert((EPI_COLS * sizeof(float)) % 16 == 0 && (CH * sizeof(float)) % 16 == 0, "chunk offsets keep the alignment");
 
@@ -320,6 +325,14 @@ __device__ __forceinline__ unit_t decode_unit(const tc8_args_t &a, int u, int ro
 // neutral elements (x * 1, x + -0) instead of branches.
 enum { EPI_NONE = 0, EPI_SIMPLE = 1, EPI_GELU_Q = 2, EPI_GENERIC = 3 };
 
+// Coefficients of the error bound of the gelu-into-8-bit fast path, in units of the quantities
+// they multiply (u = 2^-24 is one rounding):
+//   TAU_G x |A x|: fast tanh (5e-7 |x|), x within 3 ulp (2e-7 |x| through gelu' <= 1.13),
+//                  4 u from roundings of terms as large as the gelu term: 9.7e-7 needed;
+//   TAU_S x |B old|: 4 u = 2.4e-7 needed (B, the sum term on both paths, its addition);
+//   TAU_R x (range edge + |zp| + |B zp_sum|): 2 u = 1.2e-7 needed (the two last additions).
+constexpr float TAU_G = 1.5e-6f, TAU_S = 3e-7f, TAU_R = 2e-7f;
+
 struct epi_consts_t {
     float src_scale;   // 1 when unset; with per-row scales: this lane's row's
     bool src_per_row;  // the combined scale vector then holds the weights scales alone
@@ -332,16 +345,6 @@ struct epi_consts_t {
 // the exact gelu_tanh, kept out of line: it is needed for about one element in ten thousand
 // and would otherwise sit in the middle of the hot epilogue code
 __device__ __noinline__ float gelu_tanh_exact(float x) { return gelu_tanh_f32(x); }
-
-// 1 / (exp(2a) + 1) by ex2.approx / rcp.approx: tanh(a) = 1 - 2r with absolute error below 1e-6
-// on the whole range, 0 and 1 at the far ends
-__device__ __forceinline__ float sigmoid_neg2_fast(float a) {
-    float e, r;
-    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(a * 2.885390081777927f));
-    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(e + 1.f));
-    return r;
-}
-
 
 // one non-transcendental eltwise kind applied to the CH values in registers
 __device__ __forceinline__ void eltwise_simple_chunk(const b200_postop_t &e, float (&y)[CH]) {
@@ -477,8 +480,8 @@ enum { SUM_NONE = 0, SUM_8BIT = 1, SUM_OTHER = 2 };
 
 template <bool FP8, int EPI, int SUM, bool PEERS>
 __device__ __forceinline__ void epilogue_chunk(const b200_matmul_params_t &p, const uint32_t (&v)[CH], int64_t m,
-        int64_t n0, const float *wscale, const float *wsx, const float *bias, const int32_t *comp, const float *zp, const epi_consts_t &k,
-        uint32_t taddr, int lane, uint4 old_raw, bool old_prefetched) {
+        int64_t n0, const float *wscale, const float *wsx, const float *bias, const int32_t *comp, const float *zp, const float *cq,
+        const float *hq, const epi_consts_t &k, uint32_t taddr, int lane, uint4 old_raw, bool old_prefetched) {
     const int64_t nvalid = m < p.M ? (p.N - n0 < CH ? p.N - n0 : CH) : 0;
     char *drow = (char *)p.dst + (size_t)((m < p.M ? m : 0) * p.dst_sm + n0) * (dt_bits(p.dst_dt) / 8);
 
@@ -532,37 +535,42 @@ __device__ __forceinline__ void epilogue_chunk(const b200_matmul_params_t &p, co
 
     if (EPI == EPI_GELU_Q) {
         // gelu_tanh (then optionally sum) into an s8 / u8 destination, bit-exact.  The exact
-        // value needs a double-precision tanh; almost always it is not needed: evaluate with a
-        // fast tanh (ex2 / rcp, absolute error < 1e-6, saturating to +-1 by itself) and fused
-        // multiply-adds, bound the distance tau between this value and the exact one (propagated
-        // error bound with a 4x margin), and convert both o + tau and o - tau with the
+        // value needs a double-precision tanh; almost always it is not needed: evaluate a fast
+        // value o with a fast tanh (ex2 / rcp: 1 / (exp(2g) + 1) with absolute error below 1e-6
+        // on the whole range, 0 and 1 at the far ends) and fused multiply-adds, bound its
+        // distance tau from the exact value, and convert both o + tau and o - tau with the
         // saturating round-to-nearest-even conversion.  If the two bytes agree, the exact value
         // -- which lies between them -- converts to the same byte, saturation included; only
         // elements where they differ are recomputed exactly (one warp vote per chunk).
         // The chunk is handled as two independent halves of eight columns, each a sequence
         // of passes of eight independent operations, ending in packed bytes: short live
         // ranges, no per-element control flow.
-        const float sqrt_2_over_pi = 0.79788458347320556640625f, fitting_const = 0.044715f;
-        const float g_lin = sqrt_2_over_pi, g_cub = sqrt_2_over_pi * fitting_const;
+        // Fast value: with A = elt_scale / dst_scale, B = sum_scale / dst_scale and the per-column
+        // constant C = zp_dst - B * zp_sum (cq[]), o = gelu(x) * A + old * B + C in two fused
+        // multiply-adds.  Its distance from the exact value is at most
+        //   tau = TAU_G |A| |x| + TAU_S |B| |old| + TAU_R (R + |zp_dst| + |B| |zp_sum|)   (last term: hq[])
+        // with R the edge of the destination range: beyond it both conversions saturate to the
+        // same byte whatever tau is.
         const float elt_scale = p.po[0].scale;
         const float sum_scale = SUM != SUM_NONE ? p.po[1].scale : 0.f;
         const float sum_zp = SUM != SUM_NONE ? (float)p.po[1].zero_point : 0.f;
-        const float inv_abs = 2e-6f * fabsf(k.dst_inv) * fabsf(elt_scale);
+        const float A = elt_scale * k.dst_inv, B = sum_scale * k.dst_inv;
+        const float inv_abs = TAU_G * fabsf(A), c2 = TAU_S * fabsf(B);
         const bool is_s8 = p.dst_dt == B200_DT_S8;
-        const float tau0 = inv_abs + 4e-7f * (is_s8 ? 130.f : 258.f);
+        // 2 log2(e) folded into the polynomial: exp(2 g) = 2^(gl x + gc x^3)
+        const float gl = 2.885390081777927f * 0.79788458347320556640625f, gc = gl * 0.044715f;
         static_assert(CH == 16, "four packed words per chunk");
         uint32_t packed[4];
         uint32_t risky = 0;
 #pragma unroll
         for (int hb = 0; hb < CH; hb += 8) {
-            float x[8], g[8], t[8], o[8];
+            float x[8], t[8], o[8], tau[8];
 #pragma unroll
             for (int q = 0; q < 2; ++q) {
                 const float4 a = ((const float4 *)wsx)[hb / 4 + q], b = ((const float4 *)bias)[hb / 4 + q];
                 const int4 c = ((const int4 *)comp)[hb / 4 + q];
                 const float ws[4] = {a.x, a.y, a.z, a.w}, bs[4] = {b.x, b.y, b.z, b.w};
                 const int cs[4] = {c.x, c.y, c.z, c.w};
-#pragma unroll
                 float accf[4];
 #pragma unroll
                 for (int i = 0; i < 4; ++i) accf[i] = FP8 ? __uint_as_float(v[hb + 4 * q + i]) : (float)((int)v[hb + 4 * q + i] - cs[i]);
@@ -574,33 +582,49 @@ __device__ __forceinline__ void epilogue_chunk(const b200_matmul_params_t &p, co
                 for (int i = 0; i < 4; ++i) x[4 * q + i] = fmaf(accf[i], ws[i], bs[i]); // within 3 ulp of the reference's unfused value
             }
 #pragma unroll
-            for (int j = 0; j < 8; ++j) g[j] = x[j] * fmaf(g_cub, x[j] * x[j], g_lin);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) t[j] = sigmoid_neg2_fast(g[j]); // r = 1 / (exp(2g) + 1): tanh(g) = 1 - 2r
-            const float4 z0 = ((const float4 *)zp)[hb / 4], z1 = ((const float4 *)zp)[hb / 4 + 1];
-            const float zs[8] = {z0.x, z0.y, z0.z, z0.w, z1.x, z1.y, z1.z, z1.w};
+            for (int j = 0; j < 8; ++j) {
+                const float e2 = x[j] * fmaf(gc, x[j] * x[j], gl);
+                float ex;
+                asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(ex) : "f"(e2));
+                asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(t[j]) : "f"(ex + 1.f)); // r = 1 / (exp(2g) + 1): tanh(g) = 1 - 2r
+            }
+            const float4 c0 = ((const float4 *)cq)[hb / 4], c1 = ((const float4 *)cq)[hb / 4 + 1];
+            const float4 h0 = ((const float4 *)hq)[hb / 4], h1 = ((const float4 *)hq)[hb / 4 + 1];
+            const float cv[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+            const float hv[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
                 const float gelu = fmaf(-x[j], t[j], x[j]); // 0.5 x (1 + tanh) = x - x r
-                float r = __fmul_rn(gelu, elt_scale);
-                if (SUM != SUM_NONE) r = __fadd_rn(r, __fmul_rn(sum_scale, __fsub_rn(old_val(hb + j), sum_zp)));
-                r = __fmul_rn(r, k.dst_inv);
-                o[j] = FP8 ? r : __fadd_rn(r, zs[j]);
+                float s = cv[j];
+                tau[j] = fmaf(inv_abs, fabsf(x[j]), hv[j]);
+                if (SUM != SUM_NONE) {
+                    const float old = old_val(hb + j);
+                    s = fmaf(old, B, s);
+                    tau[j] = fmaf(c2, fabsf(old), tau[j]);
+                }
+                o[j] = fmaf(gelu, A, s);
             }
 #pragma unroll
             for (int q = 0; q < 2; ++q) {
-                uint32_t w = 0;
+                int up[4];
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     const int j = 4 * q + i;
-                    // the part of the bound that grows with |o| is taken at the edge of the destination
-                    // type's range: beyond it both conversions saturate whatever tau is
-                    const float tau = fmaf(inv_abs, fabsf(x[j]), tau0);
-                    const uint32_t up = is_s8 ? cvt_sat_s8(o[j] + tau) : cvt_sat_u8(o[j] + tau);
-                    const uint32_t dn = is_s8 ? cvt_sat_s8(o[j] - tau) : cvt_sat_u8(o[j] - tau);
-                    if (up != dn) risky |= 1u << (hb + j);
-                    w |= up << (8 * i);
+                    int dn;
+                    if (is_s8) {
+                        asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(up[i]) : "f"(o[j] + tau[j]));
+                        asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(dn) : "f"(o[j] - tau[j]));
+                    } else {
+                        asm("cvt.rni.sat.u8.f32 %0, %1;" : "=r"(up[i]) : "f"(o[j] + tau[j]));
+                        asm("cvt.rni.sat.u8.f32 %0, %1;" : "=r"(dn) : "f"(o[j] - tau[j]));
+                    }
+                    if (up[i] != dn) risky |= 1u << (hb + j);
                 }
+                // low bytes of the four results into one word
+                uint32_t lo, hi, w;
+                asm("prmt.b32 %0, %1, %2, 0x0040;" : "=r"(lo) : "r"(up[0]), "r"(up[1]));
+                asm("prmt.b32 %0, %1, %2, 0x0040;" : "=r"(hi) : "r"(up[2]), "r"(up[3]));
+                asm("prmt.b32 %0, %1, %2, 0x5410;" : "=r"(w) : "r"(lo), "r"(hi));
                 packed[hb / 4 + q] = w;
             }
         }
@@ -837,6 +861,7 @@ __global__ void __launch_bounds__(640, 1) matmul_tc8_kernel(const __grid_constan
         const int half = ew >> 2;          // which quarter of the tile's columns this warp converts
         float *wscale = ctrl->wscale[ew], *wsx = ctrl->wsx[ew], *bias = ctrl->bias[ew], *zpv = ctrl->zp[ew];
         int32_t *comp = ctrl->comp[ew];
+        float *cqv = ctrl->cq[ew], *hqv = ctrl->hq[ew];
         const bool has_comp = !FP8 && p.src_zp.ptr && p.wei_colsum;
         const int zp_src = has_comp ? load_int(p.src_zp.dt, p.src_zp.ptr, 0) : 0;
         epi_consts_t k;
@@ -871,6 +896,11 @@ __global__ void __launch_bounds__(640, 1) matmul_tc8_kernel(const __grid_constan
                 // the int8 path adds the zero-point (+0 when unset) whenever any attribute is set; -0 adds nothing
                 zpv[j] = !k.int8_nondefault ? -0.f
                         : (in && p.dst_zp.ptr) ? (float)((const int32_t *)p.dst_zp.ptr)[p.dst_zp.s1 ? n : 0] : 0.f;
+                if (EPI == EPI_GELU_Q) {
+                    const float bz = SUM != SUM_NONE ? p.po[1].scale * k.dst_inv * (float)p.po[1].zero_point : 0.f;
+                    cqv[j] = zpv[j] - bz;
+                    hqv[j] = TAU_R * ((p.dst_dt == B200_DT_S8 ? 130.f : 258.f) + fabsf(zpv[j]) + fabsf(bz));
+                }
             }
             __syncwarp();
             const int64_t m = m0 + quarter * 32 + lane;
@@ -906,8 +936,8 @@ __global__ void __launch_bounds__(640, 1) matmul_tc8_kernel(const __grid_constan
                 uint32_t v[CH];
                 tmem_ld16_issue(trow + c * CH, v);
                 tmem_ld_wait(v);
-                epilogue_chunk<FP8, EPI, SUM, PEERS>(p, v, m, n0 + c * CH, wscale + c * CH, wsx + c * CH, bias + c * CH, comp + c * CH, zpv + c * CH, k,
-                        trow + c * CH, lane, ob0, (ofbits & 1u) != 0);
+                epilogue_chunk<FP8, EPI, SUM, PEERS>(p, v, m, n0 + c * CH, wscale + c * CH, wsx + c * CH, bias + c * CH, comp + c * CH, zpv + c * CH,
+                        cqv + c * CH, hqv + c * CH, k, trow + c * CH, lane, ob0, (ofbits & 1u) != 0);
                 ob0 = ob1;
                 ob1 = ob2;
                 ob2 = ob3;

@@ -125,3 +125,66 @@ def test_batched_matches_oracle_per_slice(kind):
         want = B.run_oracle(c, exact_acc=1 if "i8" in impl else 0)
         g, w = dt.to_f32(got[b], c.dst_dt).astype(np.float64), dt.to_f32(want, c.dst_dt).astype(np.float64)
         assert (np.abs(g - w) <= c.atol + c.rtol * np.abs(w)).all(), "%s batch %s" % (kind, b)
+
+
+# ---- runtime dims ---------------------------------------------------------------------------
+
+RT = -(1 << 63)  # DNNL_RUNTIME_DIM_VAL
+
+
+def _rt_pd(eng):
+    a = api.PrimitiveAttr()
+    a.set_scales(api.ARG_SRC, 0, (), dt.F32)
+    a.set_scales(api.ARG_WEIGHTS, 2, (), dt.F32)
+    src = api.MemoryDesc((RT, 64), dt.S8, strides=(RT, 1))
+    wei = api.MemoryDesc((64, 48), dt.S8, strides=(1, 64))      # K contiguous
+    dst = api.MemoryDesc((RT, 48), dt.BF16, strides=(RT, 1))
+    return api.matmul_primitive_desc(eng, src, wei, dst, attr=a)
+
+
+def test_runtime_dims_descriptor_host():
+    eng = api.Engine()
+    pd = _rt_pd(eng)
+    assert pd.impl_info_str() == "cuda:runtime_dims"
+    assert not pd.next_impl()
+    # a layout must be given when sizes are not
+    with pytest.raises(api.Error):
+        api.matmul_primitive_desc(eng, api.MemoryDesc((RT, 64), dt.S8, strides=(RT, 1)),
+                                  api.MemoryDesc((64, 48), dt.S8, api.TAG_ANY), api.MemoryDesc((RT, 48), dt.BF16, strides=(RT, 1)))
+
+
+@pytest.mark.gpu
+def test_runtime_dims_execute_with_two_sizes():
+    """One primitive created with an unknown M (DNNL_RUNTIME_DIM_VAL), executed with 40 and
+    with 200 rows: each result equals the oracle's for that size."""
+    eng = api.Engine()
+    strm = api.Stream(eng)
+    prim = api.Primitive(_rt_pd(eng))
+    r = np.random.default_rng(93)
+    wei = r.integers(-127, 128, (64, 48), dtype=np.int8)
+    wscale = r.uniform(1e-3, 4e-3, 48).astype(np.float32)
+    sscale = np.float32([0.03])
+    wei_m = api.Memory(api.MemoryDesc((64, 48), dt.S8, strides=(1, 64)), eng)
+    wei_m.write(np.ascontiguousarray(wei.T))
+    ws_m = api.Memory(api.MemoryDesc((48,), dt.F32, api.TAG_A), eng)
+    ws_m.write(wscale)
+    ss_m = api.Memory(api.MemoryDesc((1,), dt.F32, api.TAG_A), eng)
+    ss_m.write(sscale)
+    for M in (40, 200):
+        src = r.integers(-128, 128, (M, 64), dtype=np.int8)
+        src_m = api.Memory(api.MemoryDesc((M, 64), dt.S8, api.TAG_AB), eng)
+        src_m.write(src)
+        dst_m = api.Memory(api.MemoryDesc((M, 48), dt.BF16, api.TAG_AB), eng)
+        prim.execute(strm, {api.ARG_SRC: src_m, api.ARG_WEIGHTS: wei_m, api.ARG_DST: dst_m,
+                            api.ARG_ATTR_SCALES | api.ARG_SRC: ss_m, api.ARG_ATTR_SCALES | api.ARG_WEIGHTS: ws_m})
+        strm.wait()
+        got = dt.to_f32(dst_m.read(dt.RAW[dt.BF16], (M, 48)), dt.BF16)
+        c = MatmulCase("rt", M, 48, 64, src=src, src_dt=dt.S8, wei=np.ascontiguousarray(wei.T), wei_dt=dt.S8, dst_dt=dt.BF16,
+                       wei_tag="ba", src_scale=Quant(sscale, dt.F32, 0), wei_scale=Quant(wscale, dt.F32, 2))
+        want = dt.to_f32(B.run_oracle(c, exact_acc=1), dt.BF16)
+        assert np.allclose(got, want, rtol=1e-2, atol=1e-2), M
+    # a memory whose fixed dim differs from the descriptor's is refused
+    bad = api.Memory(api.MemoryDesc((40, 32), dt.S8, api.TAG_AB), eng)
+    with pytest.raises(api.Error):
+        prim.execute(strm, {api.ARG_SRC: bad, api.ARG_WEIGHTS: wei_m, api.ARG_DST: dst_m,
+                            api.ARG_ATTR_SCALES | api.ARG_SRC: ss_m, api.ARG_ATTR_SCALES | api.ARG_WEIGHTS: ws_m})

@@ -11,7 +11,8 @@ BIN = Path(__file__).resolve().parents[1] / "oracle" / "_ref"
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("name,impl", [("consumer_dnnl_hpp_int8_matmul", "cuda:sm100:tcgen05_i8"),
-                                       ("consumer_dnnl_h_quantize_reorder", "cuda:reorder_quant")])
+                                       ("consumer_dnnl_h_quantize_reorder", "cuda:reorder_quant"),
+                                       ("consumer_dnnl_hpp_weights_decompression", "cuda:sm100:wc_gemv cuda:sm100:wc_tcgen05")])
 def test_reference_api_program_runs_on_the_cuda_engine(name, impl):
     exe = BIN / name
     if not exe.exists():

@@ -146,6 +146,21 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, smem_c
     return false;
 }
 
+// the same wait by polling: for the two single threads of the pair kernel whose waits are part of
+// every stage's round trip (a suspended waiter is woken later than a poll sees the phase flip)
+__device__ __forceinline__ bool mbar_wait_poll(uint64_t *bar, uint32_t parity, smem_ctrl_t *c, uint32_t *status, uint32_t code) {
+    for (uint32_t i = 0; i < WAIT_SPINS; ++i) {
+        if (mbar_test(bar, parity)) return true;
+        if ((i & 63) == 63) {
+            if (c->abort) return false;
+            __nanosleep(20);
+        }
+    }
+    c->abort = 1;
+    if (status) atomicOr(status, code);
+    return false;
+}
+
 __device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, int c0, int c1, uint64_t *bar) {
     asm volatile(
             "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
@@ -732,6 +747,7 @@ __global__ void __launch_bounds__(640, 1) matmul_tc8_kernel(const __grid_constan
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int KB = args.k_blocks;
     constexpr int NST = PAIR ? PAIR_STAGES : STAGES;
+    constexpr bool PAIR_POLL = PAIR; // see mbar_wait_poll
     constexpr int SBYTES = PAIR ? PAIR_STAGE_BYTES : STAGE_BYTES;   // one stage
     constexpr int BBYTES = PAIR ? PAIR_B_BYTES : B_BYTES;           // its weights part (wide unit)
     const uint32_t rank = PAIR ? cluster_ctarank() : 0;             // 0: leader
@@ -780,7 +796,9 @@ __global__ void __launch_bounds__(640, 1) matmul_tc8_kernel(const __grid_constan
                 const unit_t un = decode_unit(args, u, TILE_ROWS);
                 for (int kb = 0; kb < KB; ++kb, ++it) {
                     const uint32_t s = it % NST, r = it / NST;
-                    if (!(ok = mbar_wait(&ctrl->empty[s], (r & 1) ^ 1, ctrl, p.status, ST_WAIT_EMPTY))) break;
+                    if (!(ok = PAIR_POLL ? mbar_wait_poll(&ctrl->empty[s], (r & 1) ^ 1, ctrl, p.status, ST_WAIT_EMPTY)
+                                         : mbar_wait(&ctrl->empty[s], (r & 1) ^ 1, ctrl, p.status, ST_WAIT_EMPTY)))
+                        break;
                     uint8_t *sa = smem + (size_t)s * SBYTES;
                     // This CTA's share of the unit's weight rows (all of them, or half in the pair
                     // kernel) is one or two boxes: of 128 rows, or of 64 (second map) where the share
@@ -834,7 +852,9 @@ __global__ void __launch_bounds__(640, 1) matmul_tc8_kernel(const __grid_constan
                 const uint32_t tmem_d = tmem_base + a * BN;
                 for (int kb = 0; kb < KB; ++kb, ++it) {
                     const uint32_t s = it % NST, r = it / NST;
-                    if (!(ok = mbar_wait(&ctrl->full[s], r & 1, ctrl, p.status, ST_WAIT_FULL))) break;
+                    if (!(ok = PAIR_POLL ? mbar_wait_poll(&ctrl->full[s], r & 1, ctrl, p.status, ST_WAIT_FULL)
+                                         : mbar_wait(&ctrl->full[s], r & 1, ctrl, p.status, ST_WAIT_FULL)))
+                        break;
                     tcgen05_fence_after();
                     const uint64_t adesc = adesc0 + (uint64_t)(s * (SBYTES >> 4)), bdesc = bdesc0 + (uint64_t)(s * (SBYTES >> 4));
 #ifndef TC8_ABL_NOMMA

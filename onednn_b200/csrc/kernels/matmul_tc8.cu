@@ -66,6 +66,7 @@ constexpr int CH = 16;                        // columns per epilogue chunk (hel
 constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t WAIT_TRIES = 1u << 20; // bounded wait: a million suspended waits of up to a microsecond
 constexpr uint32_t WAIT_SPINS = 1u << 22; // drain loop of the producer: polls 64 ns apart
+constexpr uint32_t POLL_TRIES = 1u << 26; // polling waits of the two issuing threads
 
 enum : uint32_t { ST_WAIT_FULL = 0x1, ST_WAIT_EMPTY = 0x2, ST_WAIT_TMEM_FULL = 0x4, ST_WAIT_TMEM_EMPTY = 0x8 };
 
@@ -146,10 +147,12 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, smem_c
     return false;
 }
 
-// the same wait by polling: for the two single threads of the pair kernel whose waits are part of
-// every stage's round trip (a suspended waiter is woken later than a poll sees the phase flip)
+// The same wait by polling, for the copy-issuing and the MMA-issuing thread: their waits are
+// part of every stage's round trip, and a poll sees the phase flip sooner than a suspended
+// waiter is woken (C1: 2 us per launch).  Two single threads: the polls cost nothing else.
+// Bounded like the other: 2^26 polls, of the order of a second.
 __device__ __forceinline__ bool mbar_wait_poll(uint64_t *bar, uint32_t parity, smem_ctrl_t *c, uint32_t *status, uint32_t code) {
-    for (uint32_t i = 0; i < WAIT_SPINS; ++i) {
+    for (uint32_t i = 0; i < POLL_TRIES; ++i) {
         if (mbar_test(bar, parity)) return true;
         if ((i & 63) == 63) {
             if (c->abort) return false;
@@ -747,7 +750,6 @@ __global__ void __launch_bounds__(640, 1) matmul_tc8_kernel(const __grid_constan
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int KB = args.k_blocks;
     constexpr int NST = PAIR ? PAIR_STAGES : STAGES;
-    constexpr bool PAIR_POLL = PAIR; // see mbar_wait_poll
     constexpr int SBYTES = PAIR ? PAIR_STAGE_BYTES : STAGE_BYTES;   // one stage
     constexpr int BBYTES = PAIR ? PAIR_B_BYTES : B_BYTES;           // its weights part (wide unit)
     const uint32_t rank = PAIR ? cluster_ctarank() : 0;             // 0: leader
@@ -796,9 +798,7 @@ __global__ void __launch_bounds__(640, 1) matmul_tc8_kernel(const __grid_constan
                 const unit_t un = decode_unit(args, u, TILE_ROWS);
                 for (int kb = 0; kb < KB; ++kb, ++it) {
                     const uint32_t s = it % NST, r = it / NST;
-                    if (!(ok = PAIR_POLL ? mbar_wait_poll(&ctrl->empty[s], (r & 1) ^ 1, ctrl, p.status, ST_WAIT_EMPTY)
-                                         : mbar_wait(&ctrl->empty[s], (r & 1) ^ 1, ctrl, p.status, ST_WAIT_EMPTY)))
-                        break;
+                    if (!(ok = mbar_wait_poll(&ctrl->empty[s], (r & 1) ^ 1, ctrl, p.status, ST_WAIT_EMPTY))) break;
                     uint8_t *sa = smem + (size_t)s * SBYTES;
                     // This CTA's share of the unit's weight rows (all of them, or half in the pair
                     // kernel) is one or two boxes: of 128 rows, or of 64 (second map) where the share
@@ -847,14 +847,12 @@ __global__ void __launch_bounds__(640, 1) matmul_tc8_kernel(const __grid_constan
             for (int u = unit0; u < args.units && ok; u += ustep, ++tile_i) {
                 const uint32_t a = tile_i & 1, use = tile_i >> 1;
                 const uint32_t idesc = u < args.full_units ? args.idesc : args.idesc_tail;
-                if (!(ok = mbar_wait(&ctrl->tmem_empty[a], (use & 1) ^ 1, ctrl, p.status, ST_WAIT_TMEM_EMPTY))) break;
+                if (!(ok = mbar_wait_poll(&ctrl->tmem_empty[a], (use & 1) ^ 1, ctrl, p.status, ST_WAIT_TMEM_EMPTY))) break;
                 tcgen05_fence_after();
                 const uint32_t tmem_d = tmem_base + a * BN;
                 for (int kb = 0; kb < KB; ++kb, ++it) {
                     const uint32_t s = it % NST, r = it / NST;
-                    if (!(ok = PAIR_POLL ? mbar_wait_poll(&ctrl->full[s], r & 1, ctrl, p.status, ST_WAIT_FULL)
-                                         : mbar_wait(&ctrl->full[s], r & 1, ctrl, p.status, ST_WAIT_FULL)))
-                        break;
+                    if (!(ok = mbar_wait_poll(&ctrl->full[s], r & 1, ctrl, p.status, ST_WAIT_FULL))) break;
                     tcgen05_fence_after();
                     const uint64_t adesc = adesc0 + (uint64_t)(s * (SBYTES >> 4)), bdesc = bdesc0 + (uint64_t)(s * (SBYTES >> 4));
 #ifndef TC8_ABL_NOMMA

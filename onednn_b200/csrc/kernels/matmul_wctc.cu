@@ -125,6 +125,21 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, ctrl_t
     if (status) atomicOr(status, code);
     return false;
 }
+// The same wait by polling, for the copy-issuing and the MMA-issuing thread, whose waits are
+// part of every stage's round trip: a poll sees the phase flip sooner than a suspended waiter
+// is woken.  Bounded as well: 2^26 polls, of the order of a second.
+__device__ __forceinline__ bool mbar_wait_poll(uint64_t *bar, uint32_t parity, ctrl_t *c, uint32_t *status, uint32_t code) {
+    for (uint32_t i = 0; i < (1u << 26); ++i) {
+        if (mbar_test(bar, parity)) return true;
+        if ((i & 63) == 63) {
+            if (c->abort) return false;
+            __nanosleep(20);
+        }
+    }
+    c->abort = 1;
+    if (status) atomicOr(status, code);
+    return false;
+}
 __device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, int c0, int c1, uint64_t *bar) {
     asm volatile(
             "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
@@ -239,7 +254,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                 const int row0 = (int)((tile / args.n_tiles) * args.rows_per_pass);
                 for (int kb = 0; kb < KB; ++kb, ++it) {
                     const uint32_t s = it % STAGES, r = it / STAGES;
-                    if (!(ok = mbar_wait(&ctrl->empty[s], (r & 1) ^ 1, ctrl, p.status, ST_WAIT_EMPTY))) break;
+                    if (!(ok = mbar_wait_poll(&ctrl->empty[s], (r & 1) ^ 1, ctrl, p.status, ST_WAIT_EMPTY))) break;
                     mbar_expect_tx(&ctrl->full_a[s], b_bytes);
                     tma_load_2d(smem + (size_t)s * stage_bytes + A_BYTES, &tmap_x, kb * (TK * 2), row0, &ctrl->full_a[s]); // byte coordinates
                 }
@@ -262,12 +277,12 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             // descriptors of stage 0; a stage further on is stage_bytes / 16 more in the address field
             const uint64_t adesc0 = make_smem_desc(smem_u32(smem)), bdesc0 = make_smem_desc(smem_u32(smem) + A_BYTES);
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tile_i) {
-                if (!(ok = mbar_wait(&ctrl->acc_empty, (tile_i & 1) ^ 1, ctrl, p.status, ST_WAIT_ACC))) break;
+                if (!(ok = mbar_wait_poll(&ctrl->acc_empty, (tile_i & 1) ^ 1, ctrl, p.status, ST_WAIT_ACC))) break;
                 tc_fence_after();
                 for (int kb = 0; kb < KB; ++kb, ++it) {
                     const uint32_t s = it % STAGES, r = it / STAGES;
                     // one barrier per stage: converted weights (four warps) and activations (copy bytes)
-                    if (!(ok = mbar_wait(&ctrl->full_a[s], r & 1, ctrl, p.status, ST_WAIT_FULL))) break;
+                    if (!(ok = mbar_wait_poll(&ctrl->full_a[s], r & 1, ctrl, p.status, ST_WAIT_FULL))) break;
                     tc_fence_after();
                     const uint64_t adesc = adesc0 + (uint64_t)(s * (stage_bytes >> 4)), bdesc = bdesc0 + (uint64_t)(s * (stage_bytes >> 4));
 #pragma unroll

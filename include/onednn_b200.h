@@ -319,6 +319,13 @@ dnnl_status_t DNNL_API dnnl_post_ops_get_params_prelu(const_dnnl_post_ops_t post
 dnnl_status_t DNNL_API dnnl_matmul_primitive_desc_create(dnnl_primitive_desc_t *primitive_desc, dnnl_engine_t engine,
         const_dnnl_memory_desc_t src_desc, const_dnnl_memory_desc_t weights_desc, const_dnnl_memory_desc_t bias_desc,
         const_dnnl_memory_desc_t dst_desc, const_dnnl_primitive_attr_t attr);
+/* Inner product, forward (replaces dnnl.h:2471-2476, src/common/inner_product.cpp:37-120): 2-D
+ * src (N, IC) x weights (OC, IC), bias (OC), dst (N, OC).  Runs as the matmul with the weights'
+ * two dims exchanged; scales / zero-points / post-ops as for matmul, weights masks over (OC, IC). */
+dnnl_status_t DNNL_API dnnl_inner_product_forward_primitive_desc_create(dnnl_primitive_desc_t *primitive_desc,
+        dnnl_engine_t engine, dnnl_prop_kind_t prop_kind, const_dnnl_memory_desc_t src_desc,
+        const_dnnl_memory_desc_t weights_desc, const_dnnl_memory_desc_t bias_desc, const_dnnl_memory_desc_t dst_desc,
+        const_dnnl_primitive_attr_t attr);
 dnnl_status_t DNNL_API dnnl_reorder_primitive_desc_create(dnnl_primitive_desc_t *reorder_primitive_desc,
         const_dnnl_memory_desc_t src_desc, dnnl_engine_t src_engine, const_dnnl_memory_desc_t dst_desc,
         dnnl_engine_t dst_engine, const_dnnl_primitive_attr_t attr);

@@ -322,6 +322,15 @@ def matmul_primitive_desc(engine, src_md, weights_md, dst_md, bias_md=None, attr
     return PrimitiveDesc(h, engine)
 
 
+def inner_product_primitive_desc(engine, src_md, weights_md, dst_md, bias_md=None, attr=None, prop_kind=96):
+    """Forward inner product: src (N, IC), weights (OC, IC), bias (OC), dst (N, OC)."""
+    h = C.c_void_p()
+    _ck(lib().dnnl_inner_product_forward_primitive_desc_create(
+        C.byref(h), engine.h, prop_kind, src_md.h, weights_md.h, bias_md.h if bias_md is not None else None, dst_md.h,
+        attr.h if attr is not None else None), "inner_product_forward_primitive_desc_create")
+    return PrimitiveDesc(h, engine)
+
+
 def reorder_primitive_desc(src_engine, src_md, dst_engine, dst_md, attr=None):
     h = C.c_void_p()
     _ck(lib().dnnl_reorder_primitive_desc_create(C.byref(h), src_md.h, src_engine.h, dst_md.h, dst_engine.h,

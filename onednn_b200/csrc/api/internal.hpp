@@ -182,6 +182,9 @@ struct dnnl_primitive_desc {
     // some dims are DNNL_RUNTIME_DIM_VAL: the implementation is chosen at execution, from the
     // descriptors of the memory arguments
     bool runtime = false;
+    // kind == dnnl_inner_product: `inner` is the matmul it runs as; weights / bias keep the
+    // descriptors the caller gave, (OC, IC) and (OC)
+    bool ip = false;
 
     int64_t M() const { return dst.dims[dst.ndims - 2]; }
     int64_t N() const { return dst.dims[dst.ndims - 1]; }
@@ -204,6 +207,7 @@ dnnl_status_t matmul_validate(const dnnl_memory_desc &src, const dnnl_memory_des
 dnnl_status_t matmul_select_impl(dnnl_primitive_desc *pd, int first);
 dnnl_status_t matmul_execute(const dnnl_primitive *prim, dnnl_stream *stream, const std::map<int, dnnl_memory *> &args);
 dnnl_status_t reorder_execute(const dnnl_primitive *prim, dnnl_stream *stream, const std::map<int, dnnl_memory *> &args);
+dnnl_status_t inner_product_execute(const dnnl_primitive *prim, dnnl_stream *stream, const std::map<int, dnnl_memory *> &args);
 
 // ---- verbose (service.cpp) ----
 int verbose_level();

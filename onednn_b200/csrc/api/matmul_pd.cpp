@@ -868,3 +868,120 @@ dnnl_status_t dnnl_matmul_primitive_desc_create(dnnl_primitive_desc_t *primitive
     *primitive_desc = pd.release();
     return dnnl_success;
 }
+
+// ---- inner product (forward) as a view of the matmul -----------------------------------------
+// dst(N, OC) = src(N, IC) x weights(OC, IC)^T + bias(OC)  (src/common/inner_product.cpp:37-120).
+// The weights' (OC, IC) descriptor read with its two strides exchanged is the matmul's (K, N)
+// weights; row-major (OC, IC) -- what format_tag::any resolves to here -- is K-contiguous per
+// output channel, the operand layout of the tensor-core kernels, so nothing is repacked.
+
+dnnl_status_t dnnl_inner_product_forward_primitive_desc_create(dnnl_primitive_desc_t *primitive_desc, dnnl_engine_t engine,
+        dnnl_prop_kind_t prop_kind, const_dnnl_memory_desc_t src_desc, const_dnnl_memory_desc_t weights_desc,
+        const_dnnl_memory_desc_t bias_desc, const_dnnl_memory_desc_t dst_desc, const_dnnl_primitive_attr_t attr) {
+    if (!primitive_desc || !engine || !src_desc || !weights_desc || !dst_desc) return dnnl_invalid_arguments;
+    if (prop_kind != dnnl_forward_training && prop_kind != dnnl_forward_inference) return dnnl_invalid_arguments;
+    const dnnl_memory_desc &s = *src_desc, &w = *weights_desc, &d = *dst_desc;
+    if (s.ndims != w.ndims || d.ndims != 2) return dnnl_invalid_arguments;
+    if (s.ndims != 2) return dnnl_unimplemented; // spatial dims: not on this path
+    if (s.has_runtime_dims() || w.has_runtime_dims() || d.has_runtime_dims()) return dnnl_unimplemented;
+    if (s.dims[0] != d.dims[0] || s.dims[1] != w.dims[1] || w.dims[0] != d.dims[1]) return dnnl_invalid_arguments;
+    const bool with_bias = bias_desc && bias_desc->ndims != 0;
+    if (with_bias && (bias_desc->ndims != 1 || bias_desc->dims[0] != d.dims[1])) return dnnl_invalid_arguments;
+    if (w.format_kind == dnnl_format_kind_opaque) return dnnl_unimplemented;
+    static const dnnl_primitive_attr default_attr;
+    const dnnl_primitive_attr &a = attr ? *attr : default_attr;
+
+    auto in = std::make_shared<dnnl_primitive_desc>();
+    in->kind = dnnl_matmul;
+    in->engine = engine;
+    in->attr = a;
+    // weights masks and groups follow the exchange of the weights' two dims
+    for (auto *m : {&in->attr.scales, &in->attr.zero_points}) {
+        auto it = m->find(DNNL_ARG_WEIGHTS);
+        if (it == m->end() || !it->second.set) continue;
+        b200::quant_entry_t &q = it->second;
+        q.mask = ((q.mask & 1) << 1) | ((q.mask & 2) >> 1);
+        std::swap(q.groups[0], q.groups[1]);
+    }
+    dnnl_memory_desc wplain = w;
+    if (wplain.is_any()) make_plain(wplain);
+    in->user_src = s;
+    in->user_wei = wplain;
+    std::swap(in->user_wei.dims[0], in->user_wei.dims[1]);
+    std::swap(in->user_wei.strides[0], in->user_wei.strides[1]);
+    in->user_dst = d;
+    if (with_bias) {
+        dnnl_memory_desc b;
+        b.ndims = 2;
+        b.dims[0] = 1;
+        b.dims[1] = bias_desc->dims[0];
+        b.data_type = bias_desc->data_type;
+        b.format_kind = dnnl_blocked;
+        b.strides[1] = bias_desc->is_any() ? 1 : bias_desc->strides[0];
+        b.strides[0] = b.dims[1] * b.strides[1];
+        in->user_bias = b;
+    }
+    dnnl_status_t st = b200::matmul_validate(in->user_src, in->user_wei, with_bias ? &in->user_bias : nullptr, in->user_dst, in->attr);
+    if (st != dnnl_success) return st;
+    st = b200::matmul_select_impl(in.get(), 0);
+    if (st != dnnl_success) return st;
+
+    auto pd = std::unique_ptr<dnnl_primitive_desc>(new dnnl_primitive_desc());
+    pd->kind = dnnl_inner_product;
+    pd->engine = engine;
+    pd->attr = a;
+    pd->user_src = s;
+    pd->user_wei = w;
+    pd->user_dst = d;
+    pd->src = in->src;
+    pd->wei = wplain;
+    pd->dst = in->dst;
+    if (with_bias) {
+        pd->user_bias = *bias_desc;
+        pd->bias = *bias_desc;
+        if (pd->bias.is_any()) make_plain(pd->bias);
+    }
+    pd->impl = in->impl;
+    pd->impl_str = in->impl_str;
+    pd->scratchpad = in->scratchpad;
+    pd->inner = in;
+    pd->ip = true;
+    engine->refs.fetch_add(1);
+    *primitive_desc = pd.release();
+    return dnnl_success;
+}
+
+namespace b200 {
+
+dnnl_status_t inner_product_execute(const dnnl_primitive *prim, dnnl_stream *stream, const std::map<int, dnnl_memory *> &args) {
+    const dnnl_primitive_desc *pd = prim->pd.get();
+    const dnnl_primitive_desc *in = pd->inner.get();
+    std::map<int, dnnl_memory *> a2 = args;
+    dnnl_memory wei, bias;
+    auto wi = args.find(DNNL_ARG_WEIGHTS);
+    if (wi == args.end()) return dnnl_invalid_arguments;
+    wei = *wi->second;
+    wei.md = in->wei;          // the same bytes, dims and strides exchanged
+    wei.md.offset0 = wi->second->md.offset0;
+    wei.owned = false;
+    a2[DNNL_ARG_WEIGHTS] = &wei;
+    if (pd->bias.ndims) {
+        auto bi = args.find(DNNL_ARG_BIAS);
+        if (bi == args.end()) return dnnl_invalid_arguments;
+        bias = *bi->second;
+        bias.md = in->bias;
+        bias.md.offset0 = bi->second->md.offset0;
+        bias.owned = false;
+        a2[DNNL_ARG_BIAS] = &bias;
+    }
+    dnnl_primitive tmp;
+    tmp.pd = pd->inner;
+    tmp.lib_scratch = prim->lib_scratch; // borrowed
+    tmp.lib_scratch_bytes = prim->lib_scratch_bytes;
+    const dnnl_status_t st = matmul_execute(&tmp, stream, a2);
+    tmp.lib_scratch = nullptr;
+    tmp.pd.reset();
+    return st;
+}
+
+} // namespace b200

@@ -238,7 +238,7 @@ dnnl_status_t reorder_execute(const dnnl_primitive *prim, dnnl_stream *stream, c
 
 dnnl_status_t dnnl_primitive_desc_next_impl(dnnl_primitive_desc_t pd) {
     if (!pd) return dnnl_invalid_arguments;
-    if (pd->kind != dnnl_matmul) return dnnl_last_impl_reached;
+    if (pd->kind != dnnl_matmul) return dnnl_last_impl_reached; // reorder, inner product: one implementation
     dnnl_primitive_desc trial = *pd;
     dnnl_status_t st = matmul_select_impl(&trial, pd->impl + 1);
     if (st != dnnl_success) return dnnl_last_impl_reached;
@@ -324,7 +324,7 @@ const_dnnl_memory_desc_t dnnl_primitive_desc_query_md(const_dnnl_primitive_desc_
     switch (what) {
         case dnnl_query_src_md: return index == 0 ? &pd->src : nullptr;
         case dnnl_query_weights_md:
-            if (pd->kind != dnnl_matmul) return nullptr;
+            if (pd->kind != dnnl_matmul && pd->kind != dnnl_inner_product) return nullptr;
             return index == 0 ? &pd->wei : index == 1 ? &pd->bias : nullptr;
         case dnnl_query_dst_md: return index == 0 ? &pd->dst : nullptr;
         case dnnl_query_scratchpad_md: return index == 0 ? &pd->scratchpad : nullptr;
@@ -531,6 +531,7 @@ dnnl_status_t dnnl_primitive_execute(const_dnnl_primitive_t primitive, dnnl_stre
         cudaEventRecord(e0, (cudaStream_t)stream->cuda_stream);
     }
     dnnl_status_t st = pd->kind == dnnl_matmul ? matmul_execute(primitive, stream, m)
+            : pd->kind == dnnl_inner_product   ? inner_product_execute(primitive, stream, m)
                                                : reorder_execute(primitive, stream, m);
     if (prof) {
         cudaEventRecord(e1, (cudaStream_t)stream->cuda_stream);

@@ -188,3 +188,62 @@ def test_runtime_dims_execute_with_two_sizes():
     with pytest.raises(api.Error):
         prim.execute(strm, {api.ARG_SRC: bad, api.ARG_WEIGHTS: wei_m, api.ARG_DST: dst_m,
                             api.ARG_ATTR_SCALES | api.ARG_SRC: ss_m, api.ARG_ATTR_SCALES | api.ARG_WEIGHTS: ws_m})
+
+
+# ---- inner product -------------------------------------------------------------------------
+
+def _ip_pd(eng, wtag=api.TAG_AB):
+    a = api.PrimitiveAttr()
+    a.set_scales(api.ARG_SRC, 0, (), dt.F32)
+    a.set_scales(api.ARG_WEIGHTS, 1 << 0, (), dt.F32)          # per output channel of (OC, IC) weights
+    po = api.PostOps()
+    po.append_eltwise(W.ELTWISE["relu"], 0.0, 0.0)
+    a.set_post_ops(po)
+    return api.inner_product_primitive_desc(
+        eng, api.MemoryDesc((150, 128), dt.S8, api.TAG_AB), api.MemoryDesc((96, 128), dt.S8, wtag),
+        api.MemoryDesc((150, 96), dt.F32, api.TAG_AB), api.MemoryDesc((96,), dt.F32, api.TAG_A), a)
+
+
+def test_inner_product_descriptor_host():
+    """Forward inner product = matmul with the weights' dims exchanged: row-major (OC, IC) weights
+    are already K-contiguous, so the tensor-core kernel takes them as they are."""
+    eng = api.Engine()
+    for wtag in (api.TAG_AB, api.TAG_ANY):
+        pd = _ip_pd(eng, wtag)
+        assert pd.impl_info_str() == "cuda:sm100:tcgen05_i8"
+        assert pd.weights_desc() == api.MemoryDesc((96, 128), dt.S8, api.TAG_AB)
+        assert pd.query_md(api.QUERY_EXEC_ARG_MD, api.ARG_ATTR_SCALES | api.ARG_WEIGHTS).dims == [96]
+    with pytest.raises(api.Error):   # IC of src and weights differ
+        api.inner_product_primitive_desc(eng, api.MemoryDesc((150, 64), dt.S8, api.TAG_AB),
+                                         api.MemoryDesc((96, 128), dt.S8, api.TAG_AB), api.MemoryDesc((150, 96), dt.F32, api.TAG_AB))
+
+
+@pytest.mark.gpu
+def test_inner_product_matches_the_matmul_oracle():
+    eng = api.Engine()
+    strm = api.Stream(eng)
+    prim = api.Primitive(_ip_pd(eng))
+    r = np.random.default_rng(94)
+    src = r.integers(-128, 128, (150, 128), dtype=np.int8)
+    wei = r.integers(-127, 128, (96, 128), dtype=np.int8)       # (OC, IC)
+    bias = r.uniform(-1, 1, 96).astype(np.float32)
+    sscale, wscale = np.float32([0.02]), r.uniform(1e-3, 4e-3, 96).astype(np.float32)
+
+    def mem(md, arr):
+        m = api.Memory(md, eng)
+        m.write(np.ascontiguousarray(arr))
+        return m
+    dst_m = api.Memory(api.MemoryDesc((150, 96), dt.F32, api.TAG_AB), eng)
+    args = {api.ARG_SRC: mem(api.MemoryDesc((150, 128), dt.S8, api.TAG_AB), src),
+            api.ARG_WEIGHTS: mem(api.MemoryDesc((96, 128), dt.S8, api.TAG_AB), wei),
+            api.ARG_BIAS: mem(api.MemoryDesc((96,), dt.F32, api.TAG_A), bias), api.ARG_DST: dst_m,
+            api.ARG_ATTR_SCALES | api.ARG_SRC: mem(api.MemoryDesc((1,), dt.F32, api.TAG_A), sscale),
+            api.ARG_ATTR_SCALES | api.ARG_WEIGHTS: mem(api.MemoryDesc((96,), dt.F32, api.TAG_A), wscale)}
+    prim.execute(strm, args)
+    strm.wait()
+    got = dst_m.read(np.float32, (150, 96))
+    c = MatmulCase("ip", 150, 96, 128, src=src, src_dt=dt.S8, wei=wei, wei_dt=dt.S8, dst_dt=dt.F32, wei_tag="ba",
+                   bias=bias.reshape(1, 96), bias_dt=dt.F32, src_scale=Quant(sscale, dt.F32, 0),
+                   wei_scale=Quant(wscale, dt.F32, 2), post_ops=[W.eltwise("relu", 0.0)])
+    want = B.run_oracle(c, exact_acc=1)
+    assert np.allclose(got, want, rtol=1e-5, atol=1e-5)

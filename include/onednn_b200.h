@@ -223,6 +223,24 @@ dnnl_status_t DNNL_API dnnl_cuda_interop_engine_get_device(dnnl_engine_t engine,
  * No counterpart in the reference. */
 dnnl_status_t DNNL_API dnnl_b200_stream_selftest_bounded_wait(dnnl_stream_t stream, unsigned max_polls);
 
+/* Extensions for tests of the host library's own bookkeeping; no counterparts in the reference.
+ * dnnl_b200_debug_fail_allocations: the next `count` device or pinned-host allocations made by
+ *   this library fail, so that callers see dnnl_out_of_memory without a GPU being exhausted
+ *   (the status the reference returns from its allocators, src/common/memory.cpp:159-163).
+ * dnnl_b200_debug_mark_scratchpads_dirty: what dnnl_stream_wait does after a kernel reported a
+ *   bounded wait that ran out -- every library-owned scratchpad is cleared on the stream before
+ *   its primitive runs again.
+ * dnnl_b200_debug_counter: primitive-cache hits / entries, scratchpad re-clears, kernel launches. */
+enum {
+    DNNL_B200_COUNTER_CACHE_HITS = 0,
+    DNNL_B200_COUNTER_CACHE_SIZE = 1,
+    DNNL_B200_COUNTER_SCRATCH_RECLEARS = 2,
+    DNNL_B200_COUNTER_KERNEL_LAUNCHES = 3
+};
+dnnl_status_t DNNL_API dnnl_b200_debug_fail_allocations(int count);
+dnnl_status_t DNNL_API dnnl_b200_debug_mark_scratchpads_dirty(void);
+dnnl_status_t DNNL_API dnnl_b200_debug_counter(int which, uint64_t *value);
+
 /* ---- memory descriptors (replaces dnnl.h:826-1200; reference implementation
  *      src/common/memory_desc.cpp, memory_desc_wrapper.hpp) ----------------------- */
 dnnl_status_t DNNL_API dnnl_memory_desc_destroy(dnnl_memory_desc_t memory_desc);

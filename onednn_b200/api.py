@@ -376,7 +376,8 @@ class CasePlan:
     and reorders the plain weights into it once (the reference's recommended usage);
     ``weights="plain"`` hands the plain weights to the primitive as they are."""
 
-    def __init__(self, case, engine, stream, weights="any", impl=None, upload=True, dst_strides=None):
+    def __init__(self, case, engine, stream, weights="any", impl=None, upload=True, dst_strides=None,
+                 scratchpad="library"):
         from . import workloads as W
         self.case, self.engine, self.stream = case, engine, stream
         c = case
@@ -410,6 +411,9 @@ class CasePlan:
                 else:
                     po.append_prelu((1 if e.shape[0] > 1 else 0) | (2 if e.shape[1] > 1 else 0))
             attr.set_post_ops(po)
+        if scratchpad == "user":  # the caller owns the scratchpad and passes it as DNNL_ARG_SCRATCHPAD
+            attr.set_scratchpad_mode(1)
+        self.user_scratchpad = scratchpad == "user"
         self.attr = attr
         self.pd = matmul_primitive_desc(engine, src_md, wei_md, dst_md, bias_md, attr)
         if impl is not None:
@@ -447,6 +451,10 @@ class CasePlan:
             self.args[ARG_WEIGHTS] = packed
         if c.bias is not None:
             self.args[ARG_BIAS] = self._mem("bias", self.mds["bias"], c.bias)
+        if self.user_scratchpad:
+            smd = self.pd.scratchpad_desc()
+            if smd.get_size() > 0:
+                self.args[ARG_SCRATCHPAD] = self._mem("scratchpad", smd, None)
         if self.own_dst:
             self.args[ARG_DST] = self._mem("dst", self.mds["dst"], c.dst_init)
         for name, q, arg in (("src_scale", c.src_scale, ARG_ATTR_SCALES | ARG_SRC),

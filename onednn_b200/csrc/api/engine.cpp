@@ -111,7 +111,7 @@ static dnnl_status_t stream_make(dnnl_stream_t *stream, dnnl_engine_t engine, un
         s->cuda_stream = cs;
         s->owns_stream = true;
     }
-    if (cudaMalloc((void **)&s->status, sizeof(uint32_t)) != cudaSuccess
+    if (device_alloc((void **)&s->status, sizeof(uint32_t)) != cudaSuccess
             || cudaMemsetAsync(s->status, 0, sizeof(uint32_t), (cudaStream_t)s->cuda_stream) != cudaSuccess) {
         if (s->owns_stream) cudaStreamDestroy((cudaStream_t)s->cuda_stream);
         delete s;
@@ -151,8 +151,10 @@ dnnl_status_t dnnl_stream_wait(dnnl_stream_t stream) {
         return dnnl_runtime_error;
     if (cudaStreamSynchronize(cs) != cudaSuccess) return dnnl_runtime_error;
     if (st != 0) {
-        // a kernel gave up on a bounded wait: report once, then clear
+        // a kernel gave up on a bounded wait: report once, then clear; it may have left partial
+        // sums in a scratchpad
         cudaMemsetAsync(stream->status, 0, sizeof(uint32_t), cs);
+        g_scratch_epoch.fetch_add(1);
         return dnnl_runtime_error;
     }
     return dnnl_success;

@@ -17,6 +17,8 @@
 #include <string>
 #include <vector>
 
+#include <cuda_runtime.h>
+
 #include "onednn_b200.h"
 #include "onednn_b200_kernels.h"
 
@@ -191,10 +193,29 @@ struct dnnl_primitive_desc {
     int64_t K() const { return src.dims[src.ndims - 1]; }
 };
 
+namespace b200 {
+// Kernels that accumulate in the library-owned scratchpad rely on finding it zeroed and leave it
+// zeroed.  A kernel that gave up a bounded wait, or a launch sequence that failed half way, may
+// not have: every such event advances this epoch, and a primitive whose scratchpad was last
+// known clean in an older epoch has it cleared on the stream before its next execution.
+extern std::atomic<uint64_t> g_scratch_epoch;
+extern std::atomic<uint64_t> g_scratch_reclears; // how often that clearing was asked for (tests)
+
+// Every device / pinned-host allocation of the host library goes through these, so that an
+// allocation failure can be injected on the host (dnnl_b200_debug_fail_allocations) and the
+// dnnl_out_of_memory paths tested without exhausting a GPU.  The reference surfaces the same
+// status from its engine's allocator (src/common/engine.cpp:87-120, memory.cpp:159-163).
+cudaError_t device_alloc(void **ptr, size_t bytes);
+cudaError_t device_alloc_async(void **ptr, size_t bytes, cudaStream_t stream);
+cudaError_t pinned_alloc(void **ptr, size_t bytes);
+} // namespace b200
+
 struct dnnl_primitive {
     std::shared_ptr<dnnl_primitive_desc> pd;
     void *lib_scratch = nullptr; // library-mode scratchpad (device)
     size_t lib_scratch_bytes = 0;
+    mutable std::atomic<uint64_t> scratch_epoch {b200::g_scratch_epoch.load()}; // epoch in which lib_scratch was last known clean
+    const dnnl_primitive *scratch_owner = nullptr; // set when lib_scratch is borrowed from another primitive
     ~dnnl_primitive();
 };
 

@@ -194,6 +194,20 @@ static const char *reject(const char *impl, const char *why) {
     return why;
 }
 
+// How the tensor-core kernel gets at 8-bit weights.  One rule for dispatch, scratchpad sizing and
+// execution: plain weights are read in place only when they are K-major with a pitch and an
+// offset the TMA descriptor accepts (multiples of 16 bytes); N-major weights -- which includes
+// a single column, whose two strides are both 1 -- are transposed into the scratchpad.
+enum tc8_wei_class_t { TC8_WEI_PACKED, TC8_WEI_INPLACE_KMAJOR, TC8_WEI_PACK_NMAJOR, TC8_WEI_UNSUPPORTED };
+static tc8_wei_class_t tc8_weights_class(const dnnl_memory_desc &wei) {
+    if (wei.format_kind == dnnl_format_kind_opaque)
+        return wei.packed_layout == B200_WEI_KMAJOR ? TC8_WEI_PACKED : TC8_WEI_UNSUPPORTED;
+    if (!wei.is_plain()) return TC8_WEI_PACKED; // format_tag::any resolves to the packed layout
+    if (wei.strides[0] == 1 && wei.strides[1] % 16 == 0 && wei.offset0 % 16 == 0) return TC8_WEI_INPLACE_KMAJOR;
+    if (wei.strides[1] == 1) return TC8_WEI_PACK_NMAJOR;
+    return TC8_WEI_UNSUPPORTED;
+}
+
 // dense 8-bit tensor-core GEMM
 static bool accept_tc8(dnnl_primitive_desc *pd) {
     const char *name = "cuda:sm100:tcgen05";
@@ -210,13 +224,8 @@ static bool accept_tc8(dnnl_primitive_desc *pd) {
     if (src.is_plain() && !(src.strides[1] == 1 && src.strides[0] % 16 == 0 && src.offset0 % 16 == 0))
         return reject(name, "src must be row-major with a 16-byte pitch"), false;
     if (dst.is_plain() && dst.strides[1] != 1) return reject(name, "dst must be row-major"), false;
-    if (wei.format_kind == dnnl_format_kind_opaque) {
-        if (wei.packed_layout != B200_WEI_KMAJOR) return reject(name, "unknown packed weights layout"), false;
-    } else if (wei.is_plain()) {
-        const bool kmajor = wei.strides[0] == 1 && wei.strides[1] % 16 == 0 && wei.offset0 % 16 == 0;
-        const bool nmajor = wei.strides[1] == 1;
-        if (!kmajor && !nmajor) return reject(name, "weights strides not supported"), false;
-    }
+    if (tc8_weights_class(wei) == TC8_WEI_UNSUPPORTED)
+        return reject(name, wei.format_kind == dnnl_format_kind_opaque ? "unknown packed weights layout" : "weights strides not supported"), false;
     // source scales: one per tensor, or one per row -- what dynamic (per-token) quantisation of the
     // activations produces; the API spells it mask M+K with one group spanning all of K
     const quant_entry_t &ssc = a.scale(DNNL_ARG_SRC);
@@ -362,9 +371,10 @@ static size_t scratch_bytes_for(const dnnl_primitive_desc *pd) {
         const int64_t K = pd->K(), N = pd->N();
         // plain N-major weights are transposed into the packed layout on every
         // execution; plain K-major weights only need the column sums
-        if (pd->wei.is_plain() && pd->wei.strides[1] == 1 && pd->wei.strides[0] != 1)
+        const tc8_wei_class_t wc = tc8_weights_class(pd->wei);
+        if (wc == TC8_WEI_PACK_NMAJOR)
             bytes = b200_packed_weights_bytes(K, N, pd->wei.data_type, B200_WEI_KMAJOR);
-        else if (pd->wei.is_plain() && pd->attr.zp(DNNL_ARG_SRC).set)
+        else if (wc == TC8_WEI_INPLACE_KMAJOR && pd->attr.zp(DNNL_ARG_SRC).set)
             bytes = (size_t)N * sizeof(int32_t);
     }
     if (pd->impl == IMPL_WC) {
@@ -513,6 +523,7 @@ static dnnl_status_t batched_execute(const dnnl_primitive *prim, dnnl_stream *st
     tmp.pd = pd->inner;
     tmp.lib_scratch = prim->lib_scratch;
     tmp.lib_scratch_bytes = prim->lib_scratch_bytes;
+    tmp.scratch_owner = prim->scratch_owner ? prim->scratch_owner : prim;
     std::map<int, dnnl_memory *> a2 = args;
     for (size_t i = 0; i < mv.size(); ++i) a2[mv[i].arg] = &mv[i].mem;
     dnnl_status_t st = dnnl_success;
@@ -578,7 +589,7 @@ static dnnl_status_t runtime_execute(const dnnl_primitive *prim, dnnl_stream *st
     const size_t sb = now->scratchpad.ndims ? (size_t)now->scratchpad.dims[0] : 0;
     cudaStream_t cs = (cudaStream_t)stream->cuda_stream;
     if (sb) { // stream-ordered: no synchronisation, released after the kernels queued below
-        if (cudaMallocAsync(&tmp.lib_scratch, sb, cs) != cudaSuccess) {
+        if (device_alloc_async(&tmp.lib_scratch, sb, cs) != cudaSuccess) {
             (void)cudaGetLastError();
             tmp.lib_scratch = nullptr;
             tmp.pd.reset();
@@ -771,9 +782,15 @@ dnnl_status_t matmul_execute(const dnnl_primitive *prim, dnnl_stream *stream, co
     }
     p.scratch = scratch;
     p.scratch_bytes = scratch_bytes;
-    // the library-owned scratchpad is zeroed when the primitive is created and
-    // every kernel leaves its accumulation area zeroed
-    p.scratch_zeroed = (scratch && a.scratchpad_mode == dnnl_scratchpad_mode_library) ? 1 : 0;
+    // the library-owned scratchpad is zeroed when the primitive is created and every kernel
+    // leaves its accumulation area zeroed -- unless an execution went wrong since (g_scratch_epoch)
+    p.scratch_zeroed = 0;
+    if (scratch && a.scratchpad_mode == dnnl_scratchpad_mode_library) {
+        const dnnl_primitive *owner = prim->scratch_owner ? prim->scratch_owner : prim;
+        const uint64_t now = g_scratch_epoch.load();
+        if (owner->scratch_epoch.exchange(now) == now) p.scratch_zeroed = 1;
+        else g_scratch_reclears.fetch_add(1);
+    }
 
     b200_stream_t cs = stream->cuda_stream;
     int rc = 0;
@@ -786,7 +803,7 @@ dnnl_status_t matmul_execute(const dnnl_primitive *prim, dnnl_stream *stream, co
             if (p.wei_layout == B200_WEI_KMAJOR) {
                 if (p.src_zp.ptr)
                     p.wei_colsum = (const int32_t *)((const char *)p.wei + b200_packed_colsum_offset(p.K, p.N, p.wei_dt));
-            } else if (p.wei_sk == 1) {
+            } else if (tc8_weights_class(pd->wei) == TC8_WEI_INPLACE_KMAJOR) {
                 // plain K-major weights: usable in place; column sums into the scratchpad
                 if (p.src_zp.ptr) {
                     rc = b200_colsum_launch(p.wei, p.wei_dt, p.K, p.N, p.wei_sk, p.wei_sn, (int32_t *)scratch, cs);
@@ -978,6 +995,7 @@ dnnl_status_t inner_product_execute(const dnnl_primitive *prim, dnnl_stream *str
     tmp.pd = pd->inner;
     tmp.lib_scratch = prim->lib_scratch; // borrowed
     tmp.lib_scratch_bytes = prim->lib_scratch_bytes;
+    tmp.scratch_owner = prim->scratch_owner ? prim->scratch_owner : prim;
     const dnnl_status_t st = matmul_execute(&tmp, stream, a2);
     tmp.lib_scratch = nullptr;
     tmp.pd.reset();

@@ -336,7 +336,7 @@ dnnl_status_t dnnl_memory_create(dnnl_memory_t *memory, const_dnnl_memory_desc_t
         if (set_device(engine) != dnnl_success) return dnnl_runtime_error;
         const size_t bytes = md->size_bytes();
         if (bytes) {
-            if (cudaMalloc(&m->handle, bytes) != cudaSuccess) {
+            if (device_alloc(&m->handle, bytes) != cudaSuccess) {
                 (void)cudaGetLastError();
                 return dnnl_out_of_memory;
             }
@@ -373,7 +373,7 @@ dnnl_status_t dnnl_memory_map_data(const_dnnl_memory_t cmem, void **mapped_ptr) 
     }
     if (set_device(mem->engine) != dnnl_success) return dnnl_runtime_error;
     void *host = nullptr;
-    if (cudaMallocHost(&host, bytes) != cudaSuccess) return dnnl_out_of_memory;
+    if (pinned_alloc(&host, bytes) != cudaSuccess) return dnnl_out_of_memory;
     // every stream that may have written the buffer must have finished
     if (cudaDeviceSynchronize() != cudaSuccess
             || cudaMemcpy(host, (const char *)mem->handle + mem->md.offset0 * dt_nbits(mem->md.data_type) / 8, bytes,

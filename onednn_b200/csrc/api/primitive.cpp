@@ -393,6 +393,21 @@ int g_cache_capacity = -1;
 std::list<std::pair<std::string, std::shared_ptr<dnnl_primitive_desc>>> g_cache;
 uint64_t g_cache_hits = 0;
 
+} // namespace
+
+namespace b200 {
+uint64_t primitive_cache_hits() {
+    std::lock_guard<std::mutex> g(g_cache_mu);
+    return g_cache_hits;
+}
+uint64_t primitive_cache_size() {
+    std::lock_guard<std::mutex> g(g_cache_mu);
+    return g_cache.size();
+}
+} // namespace b200
+
+namespace {
+
 int cache_capacity_locked() {
     if (g_cache_capacity < 0) {
         g_cache_capacity = 1024;
@@ -490,11 +505,14 @@ dnnl_status_t dnnl_primitive_create(dnnl_primitive_t *primitive, const_dnnl_prim
     const size_t sb = pd->scratchpad.ndims ? (size_t)pd->scratchpad.dims[0] : 0;
     if (sb && pd->attr.scratchpad_mode == dnnl_scratchpad_mode_library) {
         if (set_device(pd->engine) != dnnl_success) return dnnl_runtime_error;
-        if (cudaMalloc(&prim->lib_scratch, sb) != cudaSuccess) {
+        if (device_alloc(&prim->lib_scratch, sb) != cudaSuccess) {
             (void)cudaGetLastError();
             return dnnl_out_of_memory;
         }
-        if (cudaMemset(prim->lib_scratch, 0, sb) != cudaSuccess) return dnnl_runtime_error;
+        // the clear runs on the legacy default stream and may return before it is done, while
+        // streams made by dnnl_stream_create do not wait for that stream: finish it here
+        if (cudaMemset(prim->lib_scratch, 0, sb) != cudaSuccess || cudaStreamSynchronize(0) != cudaSuccess)
+            return dnnl_runtime_error;
         prim->lib_scratch_bytes = sb;
     }
     verbose_create(pd, now_ms() - t0, hit);
@@ -533,6 +551,8 @@ dnnl_status_t dnnl_primitive_execute(const_dnnl_primitive_t primitive, dnnl_stre
     dnnl_status_t st = pd->kind == dnnl_matmul ? matmul_execute(primitive, stream, m)
             : pd->kind == dnnl_inner_product   ? inner_product_execute(primitive, stream, m)
                                                : reorder_execute(primitive, stream, m);
+    if (st != dnnl_success && st != dnnl_invalid_arguments && st != dnnl_unimplemented)
+        g_scratch_epoch.fetch_add(1); // a launch sequence may have stopped half way
     if (prof) {
         cudaEventRecord(e1, (cudaStream_t)stream->cuda_stream);
         std::lock_guard<std::mutex> g(stream->mu);

@@ -99,7 +99,57 @@ void verbose_dispatch(const char *impl, const char *why) {
     std::fflush(stdout);
 }
 
+std::atomic<uint64_t> g_scratch_epoch {1};
+std::atomic<uint64_t> g_scratch_reclears {0};
+
+// allocation-failure injection: the next g_fail_allocs allocations report out of memory
+static std::atomic<int> g_fail_allocs {0};
+static bool inject_failure() {
+    int n = g_fail_allocs.load();
+    while (n > 0)
+        if (g_fail_allocs.compare_exchange_weak(n, n - 1)) return true;
+    return false;
+}
+cudaError_t device_alloc(void **ptr, size_t bytes) {
+    if (inject_failure()) return cudaErrorMemoryAllocation;
+    return cudaMalloc(ptr, bytes);
+}
+cudaError_t device_alloc_async(void **ptr, size_t bytes, cudaStream_t stream) {
+    if (inject_failure()) return cudaErrorMemoryAllocation;
+    return cudaMallocAsync(ptr, bytes, stream);
+}
+cudaError_t pinned_alloc(void **ptr, size_t bytes) {
+    if (inject_failure()) return cudaErrorMemoryAllocation;
+    return cudaMallocHost(ptr, bytes);
+}
+
+uint64_t primitive_cache_hits();
+uint64_t primitive_cache_size();
+
 } // namespace b200
+
+dnnl_status_t dnnl_b200_debug_fail_allocations(int count) {
+    if (count < 0) return dnnl_invalid_arguments;
+    b200::g_fail_allocs.store(count);
+    return dnnl_success;
+}
+
+dnnl_status_t dnnl_b200_debug_mark_scratchpads_dirty(void) {
+    b200::g_scratch_epoch.fetch_add(1);
+    return dnnl_success;
+}
+
+dnnl_status_t dnnl_b200_debug_counter(int which, uint64_t *value) {
+    if (!value) return dnnl_invalid_arguments;
+    switch (which) {
+        case DNNL_B200_COUNTER_CACHE_HITS: *value = b200::primitive_cache_hits(); break;
+        case DNNL_B200_COUNTER_CACHE_SIZE: *value = b200::primitive_cache_size(); break;
+        case DNNL_B200_COUNTER_SCRATCH_RECLEARS: *value = b200::g_scratch_reclears.load(); break;
+        case DNNL_B200_COUNTER_KERNEL_LAUNCHES: *value = b200_launch_count(); break;
+        default: return dnnl_invalid_arguments;
+    }
+    return dnnl_success;
+}
 
 dnnl_status_t dnnl_set_verbose(int level) {
     if (level < 0 || level > 2) return dnnl_invalid_arguments;

@@ -855,14 +855,12 @@ __global__ void __launch_bounds__(640, 1) matmul_tc8_kernel(const __grid_constan
                     if (!(ok = mbar_wait_poll(&ctrl->full[s], r & 1, ctrl, p.status, ST_WAIT_FULL))) break;
                     tcgen05_fence_after();
                     const uint64_t adesc = adesc0 + (uint64_t)(s * (SBYTES >> 4)), bdesc = bdesc0 + (uint64_t)(s * (SBYTES >> 4));
-#ifndef TC8_ABL_NOMMA
 #pragma unroll
                     for (int k = 0; k < BK / 32; ++k) // 32 bytes of K per instruction: +2 in 16-byte units
                         if (PAIR)
                             tcgen05_mma_pair<FP8>(tmem_d, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0);
                         else
                             tcgen05_mma<FP8>(tmem_d, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0);
-#endif
                     if (PAIR) tcgen05_commit_pair(&ctrl->empty[s]);
                     else tcgen05_commit(&ctrl->empty[s]);
                 }
@@ -946,11 +944,7 @@ __global__ void __launch_bounds__(640, 1) matmul_tc8_kernel(const __grid_constan
             // one copy of the chunk code, executed once per chunk (the unrolled form does not fit
             // the instruction cache); the prefetched bytes rotate through named registers
 #pragma unroll 1
-#ifdef TC8_ABL_NOEPI
-            for (int c = 0; c < 0; ++c) {
-#else
             for (int c = 0; c < nch; ++c) {
-#endif
                 uint32_t v[CH];
                 tmem_ld16_issue(trow + c * CH, v);
                 tmem_ld_wait(v);

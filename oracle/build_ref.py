@@ -96,17 +96,55 @@ def sources(ref: Path):
     return files
 
 
+def consumer_stamp(prog: Path) -> str:
+    """Hash of everything a consumer program is compiled from on this side: its own source and
+    the CUDA engine's public headers (it is compiled against the reference's headers, which do
+    not change)."""
+    import hashlib
+    h = hashlib.sha256(prog.read_bytes())
+    for hdr in sorted((HERE.parent / "include").glob("*.h")):
+        h.update(hdr.read_bytes())
+    return h.hexdigest()
+
+
+def build_consumers(ref: Path, inc: Path, cxx: str = "/usr/bin/g++") -> int:
+    """User programs written against the reference's own C and C++ headers, linked against the
+    CUDA engine instead of the reference library (the drop-in claim, checked by
+    tests/test_consumer.py).  Beside each binary goes ``<name>.sha256``, the stamp of the sources
+    it was built from, so that a stale binary is noticed where it cannot be rebuilt."""
+    eng_lib = HERE.parent / "onednn_b200" / "libonednn_b200.so"
+    consumer = HERE.parent / "tests" / "consumer"
+    for prog in sorted(list(consumer.glob("*.cpp")) + list(consumer.glob("*.c"))):
+        if not eng_lib.exists():
+            print("skipped %s: %s not built yet" % (prog.name, eng_lib.name))
+            continue
+        out = OUT / ("consumer_" + prog.stem)
+        comp = [cxx, "-std=c++11"] if prog.suffix == ".cpp" else ["/usr/bin/gcc", "-std=c99"]
+        cmd = comp + ["-O1", str(prog), "-I", str(ref / "include"), "-I", str(inc), "-L", str(eng_lib.parent),
+                      "-lonednn_b200", "-lm", "-Wl,-rpath,$ORIGIN/../../onednn_b200", "-o", str(out)]
+        p = subprocess.run(cmd, capture_output=True, text=True)
+        if p.returncode != 0:
+            print(p.stderr[-6000:])
+            return 1
+        (OUT / (out.name + ".sha256")).write_text(consumer_stamp(prog) + "\n")
+        print("built", out)
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--ref", default=os.environ.get("ONEDNN_REF", "/root/reference"))
     ap.add_argument("-j", type=int, default=os.cpu_count() or 4)
     ap.add_argument("--cxx", default="/usr/bin/g++")
+    ap.add_argument("--consumers-only", action="store_true", help="only (re)build the programs of tests/consumer")
     args = ap.parse_args()
     ref = Path(args.ref)
     if not (ref / "src/common/matmul.cpp").exists():
         print("reference tree not found at %s: nothing built" % ref)
         return 2
     inc = gen_headers(ref)
+    if args.consumers_only:
+        return build_consumers(ref, inc, args.cxx)
     obj = OUT / "obj"
     obj.mkdir(parents=True, exist_ok=True)
     flags = [
@@ -166,24 +204,7 @@ def main():
             print(p.stderr[-6000:])
             return 1
         print("built", rlib)
-    # user programs written against the reference's own C++ header, linked against the CUDA
-    # engine instead of the reference library (the drop-in claim, checked by tests/test_consumer.py)
-    eng_lib = HERE.parent / "onednn_b200" / "libonednn_b200.so"
-    consumer = HERE.parent / "tests" / "consumer"
-    for prog in sorted(list(consumer.glob("*.cpp")) + list(consumer.glob("*.c"))):
-        if not eng_lib.exists():
-            print("skipped %s: %s not built yet" % (prog.name, eng_lib.name))
-            continue
-        out = OUT / ("consumer_" + prog.stem)
-        comp = [args.cxx, "-std=c++11"] if prog.suffix == ".cpp" else ["/usr/bin/gcc", "-std=c99"]
-        cmd = comp + ["-O1", str(prog), "-I", str(ref / "include"), "-I", str(inc), "-L", str(eng_lib.parent),
-                      "-lonednn_b200", "-lm", "-Wl,-rpath,$ORIGIN/../../onednn_b200", "-o", str(out)]
-        p = subprocess.run(cmd, capture_output=True, text=True)
-        if p.returncode != 0:
-            print(p.stderr[-6000:])
-            return 1
-        print("built", out)
-    return 0
+    return build_consumers(ref, inc, args.cxx)
 
 
 if __name__ == "__main__":

@@ -173,6 +173,19 @@ def int8_per_row_src_scales_bf16():
     return c
 
 
+def _int8_one_column(tag):
+    """A single output column: both strides of the (K, 1) weights are 1 whatever the tag."""
+    def make():
+        r, c = _int8_base(40, 1, 64, 37, dst_dt=dt.S8)
+        c.wei_tag = tag
+        c.src_scale = Quant(_f32([0.01]), dt.F32, 0)
+        c.wei_scale = Quant(_f32([0.004]), dt.F32, 2)
+        c.bias, c.bias_dt = _f32(r.uniform(-1, 1, (1, 1))), dt.F32
+        c.post_ops = [W.eltwise("relu", 0.25)]
+        return c
+    return make
+
+
 def int8_per_row_src_scales_gelu_s8():
     c = W.config1(160, 64, 96, seed=35, dst_scale=0.7)
     r = np.random.default_rng(36)
@@ -235,6 +248,8 @@ CASES = {
     "int8_per_row_src_scales_gelu_s8": int8_per_row_src_scales_gelu_s8,
     "fp8_f8dst": fp8_f8dst,
     "fp8_swish_f32": fp8_swish_f32,
+    "int8_one_column_ab": _int8_one_column("ab"),
+    "int8_one_column_ba": _int8_one_column("ba"),
 }
 
 
@@ -246,9 +261,60 @@ def _two_elt():
 
 
 def build(name):
+    if name.startswith("tame/"):
+        return build_tame(name[5:])
     c = CASES[name]()
     c.name = name
     return c
+
+
+# ---- the int8 catalogue on data whose f32 sums are exact ------------------------------------
+# The reference's scalar int8 implementation scales every product and accumulates in f32; its
+# optimised implementation and the tensor-core kernel here accumulate exactly in s32 and scale
+# once.  On inputs like those the reference's own test driver draws -- small integers
+# (tests/benchdnn/matmul/cfg.cpp:63-134) and power-of-two scales
+# (tests/benchdnn/utils/fill.cpp:118-142) -- every scaled product and every partial sum is an
+# integer times a power of two below 2^24, so the f32 accumulation is exact, the two orders of
+# operations give the same bits, and the exact-accumulation result can be pinned to the
+# reference's own output over the whole attribute catalogue.
+
+def _pow2(q):
+    """The same scales argument with every value replaced by the nearest power of two."""
+    v = dt.to_f32(q.data, q.dt).astype(np.float64)
+    v = np.exp2(np.rint(np.log2(v))).astype(np.float32)
+    return Quant(v if q.dt == dt.F32 else dt.from_f32(v, q.dt), q.dt, q.mask, q.groups)
+
+
+def is_int8_case(c):
+    return c.src_dt in (dt.S8, dt.U8) and c.wei_dt in (dt.S8, dt.U8) and not c.apply_to_int
+
+
+def build_tame(name):
+    c = build(name)
+    assert is_int8_case(c), name
+    r = np.random.default_rng(1000 + sum(map(ord, name)))
+    if c.src_dt == dt.U8:
+        c.src = r.integers(0, 9, c.src.shape, dtype=np.uint8)
+    else:
+        c.src = r.integers(-4, 5, c.src.shape, dtype=np.int8)
+    c.wei = r.integers(-4, 5, c.wei.shape, dtype=np.int8)
+    for attr in ("src_scale", "wei_scale"):
+        q = getattr(c, attr)
+        if q is not None:
+            setattr(c, attr, _pow2(q))
+    if c.src_zp is not None:
+        c.src_zp = Quant(np.array([4], dtype=np.int32), dt.S32, c.src_zp.mask, c.src_zp.groups)
+    if c.wei_zp is not None:
+        c.wei_zp = Quant(np.array([1], dtype=np.int32), dt.S32, c.wei_zp.mask, c.wei_zp.groups)
+    # the sums are now a few hundred at most: keep the requantised outputs inside the range
+    if c.dst_scale is not None:
+        c.dst_scale = Quant(_f32([2.0 ** -6]), dt.F32, 0)
+    c.name = "tame/" + name
+    return c
+
+
+def tame_names():
+    return ["tame/" + n for n in CASES if is_int8_case(CASES[n]())]
 
 
 # ---- quantising reorders -------------------------------------------------------------------

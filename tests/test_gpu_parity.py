@@ -137,14 +137,183 @@ def test_missing_runtime_scale_argument_is_rejected(ctx):
 
 
 def test_user_scratchpad_mode(ctx):
+    """scratchpad_mode::user: the primitive allocates nothing, reports the size it needs and
+    works out of the memory passed as DNNL_ARG_SCRATCHPAD; without that argument it refuses."""
     eng, strm = ctx
     c = W.config2(3, 256, 512)
     want = B.run_oracle(c)
-    plan = api.CasePlan(c, eng, strm, upload=False)
-    plan.attr.set_scratchpad_mode(1)
-    plan2 = api.CasePlan(c, eng, strm)          # library mode as the yardstick
-    plan2.execute()
-    assert_close(c, plan2.result(), want)
+    plan = api.CasePlan(c, eng, strm, scratchpad="user")
+    assert plan.pd.scratchpad_desc().get_size() > 0 and api.ARG_SCRATCHPAD in plan.args
+    for _ in range(2):  # the kernel leaves its partial sums zeroed: a second run must agree too
+        plan.execute()
+        assert_close(c, plan.result(), want)
+    del plan.args[api.ARG_SCRATCHPAD]
+    with pytest.raises(api.Error) as e:
+        plan.execute()
+    assert e.value.name == "invalid_arguments"
+    lib_plan = api.CasePlan(c, eng, strm)
+    assert lib_plan.pd.scratchpad_desc().get_size() == 0  # library mode: nothing for the user to provide
+
+
+def _counter(which):
+    v = api.C.c_uint64()
+    assert api.lib().dnnl_b200_debug_counter(which, api.C.byref(v)) == 0
+    return v.value
+
+
+def test_scratchpad_is_cleared_again_after_a_reported_failure(ctx):
+    """A kernel that gave up may leave partial sums behind; after the stream reported it (here:
+    the host-side hook that stands for that report) the next execution of every primitive with a
+    library scratchpad clears it first, exactly once."""
+    eng, strm = ctx
+    c = W.config2(2, 256, 512)
+    want = B.run_oracle(c)
+    plan = api.CasePlan(c, eng, strm)
+    plan.execute()
+    assert_close(c, plan.result(), want)
+    before = _counter(2)
+    plan.execute()
+    strm.wait()
+    assert _counter(2) == before               # clean: trusted
+    assert api.lib().dnnl_b200_debug_mark_scratchpads_dirty() == 0
+    plan.execute()
+    assert_close(c, plan.result(), want)
+    assert _counter(2) == before + 1           # cleared on the stream before the kernel
+    plan.execute()
+    assert_close(c, plan.result(), want)
+    assert _counter(2) == before + 1
+
+
+def test_allocation_failure_is_reported_as_out_of_memory(ctx):
+    """Host-side injection: the library's next allocations fail; memory and primitive creation
+    return dnnl_out_of_memory and later calls work again."""
+    eng, strm = ctx
+    L = api.lib()
+    md = api.MemoryDesc((64, 64), dt.F32, api.TAG_AB)
+    assert L.dnnl_b200_debug_fail_allocations(1) == 0
+    with pytest.raises(api.Error) as e:
+        api.Memory(md, eng)
+    assert e.value.name == "out_of_memory"
+    api.Memory(md, eng)  # the injection is used up
+    c = W.config2(2, 256, 512)
+    plan = api.CasePlan(c, eng, strm)
+    assert L.dnnl_b200_debug_fail_allocations(1) == 0
+    with pytest.raises(api.Error) as e:
+        api.Primitive(plan.pd)  # its library scratchpad cannot be allocated
+    assert e.value.name == "out_of_memory"
+    api.Primitive(plan.pd)
+    assert L.dnnl_b200_debug_fail_allocations(0) == 0
+
+
+def test_stream_profiling_returns_one_entry_per_execution():
+    """dnnl_stream_profiling + dnnl_query_profiling_data (reference: src/common/stream.cpp,
+    include/oneapi/dnnl/dnnl.h experimental profiling): one device time per execute call."""
+    eng = api.Engine()
+    strm = api.Stream(eng, flags=1 | 4)  # in_order | profiling
+    c = cases.build("c1_small")
+    plan = api.CasePlan(c, eng, strm)
+    n0 = api.C.c_int(0)
+    L = api.lib()
+    assert L.dnnl_reset_profiling(strm.h) == 0
+    for _ in range(3):
+        plan.execute()
+    strm.wait()
+    assert L.dnnl_query_profiling_data(strm.h, 1, api.C.byref(n0), None) == 0
+    assert n0.value == 3
+    data = (api.C.c_uint64 * 3)()
+    assert L.dnnl_query_profiling_data(strm.h, 1, api.C.byref(n0), data) == 0
+    assert all(0 < t < 10**9 for t in data)  # nanoseconds, well under a second each
+    assert L.dnnl_reset_profiling(strm.h) == 0
+    assert L.dnnl_query_profiling_data(strm.h, 1, api.C.byref(n0), None) == 0 and n0.value == 0
+    plain = api.Stream(eng)
+    assert L.dnnl_query_profiling_data(plain.h, 1, api.C.byref(n0), None) == 2  # not a profiling stream
+
+
+def test_primitive_cache_hits_and_eviction(ctx):
+    """Creating the same primitive twice is a cache hit; the cache never holds more entries than
+    its capacity (reference: doc/advanced/primitive_cache.md)."""
+    eng, strm = ctx
+    L = api.lib()
+    cap = api.C.c_int()
+    assert L.dnnl_get_primitive_cache_capacity(api.C.byref(cap)) == 0
+    try:
+        assert L.dnnl_set_primitive_cache_capacity(2) == 0
+        plans = [api.CasePlan(W.config0(16 * (i + 1), 32, 64), eng, strm, upload=False) for i in range(3)]
+        assert _counter(1) <= 2
+        hits = _counter(0)
+        api.Primitive(plans[2].pd)      # most recent: still cached
+        assert _counter(0) == hits + 1
+        api.Primitive(plans[0].pd)      # evicted when the third was created
+        assert _counter(0) == hits + 1
+        assert _counter(1) <= 2
+    finally:
+        L.dnnl_set_primitive_cache_capacity(cap.value)
+
+
+def test_verbose_lines_have_the_reference_shape(tmp_path):
+    """ONEDNN_VERBOSE=2 prints one create and one exec line per call in the reference's CSV shape
+    (doc/performance_considerations/verbose.md:22-45): marker, version, component, operation,
+    engine, primitive, implementation, prop kind, memory descriptors, attributes, auxiliary,
+    problem, time."""
+    import os
+    import subprocess
+    import sys
+    prog = (
+        "import sys; sys.path.insert(0, %r); sys.path.insert(0, %r)\n"
+        "import cases\nfrom onednn_b200 import api\n"
+        "eng = api.Engine(); s = api.Stream(eng)\n"
+        "p = api.CasePlan(cases.build('c1_small'), eng, s)\np.execute(); p.execute(); s.wait()\n"
+    ) % (str(api._PKG.parent), str(api._PKG.parent / "tests"))
+    env = dict(os.environ, ONEDNN_VERBOSE="2")
+    out = subprocess.run([sys.executable, "-c", prog], capture_output=True, text=True, env=env, timeout=300)
+    assert out.returncode == 0, out.stderr
+    lines = [l for l in out.stdout.splitlines() if l.startswith("onednn_verbose,")]
+    execs = [l for l in lines if ",primitive,exec," in l and ",matmul," in l]
+    creates = [l for l in lines if ",primitive,create:" in l and ",matmul," in l]
+    assert len(execs) == 2 and len(creates) >= 1
+    f = execs[0].split(",")
+    assert len(f) == 13
+    assert f[:4] == ["onednn_verbose", "v1", "primitive", "exec"] and f[4].startswith("gpu")
+    assert f[5] == "matmul" and f[6] == "cuda:sm100:tcgen05_i8" and f[7] == "undef"
+    assert f[8].startswith("src:s8::") and " wei:s8:" in f[8] and " dst:s8::" in f[8]
+    assert "attr-scales:" in f[9] and "attr-post-ops:" in f[9]
+    assert f[-2] == "96x256:256x128" and float(f[-1]) >= 0.0
+
+
+@pytest.mark.parametrize("name", cases.tame_names())
+@pytest.mark.parametrize("weights", ["any", "plain"])
+def test_tensor_core_kernel_vs_reference_bytes(ctx, name, weights):
+    """The int8 catalogue on data whose f32 sums are exact: there the bytes stored from the
+    reference's own scalar implementation are what the tensor-core kernel must produce, with
+    no oracle mode in between."""
+    import hashlib
+    from pathlib import Path
+    from golden.make_golden import input_digest
+    gold = np.load(Path(__file__).parent / "golden" / "reference_outputs.npz")
+    c = cases.build(name)
+    if str(gold[name + "/inputs_sha256"]) != input_digest(c):
+        pytest.skip("numpy produced different inputs than when the fixture was made")
+    plan = api.CasePlan(c, *ctx, weights=weights)
+    if "tcgen05_i8" not in plan.impl:
+        pytest.skip("not a case of the tensor-core kernel")
+    plan.execute()
+    got = np.ascontiguousarray(plan.result())
+    raw = got.view(np.uint8).reshape(-1)
+    want = gold[name + "/bytes"]
+    if c.exact or not _uses_tanh_or_libm(c):
+        assert np.array_equal(raw if raw.size <= 65536 else raw[::61], want)
+        assert hashlib.sha256(raw.tobytes()).hexdigest() == str(gold[name + "/sha256"])
+    else:
+        # float destination behind a transcendental: the functions differ from glibc's by an ulp
+        assert raw.size <= 65536
+        w = dt.to_f32(want.view(dt.RAW[c.dst_dt]).reshape(c.M, c.N), c.dst_dt).astype(np.float64)
+        g = dt.to_f32(got, c.dst_dt).astype(np.float64)
+        assert np.all(np.abs(g - w) <= 1e-6 + 1e-5 * np.abs(w))
+
+
+def _uses_tanh_or_libm(case):
+    tanh_like = {W.ELTWISE[k] for k in ("tanh", "gelu_tanh")}
+    return _uses_libm(case) or any(p.kind == W.PO_ELTWISE and p.alg in tanh_like for p in case.post_ops)
 
 
 def test_map_unmap_round_trip(ctx):

@@ -23,6 +23,27 @@ def test_bit_exact_vs_reference_scalar_impl(name):
     assert np.array_equal(out.view(np.uint8), ref.view(np.uint8))
 
 
+@pytest.mark.parametrize("name", cases.tame_names())
+def test_exact_accumulation_bit_exact_vs_reference_on_exact_sums(name):
+    """The whole int8 attribute catalogue on small integers and power-of-two scales, where the
+    reference's f32 accumulation is exact: its output, the oracle's and the oracle's
+    exact-accumulation mode agree bit for bit (with the portable tanh as well)."""
+    c = cases.build(name)
+    ref, impl, _, _ = B.run_reference(c, impl="ref")
+    assert impl == "ref_int8:any"
+    for kw in (dict(), dict(exact_acc=1)):
+        out = B.run_oracle(c, **kw)
+        assert np.array_equal(out.view(np.uint8), ref.view(np.uint8)), kw
+    # the portable tanh the kernels share differs from libm's tanhf by at most an ulp of an f32
+    # result; it must not move an integer output
+    out = B.run_oracle(c, exact_acc=1, tanh_mode=1)
+    if c.exact:
+        assert np.array_equal(out.view(np.uint8), ref.view(np.uint8))
+    else:
+        g, w = dt.to_f32(out, c.dst_dt).astype(np.float64), dt.to_f32(ref, c.dst_dt).astype(np.float64)
+        assert np.all(np.abs(g - w) <= 1e-6 + 1e-5 * np.abs(w))
+
+
 def test_portable_tanh_changes_no_int8_output():
     """The kernels use a portable double-precision tanh instead of libm's tanhf; on the
     benchmark's requantised configuration that must not move any s8 output."""

@@ -40,9 +40,10 @@ sys.path.insert(0, str(ROOT))
 
 METRIC = "int8_matmul_4096x4096x4096_postops_throughput"
 UNIT = "TOPS"
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the benchmark kernel, from the ncu
-# capture summarised in profiles/tc8_int8_c1_full.md (50.42 MB + 0.50 MB)
-NCU_DRAM_BYTES_PER_LAUNCH = 51.03e6
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the benchmark kernel, from the ncu
+# capture summarised in profiles/tc8_int8_c1_full.md: `bench.py --case c1 --steps 6`, which rotates
+# over the same input sets as the timed region, third launch captured
+NCU_DRAM_BYTES_PER_LAUNCH = None
 WORKLOAD = "int8 s8:s8:s8 4096x4096:4096x4096, per-N wei scales, bf16 bias, gelu_tanh + sum:0.5, dst scale 0.1 zp 3"
 
 
@@ -359,12 +360,12 @@ def main():
 
     # ---- correctness of what was timed: sampled rows / columns against the CPU oracle ----
     check = None
+    gpu_out = None
     extras = {}
     nsplit = None
     if world > 1 and not args.no_extras:
-        # collectives: every rank takes part
-        nsplit = {"nccl_all_gather": run_c4_nsplit(W, torch, dist, rank, world, local, "nccl"),
-                  "epilogue_stores_to_peers": run_c4_nsplit(W, torch, dist, rank, world, local, "p2p")}
+        # the sharded configuration: every rank takes part
+        nsplit = run_c4_sharded(W, torch, dist, rank, world, local)
     cpu_baseline = None
     if rank == 0:
         try:
@@ -374,27 +375,48 @@ def main():
             plan.prim.execute(strm, s["args"])
             strm.wait()
             got = s["dst"].cpu().numpy()
+            gpu_out = got
             c0 = W.config1(seed=20240612 + rank)
+            # the same sample under both accumulation orders: exact s32 sums scaled once (what the
+            # tensor-core kernel and the reference's optimised implementation compute), and the
+            # reference's scalar implementation, which scales every product and sums in f32
             want = B.run_oracle(c0, tanh_mode=1, exact_acc=1, m_step=61, n_step=53)
-            diff = int((got[::61, ::53] != want[::61, ::53]).sum())
-            check = {"sampled_elements": int(want[::61, ::53].size), "mismatches_vs_cpu_oracle": diff}
+            want_scalar = B.run_oracle(c0, tanh_mode=0, exact_acc=0, m_step=61, n_step=53)
+            samp = got[::61, ::53]
+            check = {"sampled_elements": int(samp.size),
+                     "mismatches_vs_cpu_oracle": int((samp != want[::61, ::53]).sum()),
+                     "mismatches_vs_oracle_in_reference_scalar_order": int((samp != want_scalar[::61, ::53]).sum()),
+                     "note": "first count: oracle with exact s32 accumulation (must be 0); second: oracle restating "
+                             "ref_int8:any, which accumulates scaled products in f32 (its own +-1 LSB deviations)"}
         except Exception as ex:  # the check must not hide the measurement
             check = {"error": repr(ex)}
 
         if not args.no_extras:
             extras = run_extras(api, W, dt, eng, strm, tstream, torch, np, peaks)
         if nsplit is not None:
-            extras["c4_int8_16384x8192x28672_n_split"] = nsplit
+            extras["c4_int8_16384x8192x28672_sharded"] = nsplit
 
         if not args.no_cpu_baseline:
             try:
                 from oracle import binding as B
                 cores = B.set_threads(0)
                 if B.have_reference():
-                    _, rimpl, rmin, ravg = B.run_reference(W.config1(), weights_any=True, iters=10)
+                    # the same seeded inputs as rank 0's GPU run, so that the outputs can be compared
+                    _, rimpl, rmin, ravg = B.run_reference(W.config1(seed=20240612), weights_any=True, iters=10)
+                    # once more, a single execution, for the output (the timed runs above each add the sum
+                    # post-op onto the previous result)
+                    rdst, _, _, _ = B.run_reference(W.config1(seed=20240612), weights_any=True, iters=0)
                     cpu_baseline = {"value": case.ops / (ravg * 1e-3) / 1e12, "unit": UNIT, "cores": cores,
                                     "kind": "reference",
                                     "sample": "the full 4096^3 problem, 10 executions of %s (weights packed by its own reorder), mean" % rimpl}
+                    if isinstance(check, dict) and "error" not in check and gpu_out is not None:
+                        d = np.abs(gpu_out.astype(np.int16) - rdst.astype(np.int16))
+                        check["all_elements"] = int(d.size)
+                        check["mismatches_vs_reference_jit_full_output"] = int((d != 0).sum())
+                        check["max_abs_diff_vs_reference_jit"] = int(d.max())
+                        check["reference_jit_impl"] = rimpl
+                    if not args.no_extras:
+                        extras["cpu_reference_other_configs"] = cpu_other_configs(B, W, cores)
                 else:
                     small = W.config1(512, 512, 1024)
                     t0 = time.time()
@@ -417,8 +439,9 @@ def main():
                        "impl": impl, "l2": "rotating %d input sets, %.0f MB in total (> 126 MB L2)" % (args.sets, set_bytes / 1e6)},
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": int8_peak, "unit": "TFLOP/s",
                          "frac": achieved / int8_peak, "traffic": NCU_DRAM_BYTES_PER_LAUNCH,
-                         "traffic_note": "dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of this kernel on "
-                                         "this workload (profiles/tc8_int8_c1_full.md); algorithmic bytes 67.1e6",
+                         "traffic_note": "dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu capture of "
+                                         "`bench.py --case c1` over rotating input sets summarised in "
+                                         "profiles/tc8_int8_c1_full.md (null until that capture exists); algorithmic bytes 67.1e6",
                          "kernel": "matmul_tc8_kernel<int8, EPI_GELU_Q, SUM_8BIT>", "kernel_ms": ms_per_step, "kernel_ms_single_launch_between_events": kern_avg,
                          "peak_note": "2 x %s bf16 dense burst (%.1f TF/s); no measured int8 figure exists; nominal 4500"
                                       % (peaks["source"], peaks["bf16"])},
@@ -439,59 +462,181 @@ def main():
 
 
 def run_one_case(args):
-    """Executes one configuration a few times through the public API; meant to be run under ncu."""
+    """Executes one configuration a few times through the public API; meant to be run under ncu.
+    c1 rotates over --sets independent copies of its activations and prior destination, like the
+    timed region, so that a captured launch finds its operands in HBM, not in L2."""
+    import numpy as np
     from onednn_b200 import api, workloads as W
     cases = {"c0": W.config0, "c1": W.config1, "c2_m1": lambda: W.config2(1), "c2_m16": lambda: W.config2(16),
              "c2_m128": lambda: W.config2(128), "c3": W.config3, "c3_4096": lambda: W.config3(4096, 4096, 4096),
              "c4": W.config4}
     eng = api.Engine()
     strm = api.Stream(eng)
-    plan = api.CasePlan(cases[args.case](), eng, strm, weights="any")
-    for _ in range(max(1, args.steps)):
-        plan.execute()
+    case = cases[args.case]()
+    plan = api.CasePlan(case, eng, strm, weights="any")
+    argsets = [plan.args]
+    if args.case == "c1":
+        for i in range(1, args.sets):
+            a = dict(plan.args)
+            src = api.Memory(plan.mds["src"], eng)
+            src.write(np.roll(case.src, i, axis=0))
+            dst = api.Memory(plan.mds["dst"], eng)
+            dst.write(np.roll(case.dst_init, i, axis=0))
+            a[api.ARG_SRC], a[api.ARG_DST] = src, dst
+            argsets.append(a)
+    for i in range(max(1, args.steps)):
+        plan.prim.execute(strm, argsets[i % len(argsets)])
     strm.wait()
-    print("executed %s x%d with %s" % (args.case, max(1, args.steps), plan.impl))
+    print("executed %s x%d with %s over %d input set(s)" % (args.case, max(1, args.steps), plan.impl, len(argsets)))
     return 0
 
 
-def run_c4_nsplit(W, torch, dist, rank, world, local, mode, reps=5):
-    """The large configuration with the weights' columns split over the ranks: every rank
-    multiplies the replicated src by its slice and every rank ends with the full row-major
-    dst -- through an NCCL all-gather plus a layout kernel (mode "nccl"), or by the matmul's
-    epilogue storing its tiles into all GPUs' copies of dst (mode "p2p").  Device-timed, max
-    over ranks; the slice matmul alone (same arguments) is timed beside the whole."""
+def cpu_other_configs(B, W, cores):
+    """The reference's CPU implementations on the other configurations, bounded samples: where its
+    JIT cannot take a configuration on this host (grouped zero-points, fp8 without AMX-FP16) the
+    scalar implementation it dispatches instead is timed, on a reduced shape where the full one
+    would take minutes, and the nearest JIT-eligible variant beside it."""
+    import copy
+    import numpy as np
+    from onednn_b200 import dtypes as dt
+    from onednn_b200.workloads import Quant
+    out = {"cores": cores}
+    try:
+        c = W.config2(1)
+        _, impl, tmin, tavg = B.run_reference(c, iters=1)
+        out["c2_wc_u4_m1"] = {"impl": impl, "ms": tavg, "GB/s": c.algorithmic_bytes() / (tavg * 1e-3) / 1e9,
+                              "sample": "the full 1x4096x14336 problem, one execution"}
+        v = copy.copy(c)  # one common zero-point instead of the grouped ones: the variant the JIT accepts
+        v.wei_zp = Quant(np.array([8], dtype=np.int32), dt.S32, 0)
+        _, impl, tmin, tavg = B.run_reference(v, weights_any=True, iters=3)
+        out["c2_variant_common_zero_point_m1"] = {"impl": impl, "ms": tavg,
+                                                  "GB/s": c.algorithmic_bytes() / (tavg * 1e-3) / 1e9,
+                                                  "sample": "1x4096x14336, grouped scales, one s32 zero-point, 3 executions, mean"}
+    except Exception as ex:
+        out["c2_error"] = repr(ex)
+    try:
+        c = W.config3(512, 512, 512)
+        _, impl, tmin, tavg = B.run_reference(c, weights_any=True, iters=1)
+        out["c3_fp8"] = {"impl": impl, "ms": tavg, "TFLOPS": c.ops / (tavg * 1e-3) / 1e12,
+                         "sample": "512^3 of the 8192^3 problem, one execution"}
+    except Exception as ex:
+        out["c3_error"] = repr(ex)
+    try:
+        c = W.config0()
+        _, impl, tmin, tavg = B.run_reference(c, weights_any=True, iters=50)
+        out["c0_int8_128x1024x1024"] = {"impl": impl, "us": tavg * 1e3, "sample": "the full problem, 50 executions, mean"}
+    except Exception as ex:
+        out["c0_error"] = repr(ex)
+    return out
+
+
+def run_c4_sharded(W, torch, dist, rank, world, local, reps=5):
+    """The large configuration (16384 x 8192 x 28672, s8 -> bf16) over the ranks, three ways:
+
+      m_split                   rows of src / dst over the ranks, weights replicated, no exchange;
+      n_split_nccl_all_gather   columns of the weights over the ranks, NCCL all-gather of the dst
+                                slices plus a layout kernel;
+      n_split_epilogue_stores   the same split with the matmul's epilogue storing its tiles into
+                                every GPU's copy of dst.
+
+    Each leg is device-timed (max over ranks) and then executed once more on a destination filled
+    with a sentinel byte and compared, element for element, with what the unsharded primitive
+    computes on the same GPU (a sharded run must reproduce it exactly); about a thousand elements
+    per rank are checked against the CPU oracle as well.  The counts are summed over ranks."""
     from onednn_b200 import multi_gpu
+    from oracle import binding as B
+    out = {}
     try:
         case = W.config4()
-        op = multi_gpu.NSplitMatmul(case, rank, world, local, mode=mode)
-        for _ in range(2):
+        full = multi_gpu.unsharded_on_this_gpu(case, local)     # (M, N * 2) bytes: the yardstick
+        elem = 2
+        # oracle sample: a 32 x 32 lattice, shifted per rank
+        ms_, ns_ = case.M // 32, case.N // 32
+        m0, n0 = (7 * rank) % ms_, (11 * rank) % ns_
+        want = B.run_oracle(case, tanh_mode=1, exact_acc=1, m_step=ms_, n_step=ns_, m0=m0, n0=n0)
+        want_s = torch.from_numpy(want[m0::ms_, n0::ns_].copy().view("uint8")).cuda()
+
+        def oracle_bad(dst_full):
+            got = dst_full.view(case.M, case.N, elem)[m0::ms_, n0::ns_].reshape(want_s.shape)
+            return int((got != want_s).view(got.shape[0], -1, elem).any(dim=2).sum().item())
+
+        def timed(op, extra=None):
+            for _ in range(2):
+                op.execute()
+            torch.cuda.synchronize()
+            dist.barrier()
+            a, b, c = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+            a.record()
+            for _ in range(reps):
+                op.execute()
+            b.record()
+            if extra is not None:
+                for _ in range(reps):
+                    extra()
+            c.record()
+            c.synchronize()
+            t = torch.tensor([a.elapsed_time(b) / reps, b.elapsed_time(c) / reps], device="cuda", dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return (float(x) for x in t.tolist())
+
+        def summed(*vals):
+            t = torch.tensor(list(vals), device="cuda", dtype=torch.int64)
+            dist.all_reduce(t, op=dist.ReduceOp.SUM)
+            return [int(x) for x in t.tolist()]
+
+        # ---- M-split ----
+        try:
+            op = multi_gpu.MSplitMatmul(case, rank, world, local)
+            ms, _ = timed(op)
+            op.dst.fill_(multi_gpu.SENTINEL)
             op.execute()
-        torch.cuda.synchronize()
-        dist.barrier()
-        a, b, c = (torch.cuda.Event(enable_timing=True) for _ in range(3))
-        a.record()
-        for _ in range(reps):
-            op.execute()
-        b.record()
-        for _ in range(reps):
-            op.plan.prim.execute(op.strm, op.args)
-        c.record()
-        c.synchronize()
-        t = torch.tensor([a.elapsed_time(b) / reps, b.elapsed_time(c) / reps], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms, ms_mm = (float(x) for x in t.tolist())
-        ns = case.N // world
-        out = {"impl": op.impl, "ranks": world, "ms": ms, "TOPS": case.ops / (ms * 1e-3) / 1e12,
-               "ms_matmul_slice_only": ms_mm,
-               "bytes_received_per_rank": (world - 1) * case.M * ns * 2,
-               "how": ("slice matmul -> ncclAllGather of [M][N/g] bf16 slices -> layout kernel" if mode == "nccl" else
-                       "slice matmul whose epilogue stores each tile into every GPU's copy of dst -> barrier")
-               + "; max over ranks"}
-        del op
+            torch.cuda.synchronize()
+            bad = multi_gpu.count_mismatched_elements(op.dst, full[op.rows], elem)
+            rows_here = [m for m in range(m0, case.M, ms_) if op.rows.start <= m < op.rows.stop]
+            got = op.dst.view(op.local.M, case.N, elem)[[m - op.rows.start for m in rows_here]][:, n0::ns_]
+            ref = want_s.view(-1, want_s.shape[1] // elem, elem)[[(m - m0) // ms_ for m in rows_here]]
+            obad = int((got != ref).any(dim=2).sum().item()) if rows_here else 0
+            bad, obad, nel, osamp = summed(bad, obad, op.local.M * case.N, len(rows_here) * ref.shape[1] if rows_here else 0)
+            out["m_split"] = {"impl": op.impl, "ranks": world, "ms": ms, "TOPS": case.ops / (ms * 1e-3) / 1e12,
+                              "rows_per_rank": op.local.M, "bytes_exchanged": 0,
+                              "mismatches_vs_unsharded_primitive": bad, "elements_compared": nel,
+                              "mismatches_vs_cpu_oracle": obad, "oracle_samples": osamp,
+                              "how": "each rank its rows through the ordinary primitive, replicated packed weights; max over ranks"}
+            del op
+        except Exception as ex:
+            out["m_split"] = {"error": repr(ex)}
         torch.cuda.empty_cache()
-        return out
+        # ---- N-split, two ways ----
+        for key, mode in (("n_split_nccl_all_gather", "nccl"), ("n_split_epilogue_stores", "p2p")):
+            try:
+                op = multi_gpu.NSplitMatmul(case, rank, world, local, mode=mode)
+                ms, ms_mm = timed(op, lambda: op.plan.prim.execute(op.strm, op.args))
+                torch.cuda.synchronize()
+                dist.barrier()
+                op.dst.fill_(multi_gpu.SENTINEL)
+                torch.cuda.synchronize()
+                dist.barrier()      # nobody stores into a copy its owner is still filling
+                op.execute()
+                torch.cuda.synchronize()
+                dist.barrier()
+                bad = multi_gpu.count_mismatched_elements(op.dst, full, elem)
+                obad = oracle_bad(op.dst)
+                bad, obad, nel, osamp = summed(bad, obad, case.M * case.N, want_s.shape[0] * want_s.shape[1] // elem)
+                nsl = case.N // world
+                out[key] = {"impl": op.impl, "ranks": world, "ms": ms, "TOPS": case.ops / (ms * 1e-3) / 1e12,
+                            "ms_matmul_slice_only": ms_mm, "bytes_received_per_rank": (world - 1) * case.M * nsl * 2,
+                            "mismatches_vs_unsharded_primitive": bad, "elements_compared": nel,
+                            "mismatches_vs_cpu_oracle": obad, "oracle_samples": osamp,
+                            "how": ("slice matmul -> ncclAllGather of [M][N/g] bf16 slices -> layout kernel" if mode == "nccl" else
+                                    "slice matmul whose epilogue stores each tile into every GPU's copy of dst -> barrier")
+                            + "; max over ranks"}
+                del op
+            except Exception as ex:
+                out[key] = {"error": repr(ex)}
+            torch.cuda.empty_cache()
     except Exception as ex:
-        return {"error": repr(ex)}
+        out["error"] = repr(ex)
+    return out
 
 
 def run_extras(api, W, dt, eng, strm, tstream, torch, np, peaks):

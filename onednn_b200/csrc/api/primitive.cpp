@@ -280,7 +280,9 @@ static const dnnl_memory_desc *arg_md(const dnnl_primitive_desc *pd, int arg) {
         case DNNL_ARG_WEIGHTS: return &pd->wei;
         case DNNL_ARG_BIAS: return &pd->bias;
         case DNNL_ARG_DST: return &pd->dst;
-        case DNNL_ARG_SCRATCHPAD: return &pd->scratchpad;
+        // what the user has to provide: nothing unless the attribute asks for a user scratchpad
+        // (the reference's primitive_desc_t::scratchpad_size, src/common/primitive_desc.hpp)
+        case DNNL_ARG_SCRATCHPAD: return pd->attr.scratchpad_mode == dnnl_scratchpad_mode_user ? &pd->scratchpad : &pd->zero_md;
         default: break;
     }
     // binary post-op operand
@@ -327,7 +329,9 @@ const_dnnl_memory_desc_t dnnl_primitive_desc_query_md(const_dnnl_primitive_desc_
             if (pd->kind != dnnl_matmul && pd->kind != dnnl_inner_product) return nullptr;
             return index == 0 ? &pd->wei : index == 1 ? &pd->bias : nullptr;
         case dnnl_query_dst_md: return index == 0 ? &pd->dst : nullptr;
-        case dnnl_query_scratchpad_md: return index == 0 ? &pd->scratchpad : nullptr;
+        case dnnl_query_scratchpad_md:
+            if (index != 0) return nullptr;
+            return pd->attr.scratchpad_mode == dnnl_scratchpad_mode_user ? &pd->scratchpad : &pd->zero_md;
         case dnnl_query_workspace_md:
         case dnnl_query_diff_src_md:
         case dnnl_query_diff_weights_md:

@@ -358,6 +358,9 @@ struct epi_consts_t {
     bool any_sum;
     int sum_dt;
     bool int8_nondefault; // the int8 path adds the destination zero-point (0 when unset) whenever any attribute is set
+    bool has_comp;        // a source zero-point is set: the per-column compensation vector is not all zero
+    bool zp_uniform;      // the destination zero-point does not vary over columns: cq / hq below apply to every column
+    float cq, hq;         // gelu-into-8-bit fast path with a uniform zero-point: its two per-column constants as scalars
 };
 
 // the exact gelu_tanh, kept out of line: it is needed for about one element in ten thousand
@@ -521,14 +524,20 @@ __device__ __forceinline__ void epilogue_chunk(const b200_matmul_params_t &p, co
     }
     // byte b of a packed word, sign- or zero-extended by one byte permute: selector nibble
     // 8|b replicates the byte's sign bit, nibble 4 picks a zero byte of the second operand
-    const uint32_t ext = k.sum_dt == B200_DT_S8 ? 0x8880u : 0x4440u;
+    // Byte b of a packed word as a float without an int-to-float conversion (those share a
+    // quarter-rate pipe with the exponentials and the final conversions of this epilogue): s8
+    // bytes are biased to 0..255 by flipping their sign bits, one byte permute drops the byte
+    // into the low mantissa bits of 2^23, and subtracting 2^23 (+ 128) leaves its value, exactly.
+    if (SUM == SUM_8BIT && k.sum_dt == B200_DT_S8) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) ow[q] ^= 0x80808080u;
+    }
+    const float unbias = k.sum_dt == B200_DT_S8 ? 8388736.f : 8388608.f;
     auto old_val = [&](int j) -> float {
         if (SUM == SUM_OTHER) return oldf[j];
-        const uint32_t b = j & 3;
-        const uint32_t sel = k.sum_dt == B200_DT_S8 ? (ext | b | (b << 4) | (b << 8) | (b << 12)) : (ext | b);
         uint32_t e;
-        asm("prmt.b32 %0, %1, %2, %3;" : "=r"(e) : "r"(ow[j >> 2]), "r"(0u), "r"(sel));
-        return (float)(int)e;
+        asm("prmt.b32 %0, %1, %2, %3;" : "=r"(e) : "r"(ow[j >> 2]), "r"(0x4b000000u), "r"(0x7440u | (uint32_t)(j & 3)));
+        return __uint_as_float(e) - unbias;
     };
 
     // per-column vectors of the chunk as 128-bit shared-memory reads
@@ -586,9 +595,12 @@ __device__ __forceinline__ void epilogue_chunk(const b200_matmul_params_t &p, co
 #pragma unroll
             for (int q = 0; q < 2; ++q) {
                 const float4 a = ((const float4 *)wsx)[hb / 4 + q], b = ((const float4 *)bias)[hb / 4 + q];
-                const int4 c = ((const int4 *)comp)[hb / 4 + q];
                 const float ws[4] = {a.x, a.y, a.z, a.w}, bs[4] = {b.x, b.y, b.z, b.w};
-                const int cs[4] = {c.x, c.y, c.z, c.w};
+                int cs[4] = {0, 0, 0, 0};
+                if (!FP8 && k.has_comp) { // warp-uniform: the vector is read only when a source zero-point exists
+                    const int4 c = ((const int4 *)comp)[hb / 4 + q];
+                    cs[0] = c.x; cs[1] = c.y; cs[2] = c.z; cs[3] = c.w;
+                }
                 float accf[4];
 #pragma unroll
                 for (int i = 0; i < 4; ++i) accf[i] = FP8 ? __uint_as_float(v[hb + 4 * q + i]) : (float)((int)v[hb + 4 * q + i] - cs[i]);
@@ -606,10 +618,16 @@ __device__ __forceinline__ void epilogue_chunk(const b200_matmul_params_t &p, co
                 asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(ex) : "f"(e2));
                 asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(t[j]) : "f"(ex + 1.f)); // r = 1 / (exp(2g) + 1): tanh(g) = 1 - 2r
             }
-            const float4 c0 = ((const float4 *)cq)[hb / 4], c1 = ((const float4 *)cq)[hb / 4 + 1];
-            const float4 h0 = ((const float4 *)hq)[hb / 4], h1 = ((const float4 *)hq)[hb / 4 + 1];
-            const float cv[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
-            const float hv[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
+            float cv[8], hv[8];
+            if (k.zp_uniform) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) cv[j] = k.cq, hv[j] = k.hq;
+            } else {
+                const float4 c0 = ((const float4 *)cq)[hb / 4], c1 = ((const float4 *)cq)[hb / 4 + 1];
+                const float4 h0 = ((const float4 *)hq)[hb / 4], h1 = ((const float4 *)hq)[hb / 4 + 1];
+                cv[0] = c0.x; cv[1] = c0.y; cv[2] = c0.z; cv[3] = c0.w; cv[4] = c1.x; cv[5] = c1.y; cv[6] = c1.z; cv[7] = c1.w;
+                hv[0] = h0.x; hv[1] = h0.y; hv[2] = h0.z; hv[3] = h0.w; hv[4] = h1.x; hv[5] = h1.y; hv[6] = h1.z; hv[7] = h1.w;
+            }
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
                 const float gelu = fmaf(-x[j], t[j], x[j]); // 0.5 x (1 + tanh) = x - x r
@@ -891,10 +909,31 @@ __global__ void __launch_bounds__(640, 1) matmul_tc8_kernel(const __grid_constan
                 && (p.npo > 0 || p.src_scale.ptr || p.wei_scale.ptr || p.dst_scale.ptr || p.src_zp.ptr || p.wei_zp.ptr
                         || p.dst_zp.ptr);
         const bool bias_per_col = p.bias && !p.bias_sm;
+        k.has_comp = has_comp;
+        k.zp_uniform = !(p.dst_zp.ptr && p.dst_zp.s1);
+        k.cq = k.hq = 0.f;
+        if (EPI == EPI_GELU_Q && k.zp_uniform) {
+            const float z = !k.int8_nondefault ? -0.f : p.dst_zp.ptr ? (float)((const int32_t *)p.dst_zp.ptr)[0] : 0.f;
+            const float bz = SUM != SUM_NONE ? p.po[1].scale * k.dst_inv * (float)p.po[1].zero_point : 0.f;
+            k.cq = z - bz;
+            k.hq = TAU_R * ((p.dst_dt == B200_DT_S8 ? 130.f : 258.f) + fabsf(z) + fabsf(bz));
+        }
         uint32_t tile_i = 0;
         bool ok = true;
         for (int u = unit0; u < args.units && ok; u += ustep, ++tile_i) {
             const unit_t un = decode_unit(args, u, TILE_ROWS);
+            if (SUM != SUM_NONE && u + ustep < args.units) {
+                // The prior destination bytes of the NEXT unit, asked into L2 now: when the epilogue
+                // is the slower side the accumulator is already waiting at the top of a unit, and
+                // the first read of those bytes would otherwise sit in the open with its DRAM latency.
+                const unit_t nx = decode_unit(args, u + ustep, TILE_ROWS);
+                const int64_t nm = nx.m0 + (int64_t)rank * BM + quarter * 32 + lane;
+                const int64_t nn = (int64_t)nx.n0 + half * (nx.width / 4);
+                if (nm < p.M && nn < p.N) {
+                    const char *pf = (const char *)p.dst + (size_t)(nm * p.dst_sm + nn) * (dt_bits(sum_dt_of(p)) / 8);
+                    asm volatile("prefetch.global.L2 [%0];" ::"l"(pf));
+                }
+            }
             // this warp's share of the unit's columns: a quarter of them, in chunks of CH
             const int ecols = un.width / 4, nch = ecols / CH;
             const int64_t m0 = un.m0 + (int64_t)rank * BM;

@@ -40,7 +40,10 @@
 //    CTAs goes one level further the same way: red.global.add into the f32
 //    scratch [M][N] plus a global per-strip counter, and the CTA that completes
 //    it applies the epilogue and leaves scratch and counter zeroed.
+#include <cstdlib>
 #include <mutex>
+#include <utility>
+#include <vector>
 
 #include "common.cuh"
 #include "launch.hpp"
@@ -491,6 +494,549 @@ __global__ void __launch_bounds__(256) wc_pack_kernel(const uint8_t *__restrict_
     }
 }
 
+
+// ---- streaming form of the decode kernel ------------------------------------------------------
+//
+// The kernel above has every lane fetch its own weights with cp.async: correct and simple, but
+// 40 % of its instructions are copy bookkeeping, and at one byte of weights per two multiply-adds
+// the instruction issue rate, not HBM, bounds it.  This form moves the stream to the copy engine
+// and fixes every warp's K range, so that the activations and everything derived from them stay
+// in registers:
+//
+//  * A chunk is one strip of 16 output columns x C = 16 * TPW tile steps of K (TPW = 4, 2 or 1:
+//    8 to 32 KiB, contiguous in the tiled layout).  When K is longer than a chunk the strip has
+//    several parts; chunks are numbered part-major, so a CTA's contiguous range of chunks keeps
+//    the same part (the same K range) almost throughout.
+//  * One producer thread streams the CTA's chunks with cp.async.bulk into a ring of shared-memory
+//    stages (full / empty mbarriers), a few copies of 8 KiB per chunk.
+//  * Consumer warp w of 16 owns tile steps [w * TPW, (w + 1) * TPW) of every chunk: its
+//    activation fragments (MB * TPW * 8 registers), their row sums per quantisation group and the
+//    group indices are loaded once per K part.  Per tile step it issues one 128-bit shared-memory
+//    load, the nibble unpack (7 logic operations per 8 weights) and the MMAs -- no addressing, no
+//    activation loads, no copy instructions.
+//  * The 16 partial sums of a strip (one per warp) go through double-buffered slabs to one
+//    epilogue warp per 8 activation rows, which adds them up and finishes the strip, so a
+//    consumer never waits for another consumer.
+//  * The CTA's range is cut in quarter chunks (4 warps' worth), which balances the grid to within
+//    one quarter chunk; a strip that is not wholly inside one CTA (range ends, several K parts) is
+//    completed through the f32 scratch and the per-strip counter like in the kernel above.
+constexpr int WS_WARPS = 16;
+constexpr int WS_MAX_STAGES = 16;
+constexpr uint32_t WS_WAIT_TRIES = 1u << 20; // bounded waits: a million suspended waits of up to a microsecond
+constexpr uint32_t WS_ST_FULL = 0x100, WS_ST_EMPTY = 0x200, WS_ST_SLAB_FULL = 0x400, WS_ST_SLAB_EMPTY = 0x800;
+__host__ __device__ constexpr int ws_threads(int mb) { return (WS_WARPS + 1 + mb) * 32; }
+
+struct ws_ctrl_t {
+    uint64_t full[WS_MAX_STAGES], empty[WS_MAX_STAGES];
+    uint64_t slab_full[2], slab_empty[2];
+    volatile uint32_t abort;
+};
+
+struct ws_args_t {
+    const unsigned char *wei;
+    const __nv_bfloat16 *x;
+    int64_t x_ld;
+    float *acc;
+    uint32_t *done;
+    int64_t M, N;
+    int m0;
+    const void *scale; int scale_dt; int64_t scale_s0, scale_s1; uint32_t scale_g0;
+    const void *zp; int zp_dt; int64_t zp_s0, zp_s1; uint32_t zp_g0;
+    float nibble_offset;
+    uint32_t kchunks;   // tile steps per strip
+    uint32_t strips;    // N / 16
+    uint32_t parts;     // K parts per strip
+    uint32_t quarters;  // strips * parts * 4: the units the grid divides
+    uint32_t stages;    // ring depth
+    int plain_bf16;     // dst is bf16 with even pitch and nothing between the sum and the store: two columns per 32-bit store
+    int simple;         // no post-ops, f32 / bf16 bias or none, f32 / bf16 dst: ws_finish_simple applies
+    wc_div_t div_strips, div_fold; // division by strips and by the tile steps of a quantisation group
+};
+
+__device__ __forceinline__ void ws_mbar_init(uint64_t *bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(wc_smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void ws_mbar_arrive(uint64_t *bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(wc_smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void ws_mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(wc_smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool ws_mbar_try(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(wc_smem_u32(bar)), "r"(parity), "r"(1000u)
+            : "memory");
+    return ok != 0;
+}
+// bounded wait (of the order of a second); false when it ran out or another role gave up.
+// The loop is out of line: the common case is one successful try.
+__device__ __noinline__ bool ws_wait_slow(uint64_t *bar, uint32_t parity, ws_ctrl_t *c, uint32_t *status, uint32_t code) {
+    for (uint32_t i = 0; i < WS_WAIT_TRIES; ++i) {
+        if (ws_mbar_try(bar, parity)) return true;
+        if (c->abort) return false;
+    }
+    c->abort = 1;
+    if (status) atomicOr(status, code);
+    return false;
+}
+__device__ __forceinline__ bool ws_wait(uint64_t *bar, uint32_t parity, ws_ctrl_t *c, uint32_t *status, uint32_t code) {
+    if (ws_mbar_try(bar, parity)) return true;
+    return ws_wait_slow(bar, parity, c, status, code);
+}
+// contiguous global -> shared copy by the copy engine; its bytes are counted on the barrier
+__device__ __forceinline__ void ws_bulk_copy(uint32_t dst, const void *src, uint32_t bytes, uint64_t *bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src),
+                 "r"(bytes), "r"(wc_smem_u32(bar))
+                 : "memory");
+}
+
+__device__ __forceinline__ void ws_group_params(const ws_args_t &a, uint32_t k, uint32_t n, float &s, float &c) {
+    s = 1.f;
+    c = a.nibble_offset;
+    if (a.scale) s = load_f32(a.scale_dt, a.scale, (int64_t)(k / a.scale_g0) * a.scale_s0 + (int64_t)n * a.scale_s1);
+    if (a.zp) c += (float)load_int(a.zp_dt, a.zp, (int64_t)(k / a.zp_g0) * a.zp_s0 + (int64_t)n * a.zp_s1);
+}
+
+// Everything behind the sum of one dst element in its general form (bias, any post-op chain,
+// destination scale, any destination type).  One out-of-line copy: inlined at every call site the
+// interpreter of the post-op chain -- some 40 KiB of code -- made the kernel a quarter of a megabyte,
+// and a kernel that runs for a few microseconds pays for every instruction-cache line it touches.
+__device__ __noinline__ void ws_finish(const b200_matmul_params_t &p, float d, int64_t m, int64_t n, float src_scale,
+        float dst_inv) {
+    if (p.src_scale.ptr) d = __fmul_rn(d, src_scale);
+    finish_element(p, d, m, n, false, dst_inv);
+}
+
+// The same for the configurations a decode layer usually has -- no post-ops, f32 / bf16 bias or
+// none, f32 / bf16 destination: a handful of instructions, inlined.
+__device__ __forceinline__ void ws_finish_simple(const b200_matmul_params_t &p, float d, int64_t m, int64_t n, float src_scale,
+        float dst_inv) {
+    if (p.src_scale.ptr) d = __fmul_rn(d, src_scale);
+    if (p.bias) {
+        const int64_t bo = m * p.bias_sm + n * p.bias_sn;
+        d = __fadd_rn(d, p.bias_dt == B200_DT_F32 ? ((const float *)p.bias)[bo]
+                                                   : __uint_as_float((uint32_t)((const uint16_t *)p.bias)[bo] << 16));
+    }
+    if (p.dst_scale.ptr) d = __fmul_rn(d, dst_inv);
+    const int64_t doff = m * p.dst_sm + n * p.dst_sn;
+    if (p.dst_dt == B200_DT_F32) ((float *)p.dst)[doff] = d;
+    else ((uint16_t *)p.dst)[doff] = f32_to_bf16_bits(d);
+}
+
+// the chunk sequence of one CTA: chunk i of its range -> (part, strip) and the quarters [qlo, qhi) it owns
+struct ws_range_t {
+    uint32_t b, e;        // quarter units [b, e)
+    uint32_t first, n;    // first chunk index, number of chunks
+    __device__ __forceinline__ void init(const ws_args_t &a) {
+        const uint32_t base = a.quarters / gridDim.x, rem = a.quarters % gridDim.x;
+        b = blockIdx.x * base + (blockIdx.x < rem ? blockIdx.x : rem);
+        e = b + base + (blockIdx.x < rem ? 1 : 0);
+        first = b >> 2;
+        n = e > b ? ((e - 1) >> 2) - first + 1 : 0;
+    }
+    // quarters [qlo, qhi) of the k-th chunk of the range that belong to this CTA
+    __device__ __forceinline__ uint32_t qlo(uint32_t k) const { return k == 0 ? (b & 3) : 0; }
+    __device__ __forceinline__ uint32_t qhi(uint32_t k) const { return k + 1 == n ? ((e - 1) & 3) + 1 : 4; }
+};
+
+// Order in which a CTA takes the chunks of its range: the last one first, then the others in
+// ascending order.  The chunks a range shares with its neighbours are its first and its last;
+// their sums travel through global memory (atomics, a fence, a counter round trip), and taken
+// first that latency passes while the whole chunks are processed instead of ending the kernel.
+struct ws_walk_t {
+    uint32_t k;    // index of the current chunk inside the range
+    uint32_t q, s; // its K part and strip
+    __device__ __forceinline__ void start(const ws_args_t &a, const ws_range_t &rg) {
+        k = rg.n ? rg.n - 1 : 0;
+        const uint32_t idx = rg.first + k;
+        q = wc_div(idx, a.div_strips);
+        s = idx - q * a.strips;
+    }
+    // the position after this one (step i -> i + 1 of the walk)
+    __device__ __forceinline__ ws_walk_t next(const ws_args_t &a, const ws_range_t &rg, uint32_t i) const {
+        ws_walk_t r;
+        if (i == 0) {
+            r.k = 0;
+            r.q = wc_div(rg.first, a.div_strips);
+            r.s = rg.first - r.q * a.strips;
+        } else {
+            r.k = k + 1;
+            r.q = q;
+            r.s = s + 1;
+            if (r.s == a.strips) {
+                r.s = 0;
+                ++r.q;
+            }
+        }
+        return r;
+    }
+};
+
+// MB: 8-row activation blocks per pass; TPW: tile steps per warp and chunk; FE: tile steps per
+// fold (the quantisation group, or all TPW when the group is longer); FASTQ: bf16 scales and u4
+// zero-points over the same groups, fetched as one 32-bit and one 8-bit load per lane and fold.
+template <int MB, int TPW, int FE, bool FASTQ>
+__global__ void __launch_bounds__(ws_threads(MB), 1)
+        wc_stream_kernel(const __grid_constant__ ws_args_t a, const __grid_constant__ b200_matmul_params_t p) {
+    constexpr uint32_t C = WS_WARPS * TPW;              // tile steps per chunk
+    constexpr uint32_t CH = C * WC_TILE_BYTES;          // bytes per chunk = per ring stage
+    constexpr uint32_t QB = CH / 4;                     // bytes per quarter chunk
+    constexpr int NF = TPW / FE;                        // folds per warp and chunk
+    extern __shared__ __align__(128) unsigned char wc_smem[];
+    const uint32_t S = a.stages;
+    unsigned char *ring = wc_smem;
+    float4 *slabs = reinterpret_cast<float4 *>(wc_smem + (size_t)S * CH);                       // [2][16][MB][32]
+    ws_ctrl_t *ctrl = reinterpret_cast<ws_ctrl_t *>(wc_smem + (size_t)S * CH + 2 * WS_WARPS * MB * 32 * sizeof(float4));
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t rows = a.M - a.m0 < MB * 8 ? (uint32_t)(a.M - a.m0) : (uint32_t)(MB * 8);
+    const uint32_t nblk = (rows + 7) / 8;
+
+    ws_range_t rg;
+    rg.init(a);
+    // The consumers' activation fragments.  The loads of the first K part are issued before
+    // anything else in the kernel -- ahead of the barrier set-up and of the producer's flood of
+    // weight requests, behind which they would otherwise queue.
+    uint32_t xr[MB][TPW][8];
+    auto fetch_x = [&](uint32_t q) {
+        const uint32_t g = lane >> 2, t = lane & 3;
+#pragma unroll
+        for (int mb = 0; mb < MB; ++mb) {
+            const int64_t m = a.m0 + mb * 8 + g;
+            const __nv_bfloat16 *xrow = a.x + (m < a.M ? m : a.M - 1) * a.x_ld + 16 * t;
+#pragma unroll
+            for (int j = 0; j < TPW; ++j) {
+                const uint4 *xp = reinterpret_cast<const uint4 *>(xrow + (size_t)(q * C + warp * TPW + j) * WC_TILE_K);
+                const uint4 u0 = xp[0], u1 = xp[1];
+                xr[mb][j][0] = u0.x; xr[mb][j][1] = u0.y; xr[mb][j][2] = u0.z; xr[mb][j][3] = u0.w;
+                xr[mb][j][4] = u1.x; xr[mb][j][5] = u1.y; xr[mb][j][6] = u1.z; xr[mb][j][7] = u1.w;
+            }
+        }
+    };
+    uint32_t cur_q = 0xffffffffu;
+    if (warp < WS_WARPS && rg.n > 0) {
+        ws_walk_t w0;
+        w0.start(a, rg);
+        fetch_x(w0.q);
+        cur_q = w0.q;
+    }
+
+    if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < S; ++s) {
+            ws_mbar_init(&ctrl->full[s], 1);
+            ws_mbar_init(&ctrl->empty[s], WS_WARPS);
+        }
+        for (int i = 0; i < 2; ++i) {
+            ws_mbar_init(&ctrl->slab_full[i], WS_WARPS);
+            ws_mbar_init(&ctrl->slab_empty[i], MB);
+        }
+        ctrl->abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    __syncthreads();
+
+    if (warp == WS_WARPS) {
+        // ---------------- producer ----------------
+        if (lane == 0) {
+            uint32_t issued = 0;
+            ws_walk_t w;
+            w.start(a, rg);
+            uint32_t st = 0, ph = 1; // stage of step i and the parity of its previous release
+            for (uint32_t i = 0; i < rg.n; ++i) {
+                if (i >= S && !ws_wait(&ctrl->empty[st], ph, ctrl, p.status, WS_ST_EMPTY)) break;
+                const uint32_t qlo = rg.qlo(w.k), qhi = rg.qhi(w.k), q = w.q, s = w.s;
+                const unsigned char *src = a.wei + ((size_t)s * a.kchunks + (size_t)q * C) * WC_TILE_BYTES + (size_t)qlo * QB;
+                const uint32_t dst = wc_smem_u32(ring + (size_t)st * CH) + qlo * QB;
+                ws_mbar_expect_tx(&ctrl->full[st], (qhi - qlo) * QB);
+                if (QB >= 4096) {
+                    for (uint32_t h = 0; h < qhi - qlo; ++h) ws_bulk_copy(dst + h * QB, src + (size_t)h * QB, QB, &ctrl->full[st]);
+                } else {
+                    ws_bulk_copy(dst, src, (qhi - qlo) * QB, &ctrl->full[st]);
+                }
+                issued = i + 1;
+                w = w.next(a, rg, i);
+                if (++st == S) {
+                    st = 0;
+                    ph ^= 1;
+                }
+            }
+            // every copy issued must have landed before the CTA may exit
+            for (uint32_t j = issued > S ? issued - S : 0; j < issued; ++j) {
+                const uint32_t st = j % S, par = (j / S) & 1;
+                for (uint32_t t = 0; t < WS_WAIT_TRIES; ++t)
+                    if (ws_mbar_try(&ctrl->full[st], par)) break;
+            }
+        }
+    } else if (warp < WS_WARPS) {
+        // ---------------- consumers ----------------
+        const uint32_t g = lane >> 2, t = lane & 3;
+        float xf[MB][NF][2];       // sums of the fragments per fold: rows 2t and 2t + 1 of the block
+        uint32_t kfold[NF];        // first k of each fold
+        uint32_t sum_q = 0xffffffffu; // the K part xf and kfold belong to
+        auto sum_x = [&](uint32_t q) {
+#pragma unroll
+            for (int f = 0; f < NF; ++f) kfold[f] = (q * C + warp * TPW + f * FE) * WC_TILE_K;
+#pragma unroll
+            for (int mb = 0; mb < MB; ++mb) {
+                float part[TPW];
+#pragma unroll
+                for (int j = 0; j < TPW; ++j) {
+                    float sum = 0.f;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i)
+                        sum += __uint_as_float(xr[mb][j][i] << 16) + __uint_as_float(xr[mb][j][i] & 0xffff0000u);
+                    // the four lanes of a group hold the four quarters of the row's 64 k
+                    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+                    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+                    part[j] = sum; // sum of row g of the block over tile step j
+                }
+#pragma unroll
+                for (int f = 0; f < NF; ++f) {
+                    float fs = 0.f;
+#pragma unroll
+                    for (int j = 0; j < FE; ++j) fs += part[f * FE + j];
+                    // accumulator slots of this lane belong to rows 2t and 2t + 1
+                    xf[mb][f][0] = __shfl_sync(0xffffffffu, fs, (2 * t) * 4);
+                    xf[mb][f][1] = __shfl_sync(0xffffffffu, fs, (2 * t + 1) * 4);
+                }
+            }
+        };
+        // scale / zero-point words of a chunk's folds (FASTQ), requested one chunk ahead
+        uint32_t qs[NF], qz[NF], qs_n[NF], qz_n[NF], grow_n[NF]; // grow_n: (group index) * N + 2g of each fold of part gq
+        uint32_t gq = 0xffffffffu;
+        auto load_q = [&](uint32_t q, uint32_t s, uint32_t (&os)[NF], uint32_t (&oz)[NF]) {
+            if (!FASTQ) return;
+            if (q != gq) {
+#pragma unroll
+                for (int f = 0; f < NF; ++f) grow_n[f] = wc_div(q * C + warp * TPW + f * FE, a.div_fold) * (uint32_t)a.N + 2 * g;
+                gq = q;
+            }
+#pragma unroll
+            for (int f = 0; f < NF; ++f) {
+                const uint32_t row = grow_n[f] + s * WC_TILE_N; // even
+                os[f] = *reinterpret_cast<const uint32_t *>((const uint16_t *)a.scale + row);
+                oz[f] = ((const uint8_t *)a.zp)[row >> 1];
+            }
+        };
+        ws_walk_t w;
+        w.start(a, rg);
+#pragma unroll
+        for (int f = 0; f < NF; ++f) qs[f] = qz[f] = qs_n[f] = qz_n[f] = grow_n[f] = 0;
+        if (rg.n > 0) load_q(w.q, w.s, qs_n, qz_n);
+        const uint32_t quarter = warp >> 2;
+        bool ok = true;
+        uint32_t st = 0, ph = 0; // ring stage of chunk i and the parity of its arrival
+#pragma unroll 1
+        for (uint32_t i = 0; i < rg.n; ++i) {
+            const uint32_t q = w.q, s = w.s;
+            if (q != cur_q) {
+                fetch_x(q);
+                cur_q = q;
+            }
+            if (q != sum_q) {
+                sum_x(q);
+                sum_q = q;
+            }
+#pragma unroll
+            for (int f = 0; f < NF; ++f) {
+                qs[f] = qs_n[f];
+                qz[f] = qz_n[f];
+            }
+            // position of the next chunk, and its group parameters
+            const ws_walk_t wn = w.next(a, rg, i);
+            if (i + 1 < rg.n) load_q(wn.q, wn.s, qs_n, qz_n);
+            const bool active = quarter >= rg.qlo(w.k) && quarter < rg.qhi(w.k);
+            ok = ws_wait(&ctrl->full[st], ph, ctrl, p.status, WS_ST_FULL);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            float tot[MB][4];
+#pragma unroll
+            for (int mb = 0; mb < MB; ++mb)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) tot[mb][e] = 0.f;
+            if (active) {
+                const uint4 *sp = reinterpret_cast<const uint4 *>(ring + (size_t)st * CH + (size_t)(warp * TPW) * WC_TILE_BYTES) + lane;
+#pragma unroll
+                for (int f = 0; f < NF; ++f) {
+                    // The MMAs of a fold go to NA independent accumulators (one per word of a
+                    // lane's 16 bytes while registers allow): a single accumulator would chain all
+                    // of them, and the latency of that chain, not any pipe, then sets the pace.
+                    constexpr int NA = MB == 1 ? 4 : (MB == 2 ? 2 : 1);
+                    float accs[NA][MB][4];
+#pragma unroll
+                    for (int u = 0; u < NA; ++u)
+#pragma unroll
+                        for (int mb = 0; mb < MB; ++mb)
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) accs[u][mb][e] = 0.f;
+#pragma unroll
+                    for (int jj = 0; jj < FE; ++jj) {
+                        const int j = f * FE + jj;
+                        const uint4 wv = sp[j * 32];
+#define WS_MMA_STEP(WORD, I0)                                                  \
+    {                                                                          \
+        const uint32_t v = (WORD);                                             \
+        uint32_t af[4];                                                        \
+        af[0] = (v & 0x000f000fu) | 0x43004300u;                               \
+        af[1] = ((v >> 4) & 0x000f000fu) | 0x43004300u;                        \
+        af[2] = ((v >> 8) & 0x000f000fu) | 0x43004300u;                        \
+        af[3] = ((v >> 12) & 0x000f000fu) | 0x43004300u;                       \
+        _Pragma("unroll") for (int mb = 0; mb < MB; ++mb)                      \
+                mma_bf16_16816(accs[((I0) / 2) % NA][mb], af, xr[mb][j][I0], xr[mb][j][(I0) + 1]); \
+    }
+                        WS_MMA_STEP(wv.x, 0)
+                        WS_MMA_STEP(wv.y, 2)
+                        WS_MMA_STEP(wv.z, 4)
+                        WS_MMA_STEP(wv.w, 6)
+#undef WS_MMA_STEP
+                    }
+                    float acc[MB][4];
+#pragma unroll
+                    for (int mb = 0; mb < MB; ++mb)
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            float t2 = accs[0][mb][e];
+#pragma unroll
+                            for (int u = 1; u < NA; ++u) t2 += accs[u][mb][e];
+                            acc[mb][e] = t2;
+                        }
+                    float s0, s1, c0, c1;
+                    if (FASTQ) {
+                        s0 = __uint_as_float(qs[f] << 16);
+                        s1 = __uint_as_float(qs[f] & 0xffff0000u);
+                        // 2^23 + nibble as a float, minus (2^23 - offset): offset + nibble, exactly
+                        c0 = __uint_as_float(0x4b000000u | (qz[f] & 0xfu)) - (8388608.f - a.nibble_offset);
+                        c1 = __uint_as_float(0x4b000000u | (qz[f] >> 4)) - (8388608.f - a.nibble_offset);
+                    } else {
+                        const uint32_t n0 = s * WC_TILE_N + 2 * g;
+                        ws_group_params(a, kfold[f], n0, s0, c0);
+                        ws_group_params(a, kfold[f], n0 + 1, s1, c1);
+                    }
+#pragma unroll
+                    for (int mb = 0; mb < MB; ++mb) {
+                        const float xe = xf[mb][f][0], xo = xf[mb][f][1];
+                        tot[mb][0] = fmaf(s0, fmaf(-c0, xe, acc[mb][0]), tot[mb][0]);
+                        tot[mb][1] = fmaf(s0, fmaf(-c0, xo, acc[mb][1]), tot[mb][1]);
+                        tot[mb][2] = fmaf(s1, fmaf(-c1, xe, acc[mb][2]), tot[mb][2]);
+                        tot[mb][3] = fmaf(s1, fmaf(-c1, xo, acc[mb][3]), tot[mb][3]);
+                    }
+                }
+            }
+            // the stage's bytes are in registers or consumed: hand it back to the producer
+            __syncwarp();
+            if (lane == 0) ws_mbar_arrive(&ctrl->empty[st]);
+            // partial sums of the strip into this warp's slab of buffer i & 1
+            const uint32_t buf = i & 1, use = i >> 1;
+            if (use > 0) {
+                ok = ws_wait(&ctrl->slab_empty[buf], (use - 1) & 1, ctrl, p.status, WS_ST_SLAB_EMPTY);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+            }
+            if (active) {
+                float4 *mine = slabs + ((size_t)(buf * WS_WARPS + warp) * MB) * 32 + lane;
+#pragma unroll
+                for (int mb = 0; mb < MB; ++mb) mine[mb * 32] = make_float4(tot[mb][0], tot[mb][1], tot[mb][2], tot[mb][3]);
+            }
+            __syncwarp();
+            if (lane == 0) ws_mbar_arrive(&ctrl->slab_full[buf]);
+            w = wn;
+            if (++st == S) {
+                st = 0;
+                ph ^= 1;
+            }
+        }
+    } else {
+        // ---------------- epilogue warps: one per 8-row block ----------------
+        const uint32_t mb = warp - WS_WARPS - 1;
+        const uint32_t g = lane >> 2, t = lane & 3;
+        const float dst_inv = dst_scale_reciprocal(p);
+        const float src_scale = p.src_scale.ptr ? load_f32(p.src_scale.dt, p.src_scale.ptr, 0) : 1.f;
+        ws_walk_t w;
+        w.start(a, rg);
+        bool ok = true;
+#pragma unroll 1
+        for (uint32_t i = 0; i < rg.n; ++i) {
+            const uint32_t buf = i & 1, use = i >> 1;
+            const uint32_t qlo = rg.qlo(w.k), qhi = rg.qhi(w.k);
+            ok = ws_wait(&ctrl->slab_full[buf], use & 1, ctrl, p.status, WS_ST_SLAB_FULL);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+            const float4 *sl = slabs + ((size_t)(buf * WS_WARPS) * MB + mb) * 32 + lane;
+            for (uint32_t w = 4 * qlo; w < 4 * qhi; ++w) {
+                const float4 v = sl[(size_t)w * MB * 32];
+                sum.x += v.x;
+                sum.y += v.y;
+                sum.z += v.z;
+                sum.w += v.w;
+            }
+            __syncwarp();
+            if (lane == 0) ws_mbar_arrive(&ctrl->slab_empty[buf]);
+            const uint32_t strip = w.s;
+            w = w.next(a, rg, i);
+            if (mb >= nblk) continue; // no valid row in this block (the barriers above still count this warp)
+            const uint32_t r0 = mb * 8 + 2 * t;             // rows r0, r0 + 1 of the pass
+            const int64_t n0 = (int64_t)strip * WC_TILE_N + 2 * g; // columns n0, n0 + 1
+            const float v[4] = {sum.x, sum.y, sum.z, sum.w}; // (r0, n0) (r0+1, n0) (r0, n0+1) (r0+1, n0+1)
+            if (a.parts == 1 && qlo == 0 && qhi == 4) {
+                // the whole strip was summed here
+                if (a.plain_bf16) {
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        const uint32_t r = r0 + e;
+                        if (r < rows)
+                            *reinterpret_cast<uint32_t *>((uint16_t *)p.dst + (a.m0 + r) * p.dst_sm + n0)
+                                    = (uint32_t)f32_to_bf16_bits(v[e]) | ((uint32_t)f32_to_bf16_bits(v[e + 2]) << 16);
+                    }
+                } else if (a.simple) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const uint32_t r = r0 + (e & 1);
+                        if (r < rows) ws_finish_simple(p, v[e], a.m0 + r, n0 + (e >> 1), src_scale, dst_inv);
+                    }
+                } else {
+#pragma unroll 1
+                    for (int e = 0; e < 4; ++e) {
+                        const uint32_t r = r0 + (e & 1);
+                        if (r < rows) ws_finish(p, v[e], a.m0 + r, n0 + (e >> 1), src_scale, dst_inv);
+                    }
+                }
+                continue;
+            }
+            // part of a strip: into the scratch; whoever completes the strip's count finishes it
+            float *out = a.acc + (int64_t)a.m0 * a.N;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const uint32_t r = r0 + (e & 1);
+                if (r < rows) atomicAdd(out + (int64_t)r * a.N + n0 + (e >> 1), v[e]);
+            }
+            __threadfence(); // the sums above are visible before the count below
+            __syncwarp();
+            const uint32_t cnt = (qhi - qlo) * (C / 4);
+            uint32_t before = 0;
+            if (lane == 0) before = atomicAdd(a.done + strip, cnt);
+            before = __shfl_sync(0xffffffffu, before, 0);
+            if (before + cnt != a.kchunks * nblk) continue;
+            __threadfence();
+            const uint32_t cells = rows * WC_TILE_N;
+            for (uint32_t c = lane; c < cells; c += 32) {
+                const uint32_t r = c / WC_TILE_N, col = c % WC_TILE_N;
+                float *cell = out + (int64_t)r * a.N + (int64_t)strip * WC_TILE_N + col;
+                const float d = __ldcg(cell);
+                *cell = 0.f;
+                if (a.simple) ws_finish_simple(p, d, a.m0 + r, (int64_t)strip * WC_TILE_N + col, src_scale, dst_inv);
+                else ws_finish(p, d, a.m0 + r, (int64_t)strip * WC_TILE_N + col, src_scale, dst_inv);
+            }
+            if (lane == 0) a.done[strip] = 0;
+        }
+    }
+}
+
 static inline size_t align256(size_t x) { return (x + 255) / 256 * 256; }
 
 } // namespace b200
@@ -536,6 +1082,99 @@ static void wc_launch_variant(const wc_args_t &a, const b200_matmul_params_t &p,
         if (unit_steps == 2) wc_gemv_kernel<MB, FASTQ, false, 2><<<ctas, threads, smem, cs>>>(a, p);
         else wc_gemv_kernel<MB, FASTQ, false, 1><<<ctas, threads, smem, cs>>>(a, p);
     }
+}
+
+// ---- launch of the streaming form ----
+typedef void (*ws_kernel_t)(const ws_args_t, const b200_matmul_params_t);
+template <int MB, int TPW, int FE>
+static ws_kernel_t ws_pick(bool fastq) {
+    return fastq ? wc_stream_kernel<MB, TPW, FE, true> : wc_stream_kernel<MB, TPW, FE, false>;
+}
+static ws_kernel_t ws_kernel_for(int mb, int tpw, int fe, bool fastq) {
+    const int key = mb * 100 + tpw * 10 + fe;
+    switch (key) {
+        case 144: return ws_pick<1, 4, 4>(fastq);
+        case 142: return ws_pick<1, 4, 2>(fastq);
+        case 141: return ws_pick<1, 4, 1>(fastq);
+        case 122: return ws_pick<1, 2, 2>(fastq);
+        case 121: return ws_pick<1, 2, 1>(fastq);
+        case 111: return ws_pick<1, 1, 1>(fastq);
+        case 222: return ws_pick<2, 2, 2>(fastq);
+        case 221: return ws_pick<2, 2, 1>(fastq);
+        case 211: return ws_pick<2, 1, 1>(fastq);
+        case 411: return ws_pick<4, 1, 1>(fastq);
+        default: return nullptr;
+    }
+}
+
+// One pass (up to 32 activation rows from a.m0) with the streaming kernel.  Returns
+// B200_ERR_UNSUPPORTED when the shape does not fit its chunking: K must be a multiple of
+// 1024 x TPW with MB x TPW <= 4, and the quantisation groups must nest with a warp's tile steps.
+static int ws_run_pass(const wc_args_t &w, const b200_matmul_params_t &p, int mb, uint32_t fold_steps, bool fastq, int sms,
+        cudaStream_t cs) {
+    int tpw = 0, fe = 0;
+    for (int cand = 4 / mb; cand >= 1; cand /= 2) {
+        if (w.kchunks % (uint32_t)(WS_WARPS * cand) != 0) continue;
+        const bool nests = fold_steps >= (uint32_t)cand ? fold_steps % cand == 0 : cand % fold_steps == 0;
+        if (!nests) continue;
+        tpw = cand;
+        fe = fold_steps >= (uint32_t)cand ? cand : (int)fold_steps;
+        break;
+    }
+    if (!tpw) return B200_ERR_UNSUPPORTED;
+    ws_kernel_t kern = ws_kernel_for(mb, tpw, fe, fastq);
+    if (!kern) return B200_ERR_UNSUPPORTED;
+    ws_args_t a;
+    a.wei = (const unsigned char *)w.wei;
+    a.x = w.x;
+    a.x_ld = w.x_ld;
+    a.acc = w.acc;
+    a.done = w.done;
+    a.M = w.M;
+    a.N = w.N;
+    a.m0 = w.m0;
+    a.scale = w.scale; a.scale_dt = w.scale_dt; a.scale_s0 = w.scale_s0; a.scale_s1 = w.scale_s1; a.scale_g0 = w.scale_g0;
+    a.zp = w.zp; a.zp_dt = w.zp_dt; a.zp_s0 = w.zp_s0; a.zp_s1 = w.zp_s1; a.zp_g0 = w.zp_g0;
+    a.nibble_offset = w.nibble_offset;
+    a.kchunks = w.kchunks;
+    a.strips = (uint32_t)(w.N / WC_TILE_N);
+    const uint32_t chunk_steps = (uint32_t)(WS_WARPS * tpw);
+    a.parts = w.kchunks / chunk_steps;
+    const uint64_t quarters = (uint64_t)a.strips * a.parts * 4;
+    if (quarters >= ((uint64_t)1 << 31)) return B200_ERR_TOO_LARGE;
+    a.quarters = (uint32_t)quarters;
+    a.div_strips = wc_make_div(a.strips);
+    a.div_fold = wc_make_div(fold_steps);
+    a.simple = p.npo == 0 && (!p.bias || p.bias_dt == B200_DT_F32 || p.bias_dt == B200_DT_BF16)
+            && (p.dst_dt == B200_DT_F32 || p.dst_dt == B200_DT_BF16);
+    a.plain_bf16 = p.dst_dt == B200_DT_BF16 && !p.bias && p.npo == 0 && !p.src_scale.ptr && !p.dst_scale.ptr && p.dst_sm % 2 == 0
+            && ((uintptr_t)p.dst & 3) == 0;
+    const size_t chunk_bytes = (size_t)chunk_steps * WC_TILE_BYTES;
+    const size_t slab_bytes = (size_t)2 * WS_WARPS * mb * 32 * sizeof(float4);
+    const size_t budget = (size_t)227 * 1024 - 1024 - slab_bytes - sizeof(ws_ctrl_t);
+    size_t stages = budget / chunk_bytes;
+    if (stages > WS_MAX_STAGES) stages = WS_MAX_STAGES;
+    if (stages < 2) return B200_ERR_UNSUPPORTED;
+    a.stages = (uint32_t)stages;
+    const size_t smem = stages * chunk_bytes + slab_bytes + sizeof(ws_ctrl_t);
+    // opt in to the large dynamic shared memory once per kernel and device
+    static std::mutex mu;
+    static std::vector<std::pair<int, const void *>> done_attr;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    {
+        std::lock_guard<std::mutex> g(mu);
+        bool seen = false;
+        for (auto &e : done_attr) seen |= e.first == dev && e.second == (const void *)kern;
+        if (!seen) {
+            const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+            if (e != cudaSuccess) return (int)e;
+            done_attr.emplace_back(dev, (const void *)kern);
+        }
+    }
+    const unsigned ctas = a.quarters < (uint32_t)sms ? a.quarters : (unsigned)sms;
+    kern<<<ctas, ws_threads(mb), smem, cs>>>(a, p);
+    return after_launch();
 }
 
 // Checks shared by the two entry points; on success the K-group sizes of scales and
@@ -621,11 +1260,21 @@ static int wc_run(const b200_matmul_params_t *p, const uint4 *wei, const __nv_bf
         a.max_segs = (share / a.ups + 2 + 3) / 4 * 4;
         if (a.max_segs > 8192) return B200_ERR_TOO_LARGE;
     }
+    // the streaming form where the shape fits its chunking (ONEDNN_B200_WC_STREAM=0 keeps the per-lane copy form)
+    const char *se = std::getenv("ONEDNN_B200_WC_STREAM");
+    const bool use_stream = !(se && se[0] == '0');
     // activation rows in passes of up to 32 (the weights are re-read from L2)
     for (int64_t m0 = 0; m0 < p->M; m0 += 32) {
         a.m0 = (int)m0;
         const int64_t rows = p->M - m0;
         const int mb = rows <= 8 ? 1 : rows <= 16 ? 2 : 4;
+        if (use_stream) {
+            const int rc = ws_run_pass(a, *p, mb, fold_steps, fastq, sms, cs);
+            if (rc != B200_ERR_UNSUPPORTED) {
+                if (rc) return rc;
+                continue;
+            }
+        }
         const size_t table = (size_t)a.kchunks * mb * 8 * sizeof(float);
         const bool xtab = table <= WC_XTAB_MAX_BYTES;
         const size_t nw = wc_warps(mb);

@@ -51,6 +51,69 @@ def assemble_rows_host(parts) -> np.ndarray:
     return np.concatenate(list(parts), axis=0)
 
 
+SENTINEL = 0xA5  # byte pattern a destination is filled with before a checked execution
+
+
+class MSplitMatmul:
+    """dst rows ``[r*M/g, (r+1)*M/g)`` on rank r: the row shard of ``case`` through the
+    library's primitive, weights replicated, nothing exchanged.  ``self.dst`` is a torch byte
+    tensor ``(M/g, N * elem)`` holding this rank's rows."""
+
+    def __init__(self, case: MatmulCase, rank: int, world: int, device_index: int):
+        import torch
+        from . import api
+        if case.M % world != 0:
+            raise ValueError("M must be a multiple of the number of ranks")
+        self.torch, self.api = torch, api
+        self.rank, self.world, self.case = rank, world, case
+        self.local = m_split(case, rank, world)
+        self.eng = api.Engine(index=device_index)
+        self.tstream = torch.cuda.current_stream()
+        self.strm = api.Stream(self.eng, cuda_stream=self.tstream.cuda_stream)
+        self.elem = np.dtype(dt.RAW[case.dst_dt]).itemsize
+        self.plan = api.CasePlan(self.local, self.eng, self.strm, weights="any")
+        self.dst = torch.empty((self.local.M, case.N * self.elem), dtype=torch.uint8, device="cuda")
+        self.args = dict(self.plan.args)
+        self.args[api.ARG_DST] = api.Memory(self.plan.mds["dst"], self.eng, handle=self.dst.data_ptr())
+        self.rows = slice(rank * self.local.M, (rank + 1) * self.local.M)
+
+    @property
+    def impl(self):
+        return self.plan.impl
+
+    def execute(self):
+        self.plan.prim.execute(self.strm, self.args)
+
+
+def unsharded_on_this_gpu(case: MatmulCase, device_index: int):
+    """The whole problem through the ordinary primitive on this GPU: the yardstick a sharded run
+    must equal byte for byte (every dst element is a function of its own row of src and column
+    of the weights only).  Returns a torch byte tensor ``(M, N * elem)``."""
+    import torch
+    from . import api
+    eng = api.Engine(index=device_index)
+    tstream = torch.cuda.current_stream()
+    strm = api.Stream(eng, cuda_stream=tstream.cuda_stream)
+    elem = np.dtype(dt.RAW[case.dst_dt]).itemsize
+    plan = api.CasePlan(case, eng, strm, weights="any")
+    out = torch.empty((case.M, case.N * elem), dtype=torch.uint8, device="cuda")
+    if case.dst_init is not None:
+        out.copy_(torch.from_numpy(np.ascontiguousarray(case.dst_init).view(np.uint8).reshape(case.M, -1)))
+    args = dict(plan.args)
+    args[api.ARG_DST] = api.Memory(plan.mds["dst"], eng, handle=out.data_ptr())
+    plan.prim.execute(strm, args)
+    strm.wait()
+    return out
+
+
+def count_mismatched_elements(got, want, elem: int) -> int:
+    """Number of dst elements (of ``elem`` bytes) whose bytes differ between two byte tensors."""
+    ne = (got != want)
+    if elem > 1:
+        ne = ne.view(ne.shape[0], -1, elem).any(dim=2)
+    return int(ne.sum().item())
+
+
 class NSplitMatmul:
     """dst = matmul(src, W) with W's columns split over the ranks of ``group``; after
     ``execute()`` every rank holds the full row-major dst in ``self.dst`` (a torch byte

@@ -218,7 +218,12 @@ def test_dispatch_and_next_impl(eng):
     pd = _pd(eng, 1, 4096, 14336, dt.BF16, dt.U4, dt.BF16, wtag=api.TAG_ANY, attr=a)
     assert pd.impl_info_str() == "cuda:sm100:wc_gemv"
     assert pd.weights_desc().get_size() == 4096 * 14336 // 2
-    assert pd.scratchpad_desc().get_size() >= 14336 * 4
+    assert pd.scratchpad_desc().get_size() == 0                # library mode: the user provides nothing
+    mem = C.c_int64()
+    assert api.lib().dnnl_primitive_desc_query(pd.h, 6, 0, C.byref(mem)) == 0   # memory_consumption_s64
+    assert mem.value >= 14336 * 4
+    a.set_scratchpad_mode(1)
+    assert _pd(eng, 1, 4096, 14336, dt.BF16, dt.U4, dt.BF16, wtag=api.TAG_ANY, attr=a).scratchpad_desc().get_size() >= 14336 * 4
     # attr is copied into the pd: later changes do not reach it
     a.set_scales(api.ARG_WEIGHTS, 0)
     md = pd.query_md(api.QUERY_EXEC_ARG_MD, api.ARG_ATTR_SCALES | api.ARG_WEIGHTS)

@@ -101,6 +101,25 @@ def test_gather_columns_kernel():
     assert kernels_abi.lib().b200_gather_columns_launch(st.data_ptr(), dst.data_ptr(), M, 4 * 10, 4, 1, 0) == -1
 
 
+def _checked_n_split(op, case, want_full, dist=None):
+    """Run ``op`` once on a destination filled with a sentinel and count the elements that differ
+    from the unsharded primitive's result on the same GPU; then once more on the already full
+    destination (a store that is skipped the second time would otherwise hide behind the first)."""
+    import torch
+    bad = []
+    for _ in range(2):
+        op.dst.fill_(multi_gpu.SENTINEL)
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()   # nobody's kernel stores into a copy that its owner is still filling
+        op.execute()
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+        bad.append(multi_gpu.count_mismatched_elements(op.dst, want_full, op.elem))
+    return bad
+
+
 def _nccl_rank(rank, world, port, q, mode="nccl"):
     import torch
     import torch.distributed as dist
@@ -109,15 +128,14 @@ def _nccl_rank(rank, world, port, q, mode="nccl"):
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
     try:
         case = W.config4(256, 512, 128, seed=9)
+        want_full = multi_gpu.unsharded_on_this_gpu(case, rank)
         op = multi_gpu.NSplitMatmul(case, rank, world, rank, mode=mode)
-        for _ in range(2):   # twice: the second run overwrites a destination that is already full
-            op.execute()
-        got = op.result()
-        want = ob.run_oracle(case, tanh_mode=1, exact_acc=1)
-        a, b = dt.to_f32(got, case.dst_dt), dt.to_f32(want, case.dst_dt)
-        q.put((rank, op.impl, float(np.abs(a - b).max()), float(np.abs(b).max())))
+        bad = _checked_n_split(op, case, want_full, dist)
+        oracle = ob.run_oracle(case, tanh_mode=1, exact_acc=1)
+        vs_oracle = int((op.result().view(np.uint16) != oracle.view(np.uint16)).sum())
+        q.put((rank, op.impl, op.mode, bad, vs_oracle))
     except Exception as ex:  # the parent must hear about it instead of waiting
-        q.put((rank, "error: %r" % (ex,), float("inf"), 0.0))
+        q.put((rank, "error: %r" % (ex,), mode, [-1], -1))
     finally:
         dist.destroy_process_group()
 
@@ -125,18 +143,21 @@ def _nccl_rank(rank, world, port, q, mode="nccl"):
 @pytest.mark.gpu
 @pytest.mark.parametrize("mode", ["nccl", "p2p"])
 def test_n_split_cuda(mode):
-    """N-split through the library: on two GPUs when the box has them (NCCL all-gather, or
-    slices stored into the peers' copies by the matmul's epilogue), else the same code path
-    with a single rank."""
+    """N-split through the library on two GPUs (NCCL all-gather, or slices stored into the peers'
+    copies by the matmul's epilogue): the assembled dst on every rank equals, byte for byte, what
+    the unsharded primitive gives on that GPU and what the CPU oracle gives.  With one GPU the
+    all-gather path runs with a single rank; the peer-store kernel has its own one-GPU test below."""
     import torch
     world = 2 if torch.cuda.device_count() >= 2 else 1
     if world == 1:
+        if mode == "p2p":
+            pytest.skip("needs two GPUs; test_peer_store_kernel_with_local_mirrors covers the kernel on one")
         case = W.config4(256, 512, 128, seed=9)
         op = multi_gpu.NSplitMatmul(case, 0, 1, 0, mode=mode)
-        op.execute()
-        got = op.result()
+        bad = _checked_n_split(op, case, multi_gpu.unsharded_on_this_gpu(case, 0))
+        assert bad == [0, 0]
         want = ob.run_oracle(case, tanh_mode=1, exact_acc=1)
-        assert np.allclose(dt.to_f32(got, case.dst_dt), dt.to_f32(want, case.dst_dt), rtol=1e-2, atol=1e-2)
+        assert np.array_equal(op.result().view(np.uint16), want.view(np.uint16))
         return
     import torch.multiprocessing as mp
     ctx = mp.get_context("spawn")
@@ -149,5 +170,43 @@ def test_n_split_cuda(mode):
     for p in procs:
         p.join(timeout=60)
         assert p.exitcode == 0
-    for rank, impl, err, mag in out:
-        assert err <= 1e-2 * max(1.0, mag), (rank, impl, err, mag)
+    for rank, impl, ran_as, bad, vs_oracle in out:
+        assert ran_as == mode, (rank, impl, ran_as)
+        assert bad == [0, 0] and vs_oracle == 0, (rank, impl, bad, vs_oracle)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("parts", [2, 4])
+def test_peer_store_kernel_with_local_mirrors(parts):
+    """The kernel variant that also stores every finished block into the other ranks' copies of
+    dst, on ONE GPU: the copies are further buffers on the same device and the ranks' column
+    slices run one after the other.  Every copy must end up equal, byte for byte, to the
+    unsharded primitive's result -- the same check the two-GPU test makes, so the kernel has
+    correctness evidence wherever the tests run."""
+    import torch
+    from onednn_b200 import api
+    case = W.config4(300, 128 * parts, 128, seed=10)   # ragged rows, several tiles per slice
+    eng = api.Engine()
+    ts = torch.cuda.current_stream()
+    strm = api.Stream(eng, cuda_stream=ts.cuda_stream)
+    want = multi_gpu.unsharded_on_this_gpu(case, 0)
+    elem = 2
+    copies = [torch.full((case.M, case.N * elem), multi_gpu.SENTINEL, dtype=torch.uint8, device="cuda") for _ in range(parts)]
+    ns = case.N // parts
+    keep = []
+    for r in range(parts):
+        plan = api.CasePlan(W.shard(case, r, parts, "n"), eng, strm, weights="any", dst_strides=(case.N, 1))
+        assert "tcgen05_i8" in plan.impl
+        off = r * ns * elem
+        args = dict(plan.args)
+        args[api.ARG_DST] = api.Memory(plan.mds["dst"], eng, handle=copies[r].data_ptr() + off)
+        i = 0
+        for o in range(parts):
+            if o != r:
+                args[api.ARG_B200_DST_PEER0 + i] = api.Memory(plan.mds["dst"], eng, handle=copies[o].data_ptr() + off)
+                i += 1
+        plan.prim.execute(strm, args)
+        keep.append((plan, args))
+    strm.wait()
+    for r in range(parts):
+        assert multi_gpu.count_mismatched_elements(copies[r], want, elem) == 0, "copy %d" % r

@@ -240,6 +240,15 @@ enum {
 dnnl_status_t DNNL_API dnnl_b200_debug_fail_allocations(int count);
 dnnl_status_t DNNL_API dnnl_b200_debug_mark_scratchpads_dirty(void);
 dnnl_status_t DNNL_API dnnl_b200_debug_counter(int which, uint64_t *value);
+/* Primitive-cache introspection for test drivers (the reference's driver uses the internal
+ * is_pd_in_cache / is_primitive_in_cache / set_primitive_cache_capacity_without_clearing of
+ * src/common/primitive_cache.hpp; these are their C-ABI forms).  Pass a descriptor or a primitive. */
+dnnl_status_t DNNL_API dnnl_b200_primitive_cache_contains(const_dnnl_primitive_desc_t pd, const_dnnl_primitive_t primitive,
+        int *result);
+dnnl_status_t DNNL_API dnnl_b200_set_primitive_cache_capacity_without_clearing(int capacity);
+/* Device memory of a CUDA engine: total, largest allocation available now, L2 size. */
+dnnl_status_t DNNL_API dnnl_b200_engine_get_memory_info(dnnl_engine_t engine, size_t *total_bytes, size_t *max_alloc_bytes,
+        size_t *l2_bytes);
 
 /* ---- memory descriptors (replaces dnnl.h:826-1200; reference implementation
  *      src/common/memory_desc.cpp, memory_desc_wrapper.hpp) ----------------------- */

@@ -22,8 +22,17 @@
 #include "onednn_b200.h"
 #include "onednn_b200_kernels.h"
 
+// packed_layout value of an opaque descriptor that stands for a blocked layout of another engine
+// (created from a blocked format tag): it can be described, compared and sized, nothing reads it
+#define B200_LAYOUT_FOREIGN 100
+
 namespace b200 {
 
+// a data type a memory descriptor may carry (the whole enum of the reference); which of them a
+// primitive here computes with is dt_valid below
+inline bool dt_known(int dt) {
+    return dt >= dnnl_f16 && dt <= dnnl_f4_e3m0;
+}
 inline bool dt_valid(int dt) {
     switch (dt) {
         case dnnl_f16: case dnnl_bf16: case dnnl_f32: case dnnl_s32: case dnnl_s8: case dnnl_u8:
@@ -86,9 +95,10 @@ struct dnnl_memory_desc {
 struct dnnl_engine {
     dnnl_engine_kind_t kind = dnnl_gpu;
     int device = -1; // CUDA ordinal; -1 = descriptor-only engine (no device present)
+    bool host = false; // the dnnl_cpu engine: host memory and reorders only (host_engine.cpp)
     std::atomic<int> refs {1};
     int sm_major = 0, sm_minor = 0, sm_count = 0;
-    bool usable() const { return device >= 0; }
+    bool usable() const { return host || device >= 0; }
 };
 
 struct dnnl_stream {
@@ -228,6 +238,11 @@ dnnl_status_t matmul_validate(const dnnl_memory_desc &src, const dnnl_memory_des
 dnnl_status_t matmul_select_impl(dnnl_primitive_desc *pd, int first);
 dnnl_status_t matmul_execute(const dnnl_primitive *prim, dnnl_stream *stream, const std::map<int, dnnl_memory *> &args);
 dnnl_status_t reorder_execute(const dnnl_primitive *prim, dnnl_stream *stream, const std::map<int, dnnl_memory *> &args);
+// ---- host engine (host_engine.cpp) ----
+dnnl_status_t host_reorder_pd_create(dnnl_primitive_desc_t *out, const dnnl_memory_desc &s, dnnl_engine *se,
+        const dnnl_memory_desc &d, dnnl_engine *de, const dnnl_primitive_attr *attr);
+dnnl_status_t host_reorder_execute(const dnnl_primitive *prim, dnnl_stream *stream, const dnnl_memory *from,
+        const dnnl_memory *to);
 dnnl_status_t inner_product_execute(const dnnl_primitive *prim, dnnl_stream *stream, const std::map<int, dnnl_memory *> &args);
 
 // ---- verbose (service.cpp) ----

@@ -61,7 +61,8 @@ dnnl_status_t matmul_validate(const dnnl_memory_desc &src, const dnnl_memory_des
     const bool src_int8 = dt_is_int8(sdt), src_fp8 = dt_is_fp8(sdt);
     const bool wei_int = dt_is_int8(wdt) || dt_is_int4(wdt);
     const bool src_fp = sdt == dnnl_f32 || sdt == dnnl_bf16 || sdt == dnnl_f16;
-    INVALID_IF(!dt_valid(sdt) || !dt_valid(wdt) || !dt_valid(ddt));
+    INVALID_IF(!dt_known(sdt) || !dt_known(wdt) || !dt_known(ddt));
+    UNIMPL_IF(!dt_valid(sdt) || !dt_valid(wdt) || !dt_valid(ddt)); // f64, e8m0, f4: descriptors only
     INVALID_IF(!(src_int8 || src_fp8 || src_fp));
 
     // ---- attribute rules ----
@@ -607,6 +608,14 @@ static dnnl_status_t runtime_execute(const dnnl_primitive *prim, dnnl_stream *st
 
 dnnl_status_t matmul_select_impl(dnnl_primitive_desc *pd, int first) {
     if (pd->runtime) return dnnl_last_impl_reached; // nothing to iterate over before the sizes are known
+    // layouts of other engines (blocked tags such as AB16b16a arrive as opaque descriptors that only
+    // record the tag was foreign): no implementation here reads them
+    for (const dnnl_memory_desc *md : {&pd->user_src, &pd->user_wei, &pd->user_bias, &pd->user_dst})
+        if (md->format_kind == dnnl_format_kind_opaque && md->packed_layout == B200_LAYOUT_FOREIGN)
+            return first == 0 ? dnnl_unimplemented : dnnl_last_impl_reached;
+    if (pd->user_src.format_kind == dnnl_format_kind_opaque || pd->user_dst.format_kind == dnnl_format_kind_opaque
+            || pd->user_bias.format_kind == dnnl_format_kind_opaque)
+        return first == 0 ? dnnl_unimplemented : dnnl_last_impl_reached;
     if (pd->user_dst.ndims > 2) return select_batched(pd, first);
     for (int id = first; id <= IMPL_GENERIC; ++id) {
         bool ok = false;
@@ -851,12 +860,17 @@ dnnl_status_t dnnl_matmul_primitive_desc_create(dnnl_primitive_desc_t *primitive
     const dnnl_primitive_attr &a = attr ? *attr : default_attr;
     dnnl_status_t st = matmul_validate(*src_desc, *weights_desc, bias_desc, *dst_desc, a);
     if (st != dnnl_success) return st;
+    if (engine->host) return dnnl_unimplemented; // the host engine holds memory and reorders; it computes nothing
     const bool runtime = src_desc->has_runtime_dims() || weights_desc->has_runtime_dims() || dst_desc->has_runtime_dims()
             || (bias_desc && bias_desc->has_runtime_dims());
     auto pd = std::unique_ptr<dnnl_primitive_desc>(new dnnl_primitive_desc());
     pd->kind = dnnl_matmul;
     pd->engine = engine;
     pd->attr = a; // copied: later changes to the caller's attr have no effect
+    // a binary post-op operand left to the implementation (format_tag::any) is dense row-major here;
+    // the resolved descriptor is what dnnl_query_exec_arg_md returns for it
+    for (auto &e : pd->attr.post_ops.entries)
+        if (e.kind == dnnl_binary && e.src1.is_any() && !e.src1.has_runtime_dims()) make_plain(e.src1);
     pd->user_src = *src_desc;
     pd->user_wei = *weights_desc;
     if (bias_desc) pd->user_bias = *bias_desc;
@@ -865,13 +879,15 @@ dnnl_status_t dnnl_matmul_primitive_desc_create(dnnl_primitive_desc_t *primitive
         // Sizes known only at execution (DNNL_RUNTIME_DIM_VAL, src/common/matmul.cpp:374-401):
         // nothing can be dispatched yet.  Layouts must be given (no format_tag::any); the
         // implementation is selected per execution from the memory arguments' descriptors.
-        if (src_desc->is_any() || weights_desc->is_any() || dst_desc->is_any() || (bias_desc && bias_desc->is_any()))
-            return dnnl_unimplemented;
+        if (src_desc->is_any() || weights_desc->is_any() || dst_desc->is_any()) return dnnl_unimplemented;
+        // a bias of known size may be left to the implementation: dense row-major
+        if (bias_desc && bias_desc->is_any() && bias_desc->has_runtime_dims()) return dnnl_unimplemented;
         if (a.scratchpad_mode == dnnl_scratchpad_mode_user) return dnnl_unimplemented; // its size is not known here
         pd->src = pd->user_src;
         pd->wei = pd->user_wei;
         pd->dst = pd->user_dst;
         pd->bias = pd->user_bias;
+        if (pd->bias.is_any()) make_plain(pd->bias);
         pd->impl = IMPL_GENERIC;
         pd->impl_str = "cuda:runtime_dims";
         pd->runtime = true;
@@ -897,6 +913,7 @@ dnnl_status_t dnnl_inner_product_forward_primitive_desc_create(dnnl_primitive_de
         const_dnnl_memory_desc_t bias_desc, const_dnnl_memory_desc_t dst_desc, const_dnnl_primitive_attr_t attr) {
     if (!primitive_desc || !engine || !src_desc || !weights_desc || !dst_desc) return dnnl_invalid_arguments;
     if (prop_kind != dnnl_forward_training && prop_kind != dnnl_forward_inference) return dnnl_invalid_arguments;
+    if (engine->host) return dnnl_unimplemented;
     const dnnl_memory_desc &s = *src_desc, &w = *weights_desc, &d = *dst_desc;
     if (s.ndims != w.ndims || d.ndims != 2) return dnnl_invalid_arguments;
     if (s.ndims != 2) return dnnl_unimplemented; // spatial dims: not on this path

@@ -10,6 +10,8 @@
 #include <algorithm>
 #include <cstdio>
 
+#include <cstdlib>
+
 #include "internal.hpp"
 
 using namespace b200;
@@ -37,6 +39,11 @@ const char *dt_name(int dt) {
 size_t dnnl_memory_desc::size_bytes() const {
     if (ndims == 0 || is_any() || has_runtime_dims()) return 0;
     if (has_zero_dim()) return 0;
+    if (format_kind == dnnl_format_kind_opaque && packed_layout == B200_LAYOUT_FOREIGN) {
+        int64_t n = 1; // an upper bound: every dim padded to a multiple of 64
+        for (int i = 0; i < ndims; ++i) n *= (dims[i] + 63) / 64 * 64;
+        return (size_t)((n * dt_nbits(data_type) + 7) / 8);
+    }
     if (format_kind == dnnl_format_kind_opaque)
         return b200_packed_weights_bytes(dims[ndims - 2], dims[ndims - 1], data_type, packed_layout);
     int64_t span = 1;
@@ -97,7 +104,7 @@ static dnnl_status_t check_dims(int ndims, const dnnl_dims_t dims, dnnl_data_typ
     if (ndims < 0 || ndims > DNNL_MAX_NDIMS) return dnnl_invalid_arguments;
     if (ndims == 0) return dnnl_success;
     if (!dims) return dnnl_invalid_arguments;
-    if (!dt_valid(dt)) return dnnl_invalid_arguments;
+    if (!dt_known(dt)) return dnnl_invalid_arguments;
     for (int i = 0; i < ndims; ++i)
         if (dims[i] < 0 && dims[i] != DNNL_RUNTIME_DIM_VAL) return dnnl_invalid_arguments;
     return dnnl_success;
@@ -196,10 +203,13 @@ dnnl_status_t dnnl_memory_desc_create_with_tag(dnnl_memory_desc_t *memory_desc, 
     if ((int)order.size() != ndims) return dnnl_invalid_arguments;
     dnnl_dims_t strides;
     int64_t s = 1;
+    // a stride that depends on a dim known only at execution is itself known only then
+    // (reference: memory_desc_init_by_tag with runtime dims, src/common/memory_desc.cpp)
+    bool rt = false;
     for (int j = ndims - 1; j >= 0; --j) {
-        if (dims[order[j]] == DNNL_RUNTIME_DIM_VAL) return dnnl_unimplemented;
-        strides[order[j]] = s;
-        s *= std::max<int64_t>(dims[order[j]], 1);
+        strides[order[j]] = rt ? DNNL_RUNTIME_DIM_VAL : s;
+        if (dims[order[j]] == DNNL_RUNTIME_DIM_VAL) rt = true;
+        else s *= std::max<int64_t>(dims[order[j]], 1);
     }
     return dnnl_memory_desc_create_with_strides(memory_desc, ndims, dims, data_type, strides);
 }
@@ -332,7 +342,11 @@ dnnl_status_t dnnl_memory_create(dnnl_memory_t *memory, const_dnnl_memory_desc_t
     auto m = std::unique_ptr<dnnl_memory>(new dnnl_memory());
     m->md = *md;
     m->engine = engine;
-    if (handle == DNNL_MEMORY_ALLOCATE) {
+    if (handle == DNNL_MEMORY_ALLOCATE && engine->host) {
+        const size_t bytes = md->size_bytes();
+        if (bytes && !(m->handle = std::aligned_alloc(64, (bytes + 63) / 64 * 64))) return dnnl_out_of_memory;
+        m->owned = true;
+    } else if (handle == DNNL_MEMORY_ALLOCATE) {
         if (set_device(engine) != dnnl_success) return dnnl_runtime_error;
         const size_t bytes = md->size_bytes();
         if (bytes) {
@@ -371,6 +385,10 @@ dnnl_status_t dnnl_memory_map_data(const_dnnl_memory_t cmem, void **mapped_ptr) 
         *mapped_ptr = nullptr;
         return dnnl_success;
     }
+    if (mem->engine->host) { // host memory is its own mapping
+        *mapped_ptr = mem->handle;
+        return dnnl_success;
+    }
     if (set_device(mem->engine) != dnnl_success) return dnnl_runtime_error;
     void *host = nullptr;
     if (pinned_alloc(&host, bytes) != cudaSuccess) return dnnl_out_of_memory;
@@ -390,6 +408,7 @@ dnnl_status_t dnnl_memory_map_data(const_dnnl_memory_t cmem, void **mapped_ptr) 
 dnnl_status_t dnnl_memory_unmap_data(const_dnnl_memory_t cmem, void *mapped_ptr) {
     if (!cmem) return dnnl_invalid_arguments;
     dnnl_memory *mem = const_cast<dnnl_memory *>(cmem);
+    if (mem->engine->host) return dnnl_success;
     if (!mem->mapped) return mapped_ptr ? dnnl_invalid_arguments : dnnl_success;
     if (mapped_ptr != mem->mapped) return dnnl_invalid_arguments;
     if (set_device(mem->engine) != dnnl_success) return dnnl_runtime_error;
@@ -410,8 +429,12 @@ dnnl_status_t dnnl_memory_get_data_handle(const_dnnl_memory_t memory, void **han
 dnnl_status_t dnnl_memory_set_data_handle(dnnl_memory_t memory, void *handle) {
     if (!memory) return dnnl_invalid_arguments;
     if (memory->owned && memory->handle) {
-        cudaSetDevice(memory->engine->device);
-        cudaFree(memory->handle);
+        if (memory->engine->host) {
+            std::free(memory->handle);
+        } else {
+            cudaSetDevice(memory->engine->device);
+            cudaFree(memory->handle);
+        }
     }
     memory->owned = false;
     memory->handle = handle;
@@ -419,8 +442,10 @@ dnnl_status_t dnnl_memory_set_data_handle(dnnl_memory_t memory, void *handle) {
 }
 
 dnnl_status_t dnnl_memory_destroy(dnnl_memory_t memory) {
-    if (!memory) return dnnl_invalid_arguments;
-    if (memory->engine->usable()) {
+    if (!memory) return dnnl_success; // like delete: nothing to do
+    if (memory->engine->host) {
+        if (memory->owned && memory->handle) std::free(memory->handle);
+    } else if (memory->engine->usable()) {
         cudaSetDevice(memory->engine->device);
         if (memory->mapped) cudaFreeHost(memory->mapped);
         if (memory->owned && memory->handle) cudaFree(memory->handle);

@@ -7,6 +7,8 @@
 
 #include <list>
 
+#include <iterator>
+
 #include "internal.hpp"
 
 using namespace b200;
@@ -64,13 +66,15 @@ dnnl_status_t dnnl_reorder_primitive_desc_create(dnnl_primitive_desc_t *reorder_
         const_dnnl_memory_desc_t src_desc, dnnl_engine_t src_engine, const_dnnl_memory_desc_t dst_desc,
         dnnl_engine_t dst_engine, const_dnnl_primitive_attr_t attr) {
     if (!reorder_primitive_desc || !src_desc || !dst_desc || !src_engine || !dst_engine) return dnnl_invalid_arguments;
-    if (src_engine != dst_engine && src_engine->device != dst_engine->device) return dnnl_unimplemented;
+    const bool with_host = src_engine->host || dst_engine->host;
+    if (!with_host && src_engine != dst_engine && src_engine->device != dst_engine->device) return dnnl_unimplemented;
     const dnnl_memory_desc &s = *src_desc, &d = *dst_desc;
     if (s.is_any() || d.is_any()) return dnnl_invalid_arguments;
     if (s.ndims != d.ndims) return dnnl_invalid_arguments;
     for (int i = 0; i < s.ndims; ++i)
         if (s.dims[i] != d.dims[i]) return dnnl_invalid_arguments;
     if (s.has_runtime_dims()) return dnnl_unimplemented;
+    if (with_host) return host_reorder_pd_create(reorder_primitive_desc, s, src_engine, d, dst_engine, attr);
     const bool quantising = attr && (!attr->scales.empty() || !attr->zero_points.empty() || !attr->post_ops.entries.empty());
     if (quantising) {
         const dnnl_status_t st = reorder_quant_validate(s, d, *attr);
@@ -167,6 +171,7 @@ dnnl_status_t reorder_execute(const dnnl_primitive *prim, dnnl_stream *stream, c
     const dnnl_memory *from = f->second, *to = t->second;
     if (pd->src.has_zero_dim()) return dnnl_success;
     if (!from->handle || !to->handle) return dnnl_invalid_arguments;
+    if (pd->impl_str.compare(0, 5, "host:") == 0) return host_reorder_execute(prim, stream, from, to);
     const dnnl_memory_desc &s = pd->src, &d = pd->dst;
     if (pd->impl_str == "cuda:reorder_quant") return reorder_quant_execute(pd, stream, from, to, args);
     b200_reorder_params_t r;
@@ -470,6 +475,30 @@ dnnl_status_t dnnl_set_primitive_cache_capacity(int capacity) {
     return dnnl_success;
 }
 
+// Is the descriptor (or the one a primitive was made from) an entry of the primitive cache?
+// What the reference's test driver asks through its internal is_pd_in_cache /
+// is_primitive_in_cache (src/common/primitive_cache.hpp), offered here over the C ABI.
+dnnl_status_t dnnl_b200_primitive_cache_contains(const_dnnl_primitive_desc_t pd, const_dnnl_primitive_t primitive,
+        int *result) {
+    if (!result || (!pd && !primitive)) return dnnl_invalid_arguments;
+    const dnnl_primitive_desc *d = pd ? pd : primitive->pd.get();
+    std::lock_guard<std::mutex> g(g_cache_mu);
+    const std::string key = make_key(d);
+    *result = 0;
+    for (const auto &e : g_cache)
+        if (e.first == key) *result = 1;
+    return dnnl_success;
+}
+
+// the capacity changed without dropping entries above it (the driver's cache-hit checks)
+dnnl_status_t dnnl_b200_set_primitive_cache_capacity_without_clearing(int capacity) {
+    if (capacity < 0) return dnnl_invalid_arguments;
+    std::lock_guard<std::mutex> g(g_cache_mu);
+    (void)cache_capacity_locked();
+    g_cache_capacity = capacity;
+    return dnnl_success;
+}
+
 // ---- primitive API -----------------------------------------------------------------------
 
 dnnl_status_t dnnl_primitive_create(dnnl_primitive_t *primitive, const_dnnl_primitive_desc_t pd) {
@@ -529,14 +558,19 @@ dnnl_status_t dnnl_primitive_execute(const_dnnl_primitive_t primitive, dnnl_stre
     if (!primitive || !stream) return dnnl_invalid_arguments;
     if (nargs < 0 || (nargs > 0 && !args)) return dnnl_invalid_arguments;
     const dnnl_primitive_desc *pd = primitive->pd.get();
-    if (stream->engine != pd->engine && stream->engine->device != pd->engine->device) return dnnl_invalid_arguments;
+    const bool host_reorder = pd->kind == dnnl_reorder && pd->impl_str.compare(0, 5, "host:") == 0;
+    if (!host_reorder && stream->engine != pd->engine && stream->engine->device != pd->engine->device) return dnnl_invalid_arguments;
     std::map<int, dnnl_memory *> m;
     for (int i = 0; i < nargs; ++i) {
-        if (!args[i].memory) return dnnl_invalid_arguments;
         if (m.count(args[i].arg)) return dnnl_invalid_arguments; // the same argument twice
-        if (args[i].memory->engine->device != pd->engine->device) return dnnl_invalid_arguments;
+        if (!args[i].memory) { // an argument given without a memory object counts as not given
+            m[args[i].arg] = nullptr;
+            continue;
+        }
+        if (!host_reorder && args[i].memory->engine->device != pd->engine->device) return dnnl_invalid_arguments;
         m[args[i].arg] = args[i].memory;
     }
+    for (auto it = m.begin(); it != m.end();) it = it->second ? std::next(it) : m.erase(it);
     if (set_device(pd->engine) != dnnl_success) return dnnl_runtime_error;
 
     const bool timed = verbose_level() >= 1;

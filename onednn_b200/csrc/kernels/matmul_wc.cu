@@ -1140,6 +1140,10 @@ static int ws_run_pass(const wc_args_t &w, const b200_matmul_params_t &p, int mb
     a.strips = (uint32_t)(w.N / WC_TILE_N);
     const uint32_t chunk_steps = (uint32_t)(WS_WARPS * tpw);
     a.parts = w.kchunks / chunk_steps;
+    // Several K parts per strip send every strip's sums through the global scratch (atomics, a
+    // fence and a counter round trip per chunk on one epilogue warp): measured several times slower
+    // than the per-lane copy form, which is therefore kept for those shapes.
+    if (a.parts != 1) return B200_ERR_UNSUPPORTED;
     const uint64_t quarters = (uint64_t)a.strips * a.parts * 4;
     if (quarters >= ((uint64_t)1 << 31)) return B200_ERR_TOO_LARGE;
     a.quarters = (uint32_t)quarters;

@@ -46,11 +46,95 @@ def test_version_and_engine_kinds():
                     ("cpu_runtime", C.c_uint), ("gpu_runtime", C.c_uint)]
     v = V.from_address(L.dnnl_version())
     assert (v.major, v.minor) == (3, 8) and v.cpu_runtime == 0
-    # there is no CPU engine: no fallback path exists
+    # the CPU engine holds host memory and reorders for the callers either side of the matmul; it
+    # computes nothing, so no fallback path exists
+    assert api.Engine.get_count(1) == 1
+    cpu = api.Engine(kind=1)
     with pytest.raises(api.Error) as e:
-        api.Engine(kind=1)
+        api.Engine(kind=1, index=1)
     assert e.value.name == "invalid_arguments"
-    assert api.Engine.get_count(1) == 0
+    md = api.MemoryDesc((8, 16), dt.S8, api.TAG_AB)
+    with pytest.raises(api.Error) as e:
+        api.matmul_primitive_desc(cpu, md, api.MemoryDesc((16, 8), dt.S8, api.TAG_AB), api.MemoryDesc((8, 8), dt.S32, api.TAG_AB))
+    assert e.value.name == "unimplemented"
+
+
+def _host_mem(cpu, a, dtype, tag=None, strides=None):
+    md = api.MemoryDesc(a.shape, dtype, tag, strides=strides) if strides else api.MemoryDesc(a.shape, dtype, tag)
+    m = api.Memory(md, cpu)
+    p = C.c_void_p()
+    assert api.lib().dnnl_memory_map_data(m.h, C.byref(p)) == 0
+    return md, m, p
+
+
+def test_host_engine_reorders_convert_like_the_reference():
+    """f32 -> every integer / float type on the host engine: saturate, round to nearest even,
+    bf16 with one rounding, 4-bit values packed two per byte (even index in the low nibble),
+    transposed and strided destinations; and back to f32."""
+    import numpy as np
+    L = api.lib()
+    cpu = api.Engine(kind=1)
+    strm = api.Stream(cpu)
+    a = np.array([[-200.5, -3.5, -2.5, -0.5, 0.5, 1.5], [2.5, 7.49, 7.5, 15.5, 127.5, 300.0]], dtype=np.float32)
+    smd, src, sp = _host_mem(cpu, a, dt.F32, api.TAG_AB)
+    C.memmove(sp, a.ctypes.data, a.nbytes)
+
+    def run(dst_dt, tag=api.TAG_AB, strides=None):
+        dmd, dst, dp = _host_mem(cpu, a, dst_dt, tag, strides)
+        pd = api.reorder_primitive_desc(cpu, smd, cpu, dmd)
+        assert pd.impl_info_str() == "host:reorder"
+        api.Primitive(pd).execute(strm, {api.ARG_FROM: src, api.ARG_TO: dst})
+        strm.wait()
+        return dmd, dst, dp
+
+    _, _, p = run(dt.S8)
+    got = np.ctypeslib.as_array(C.cast(p, C.POINTER(C.c_int8)), a.shape)
+    assert np.array_equal(got, np.clip(np.rint(a), -128, 127).astype(np.int8))
+    _, _, p = run(dt.U8, api.TAG_BA)
+    got = np.ctypeslib.as_array(C.cast(p, C.POINTER(C.c_uint8)), a.shape[::-1]).T
+    assert np.array_equal(got, np.clip(np.rint(a), 0, 255).astype(np.uint8))
+    _, _, p = run(dt.BF16)
+    got = np.ctypeslib.as_array(C.cast(p, C.POINTER(C.c_uint16)), a.shape)
+    assert np.array_equal(got, dt.f32_to_bf16(a))
+    _, _, p = run(dt.U4)
+    got = np.ctypeslib.as_array(C.cast(p, C.POINTER(C.c_uint8)), (a.size // 2,))
+    want = np.clip(np.rint(a), 0, 15).astype(np.uint8).reshape(-1)
+    assert np.array_equal(got, want[0::2] | (want[1::2] << 4))
+    _, _, p = run(dt.S4)
+    got = np.ctypeslib.as_array(C.cast(p, C.POINTER(C.c_uint8)), (a.size // 2,))
+    want = (np.clip(np.rint(a), -8, 7).astype(np.int8).reshape(-1) & 0xF).astype(np.uint8)
+    assert np.array_equal(got, want[0::2] | (want[1::2] << 4))
+    # s32 with a row pitch of 8 elements, then back to dense f32
+    dmd, dst, p = run(dt.S32, strides=(8, 1))
+    got = np.ctypeslib.as_array(C.cast(p, C.POINTER(C.c_int32)), (2, 8))[:, :6]
+    assert np.array_equal(got, np.rint(a).astype(np.int32))
+    bmd, back, bp = _host_mem(cpu, a, dt.F32, api.TAG_AB)
+    api.Primitive(api.reorder_primitive_desc(cpu, dmd, cpu, bmd)).execute(strm, {api.ARG_FROM: dst, api.ARG_TO: back})
+    assert np.array_equal(np.ctypeslib.as_array(C.cast(bp, C.POINTER(C.c_float)), a.shape), np.rint(a))
+    # quantising reorders stay with the CUDA engine
+    attr = api.PrimitiveAttr()
+    attr.set_scales(api.ARG_DST, 0)
+    with pytest.raises(api.Error) as e:
+        api.reorder_primitive_desc(cpu, smd, cpu, api.MemoryDesc(a.shape, dt.S8, api.TAG_AB), attr)
+    assert e.value.name == "unimplemented"
+
+
+def test_string_tags_and_runtime_strides():
+    L = api.lib()
+    md = C.c_void_p()
+    dims = (C.c_int64 * 12)(2, 3, 5)
+    assert L.dnnl_memory_desc_create_with_string_tag(C.byref(md), 3, dims, dt.F32, b"acb") == 0
+    m = api.MemoryDesc(handle=md.value)
+    assert m.strides == [15, 1, 3]
+    assert L.dnnl_memory_desc_create_with_string_tag(C.byref(md), 3, dims, dt.F32, b"aBc16b") == 3      # blocked: other engines
+    assert L.dnnl_memory_desc_create_with_string_tag(C.byref(md), 3, dims, dt.F32, b"abb") == 2
+    # a stride that depends on a runtime dim is a runtime value
+    RT = -(2 ** 63)
+    dims = (C.c_int64 * 12)(4, RT)
+    assert L.dnnl_memory_desc_create_with_string_tag(C.byref(md), 2, dims, dt.S8, b"ab") == 0
+    assert api.MemoryDesc(handle=md.value).strides == [RT, 1]
+    assert L.dnnl_memory_desc_create_with_string_tag(C.byref(md), 2, dims, dt.S8, b"ba") == 0
+    assert api.MemoryDesc(handle=md.value).strides == [1, 4]
 
 
 @pytest.fixture(scope="module")

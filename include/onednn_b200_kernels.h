@@ -170,10 +170,12 @@ B200_API int b200_matmul_wc_launch(const b200_matmul_params_t *p, b200_stream_t 
  * and dst are still passed in by the caller (p->scratch is ignored).
  *
  * Limits: bf16 activations (src_dt == B200_DT_BF16), weights already in
- * B200_WEI_WC4_TILED layout, and M * N * 4 bytes must fit the array
- * (b200_matmul_wc_noalloc_max_bytes(), i.e. M * N <= 524288); anything larger
- * returns B200_ERR_TOO_LARGE, anything else unsupported B200_ERR_UNSUPPORTED,
- * and nothing is launched.
+ * B200_WEI_WC4_TILED layout, and the partial sums plus the per-strip counters
+ * must fit the array: M * N * 4 bytes rounded up to 256, plus N / 16 * 4 bytes
+ * rounded up to 256, at most b200_matmul_wc_noalloc_max_bytes() (2 MiB) -- for
+ * N = 14336 that is M <= 36, and M * N = 524288 itself does not fit because the
+ * counters share the array.  Anything larger returns B200_ERR_TOO_LARGE,
+ * anything else unsupported B200_ERR_UNSUPPORTED, and nothing is launched.
  *
  * The first call on a device looks up the array's device address
  * (cudaGetSymbolAddress) with that device current; make that first call before
@@ -278,6 +280,14 @@ B200_API int b200_gather_columns_launch(const void *staged, void *dst, int64_t M
  * B200_STATUS_SELFTEST_WAIT into *status and returns.  The context stays usable. */
 #define B200_STATUS_SELFTEST_WAIT 0x80000000u
 B200_API int b200_selftest_bounded_wait_launch(uint32_t *status, uint32_t max_polls, b200_stream_t stream);
+
+/* The tensor-pipe peak as measured with this library's own instruction: one CTA per SM issues
+ * `iters` groups of four tcgen05.mma (kind::i8, or kind::f8f6f4 when fp8 != 0; 128 x 256 x 32 each)
+ * on operands resident in shared memory -- no copies, no epilogue.  The caller times the launch
+ * with CUDA events; *ops_out receives the operations it performs (2 x MACs).  The denominator the
+ * dense kernels' roofline fraction can be quoted against besides the bf16-derived proxy.  No
+ * counterpart in the reference. */
+B200_API int b200_tc8_mma_peak_launch(int32_t fp8, uint32_t iters, uint32_t *status, uint64_t *ops_out, b200_stream_t stream);
 
 /* number of kernel launches issued by this library since load (for benchmarks) */
 B200_API uint64_t b200_launch_count(void);

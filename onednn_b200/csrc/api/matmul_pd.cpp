@@ -454,6 +454,12 @@ static dnnl_status_t select_batched(dnnl_primitive_desc *pd, int first) {
     in->user_wei = slice_2d(pd->user_wei); // weights given as `any` stay plain: packing is per 2-D matrix
     in->user_dst = slice_2d(pd->user_dst);
     if (pd->user_bias.ndims) in->user_bias = slice_2d(pd->user_bias);
+    // every batch index must start a 4-bit tensor on a byte: the 2-D slices are addressed by pointer
+    for (const dnnl_memory_desc *md : {&pd->user_src, &pd->user_wei, &pd->user_dst}) {
+        if (dt_nbits(md->data_type) != 4 || !md->is_plain()) continue;
+        for (int d = 0; d < nb; ++d)
+            if (md->dims[d] > 1 && (md->strides[d] & 1)) return first == 0 ? dnnl_unimplemented : dnnl_last_impl_reached;
+    }
     const dnnl_status_t st = matmul_select_impl(in.get(), first);
     if (st != dnnl_success) return st;
     pd->src = pd->user_src;

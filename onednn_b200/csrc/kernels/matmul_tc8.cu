@@ -1017,6 +1017,60 @@ __global__ void __launch_bounds__(640, 1) matmul_tc8_kernel(const __grid_constan
     }
 }
 
+// ---- measured tensor-pipe peak -------------------------------------------------------------
+//
+// The denominator of the dense kernels' roofline: how fast this GPU's tensor cores run the very
+// instruction the kernel above issues (tcgen05.mma cta_group::1, kind::i8 or kind::f8f6f4,
+// 128 x 256 x 32) when nothing else is in the way -- operands resident in shared memory (whatever
+// bytes are there: the arithmetic does not depend on the values), no copies, no epilogue.  One CTA
+// per SM, one thread issues `iters` groups of four MMAs over two operand stages and two accumulators
+// and commits after each group; the kernel ends when the last commit has arrived.  Timed by
+// the caller with CUDA events; ops = 2 * 128 * 256 * 32 * 4 * iters * CTAs.
+template <bool FP8>
+__global__ void __launch_bounds__(128, 1) tc8_mma_peak_kernel(uint32_t iters, uint32_t idesc, uint32_t *status) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    __shared__ uint64_t done_bar;
+    __shared__ uint32_t tmem_base_s;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        mbar_init(&done_bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "r"(TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = tmem_base_s;
+    if (warp == 0 && lane == 0) {
+        const uint64_t adesc0 = make_smem_desc(smem_u32(smem)), bdesc0 = make_smem_desc(smem_u32(smem) + A_BYTES);
+        for (uint32_t it = 0; it < iters; ++it) {
+            const uint32_t s = it & 1;
+            const uint64_t adesc = adesc0 + (uint64_t)(s * (STAGE_BYTES >> 4)), bdesc = bdesc0 + (uint64_t)(s * (STAGE_BYTES >> 4));
+#pragma unroll
+            for (int k = 0; k < BK / 32; ++k) tcgen05_mma<FP8>(tmem_base + s * BN, adesc + 2 * k, bdesc + 2 * k, idesc, (it > 1) || k != 0);
+        }
+        tcgen05_commit(&done_bar);
+        // bounded like every wait here: a few seconds at most
+        bool ok = false;
+        for (uint32_t i = 0; i < (1u << 26) && !ok; ++i) {
+            ok = mbar_test(&done_bar, 0);
+            if (!ok) __nanosleep(64);
+        }
+        if (!ok && status) atomicOr(status, ST_WAIT_TMEM_FULL);
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 0) {
+        tcgen05_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
 // ---- host side ------------------------------------------------------------------------------
 
 typedef CUresult (*encode_tiled_fn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
@@ -1071,6 +1125,20 @@ static uint32_t make_idesc(bool fp8, int a_dt, int b_dt, int n, int m) {
 } // namespace b200
 
 using namespace b200;
+
+extern "C" int b200_tc8_mma_peak_launch(int32_t fp8, uint32_t iters, uint32_t *status, uint64_t *ops_out, b200_stream_t stream) {
+    if (iters == 0 || iters > (1u << 20)) return B200_ERR_BAD_ARG;
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const size_t smem = 1024 + 2 * (size_t)STAGE_BYTES;
+    const uint32_t idesc = make_idesc(fp8 != 0, fp8 ? B200_DT_F8_E4M3 : B200_DT_S8, fp8 ? B200_DT_F8_E4M3 : B200_DT_S8, BN, BM);
+    auto kern = fp8 ? tc8_mma_peak_kernel<true> : tc8_mma_peak_kernel<false>;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return (int)cudaGetLastError();
+    kern<<<sms, 128, smem, (cudaStream_t)stream>>>(iters, idesc, status);
+    if (ops_out) *ops_out = (uint64_t)2 * BM * BN * 32 * (BK / 32) * iters * (uint64_t)sms;
+    return after_launch();
+}
 
 extern "C" int b200_matmul_tc8_launch(const b200_matmul_params_t *p, b200_stream_t stream) {
     if (!p || !p->src || !p->wei || !p->dst) return B200_ERR_BAD_ARG;

@@ -62,4 +62,6 @@ def lib():
         getattr(L, name).restype = C.c_int
     L.b200_wc_pack_launch.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int32, C.c_void_p]
     L.b200_wc_pack_launch.restype = C.c_int
+    L.b200_tc8_mma_peak_launch.argtypes = [C.c_int32, C.c_uint32, C.c_void_p, C.POINTER(C.c_uint64), C.c_void_p]
+    L.b200_tc8_mma_peak_launch.restype = C.c_int
     return L

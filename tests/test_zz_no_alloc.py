@@ -87,6 +87,22 @@ def test_no_alloc_entry_point_rejects_what_does_not_fit():
     p = _params(case, buf, buf, buf, buf, buf, None)
     p.M, p.N = 64, limit // 4 // 64 + 16          # M * N * 4 bytes just over the array
     assert L.b200_matmul_wc_noalloc_launch(C.byref(p), None) == K.ERR_TOO_LARGE
+    # exactly at the boundary: the partial sums (rounded up to 256 bytes) and the strip counters
+    # (N / 16 words, rounded up to 256 bytes) share the array
+    N = 1024
+    counters = (N // 16 * 4 + 255) // 256 * 256
+    rows_fit = (limit - counters) // (N * 4)
+    x = torch.zeros(rows_fit + 1, 128, dtype=torch.bfloat16, device=dev)
+    w = torch.zeros(128 * N // 2, dtype=torch.uint8, device=dev)
+    sz = torch.zeros(N, dtype=torch.bfloat16, device=dev)
+    out = torch.zeros((rows_fit + 1) * N, dtype=torch.bfloat16, device=dev)
+    edge = W.config2(1, N=N, K=128)
+    for rows, want in ((rows_fit, 0), (rows_fit + 1, K.ERR_TOO_LARGE)):
+        p = _params(edge, x, w, sz, w, out, None)
+        p.M = rows
+        assert (rows * N * 4 + 255) // 256 * 256 + counters <= limit or want != 0
+        assert L.b200_matmul_wc_noalloc_launch(C.byref(p), torch.cuda.current_stream().cuda_stream) == want
+    torch.cuda.synchronize()
     p = _params(case, buf, buf, buf, buf, buf, None)
     p.wei_layout = K.WEI_PLAIN                    # would need a packing scratch
     assert L.b200_matmul_wc_noalloc_launch(C.byref(p), None) == K.ERR_UNSUPPORTED

@@ -210,6 +210,7 @@ def main():
     ap.add_argument("--sets", type=int, default=4, help="independent input sets rotated over (L2 defeat)")
     ap.add_argument("--no-extras", action="store_true", help="skip the secondary configurations")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-sustained", action="store_true", help="skip the two-second sustained run (launch lists under a profiler)")
     ap.add_argument("--case", default=None,
                     help="profiling aid: execute one named configuration --steps times and exit "
                          "(c0, c1, c2_m1, c2_m16, c2_m128, c3, c3_4096, c4); prints no benchmark line")
@@ -328,7 +329,7 @@ def main():
 
     # ---- the same kernel sustained: two seconds of back-to-back launches, clocks sampled throughout ----
     sustained = None
-    if not args.no_extras:
+    if not args.no_extras and not args.no_sustained:
         try:
             sus = ClockSampler(local)
             n_sus = max(args.steps, int(2.0 / (ms_total / args.steps * 1e-3)))

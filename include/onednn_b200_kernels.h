@@ -129,6 +129,9 @@ typedef struct {
      * b200_matmul_tc8_launch; the other kernels return B200_ERR_UNSUPPORTED when it is set. */
     int32_t n_dst_peers; int32_t reserved4;
     void *dst_peer[B200_MAX_DST_PEERS];
+    /* s32 row sums of src, sum_k src[m][k], length M: needed by b200_matmul_tc8_launch when
+     * weights zero-points are set (b200_colsum_launch on src seen as its transpose gives them) */
+    const int32_t *src_rowsum;
 } b200_matmul_params_t;
 
 /* ---- matmul kernels ----------------------------------------------------- */

@@ -236,9 +236,10 @@ static bool accept_tc8(dnnl_primitive_desc *pd) {
     if (!quant_simple(a.scale(DNNL_ARG_WEIGHTS), 2)) return reject(name, "weights scales must be per-tensor or per-N"), false;
     if (!quant_simple(a.scale(DNNL_ARG_DST), 0)) return reject(name, "dst scales must be per-tensor"), false;
     if (!quant_simple(a.zp(DNNL_ARG_SRC), 0)) return reject(name, "src zero-point must be per-tensor"), false;
-    if (a.zp(DNNL_ARG_WEIGHTS).set) return reject(name, "weights zero-points not supported"), false;
+    // weights zero-points, one per tensor or per column: folded in by the epilogue from the row sums of src
+    if (!quant_simple(a.zp(DNNL_ARG_WEIGHTS), 2)) return reject(name, "weights zero-points must be per-tensor or per-N"), false;
     if (!quant_simple(a.zp(DNNL_ARG_DST), 2)) return reject(name, "dst zero-point mask"), false;
-    if (f8 && (a.zp(DNNL_ARG_SRC).set)) return reject(name, "fp8 with src zero-point"), false;
+    if (f8 && (a.zp(DNNL_ARG_SRC).set || a.zp(DNNL_ARG_WEIGHTS).set)) return reject(name, "fp8 with zero-points"), false;
     // resolve layouts
     pd->src = src;
     if (src.is_any()) make_plain(pd->src);
@@ -366,17 +367,26 @@ static bool accept_generic(dnnl_primitive_desc *pd) {
     return true;
 }
 
+// tcgen05 8-bit implementation: the part of the scratchpad that holds weights-side data (the
+// row sums of src, needed with weights zero-points, follow it at a 256-byte boundary)
+static size_t tc8_weights_scratch_bytes(const dnnl_primitive_desc *pd) {
+    const int64_t K = pd->K(), N = pd->N();
+    size_t bytes = 0;
+    // plain N-major weights are transposed into the packed layout on every
+    // execution; plain K-major weights only need the column sums
+    const tc8_wei_class_t wc = tc8_weights_class(pd->wei);
+    if (wc == TC8_WEI_PACK_NMAJOR)
+        bytes = b200_packed_weights_bytes(K, N, pd->wei.data_type, B200_WEI_KMAJOR);
+    else if (wc == TC8_WEI_INPLACE_KMAJOR && pd->attr.zp(DNNL_ARG_SRC).set)
+        bytes = (size_t)N * sizeof(int32_t);
+    return (bytes + 255) / 256 * 256;
+}
+
 static size_t scratch_bytes_for(const dnnl_primitive_desc *pd) {
     size_t bytes = 0;
     if (pd->impl == IMPL_TC8) {
-        const int64_t K = pd->K(), N = pd->N();
-        // plain N-major weights are transposed into the packed layout on every
-        // execution; plain K-major weights only need the column sums
-        const tc8_wei_class_t wc = tc8_weights_class(pd->wei);
-        if (wc == TC8_WEI_PACK_NMAJOR)
-            bytes = b200_packed_weights_bytes(K, N, pd->wei.data_type, B200_WEI_KMAJOR);
-        else if (wc == TC8_WEI_INPLACE_KMAJOR && pd->attr.zp(DNNL_ARG_SRC).set)
-            bytes = (size_t)N * sizeof(int32_t);
+        bytes = tc8_weights_scratch_bytes(pd);
+        if (pd->attr.zp(DNNL_ARG_WEIGHTS).set) bytes += (size_t)pd->M() * sizeof(int32_t);
     }
     if (pd->impl == IMPL_WC) {
         b200_matmul_params_t q;
@@ -842,6 +852,12 @@ dnnl_status_t matmul_execute(const dnnl_primitive *prim, dnnl_stream *stream, co
                 p.wei = scratch;
                 p.wei_layout = B200_WEI_KMAJOR;
                 p.wei_colsum = (const int32_t *)((const char *)scratch + b200_packed_colsum_offset(p.K, p.N, p.wei_dt));
+            }
+            if (rc == 0 && p.wei_zp.ptr) {
+                // sum over k of src[m][k]: the column sums of src seen as its own transpose
+                int32_t *rowsum = (int32_t *)((char *)scratch + tc8_weights_scratch_bytes(pd));
+                rc = b200_colsum_launch(p.src, p.src_dt, p.K, p.M, p.src_sk, p.src_sm, rowsum, cs);
+                p.src_rowsum = rowsum;
             }
             if (rc == 0) rc = b200_matmul_tc8_launch(&p, cs);
         } break;

@@ -341,7 +341,9 @@ __device__ __forceinline__ unit_t decode_unit(const tc8_args_t &a, int u, int ro
 // independent dependency chains: an epilogue warp has at most one other warp on
 // its scheduler to hide latency behind.  Unset scales / bias / zero-points are
 // neutral elements (x * 1, x + -0) instead of branches.
-enum { EPI_NONE = 0, EPI_SIMPLE = 1, EPI_GELU_Q = 2, EPI_GENERIC = 3 };
+//   EPI_SIMPLE_WZ  EPI_SIMPLE (or an empty chain) with weights zero-points: a kernel of its own so
+//               that the others carry neither the extra registers nor the branch.
+enum { EPI_NONE = 0, EPI_SIMPLE = 1, EPI_GELU_Q = 2, EPI_GENERIC = 3, EPI_SIMPLE_WZ = 4 };
 
 // Coefficients of the error bound of the gelu-into-8-bit fast path, in units of the quantities
 // they multiply (u = 2^-24 is one rounding):
@@ -361,6 +363,12 @@ struct epi_consts_t {
     bool has_comp;        // a source zero-point is set: the per-column compensation vector is not all zero
     bool zp_uniform;      // the destination zero-point does not vary over columns: cq / hq below apply to every column
     float cq, hq;         // gelu-into-8-bit fast path with a uniform zero-point: its two per-column constants as scalars
+    // Weights zero-points (int8): sum_k (s - zs)(w - zw[n]) = acc - zs colsum[n] - zw[n] rowsum[m] + zs zw[n] K.
+    // The two terms that depend on the column alone are in the compensation vector; the epilogue
+    // subtracts zw[n] * rowsum[m] (the zero-points travel in the cq[] vector, as integers: the
+    // gelu-into-8-bit path, its only other user, is not chosen together with them).
+    bool has_wzp;
+    int rowsum;           // this lane's row's sum of src
 };
 
 // the exact gelu_tanh, kept out of line: it is needed for about one element in ten thousand
@@ -548,7 +556,8 @@ __device__ __forceinline__ void epilogue_chunk(const b200_matmul_params_t &p, co
         for (int j = 0; j < CH; ++j) {
             const uint32_t raw = tmem_ld1(taddr + j);
             if (j >= nvalid) continue;
-            const float acc = FP8 ? __uint_as_float(raw) : (float)((int)raw - comp[j]);
+            const float acc = FP8 ? __uint_as_float(raw)
+                                  : (float)((int)raw - comp[j] - (k.has_wzp ? __float_as_int(cq[j]) * k.rowsum : 0));
             float x = __fadd_rn(__fmul_rn(__fmul_rn(acc, k.src_scale), wscale[j]), bias[j]);
             if (p.bias && p.bias_sm) // a bias that varies along M is not part of the per-column vector
                 x = __fadd_rn(x, load_f32(p.bias_dt, p.bias, m * p.bias_sm + (n0 + j) * p.bias_sn));
@@ -709,7 +718,11 @@ __device__ __forceinline__ void epilogue_chunk(const b200_matmul_params_t &p, co
         const float4 a = ((const float4 *)wscale)[q], b = ((const float4 *)bias)[q];
         const int4 c = ((const int4 *)comp)[q];
         const float ws[4] = {a.x, a.y, a.z, a.w}, bs[4] = {b.x, b.y, b.z, b.w};
-        const int cs[4] = {c.x, c.y, c.z, c.w};
+        int cs[4] = {c.x, c.y, c.z, c.w};
+        if (!FP8 && EPI == EPI_SIMPLE_WZ) {
+            const int4 z = ((const int4 *)cq)[q];
+            cs[0] += z.x * k.rowsum; cs[1] += z.y * k.rowsum; cs[2] += z.z * k.rowsum; cs[3] += z.w * k.rowsum;
+        }
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const int j = 4 * q + i;
@@ -726,7 +739,7 @@ __device__ __forceinline__ void epilogue_chunk(const b200_matmul_params_t &p, co
     if (EPI == EPI_NONE) {
 #pragma unroll
         for (int j = 0; j < CH; ++j) y[j] = tail(y[j], j);
-    } else if (EPI == EPI_SIMPLE) {
+    } else if (EPI == EPI_SIMPLE || EPI == EPI_SIMPLE_WZ) {
         for (int i = 0; i < p.npo; ++i) {
             const b200_postop_t &e = p.po[i];
             if (e.kind == B200_PO_SUM) {
@@ -910,6 +923,8 @@ __global__ void __launch_bounds__(640, 1) matmul_tc8_kernel(const __grid_constan
                         || p.dst_zp.ptr);
         const bool bias_per_col = p.bias && !p.bias_sm;
         k.has_comp = has_comp;
+        k.has_wzp = !FP8 && (EPI == EPI_SIMPLE_WZ || EPI == EPI_GENERIC) && p.wei_zp.ptr && p.src_rowsum;
+        k.rowsum = 0;
         k.zp_uniform = !(p.dst_zp.ptr && p.dst_zp.s1);
         k.cq = k.hq = 0.f;
         if (EPI == EPI_GELU_Q && k.zp_uniform) {
@@ -948,6 +963,11 @@ __global__ void __launch_bounds__(640, 1) matmul_tc8_kernel(const __grid_constan
                 wsx[j] = wscale[j] * src_scale_all;
                 bias[j] = (in && bias_per_col) ? load_f32(p.bias_dt, p.bias, n * p.bias_sn) : -0.f;
                 comp[j] = (in && has_comp) ? zp_src * p.wei_colsum[n] : 0;
+                if ((EPI == EPI_SIMPLE_WZ || EPI == EPI_GENERIC) && k.has_wzp) {
+                    const int zw = in ? load_int(p.wei_zp.dt, p.wei_zp.ptr, n * p.wei_zp.s1) : 0;
+                    cqv[j] = __int_as_float(zw);
+                    comp[j] -= zp_src * zw * (int)p.K; // wraps like the sum it is part of; the total is exact whenever it fits 32 bits
+                }
                 // the int8 path adds the zero-point (+0 when unset) whenever any attribute is set; -0 adds nothing
                 zpv[j] = !k.int8_nondefault ? -0.f
                         : (in && p.dst_zp.ptr) ? (float)((const int32_t *)p.dst_zp.ptr)[p.dst_zp.s1 ? n : 0] : 0.f;
@@ -960,6 +980,7 @@ __global__ void __launch_bounds__(640, 1) matmul_tc8_kernel(const __grid_constan
             __syncwarp();
             const int64_t m = m0 + quarter * 32 + lane;
             if (k.src_per_row) k.src_scale = m < p.M ? ((const float *)p.src_scale.ptr)[m] : 1.f;
+            if ((EPI == EPI_SIMPLE_WZ || EPI == EPI_GENERIC) && k.has_wzp) k.rowsum = m < p.M ? p.src_rowsum[m] : 0;
             const uint32_t trow = tmem_base + ((uint32_t)(quarter * 32) << 16) + a * BN + half * ecols;
             // Prior destination bytes of this warp's columns (sum post-op): requested now, for
             // the whole tile, so that the DRAM latency passes while the accumulator is still
@@ -1164,7 +1185,8 @@ extern "C" int b200_matmul_tc8_launch(const b200_matmul_params_t *p, b200_stream
     if (p->wei_scale.ptr && (p->wei_scale.s0 || p->wei_scale.g1 != 1)) return B200_ERR_UNSUPPORTED;
     if (p->dst_scale.ptr && (p->dst_scale.s0 || p->dst_scale.s1)) return B200_ERR_UNSUPPORTED;
     if (p->src_zp.ptr && (p->src_zp.s0 || p->src_zp.s1 || !p->wei_colsum || f8)) return B200_ERR_UNSUPPORTED;
-    if (p->wei_zp.ptr) return B200_ERR_UNSUPPORTED;
+    // weights zero-points: per tensor or per column, with the row sums of src supplied
+    if (p->wei_zp.ptr && (p->wei_zp.s0 || p->wei_zp.g0 != 1 || p->wei_zp.g1 != 1 || !p->src_rowsum || f8)) return B200_ERR_UNSUPPORTED;
     if (p->dst_zp.ptr && (p->dst_zp.s0 || p->dst_zp.dt != B200_DT_S32 || f8)) return B200_ERR_UNSUPPORTED;
     if (((uintptr_t)p->src & 15) || ((uintptr_t)p->wei & 15) || (p->src_sm & 15) || (wpitch & 15)) return B200_ERR_BAD_ARG;
     if (p->M > INT32_MAX || p->N > INT32_MAX || p->K > INT32_MAX) return B200_ERR_TOO_LARGE;
@@ -1236,10 +1258,15 @@ extern "C" int b200_matmul_tc8_launch(const b200_matmul_params_t *p, b200_stream
         epi = simple ? EPI_SIMPLE : gelu_q ? EPI_GELU_Q : EPI_GENERIC;
     }
     if (p->bias && p->bias_sm) epi = EPI_GENERIC; // a bias that varies along M is added by the interpreted path
+    if (p->wei_zp.ptr) {
+        // the straight-line path with an empty or simple chain, the interpreted one otherwise
+        if (epi == EPI_NONE || epi == EPI_SIMPLE) epi = EPI_SIMPLE_WZ;
+        else if (epi == EPI_GELU_Q) epi = EPI_GENERIC;
+    }
 
     // how the sum post-op reads the prior destination
     int sum = SUM_NONE;
-    if (epi == EPI_SIMPLE || epi == EPI_GELU_Q) {
+    if (epi == EPI_SIMPLE || epi == EPI_SIMPLE_WZ || epi == EPI_GELU_Q) {
         for (int i = 0; i < p->npo; ++i)
             if (p->po[i].kind == B200_PO_SUM) {
                 const int sdt = p->po[i].dt != B200_DT_UNDEF ? p->po[i].dt : p->dst_dt;
@@ -1254,8 +1281,11 @@ extern "C" int b200_matmul_tc8_launch(const b200_matmul_params_t *p, b200_stream
             {matmul_tc8_kernel<F, EPI_SIMPLE, SUM_NONE, false, P>, matmul_tc8_kernel<F, EPI_SIMPLE, SUM_8BIT, false, P>, \
                     matmul_tc8_kernel<F, EPI_SIMPLE, SUM_OTHER, false, P>}, \
             {matmul_tc8_kernel<F, EPI_GELU_Q, SUM_NONE, false, P>, matmul_tc8_kernel<F, EPI_GELU_Q, SUM_8BIT, false, P>, nullptr}, \
-            {matmul_tc8_kernel<F, EPI_GENERIC, SUM_NONE, false, P>, nullptr, nullptr}}
-    static const kernel_t table[2][2][4][3] = {{TC8_ROW(false, false), TC8_ROW(true, false)}, {TC8_ROW(false, true), TC8_ROW(true, true)}};
+            {matmul_tc8_kernel<F, EPI_GENERIC, SUM_NONE, false, P>, nullptr, nullptr}, \
+            {F ? nullptr : (kernel_t)matmul_tc8_kernel<false, EPI_SIMPLE_WZ, SUM_NONE, false, P>, \
+                    F ? nullptr : (kernel_t)matmul_tc8_kernel<false, EPI_SIMPLE_WZ, SUM_8BIT, false, P>, \
+                    F ? nullptr : (kernel_t)matmul_tc8_kernel<false, EPI_SIMPLE_WZ, SUM_OTHER, false, P>}}
+    static const kernel_t table[2][2][5][3] = {{TC8_ROW(false, false), TC8_ROW(true, false)}, {TC8_ROW(false, true), TC8_ROW(true, true)}};
 #undef TC8_ROW
     kernel_t kern = table[pair ? 1 : 0][f8 ? 1 : 0][epi][sum];
     if (p->n_dst_peers) {
@@ -1269,10 +1299,10 @@ extern "C" int b200_matmul_tc8_launch(const b200_matmul_params_t *p, b200_stream
     if (!kern) return B200_ERR_UNSUPPORTED;
     // opt in to the large dynamic shared memory once per kernel and device
     static std::mutex attr_mu;
-    static bool attr_done[64][2][2][4][3] = {};
+    static bool attr_done[64][2][2][5][3] = {};
     {
         std::lock_guard<std::mutex> g(attr_mu);
-        static bool attr_done_peers[64][2][4] = {};
+        static bool attr_done_peers[64][2][5] = {};
         bool &done = p->n_dst_peers ? attr_done_peers[dev & 63][f8 ? 1 : 0][epi] : attr_done[dev & 63][pair ? 1 : 0][f8 ? 1 : 0][epi][sum];
         if (dev < 64 && !done) {
             cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);

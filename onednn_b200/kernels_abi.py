@@ -40,6 +40,7 @@ class MatmulParams(C.Structure):
         ("scratch", C.c_void_p), ("scratch_bytes", C.c_size_t),
         ("scratch_zeroed", C.c_int32), ("reserved3", C.c_int32),
         ("n_dst_peers", C.c_int32), ("reserved4", C.c_int32), ("dst_peer", C.c_void_p * 7),
+        ("src_rowsum", C.c_void_p),
     ]
 
 

@@ -63,6 +63,32 @@ def int8_wei_zp_common():
     return c
 
 
+def int8_wei_zp_per_n_relu():
+    """Zero-points on both sides, the weights' one per column: several tiles, ragged edges,
+    a straight-line post-op chain (the tensor-core kernel folds them in from the row sums of src)."""
+    r, c = _int8_base(200, 328, 256, 24, src_dt=dt.U8, dst_dt=dt.S8)
+    c.src_scale = Quant(_f32([0.02]), dt.F32, 0)
+    c.wei_scale = Quant(_f32(r.uniform(2e-3, 6e-3, 328)), dt.F32, 2)
+    c.src_zp = Quant(np.array([121], dtype=np.int32), dt.S32, 0)
+    c.wei_zp = Quant(r.integers(-9, 10, 328).astype(np.int32), dt.S32, 2)
+    c.dst_scale = Quant(_f32([0.125]), dt.F32, 0)
+    c.dst_zp = Quant(np.array([-7], dtype=np.int32), dt.S32, 0)
+    c.post_ops = [W.eltwise("relu", 0.25)]
+    return c
+
+
+def int8_wei_zp_gelu_sum():
+    """Weights zero-point (no source zero-point) under gelu_tanh and sum: the interpreted chain."""
+    r, c = _int8_base(70, 144, 128, 25, dst_dt=dt.S8)
+    c.dst_init = r.integers(-128, 128, (70, 144), dtype=np.int8)
+    c.src_scale = Quant(_f32([0.03]), dt.F32, 0)
+    c.wei_scale = Quant(_f32([0.005]), dt.F32, 0)
+    c.wei_zp = Quant(np.array([-11], dtype=np.int32), dt.S32, 0)
+    c.dst_scale = Quant(_f32([0.05]), dt.F32, 0)
+    c.post_ops = [W.eltwise("gelu_tanh"), W.sum_(0.5)]
+    return c
+
+
 def int8_sum_u8_as_s8():
     """sum post-op that reads the u8 dst as s8 with its own zero-point, then clip."""
     r, c = _int8_base(20, 32, 48, 5, dst_dt=dt.U8)
@@ -209,6 +235,8 @@ CASES = {
     "int8_ragged_tiny": int8_ragged_tiny,
     "int8_u8dst_binary_prelu": int8_u8dst_binary_prelu,
     "int8_wei_zp_common": int8_wei_zp_common,
+    "int8_wei_zp_per_n_relu": int8_wei_zp_per_n_relu,
+    "int8_wei_zp_gelu_sum": int8_wei_zp_gelu_sum,
     "int8_sum_u8_as_s8": int8_sum_u8_as_s8,
     "int8_bf16_dst_transposed_wei": int8_bf16_dst_transposed_wei,
     "elt_tanh": _elt_case("tanh"),
@@ -305,7 +333,7 @@ def build_tame(name):
     if c.src_zp is not None:
         c.src_zp = Quant(np.array([4], dtype=np.int32), dt.S32, c.src_zp.mask, c.src_zp.groups)
     if c.wei_zp is not None:
-        c.wei_zp = Quant(np.array([1], dtype=np.int32), dt.S32, c.wei_zp.mask, c.wei_zp.groups)
+        c.wei_zp = Quant(np.ones(c.wei_zp.data.shape, dtype=np.int32), dt.S32, c.wei_zp.mask, c.wei_zp.groups)
     # the sums are now a few hundred at most: keep the requantised outputs inside the range
     if c.dst_scale is not None:
         c.dst_scale = Quant(_f32([2.0 ** -6]), dt.F32, 0)

@@ -102,6 +102,11 @@ def test_fast_kernels_are_dispatched(ctx):
     assert api.CasePlan(cases.build("c1_small"), eng, strm, upload=False).impl == "cuda:sm100:tcgen05_i8"
     assert api.CasePlan(cases.build("c3_small"), eng, strm, upload=False).impl == "cuda:sm100:tcgen05_f8"
     assert api.CasePlan(W.config2(1, 256, 512), eng, strm, upload=False).impl == "cuda:sm100:wc_gemv"
+    # weights zero-points (per tensor, per column) stay on the tensor cores
+    for name in ("int8_wei_zp_common", "int8_wei_zp_per_n_relu", "int8_wei_zp_gelu_sum"):
+        c = cases.build(name)
+        if c.K % 16 == 0:
+            assert api.CasePlan(c, eng, strm, upload=False).impl == "cuda:sm100:tcgen05_i8", name
 
 
 def test_repeated_execution_and_sum_in_place(ctx):

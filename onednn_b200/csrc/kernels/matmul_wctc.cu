@@ -47,24 +47,32 @@ namespace wctc {
 
 constexpr int TN = 128;              // output columns per tile (UMMA M, TMEM lanes)
 constexpr int TK = 64;               // k per stage: 128 bytes of bf16 = one swizzle row
-constexpr int STAGES = 4;            // operand stages; stage g belongs to warp group g
-constexpr int GROUPS = STAGES;       // dequantising warp groups, each converts every fourth k-block
+constexpr int GROUPS = 4;            // dequantising warp groups, each converts every fourth k-block
+constexpr int A_STAGES = 4;          // stages of converted weights, one per group
+constexpr int MAX_B_STAGES = 16;     // stages of activations: as many as fit (a power of two), at least A_STAGES
 constexpr int GROUP_WARPS = TN / 32; // one thread per output column of the tile
 constexpr int DQ_WARPS = GROUPS * GROUP_WARPS;
 // per weight width (4 or 8 bits): packed bytes of one column in one k-block, of a whole block,
 // and the number of its own k-blocks a group requests ahead (64 KiB of ring either way)
 __host__ __device__ constexpr int pf_bytes(int wbits) { return TK * wbits / 8; }
 __host__ __device__ constexpr int block_bytes(int wbits) { return TN * TK * wbits / 8; }
-__host__ __device__ constexpr int pfs(int wbits) { return wbits == 4 ? 4 : 2; }
+__host__ __device__ constexpr int pfs(int wbits) { return 2; }
 constexpr int NUM_THREADS = 64 + DQ_WARPS * 32;
 constexpr int A_BYTES = TN * TK * 2; // dequantised weights tile, 16 KiB
 constexpr uint32_t WAIT_SPINS = 1u << 24; // polls of the drain loop
 constexpr uint32_t WAIT_TRIES = 1u << 19; // hardware-suspended waits of up to ~2 us each
 enum : uint32_t { ST_WAIT_FULL = 0x1000, ST_WAIT_EMPTY = 0x2000, ST_WAIT_ACC = 0x4000 };
 
+// One pair of barriers per k-block modulo the depth B of the activations ring (B >= 4, a power of
+// two): full[i] collects the four warp arrivals of the converted weights and the bytes of the
+// activations' copy of block i; done[i] is the arrival of the commit behind block i's MMAs.  The
+// converters wait on done for block i - 4 (their stage of the weights ring), the copy-issuing
+// thread for block i - B: one wait and one commit per block for the MMA-issuing thread, whose
+// loop sets the pace.  The activations ring is the deep one because a copy of 128-byte row
+// pieces from L2 takes about 1.4 us to land, several times what a block's conversion and MMAs take.
 struct ctrl_t {
-    uint64_t full_a[STAGES]; // converted weights (four warp arrivals) and activations (copy bytes) of a stage
-    uint64_t empty[STAGES];
+    uint64_t full_a[MAX_B_STAGES];
+    uint64_t empty[MAX_B_STAGES];
     uint64_t acc_full, acc_empty;
     uint32_t tmem_base;
     volatile uint32_t abort;
@@ -81,6 +89,7 @@ struct args_t {
     uint32_t gs_blocks, gz_blocks; // K-group sizes of scales and zero-points in k-blocks of 64 (K / 64 when not grouped)
     uint32_t gs_shift, gz_shift;   // their base-2 logarithms (the FASTQ instantiation requires powers of two)
     uint32_t wait_mode;            // bit 0: the two issuing threads wait suspended instead of polling; bit 1: the converters poll
+    uint32_t b_stages;             // depth of the activations ring: 4, 8 or 16
     float nibble_offset;     // 4-bit weights: 128 (u4) or 136 (s4 stored offset by 8)
     uint32_t byte_xor;       // 8-bit weights: 0x80808080 for s8 (to offset binary), 0 for u8
 };
@@ -222,16 +231,20 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     const b200_matmul_params_t &p = args.p;
     const int nb = args.nb;
-    const uint32_t b_bytes = (uint32_t)nb * (TK * 2);
-    const uint32_t stage_bytes = A_BYTES + b_bytes;
-    uint8_t *pf_ring = smem + (size_t)STAGES * stage_bytes;                    // [PFS][threads][PF_BYTES] packed weights in flight
-    ctrl_t *ctrl = (ctrl_t *)(smem + (size_t)STAGES * stage_bytes + (size_t)PFS * DQ_WARPS * 32 * PF_BYTES);
+    const uint32_t b_bytes = (uint32_t)nb * (TK * 2); // a multiple of 2 KiB: every stage of either ring starts on a 1 KiB boundary
+    // both ring depths are powers of two: block index -> stage and use count by mask and shift (the
+    // loops of the two issuing threads set the pace; a division there costs more than the MMAs' issue)
+    constexpr uint32_t SA = A_STAGES, SA_MASK = SA - 1;
+    const uint32_t SB = args.b_stages, SB_MASK = SB - 1, SB_SHIFT = SB == 16 ? 4 : SB == 8 ? 3 : 2;
+    uint8_t *smem_b = smem + (size_t)SA * A_BYTES;                             // [SB][nb][128 bytes] activations
+    uint8_t *pf_ring = smem_b + (size_t)SB * b_bytes;                          // [PFS][threads][PF_BYTES] packed weights in flight
+    ctrl_t *ctrl = (ctrl_t *)(pf_ring + (size_t)PFS * DQ_WARPS * 32 * PF_BYTES);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int num_tiles = args.n_tiles * args.m_passes;
     const int KB = args.k_blocks;
 
     if (threadIdx.x == 0) {
-        for (uint32_t s = 0; s < STAGES; ++s) {
+        for (uint32_t s = 0; s < SB; ++s) {
             mbar_init(&ctrl->full_a[s], GROUP_WARPS + 1); // the group's warps and the activations' copy
             mbar_init(&ctrl->empty[s], 1);
         }
@@ -260,18 +273,21 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
                 const int row0 = (int)((tile / args.n_tiles) * args.rows_per_pass);
                 for (int kb = 0; kb < KB; ++kb, ++it) {
-                    const uint32_t s = it % STAGES, r = it / STAGES;
-                    if (!(ok = (args.wait_mode & 1) ? mbar_wait(&ctrl->empty[s], (r & 1) ^ 1, ctrl, p.status, ST_WAIT_EMPTY)
-                                                    : mbar_wait_poll(&ctrl->empty[s], (r & 1) ^ 1, ctrl, p.status, ST_WAIT_EMPTY)))
-                        break;
-                    mbar_expect_tx(&ctrl->full_a[s], b_bytes);
-                    tma_load_2d(smem + (size_t)s * stage_bytes + A_BYTES, &tmap_x, kb * (TK * 2), row0, &ctrl->full_a[s]); // byte coordinates
+                    // this block's stage of the activations ring was last read by block it - SB
+                    if (it >= SB) {
+                        const uint32_t prev = it - SB;
+                        if (!(ok = (args.wait_mode & 1) ? mbar_wait(&ctrl->empty[prev & SB_MASK], (prev >> SB_SHIFT) & 1, ctrl, p.status, ST_WAIT_EMPTY)
+                                                        : mbar_wait_poll(&ctrl->empty[prev & SB_MASK], (prev >> SB_SHIFT) & 1, ctrl, p.status, ST_WAIT_EMPTY)))
+                            break;
+                    }
+                    mbar_expect_tx(&ctrl->full_a[it & SB_MASK], b_bytes);
+                    tma_load_2d(smem_b + (size_t)(it & SB_MASK) * b_bytes, &tmap_x, kb * (TK * 2), row0, &ctrl->full_a[it & SB_MASK]); // byte coordinates
                 }
             }
             // drain: every copy this thread issued must have landed before the CTA may exit
             const uint32_t issued = it;
-            for (uint32_t j = issued > STAGES ? issued - STAGES : 0; j < issued; ++j) {
-                const uint32_t s = j % STAGES, r = j / STAGES;
+            for (uint32_t j = issued > SB ? issued - SB : 0; j < issued; ++j) {
+                const uint32_t s = j & SB_MASK, r = j >> SB_SHIFT;
                 for (uint32_t i = 0; i < WAIT_SPINS; ++i) {
                     if (mbar_test(&ctrl->full_a[s], r & 1)) break;
                     __nanosleep(64);
@@ -284,22 +300,31 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             uint32_t it = 0, tile_i = 0;
             bool ok = true;
             // descriptors of stage 0; a stage further on is stage_bytes / 16 more in the address field
-            const uint64_t adesc0 = make_smem_desc(smem_u32(smem)), bdesc0 = make_smem_desc(smem_u32(smem) + A_BYTES);
+            const uint64_t adesc0 = make_smem_desc(smem_u32(smem)), bdesc0 = make_smem_desc(smem_u32(smem_b));
+            // This thread's loop sets the pace of the kernel: per k-block one look at a barrier, four
+            // MMAs, one commit.  A look at a barrier costs about 200 cycles even when the phase has long
+            // completed, so the look for block i + 1 is issued before the MMAs of block i and its
+            // answer read after them; only when that early look says "not yet" does the thread poll.
+            // No tcgen05 fence inside the loop: the operands are in shared memory, written through
+            // the async proxy (the copies) or published with fence.proxy.async (the converters), and
+            // ordered by the barrier; the fence belongs where tensor memory changes hands (below).
+            bool early = false; // the early look's answer for the block at hand
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tile_i) {
                 if (!(ok = mbar_wait_poll(&ctrl->acc_empty, (tile_i & 1) ^ 1, ctrl, p.status, ST_WAIT_ACC))) break;
                 tc_fence_after();
                 for (int kb = 0; kb < KB; ++kb, ++it) {
-                    const uint32_t s = it % STAGES, r = it / STAGES;
-                    // one barrier per stage: converted weights (four warps) and activations (copy bytes)
-                    if (!(ok = (args.wait_mode & 1) ? mbar_wait(&ctrl->full_a[s], r & 1, ctrl, p.status, ST_WAIT_FULL)
-                                                    : mbar_wait_poll(&ctrl->full_a[s], r & 1, ctrl, p.status, ST_WAIT_FULL)))
-                        break;
-                    tc_fence_after();
-                    const uint64_t adesc = adesc0 + (uint64_t)(s * (stage_bytes >> 4)), bdesc = bdesc0 + (uint64_t)(s * (stage_bytes >> 4));
+                    const uint32_t s = it & SB_MASK, r = it >> SB_SHIFT;
+                    // one barrier per block: converted weights (four warps) and activations (copy bytes)
+                    if (!early && !(ok = mbar_wait_poll(&ctrl->full_a[s], r & 1, ctrl, p.status, ST_WAIT_FULL))) break;
+                    if (args.wait_mode & 4) tc_fence_after();
+                    const uint32_t nx = it + 1;
+                    const bool next_early = (args.wait_mode & 8) ? false : mbar_test(&ctrl->full_a[nx & SB_MASK], (nx >> SB_SHIFT) & 1);
+                    const uint64_t adesc = adesc0 + (uint64_t)((it & SA_MASK) * (A_BYTES >> 4)), bdesc = bdesc0 + (uint64_t)(s * (b_bytes >> 4));
 #pragma unroll
                     for (int k = 0; k < TK / 16; ++k) // 16 bf16 = 32 bytes of K per instruction: +2 in 16-byte units
                         tc_mma_bf16(tmem_base, adesc + 2 * k, bdesc + 2 * k, args.idesc, (kb | k) != 0);
                     tc_commit(&ctrl->empty[s]);
+                    early = next_early;
                 }
                 if (ok) tc_commit(&ctrl->acc_full);
             }
@@ -318,11 +343,11 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         const bool simple_epilogue = p.npo == 0 && !p.dst_scale.ptr && (!p.bias || p.bias_sm == 0)
                 && (p.dst_dt == B200_DT_BF16 || p.dst_dt == B200_DT_F32);
         const float src_scale = p.src_scale.ptr ? load_f32(p.src_scale.dt, p.src_scale.ptr, 0) : 1.f;
-        uint8_t *tile_a = smem + (size_t)grp * stage_bytes + (uint32_t)r * 128;
+        uint8_t *const row_a = smem + (uint32_t)r * 128; // this thread's row in stage 0
         uint8_t *my_ring = pf_ring + (size_t)dq * PF_BYTES;
         const uint32_t my_ring_s = smem_u32(my_ring);
         constexpr uint32_t RING_STRIDE = DQ_WARPS * 32 * PF_BYTES;
-        uint32_t uses = 0, tile_i = 0; // times this group has filled its stage
+        uint32_t tile_i = 0;
         bool ok = true;
 
         for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tile_i) {
@@ -330,12 +355,13 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             const int64_t ncol = (int64_t)nt * TN + r;
             const bool col_ok = ncol < p.N;
             // the k-blocks of this tile that fall into this group's stage
-            const int first_kb = (int)((grp + STAGES - (uint32_t)(((uint64_t)tile_i * KB) % STAGES)) % STAGES);
-            const int iters = first_kb < KB ? (KB - first_kb + STAGES - 1) / STAGES : 0;
+            const uint32_t it0 = tile_i * (uint32_t)KB; // running index of the tile's first k-block
+            const int first_kb = (int)((grp + GROUPS - it0 % GROUPS) % GROUPS);
+            const int iters = first_kb < KB ? (KB - first_kb + GROUPS - 1) / GROUPS : 0;
             const uint8_t *wsrc = args.wei + ((size_t)nt * KB + first_kb) * BLOCK_BYTES + (size_t)r * PF_BYTES;
             auto request = [&](int j) { // packed row of this thread's j-th k-block, 16-byte copies
                 if (j < iters) {
-                    const uint8_t *src = wsrc + (size_t)j * (STAGES * BLOCK_BYTES);
+                    const uint8_t *src = wsrc + (size_t)j * (GROUPS * BLOCK_BYTES);
                     const uint32_t dst = my_ring_s + (uint32_t)(j % PFS) * RING_STRIDE;
 #pragma unroll
                     for (int q = 0; q < PF_BYTES; q += 16)
@@ -394,12 +420,23 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                 return p.wei_zp.dt == B200_DT_S4 ? (z ^ 8) - 8 : z;
             };
             load_q(first_kb);
-            for (int j = 0; j < iters; ++j, ++uses) {
-                const int kb = first_kb + j * STAGES;
+            for (int j = 0; j < iters; ++j) {
+                const int kb = first_kb + j * GROUPS;
+                const uint32_t it = it0 + (uint32_t)kb; // the block's running index: stage grp of the weights ring
+                uint8_t *tile_a = row_a + (size_t)grp * A_BYTES;
                 // decode this block's scale and zero-point, then ask for the next block's
                 const float sf = FASTQ ? 0.f : scale_f32();
                 const int zpi = FASTQ ? 0 : zp_int();
-                load_q(kb + STAGES);
+                // FASTQ: the scale's own bits (zeros for a padding column, 1.0 when unset) and the
+                // zero-point nibble, sign-extended for s4 -- taken before the next block's are requested
+                uint32_t sbits = 0;
+                int zq = 0;
+                if (FASTQ) {
+                    sbits = !col_ok ? 0u : has_s ? sraw : 0x3f80u;
+                    zq = has_zp ? (int)((zraw >> zshift) & 0xfu) : 0;
+                    if (p.wei_zp.dt == B200_DT_S4) zq = (zq ^ 8) - 8;
+                }
+                load_q(kb + GROUPS);
                 asm volatile("cp.async.wait_group %0;" ::"n"(PFS - 1) : "memory"); // this thread's j-th row has landed
                 const uint4 *slot = reinterpret_cast<const uint4 *>(my_ring + (size_t)(j % PFS) * RING_STRIDE);
                 uint32_t words[PF_BYTES / 4];
@@ -408,8 +445,11 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                     const uint4 t4 = slot[q];
                     words[4 * q] = t4.x, words[4 * q + 1] = t4.y, words[4 * q + 2] = t4.z, words[4 * q + 3] = t4.w;
                 }
-                if (!(ok = (args.wait_mode & 2) ? mbar_wait_poll(&ctrl->empty[grp], (uses & 1) ^ 1, ctrl, p.status, ST_WAIT_EMPTY)
-                                                : mbar_wait(&ctrl->empty[grp], (uses & 1) ^ 1, ctrl, p.status, ST_WAIT_EMPTY))) {
+                // the stage was last read by the MMAs of block it - 4
+                const uint32_t prev = it - SA;
+                if (it >= SA
+                        && !(ok = (args.wait_mode & 2) ? mbar_wait_poll(&ctrl->empty[prev & SB_MASK], (prev >> SB_SHIFT) & 1, ctrl, p.status, ST_WAIT_EMPTY)
+                                                       : mbar_wait(&ctrl->empty[prev & SB_MASK], (prev >> SB_SHIFT) & 1, ctrl, p.status, ST_WAIT_EMPTY))) {
                     asm volatile("cp.async.wait_group 0;" ::: "memory");
                     break;
                 }
@@ -418,14 +458,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                     // rounded once: the bf16 rounding of the reference's f32 (q - zp) * scale
                     __nv_bfloat162 sc, cc;
                     if (FASTQ) {
-                        // the scale's own bits in both halves (zeros for a padding column, 1.0 when unset);
-                        // the zero-point nibble, sign-extended for s4
-                        const uint32_t sb = !col_ok ? 0u : has_s ? sraw : 0x3f80u;
-                        const uint32_t sb2 = sb | (sb << 16);
+                        const uint32_t sb2 = sbits | (sbits << 16);
                         sc = *reinterpret_cast<const __nv_bfloat162 *>(&sb2);
-                        int z = has_zp ? (int)((zraw >> zshift) & 0xfu) : 0;
-                        if (p.wei_zp.dt == B200_DT_S4) z = (z ^ 8) - 8;
-                        cc = __float2bfloat162_rn(args.nibble_offset + (float)z);
+                        cc = __float2bfloat162_rn(args.nibble_offset + (float)zq);
                     } else {
                         sc = __float2bfloat162_rn(sf);                                // exact: the scale is bf16
                         cc = __float2bfloat162_rn(args.nibble_offset + (float)zpi);   // exact: an integer below 256
@@ -468,7 +503,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                 // generic-proxy writes -> visible to the tensor core's (async proxy) reads
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&ctrl->full_a[grp]);
+                if (lane == 0) mbar_arrive(&ctrl->full_a[it & SB_MASK]);
                 request(j + PFS); // the ring slot of iteration j is free again
             }
             if (!ok) break;
@@ -718,8 +753,21 @@ extern "C" int b200_matmul_wc_tc_launch(const b200_matmul_params_t *p, b200_stre
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     const int64_t tiles = (int64_t)a.n_tiles * a.m_passes;
     const unsigned grid = (unsigned)(tiles < sms ? tiles : sms);
-    const size_t smem = 1024 + (size_t)STAGES * (A_BYTES + (size_t)a.nb * TK * 2)
-            + (size_t)pfs(wbits) * DQ_WARPS * 32 * pf_bytes(wbits) + sizeof(ctrl_t);
+    // shared memory: the four stages of converted weights, the packed-weights ring, and as many
+    // stages of activations as fit (a power of two, 4 .. 16)
+    const size_t b_bytes = (size_t)a.nb * TK * 2;
+    const size_t fixed = 1024 + (size_t)A_STAGES * A_BYTES + (size_t)pfs(wbits) * DQ_WARPS * 32 * pf_bytes(wbits) + sizeof(ctrl_t);
+    size_t sb = (227 * 1024 - fixed) / b_bytes;
+    static const int b_stages_env = [] {
+        const char *v = std::getenv("ONEDNN_B200_WCTC_BSTAGES");
+        return v ? std::atoi(v) : 0;
+    }();
+    if (b_stages_env >= 4 && (size_t)b_stages_env < sb) sb = (size_t)b_stages_env;
+    if (sb > MAX_B_STAGES) sb = MAX_B_STAGES;
+    if (sb < A_STAGES) return B200_ERR_UNSUPPORTED;
+    while (sb & (sb - 1)) sb &= sb - 1; // a power of two
+    a.b_stages = (uint32_t)sb;
+    const size_t smem = fixed + sb * b_bytes;
     static std::mutex mu;
     static bool attr_done[64] = {};
     {

@@ -261,11 +261,15 @@ CASES = {
     "wc_tc_u4_g64_m33_ragged": _wc_case(33, 208, 128, 64, dt.U4, seed=18),
     "wc_tc_u4_g128_m40_wide": _wc_case(40, 2560, 256, 128, dt.U4, seed=20),
     "wc_tc_s4_perN_m300": _wc_case(300, 144, 192, 192, dt.S4, seed=19, zp="none"),
+    # the same kernel with fewer tiles than SMs and a long K: the operand rings wrap many times
+    "wc_tc_u4_g128_m40_longk": _wc_case(40, 1280, 1024, 128, dt.U4, seed=26),
+    "wc_tc_s4_g256_m130_longk": _wc_case(130, 640, 2048, 256, dt.S4, seed=27),
     # 8-bit weight decompression on the tensor cores (any M): s8 with grouped f32-free bf16 scales and s8
     # zero-points, u8 per-column without zero-points, one row
     "wc8_s8_g64_m5": _wc_case(5, 200, 256, 64, dt.S8, seed=21),
     "wc8_u8_perN_m70": _wc_case(70, 136, 192, 192, dt.U8, seed=22, zp="none"),
     "wc8_s8_g128_m1_common_zp": _wc_case(1, 384, 256, 128, dt.S8, seed=23, zp="common"),
+    "wc8_s8_g64_m5_longk": _wc_case(5, 1280, 1024, 64, dt.S8, seed=28),
     "wc_s4_g32_m2_f32dst": _wc_case(2, 32, 128, 32, dt.S4, dst_dt=dt.F32),
     "wc_s8_perN_common_zp": _wc_case(5, 48, 96, 96, dt.S8, zp="common"),
     "wc_u8_g32_nozp": _wc_case(4, 40, 64, 32, dt.U8, zp="none"),

@@ -19,8 +19,10 @@
 // column per lane, so that stores of a dst row are coalesced.
 //
 //   warp 0        TMA producer (activations)           waits empty[s]   -> full_a[s] (tx bytes)
-//   warp 1        TMEM owner and MMA issuer            waits full_a[s]  -> empty[s], acc_full
-//   warps 2..17   four dequantising groups (group g    waits empty[g]   -> full_a[g]; acc_full -> acc_empty
+//   warps 1, 2    MMA issuers (warp 1 owns TMEM):      wait full_a[i]   -> empty[i], acc_full
+//                 issuer j takes the tile's k-blocks
+//                 j, j + 2, ... into accumulator j
+//   warps 3..18   four dequantising groups (group g    wait empty[i - 4] -> full_a[i]; acc_full -> acc_empty
 //                 owns stage g), then the epilogue
 //
 // Weights are read in the layouts written by the pack kernels below.  B200_WEI_WC4_TC:
@@ -48,8 +50,7 @@ namespace wctc {
 constexpr int TN = 128;              // output columns per tile (UMMA M, TMEM lanes)
 constexpr int TK = 64;               // k per stage: 128 bytes of bf16 = one swizzle row
 constexpr int GROUPS = 4;            // dequantising warp groups, each converts every fourth k-block
-constexpr int A_STAGES = 4;          // stages of converted weights, one per group
-constexpr int MAX_B_STAGES = 16;     // stages of activations: as many as fit (a power of two), at least A_STAGES
+constexpr int MAX_STAGES = 8;        // ring depths are 4, 6 or 8: converted weights SA, activations SB <= SA
 constexpr int GROUP_WARPS = TN / 32; // one thread per output column of the tile
 constexpr int DQ_WARPS = GROUPS * GROUP_WARPS;
 // per weight width (4 or 8 bits): packed bytes of one column in one k-block, of a whole block,
@@ -57,22 +58,29 @@ constexpr int DQ_WARPS = GROUPS * GROUP_WARPS;
 __host__ __device__ constexpr int pf_bytes(int wbits) { return TK * wbits / 8; }
 __host__ __device__ constexpr int block_bytes(int wbits) { return TN * TK * wbits / 8; }
 __host__ __device__ constexpr int pfs(int wbits) { return 2; }
-constexpr int NUM_THREADS = 64 + DQ_WARPS * 32;
+// One thread issuing a k-block's four MMAs and its commit, with one look at a barrier, takes about
+// 800 cycles per block however small the MMAs are, three times what the tensor pipe needs for them
+// at 128 activation rows -- so two threads issue alternate k-blocks, each into an accumulator of
+// its own (f32 partial sums added by the epilogue), and together keep the pipe fed.
+constexpr int ISSUERS = 2;
+constexpr int FIRST_DQ_WARP = 1 + ISSUERS;
+constexpr int NUM_THREADS = (FIRST_DQ_WARP + DQ_WARPS) * 32;
 constexpr int A_BYTES = TN * TK * 2; // dequantised weights tile, 16 KiB
 constexpr uint32_t WAIT_SPINS = 1u << 24; // polls of the drain loop
 constexpr uint32_t WAIT_TRIES = 1u << 19; // hardware-suspended waits of up to ~2 us each
 enum : uint32_t { ST_WAIT_FULL = 0x1000, ST_WAIT_EMPTY = 0x2000, ST_WAIT_ACC = 0x4000 };
 
-// One pair of barriers per k-block modulo the depth B of the activations ring (B >= 4, a power of
-// two): full[i] collects the four warp arrivals of the converted weights and the bytes of the
-// activations' copy of block i; done[i] is the arrival of the commit behind block i's MMAs.  The
-// converters wait on done for block i - 4 (their stage of the weights ring), the copy-issuing
-// thread for block i - B: one wait and one commit per block for the MMA-issuing thread, whose
-// loop sets the pace.  The activations ring is the deep one because a copy of 128-byte row
-// pieces from L2 takes about 1.4 us to land, several times what a block's conversion and MMAs take.
+// One pair of barriers per k-block modulo the depth SA of the weights ring (4, 6 or 8; the
+// activations ring has SB <= SA stages): full[i] collects the four warp arrivals of the converted
+// weights and the bytes of the activations' copy of block i; done[i] ("empty" below) is the
+// arrival of the commit behind block i's MMAs.  The converters wait on done for block i - SA,
+// the copy-issuing thread for block i - SB: one look and one commit per block for an MMA-issuing
+// thread.  Both rings want depth: a copy of 128-byte row pieces from L2 takes about 1.4 us to
+// land, and a group may only refill a weights stage when the MMAs that read it have retired, a
+// microsecond after they were issued; at 128 activation rows six stages of each fit.
 struct ctrl_t {
-    uint64_t full_a[MAX_B_STAGES];
-    uint64_t empty[MAX_B_STAGES];
+    uint64_t full_a[MAX_STAGES];
+    uint64_t empty[MAX_STAGES];
     uint64_t acc_full, acc_empty;
     uint32_t tmem_base;
     volatile uint32_t abort;
@@ -88,8 +96,7 @@ struct args_t {
     uint32_t tmem_cols;
     uint32_t gs_blocks, gz_blocks; // K-group sizes of scales and zero-points in k-blocks of 64 (K / 64 when not grouped)
     uint32_t gs_shift, gz_shift;   // their base-2 logarithms (the FASTQ instantiation requires powers of two)
-    uint32_t wait_mode;            // bit 0: the two issuing threads wait suspended instead of polling; bit 1: the converters poll
-    uint32_t b_stages;             // depth of the activations ring: 4, 8 or 16
+    uint32_t a_stages, b_stages;   // ring depths (4, 6 or 8): converted weights, activations (b_stages <= a_stages)
     float nibble_offset;     // 4-bit weights: 128 (u4) or 136 (s4 stored offset by 8)
     uint32_t byte_xor;       // 8-bit weights: 0x80808080 for s8 (to offset binary), 0 for u8
 };
@@ -234,8 +241,12 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     const uint32_t b_bytes = (uint32_t)nb * (TK * 2); // a multiple of 2 KiB: every stage of either ring starts on a 1 KiB boundary
     // both ring depths are powers of two: block index -> stage and use count by mask and shift (the
     // loops of the two issuing threads set the pace; a division there costs more than the MMAs' issue)
-    constexpr uint32_t SA = A_STAGES, SA_MASK = SA - 1;
-    const uint32_t SB = args.b_stages, SB_MASK = SB - 1, SB_SHIFT = SB == 16 ? 4 : SB == 8 ? 3 : 2;
+    // block index -> stage and use count; the depths are 4, 6 or 8 so that this is a mask and a shift or
+    // a division by a constant (the loops of the issuing threads set the pace: a division by a
+    // run-time value there costs more than the MMAs' issue)
+    const uint32_t SA = args.a_stages, SB = args.b_stages;
+    auto rmod = [](uint32_t x, uint32_t n) -> uint32_t { return n == 8 ? (x & 7u) : n == 6 ? x % 6u : (x & 3u); };
+    auto rdiv = [](uint32_t x, uint32_t n) -> uint32_t { return n == 8 ? (x >> 3) : n == 6 ? x / 6u : (x >> 2); };
     uint8_t *smem_b = smem + (size_t)SA * A_BYTES;                             // [SB][nb][128 bytes] activations
     uint8_t *pf_ring = smem_b + (size_t)SB * b_bytes;                          // [PFS][threads][PF_BYTES] packed weights in flight
     ctrl_t *ctrl = (ctrl_t *)(pf_ring + (size_t)PFS * DQ_WARPS * 32 * PF_BYTES);
@@ -244,11 +255,11 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     const int KB = args.k_blocks;
 
     if (threadIdx.x == 0) {
-        for (uint32_t s = 0; s < SB; ++s) {
+        for (uint32_t s = 0; s < SA; ++s) {
             mbar_init(&ctrl->full_a[s], GROUP_WARPS + 1); // the group's warps and the activations' copy
             mbar_init(&ctrl->empty[s], 1);
         }
-        mbar_init(&ctrl->acc_full, 1);
+        mbar_init(&ctrl->acc_full, ISSUERS);
         mbar_init(&ctrl->acc_empty, DQ_WARPS);
         ctrl->abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -270,34 +281,41 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         if (lane == 0) {
             uint32_t it = 0;
             bool ok = true;
+            // stage indices and the parity to wait for are carried along and wrapped by hand: this
+            // loop and the issuers' set the pace, and every instruction in them counts
+            uint32_t sa = 0, sb = 0;          // barrier / activations stage of block `it`
+            uint32_t pa = 0, ppar = 0;        // barrier of block it - SB and the parity of its commit (valid once it >= SB)
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
                 const int row0 = (int)((tile / args.n_tiles) * args.rows_per_pass);
                 for (int kb = 0; kb < KB; ++kb, ++it) {
                     // this block's stage of the activations ring was last read by block it - SB
                     if (it >= SB) {
-                        const uint32_t prev = it - SB;
-                        if (!(ok = (args.wait_mode & 1) ? mbar_wait(&ctrl->empty[prev & SB_MASK], (prev >> SB_SHIFT) & 1, ctrl, p.status, ST_WAIT_EMPTY)
-                                                        : mbar_wait_poll(&ctrl->empty[prev & SB_MASK], (prev >> SB_SHIFT) & 1, ctrl, p.status, ST_WAIT_EMPTY)))
-                            break;
+                        if (!(ok = mbar_wait_poll(&ctrl->empty[pa], ppar, ctrl, p.status, ST_WAIT_EMPTY))) break;
+                        if (++pa == SA) pa = 0, ppar ^= 1;
                     }
-                    mbar_expect_tx(&ctrl->full_a[it & SB_MASK], b_bytes);
-                    tma_load_2d(smem_b + (size_t)(it & SB_MASK) * b_bytes, &tmap_x, kb * (TK * 2), row0, &ctrl->full_a[it & SB_MASK]); // byte coordinates
+                    uint64_t *full = &ctrl->full_a[sa];
+                    mbar_expect_tx(full, b_bytes);
+                    tma_load_2d(smem_b + (size_t)sb * b_bytes, &tmap_x, kb * (TK * 2), row0, full); // byte coordinates
+                    if (++sa == SA) sa = 0;
+                    if (++sb == SB) sb = 0;
                 }
             }
             // drain: every copy this thread issued must have landed before the CTA may exit
             const uint32_t issued = it;
             for (uint32_t j = issued > SB ? issued - SB : 0; j < issued; ++j) {
-                const uint32_t s = j & SB_MASK, r = j >> SB_SHIFT;
+                const uint32_t s = rmod(j, SA), r = rdiv(j, SA);
                 for (uint32_t i = 0; i < WAIT_SPINS; ++i) {
                     if (mbar_test(&ctrl->full_a[s], r & 1)) break;
                     __nanosleep(64);
                 }
             }
         }
-    } else if (warp == 1) {
-        // ---------------- MMA issuer ----------------
+    } else if (warp <= ISSUERS) {
+        // ---------------- MMA issuers ----------------
         if (lane == 0) {
-            uint32_t it = 0, tile_i = 0;
+            const int me = warp - 1;                                 // this issuer's k-blocks: me, me + ISSUERS, ...
+            const uint32_t tmem_d = tmem_base + (uint32_t)(me * nb); // and its accumulator: nb columns of tensor memory
+            uint32_t it0 = 0, tile_i = 0;
             bool ok = true;
             // descriptors of stage 0; a stage further on is stage_bytes / 16 more in the address field
             const uint64_t adesc0 = make_smem_desc(smem_u32(smem)), bdesc0 = make_smem_desc(smem_u32(smem_b));
@@ -308,23 +326,32 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             // No tcgen05 fence inside the loop: the operands are in shared memory, written through
             // the async proxy (the copies) or published with fence.proxy.async (the converters), and
             // ordered by the barrier; the fence belongs where tensor memory changes hands (below).
+            // (The look ISSUERS blocks ahead is unambiguous: the phase before the one asked about, on
+            // the same barrier, belongs to one of this thread's own earlier blocks -- the ring depth is
+            // a multiple of ISSUERS.)
             bool early = false; // the early look's answer for the block at hand
-            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tile_i) {
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tile_i, it0 += (uint32_t)KB) {
                 if (!(ok = mbar_wait_poll(&ctrl->acc_empty, (tile_i & 1) ^ 1, ctrl, p.status, ST_WAIT_ACC))) break;
                 tc_fence_after();
-                for (int kb = 0; kb < KB; ++kb, ++it) {
-                    const uint32_t s = it & SB_MASK, r = it >> SB_SHIFT;
+                early = false; // looks do not cross tiles: the next tile's first block is another distance away
+                // stage, parity and activations stage of this thread's first block of the tile; from
+                // there on they advance by ISSUERS with a wrap (SA and SB are multiples of ISSUERS)
+                uint32_t s = rmod(it0 + (uint32_t)me, SA), par = rdiv(it0 + (uint32_t)me, SA) & 1, sb = rmod(it0 + (uint32_t)me, SB);
+                for (int kb = me; kb < KB; kb += ISSUERS) {
                     // one barrier per block: converted weights (four warps) and activations (copy bytes)
-                    if (!early && !(ok = mbar_wait_poll(&ctrl->full_a[s], r & 1, ctrl, p.status, ST_WAIT_FULL))) break;
-                    if (args.wait_mode & 4) tc_fence_after();
-                    const uint32_t nx = it + 1;
-                    const bool next_early = (args.wait_mode & 8) ? false : mbar_test(&ctrl->full_a[nx & SB_MASK], (nx >> SB_SHIFT) & 1);
-                    const uint64_t adesc = adesc0 + (uint64_t)((it & SA_MASK) * (A_BYTES >> 4)), bdesc = bdesc0 + (uint64_t)(s * (b_bytes >> 4));
+                    if (!early && !(ok = mbar_wait_poll(&ctrl->full_a[s], par, ctrl, p.status, ST_WAIT_FULL))) break;
+                    uint32_t s2 = s + ISSUERS, par2 = par;
+                    if (s2 >= SA) s2 -= SA, par2 ^= 1;
+                    const bool next_early = kb + ISSUERS < KB && mbar_test(&ctrl->full_a[s2], par2);
+                    const uint64_t adesc = adesc0 + (uint64_t)(s * (A_BYTES >> 4)), bdesc = bdesc0 + (uint64_t)(sb * (b_bytes >> 4));
 #pragma unroll
                     for (int k = 0; k < TK / 16; ++k) // 16 bf16 = 32 bytes of K per instruction: +2 in 16-byte units
-                        tc_mma_bf16(tmem_base, adesc + 2 * k, bdesc + 2 * k, args.idesc, (kb | k) != 0);
+                        tc_mma_bf16(tmem_d, adesc + 2 * k, bdesc + 2 * k, args.idesc, (kb >= ISSUERS) | (k != 0));
                     tc_commit(&ctrl->empty[s]);
                     early = next_early;
+                    s = s2, par = par2;
+                    sb += ISSUERS;
+                    if (sb >= SB) sb -= SB;
                 }
                 if (ok) tc_commit(&ctrl->acc_full);
             }
@@ -335,10 +362,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         // land in operand stage g, i.e. every fourth one: a thread then has a quarter of the
         // iterations, each with a whole 64-k row to convert, and the four groups work on four
         // different stages at the same time.
-        const int dq = threadIdx.x - 64;    // 0 .. 511
+        const int dq = threadIdx.x - FIRST_DQ_WARP * 32; // 0 .. 511
         const int grp = dq >> 7, r = dq & 127;
         const int quarter = warp & 3;       // TMEM lanes this warp may read: 32*quarter .. +31
-        const int which = (warp - 2) >> 2;  // four warps share a quarter and split the chunks of columns
+        const int which = (warp - FIRST_DQ_WARP) >> 2; // four warps share a quarter and split the chunks of columns
         const uint32_t sw = (uint32_t)(r & 7);
         const bool simple_epilogue = p.npo == 0 && !p.dst_scale.ptr && (!p.bias || p.bias_sm == 0)
                 && (p.dst_dt == B200_DT_BF16 || p.dst_dt == B200_DT_F32);
@@ -422,8 +449,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             load_q(first_kb);
             for (int j = 0; j < iters; ++j) {
                 const int kb = first_kb + j * GROUPS;
-                const uint32_t it = it0 + (uint32_t)kb; // the block's running index: stage grp of the weights ring
-                uint8_t *tile_a = row_a + (size_t)grp * A_BYTES;
+                const uint32_t it = it0 + (uint32_t)kb, stage = rmod(it, SA); // the block's running index and its stage of the weights ring
+                uint8_t *tile_a = row_a + (size_t)stage * A_BYTES;
                 // decode this block's scale and zero-point, then ask for the next block's
                 const float sf = FASTQ ? 0.f : scale_f32();
                 const int zpi = FASTQ ? 0 : zp_int();
@@ -447,9 +474,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                 }
                 // the stage was last read by the MMAs of block it - 4
                 const uint32_t prev = it - SA;
-                if (it >= SA
-                        && !(ok = (args.wait_mode & 2) ? mbar_wait_poll(&ctrl->empty[prev & SB_MASK], (prev >> SB_SHIFT) & 1, ctrl, p.status, ST_WAIT_EMPTY)
-                                                       : mbar_wait(&ctrl->empty[prev & SB_MASK], (prev >> SB_SHIFT) & 1, ctrl, p.status, ST_WAIT_EMPTY))) {
+                if (it >= SA && !(ok = mbar_wait(&ctrl->empty[stage], rdiv(prev, SA) & 1, ctrl, p.status, ST_WAIT_EMPTY))) {
                     asm volatile("cp.async.wait_group 0;" ::: "memory");
                     break;
                 }
@@ -503,7 +528,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                 // generic-proxy writes -> visible to the tensor core's (async proxy) reads
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&ctrl->full_a[it & SB_MASK]);
+                if (lane == 0) mbar_arrive(&ctrl->full_a[stage]);
                 request(j + PFS); // the ring slot of iteration j is free again
             }
             if (!ok) break;
@@ -522,6 +547,12 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                 if (m0 + c * 16 >= m_end) break; // warp-uniform: nothing but padding from here on
                 uint32_t v[16];
                 tmem_ld16(trow + c * 16, v);
+                if (KB > 1) { // the second issuer's partial sums (it has none when the tile is a single k-block)
+                    uint32_t w[16];
+                    tmem_ld16(trow + nb + c * 16, w);
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) + __uint_as_float(w[j]));
+                }
                 if (simple_epilogue) {
                     // no post-ops, no dst scale, bias per column or none, bf16 / f32 dst: a handful of
                     // instructions per element, lanes along a dst row
@@ -720,15 +751,10 @@ extern "C" int b200_matmul_wc_tc_launch(const b200_matmul_params_t *p, b200_stre
     const bool z4 = p->wei_zp.ptr && (p->wei_zp.dt == B200_DT_U4 || p->wei_zp.dt == B200_DT_S4);
     const bool fastq = w4 && pow2(a.gs_blocks) && pow2(a.gz_blocks) && (!p->wei_scale.ptr || p->wei_scale.dt == B200_DT_BF16)
             && (!p->wei_zp.ptr || z4) && (p->K / TK + 1) * (p->N + 1) < ((int64_t)1 << 31);
-    static const uint32_t wait_mode_env = [] {
-        const char *v = std::getenv("ONEDNN_B200_WCTC_WAIT");
-        return v ? (uint32_t)std::atoi(v) : 0u;
-    }();
-    a.wait_mode = wait_mode_env;
     a.nibble_offset = p->wei_dt == B200_DT_S4 ? 136.f : 128.f;
     a.byte_xor = p->wei_dt == B200_DT_S8 ? 0x80808080u : 0u;
     a.tmem_cols = 32;
-    while ((int)a.tmem_cols < a.nb) a.tmem_cols *= 2;
+    while ((int)a.tmem_cols < ISSUERS * a.nb) a.tmem_cols *= 2; // one accumulator of nb columns per issuing thread
     // instruction descriptor: D f32, A and B bf16, both K-major, N = nb, M = 128
     a.idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(a.nb >> 3) << 17) | ((uint32_t)(TN >> 4) << 24);
 
@@ -753,21 +779,19 @@ extern "C" int b200_matmul_wc_tc_launch(const b200_matmul_params_t *p, b200_stre
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     const int64_t tiles = (int64_t)a.n_tiles * a.m_passes;
     const unsigned grid = (unsigned)(tiles < sms ? tiles : sms);
-    // shared memory: the four stages of converted weights, the packed-weights ring, and as many
-    // stages of activations as fit (a power of two, 4 .. 16)
+    // shared memory: the packed-weights ring, then the deepest pair of rings that fits
     const size_t b_bytes = (size_t)a.nb * TK * 2;
-    const size_t fixed = 1024 + (size_t)A_STAGES * A_BYTES + (size_t)pfs(wbits) * DQ_WARPS * 32 * pf_bytes(wbits) + sizeof(ctrl_t);
-    size_t sb = (227 * 1024 - fixed) / b_bytes;
-    static const int b_stages_env = [] {
-        const char *v = std::getenv("ONEDNN_B200_WCTC_BSTAGES");
-        return v ? std::atoi(v) : 0;
-    }();
-    if (b_stages_env >= 4 && (size_t)b_stages_env < sb) sb = (size_t)b_stages_env;
-    if (sb > MAX_B_STAGES) sb = MAX_B_STAGES;
-    if (sb < A_STAGES) return B200_ERR_UNSUPPORTED;
-    while (sb & (sb - 1)) sb &= sb - 1; // a power of two
-    a.b_stages = (uint32_t)sb;
-    const size_t smem = fixed + sb * b_bytes;
+    const size_t fixed = 1024 + (size_t)pfs(wbits) * DQ_WARPS * 32 * pf_bytes(wbits) + sizeof(ctrl_t);
+    static const int depths[][2] = {{8, 8}, {8, 6}, {6, 6}, {6, 4}, {4, 4}};
+    a.a_stages = a.b_stages = 0;
+    for (const auto &d : depths)
+        if (fixed + (size_t)d[0] * A_BYTES + (size_t)d[1] * b_bytes <= 227 * 1024) {
+            a.a_stages = (uint32_t)d[0];
+            a.b_stages = (uint32_t)d[1];
+            break;
+        }
+    if (!a.a_stages) return B200_ERR_UNSUPPORTED;
+    const size_t smem = fixed + (size_t)a.a_stages * A_BYTES + (size_t)a.b_stages * b_bytes;
     static std::mutex mu;
     static bool attr_done[64] = {};
     {

@@ -871,43 +871,68 @@ __global__ void __launch_bounds__(640, 1) matmul_tc8_kernel(const __grid_constan
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
         if (lane == 0 && rank == 0) {
-            uint32_t it = 0, tile_i = 0;
+            uint32_t tile_i = 0;
             bool ok = true;
-            bool early = false; // the early look's answer for the k-block at hand
-            // descriptors of stage 0; a stage further on is STAGE_BYTES / 16 more in the address field
+            bool early = false;       // the early look's answer for the k-block at hand
+            uint32_t st = 0, par = 0; // stage of the k-block at hand and the parity of its fill
+            // descriptors of stage 0; a stage further on is STAGE_BYTES / 16 more in the address field,
+            // a k-step of 32 bytes 2 more
             const uint64_t adesc0 = make_smem_desc(smem_u32(smem)), bdesc0 = make_smem_desc(smem_u32(smem) + A_BYTES);
+            constexpr bool FULLDESC = NST <= 4;
+            constexpr int DK = FULLDESC ? BK / 32 : 1;
+            uint64_t adesc[NST][DK], bdesc[NST][DK];
+#pragma unroll
+            for (int s = 0; s < NST; ++s)
+#pragma unroll
+                for (int k = 0; k < DK; ++k) {
+                    adesc[s][k] = adesc0 + (uint64_t)(s * (SBYTES >> 4) + 2 * k);
+                    bdesc[s][k] = bdesc0 + (uint64_t)(s * (SBYTES >> 4) + 2 * k);
+                }
             for (int u = unit0; u < args.units && ok; u += ustep, ++tile_i) {
                 const uint32_t a = tile_i & 1, use = tile_i >> 1;
                 const uint32_t idesc = u < args.full_units ? args.idesc : args.idesc_tail;
                 if (!(ok = mbar_wait_poll(&ctrl->tmem_empty[a], (use & 1) ^ 1, ctrl, p.status, ST_WAIT_TMEM_EMPTY))) break;
                 tcgen05_fence_after();
                 const uint32_t tmem_d = tmem_base + a * BN;
-                for (int kb = 0; kb < KB; ++kb, ++it) {
-                    const uint32_t s = it % NST, r = it / NST;
-                    // This thread's loop is what the tensor pipe waits for: a look at a barrier costs a
-                    // few hundred cycles even when its phase completed long ago, which is more than the
-                    // pipe needs for half a k-block.  So the look for k-block i + 1 is issued before the
-                    // MMAs of k-block i and its answer read after them; the thread polls only when that
-                    // early look said "not yet".  No tcgen05 fence per k-block: the operands are in shared
-                    // memory, written through the async proxy and ordered by the barrier; the fence
-                    // belongs where tensor memory changes hands (above).
-                    if (!early && !(ok = mbar_wait_poll(&ctrl->full[s], r & 1, ctrl, p.status, ST_WAIT_FULL))) break;
-                    // (The look is unambiguous: the phase before the one asked about belongs to a block
-                    // this thread has already consumed.  Measured on 4096^3, 16384 x 8192 x 28672 and
-                    // fp8 8192^3: 9 %, 4 % and 6 % faster than polling at the top of every k-block;
-                    // looking two blocks ahead was slower again.)
-                    const uint32_t nx = it + 1;
-                    const bool next_early = mbar_test(&ctrl->full[nx % NST], (nx / NST) & 1);
-                    const uint64_t adesc = adesc0 + (uint64_t)(s * (SBYTES >> 4)), bdesc = bdesc0 + (uint64_t)(s * (SBYTES >> 4));
+                // This thread's loop is what the tensor pipe waits for, and it shares its scheduler with
+                // four epilogue warps: once those are busy every instruction here takes about twice as
+                // long, and a k-block whose four MMAs keep the pipe busy for 550 cycles took 900 to issue.
+                // So the loop is unrolled over the stages of the ring, with the operand descriptors of
+                // every stage and k-step held in registers (the single-CTA kernel; the pair kernel, with
+                // six stages, keeps one per stage and adds the k-step): no index or descriptor arithmetic
+                // is left per k-block.  And since a look at a barrier costs a few hundred cycles even when
+                // its phase completed long ago, the look for k-block i + 1 is issued before the MMAs of
+                // k-block i and its answer read after them; the thread polls only when that early look
+                // said "not yet" (the look is unambiguous: the phase before the one asked about belongs to
+                // a block this thread has already consumed; looking two blocks ahead was slower again).
+                // No tcgen05 fence per k-block: the operands are in shared memory, written through the
+                // async proxy and ordered by the barrier; the fence belongs where tensor memory changes
+                // hands (above).
+                for (int kb = 0; kb < KB && ok;) {
 #pragma unroll
-                    for (int k = 0; k < BK / 32; ++k) // 32 bytes of K per instruction: +2 in 16-byte units
-                        if (PAIR)
-                            tcgen05_mma_pair<FP8>(tmem_d, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0);
-                        else
-                            tcgen05_mma<FP8>(tmem_d, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0);
-                    if (PAIR) tcgen05_commit_pair(&ctrl->empty[s]);
-                    else tcgen05_commit(&ctrl->empty[s]);
-                    early = next_early;
+                    for (int s = 0; s < NST; ++s) {
+                        if (st == (uint32_t)s && kb < KB && ok) {
+                            if (!early) ok = mbar_wait_poll(&ctrl->full[s], par, ctrl, p.status, ST_WAIT_FULL);
+                            if (ok) {
+                                const int s2 = (s + 1) % NST; // a constant in each unrolled copy
+                                const uint32_t par2 = s2 == 0 ? par ^ 1u : par;
+                                const bool next_early = mbar_test(&ctrl->full[s2], par2);
+#pragma unroll
+                                for (int k = 0; k < BK / 32; ++k) { // 32 bytes of K per instruction: +2 in 16-byte units
+                                    const uint64_t ad = FULLDESC ? adesc[s][k] : adesc[s][0] + 2 * k;
+                                    const uint64_t bd = FULLDESC ? bdesc[s][k] : bdesc[s][0] + 2 * k;
+                                    if (PAIR) tcgen05_mma_pair<FP8>(tmem_d, ad, bd, idesc, (kb | k) != 0);
+                                    else tcgen05_mma<FP8>(tmem_d, ad, bd, idesc, (kb | k) != 0);
+                                }
+                                if (PAIR) tcgen05_commit_pair(&ctrl->empty[s]);
+                                else tcgen05_commit(&ctrl->empty[s]);
+                                early = next_early;
+                                st = (uint32_t)s2;
+                                par = par2;
+                                ++kb;
+                            }
+                        }
+                    }
                 }
                 if (ok) {
                     if (PAIR) tcgen05_commit_pair(&ctrl->tmem_full[a]);

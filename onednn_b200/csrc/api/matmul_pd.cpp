@@ -152,7 +152,9 @@ dnnl_status_t matmul_validate(const dnnl_memory_desc &src, const dnnl_memory_des
             sum_dt = e.dt;
         } else if (e.kind == dnnl_binary) {
             INVALID_IF(e.src1.ndims != ndims);
-            for (int d = 0; d < ndims; ++d) INVALID_IF(!one_of(e.src1.dims[d], 1, dst.dims[d]));
+            // (a dst dim known only at execution is checked then, on the concrete descriptors)
+            for (int d = 0; d < ndims; ++d)
+                INVALID_IF(dst.dims[d] != DNNL_RUNTIME_DIM_VAL && !one_of(e.src1.dims[d], 1, dst.dims[d]));
         } else if (e.kind != dnnl_eltwise && e.kind != dnnl_prelu) {
             return dnnl_unimplemented;
         }

@@ -43,7 +43,7 @@ UNIT = "TOPS"
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the benchmark kernel, from the ncu
 # capture summarised in profiles/tc8_int8_c1_full.md: `bench.py --case c1 --steps 6`, which rotates
 # over the same input sets as the timed region, third launch captured
-NCU_DRAM_BYTES_PER_LAUNCH = None
+NCU_DRAM_BYTES_PER_LAUNCH = 50.74e6  # dram__bytes_read.sum + dram__bytes_write.sum of one launch, profiles/tc8_int8_c1_full.md
 WORKLOAD = "int8 s8:s8:s8 4096x4096:4096x4096, per-N wei scales, bf16 bias, gelu_tanh + sum:0.5, dst scale 0.1 zp 3"
 
 
@@ -493,7 +493,8 @@ def main():
                          "frac": achieved / int8_peak, "traffic": NCU_DRAM_BYTES_PER_LAUNCH,
                          "traffic_note": "dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu capture of "
                                          "`bench.py --case c1` over rotating input sets summarised in "
-                                         "profiles/tc8_int8_c1_full.md (null until that capture exists); algorithmic bytes 67.1e6",
+                                         "profiles/tc8_int8_c1_full.md (below the algorithmic 67.1e6 bytes: the rotating sets partly survive in "
+                                         "L2 and the s8 dst is written back after the kernel)",
                          "kernel": "matmul_tc8_kernel<int8, EPI_GELU_Q, SUM_8BIT>", "kernel_ms": ms_per_step, "kernel_ms_single_launch_between_events": kern_avg,
                          "peak_note": "2 x %s bf16 dense burst (%.1f TF/s): MEASURED_PEAKS.json holds no int8 figure; nominal 4500; "
                                       "`measured_mma_peak` is this run's own bare tcgen05.mma issue loop"

@@ -191,6 +191,7 @@ struct dnnl_primitive_desc {
     // batched problems (more than two dims): the descriptor of one 2-D slice, which the
     // selected implementation runs once per batch index
     std::shared_ptr<dnnl_primitive_desc> inner;
+    bool collapsed = false; // batched with broadcast weights and dense rows: `inner` is the whole problem as one 2-D matmul
     // some dims are DNNL_RUNTIME_DIM_VAL: the implementation is chosen at execution, from the
     // descriptors of the memory arguments
     bool runtime = false;

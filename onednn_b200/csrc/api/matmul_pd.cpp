@@ -437,6 +437,65 @@ static dnnl_memory_desc slice_2d(const dnnl_memory_desc &md) {
     return o;
 }
 
+// (batch..., R, C) seen as (prod(batch) * R, C): possible when the batch dims and R form one dense run of rows
+static bool collapse_rows(const dnnl_memory_desc &md, int nb, dnnl_memory_desc &out) {
+    dnnl_memory_desc r = md;
+    if (r.is_any()) make_plain(r);
+    if (!r.is_plain()) return false;
+    const int nd = r.ndims;
+    int64_t rows = r.dims[nd - 2];
+    for (int d = nb - 1; d >= 0; --d) {
+        if (r.strides[d] != r.strides[d + 1] * r.dims[d + 1]) return false;
+        rows *= r.dims[d];
+    }
+    out = dnnl_memory_desc();
+    out.ndims = 2;
+    out.data_type = r.data_type;
+    out.format_kind = r.format_kind;
+    out.packed_layout = r.packed_layout;
+    out.offset0 = r.offset0;
+    out.dims[0] = rows;
+    out.dims[1] = r.dims[nd - 1];
+    out.strides[0] = r.strides[nd - 2];
+    out.strides[1] = r.strides[nd - 1];
+    return true;
+}
+
+// A batched problem whose weights are the same for every batch index (all their batch dims 1) and
+// whose src and dst rows run densely through the batch dims is one 2-D matmul with
+// prod(batch) * M rows: one launch instead of one per batch index.  Everything that varies with
+// the row inside a batch index (per-row quantisation, a prelu mask over M, a binary operand that
+// is neither per-column nor a full dense tensor) keeps the per-index form.
+static bool collapsible(const dnnl_primitive_desc *pd, int nb, dnnl_memory_desc &src2, dnnl_memory_desc &dst2,
+        std::vector<dnnl_memory_desc> &src1_2d) {
+    for (int d = 0; d < nb; ++d)
+        if (pd->user_wei.dims[d] != 1) return false;
+    if (pd->user_src.is_any() || pd->user_dst.is_any()) return false; // `any` would be dense, but keep the given-layout rule simple
+    if (!collapse_rows(pd->user_src, nb, src2) || !collapse_rows(pd->user_dst, nb, dst2)) return false;
+    if (dt_nbits(src2.data_type) == 4 || dt_nbits(dst2.data_type) == 4) return false;
+    if (pd->user_bias.ndims)
+        for (int d = 0; d <= nb; ++d)
+            if (pd->user_bias.dims[d] != 1) return false;
+    for (auto *m : {&pd->attr.scales, &pd->attr.zero_points})
+        for (auto &kv : *m)
+            if (kv.second.set && kv.first != DNNL_ARG_WEIGHTS && (kv.second.mask & (1 << nb))) return false; // varies along M
+    const auto &po = pd->attr.post_ops.entries;
+    src1_2d.assign(po.size(), dnnl_memory_desc());
+    for (size_t i = 0; i < po.size(); ++i) {
+        if (po[i].kind == dnnl_prelu && (po[i].mask & (1 << nb))) return false;
+        if (po[i].kind != dnnl_binary) continue;
+        const dnnl_memory_desc &s1 = po[i].src1;
+        bool all_one = true, all_full = true;
+        for (int d = 0; d <= nb; ++d) {
+            all_one = all_one && s1.dims[d] == 1;
+            all_full = all_full && s1.dims[d] == pd->user_dst.dims[d];
+        }
+        if (all_one) src1_2d[i] = slice_2d(s1);
+        else if (!(all_full && !s1.is_any() && collapse_rows(s1, nb, src1_2d[i]))) return false;
+    }
+    return true;
+}
+
 static dnnl_status_t select_batched(dnnl_primitive_desc *pd, int first) {
     const int nd = pd->user_dst.ndims, nb = nd - 2;
     if (pd->user_src.format_kind == dnnl_format_kind_opaque || pd->user_wei.format_kind == dnnl_format_kind_opaque
@@ -453,18 +512,23 @@ static dnnl_status_t select_batched(dnnl_primitive_desc *pd, int first) {
             if (kv.second.mask & ((1 << nb) - 1)) return first == 0 ? dnnl_unimplemented : dnnl_last_impl_reached;
             kv.second.mask >>= nb;
         }
-    for (auto &e : in->attr.post_ops.entries) {
+    for (auto &e : in->attr.post_ops.entries)
+        if (e.kind == dnnl_binary && e.src1.ndims != nd) return dnnl_invalid_arguments;
+    dnnl_memory_desc src2, dst2;
+    std::vector<dnnl_memory_desc> src1_2d;
+    const bool collapse = collapsible(pd, nb, src2, dst2, src1_2d);
+    for (size_t i = 0; i < in->attr.post_ops.entries.size(); ++i) {
+        auto &e = in->attr.post_ops.entries[i];
         if (e.kind == dnnl_binary) {
-            if (e.src1.ndims != nd) return dnnl_invalid_arguments;
-            e.src1 = slice_2d(e.src1);
+            e.src1 = collapse ? src1_2d[i] : slice_2d(e.src1);
         } else if (e.kind == dnnl_prelu) {
             if (e.mask & ((1 << nb) - 1)) return first == 0 ? dnnl_unimplemented : dnnl_last_impl_reached;
             e.mask >>= nb;
         }
     }
-    in->user_src = slice_2d(pd->user_src);
+    in->user_src = collapse ? src2 : slice_2d(pd->user_src);
     in->user_wei = slice_2d(pd->user_wei); // weights given as `any` stay plain: packing is per 2-D matrix
-    in->user_dst = slice_2d(pd->user_dst);
+    in->user_dst = collapse ? dst2 : slice_2d(pd->user_dst);
     if (pd->user_bias.ndims) in->user_bias = slice_2d(pd->user_bias);
     // every batch index must start a 4-bit tensor on a byte: the 2-D slices are addressed by pointer
     for (const dnnl_memory_desc *md : {&pd->user_src, &pd->user_wei, &pd->user_dst}) {
@@ -486,6 +550,7 @@ static dnnl_status_t select_batched(dnnl_primitive_desc *pd, int first) {
     pd->impl_str = in->impl_str;
     pd->scratchpad = in->scratchpad;
     pd->inner = in;
+    pd->collapsed = collapse;
     return dnnl_success;
 }
 
@@ -504,6 +569,7 @@ static dnnl_status_t batched_execute(const dnnl_primitive *prim, dnnl_stream *st
     int64_t total = 1;
     for (int d = 0; d < nb; ++d) total *= pd->dst.dims[d];
     if (total == 0 || pd->dst.has_zero_dim() || pd->src.has_zero_dim() || pd->wei.has_zero_dim()) return dnnl_success;
+    if (pd->collapsed) total = 1; // the inner descriptor is the whole problem: one execution from the tensors' starts
     // the tensors that move with the batch index, their N-D descriptors and their 2-D slices
     struct moving_t { int arg; const dnnl_memory_desc *full; dnnl_memory_desc slice; dnnl_memory mem; };
     std::vector<moving_t> mv;

@@ -127,6 +127,40 @@ def test_batched_matches_oracle_per_slice(kind):
         assert (np.abs(g - w) <= c.atol + c.rtol * np.abs(w)).all(), "%s batch %s" % (kind, b)
 
 
+def _launches():
+    import ctypes as C
+    v = C.c_uint64()
+    assert api.lib().dnnl_b200_debug_counter(3, C.byref(v)) == 0
+    return v.value
+
+
+@pytest.mark.gpu
+def test_broadcast_weights_run_as_one_matmul():
+    """Weights shared by every batch index, src and dst rows dense through the batch dim: the
+    whole problem is one 2-D matmul of batch * M rows -- one pass of the kernels (weights pack,
+    their column sums, matmul) instead of one per batch index -- and equals the per-index results
+    of the oracle."""
+    eng = api.Engine()
+    strm = api.Stream(eng)
+    r = np.random.default_rng(95)
+    batch, wbatch, (M, N, K) = (2, 3), (1, 1), (40, 48, 64)
+    base = MatmulCase("bcast", M, N, K, src=r.integers(-128, 128, batch + (M, K), dtype=np.int8), src_dt=dt.S8,
+                      wei=r.integers(-127, 128, wbatch + (K, N), dtype=np.int8), wei_dt=dt.S8, dst_dt=dt.S8,
+                      src_scale=Quant(np.float32([0.02]), dt.F32, 0),
+                      wei_scale=Quant(r.uniform(1e-3, 4e-3, N).astype(np.float32), dt.F32, 2),
+                      dst_scale=Quant(np.float32([0.05]), dt.F32, 0),
+                      bias=r.uniform(-1, 1, (1, N)).astype(np.float32), bias_dt=dt.F32,
+                      post_ops=[W.eltwise("relu", 0.0)], exact=True, rtol=0, atol=0)
+    before = _launches()
+    got, impl = _run_batched(eng, strm, batch, wbatch, base)
+    used = _launches() - before
+    assert "tcgen05_i8" in impl
+    assert used <= 3, "%d launches for a problem that collapses into one matmul (six batch indices)" % used
+    for b in np.ndindex(*batch):
+        want = B.run_oracle(_slice_case(base, b, (0, 0)), exact_acc=1)
+        assert np.array_equal(got[b], want), "batch %s" % (b,)
+
+
 # ---- runtime dims ---------------------------------------------------------------------------
 
 RT = -(1 << 63)  # DNNL_RUNTIME_DIM_VAL

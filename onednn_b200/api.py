@@ -540,6 +540,8 @@ class ReorderPlan:
         self.stream.wait()
         c = self.case
         shape = (c.rows, c.cols) if c.dst_tag == "ab" else (c.cols, c.rows)
+        if c.dst_dt in (dt.S4, dt.U4):  # two values per byte along the contiguous dim
+            shape = (shape[0], shape[1] // 2)
         return self.mem["dst"].read(dt.RAW[c.dst_dt], shape)
 
 

@@ -29,7 +29,16 @@ static dnnl_status_t reorder_quant_validate(const dnnl_memory_desc &s, const dnn
         const dnnl_primitive_attr &attr) {
     if (!s.is_plain() || !d.is_plain()) return dnnl_unimplemented;
     if (s.ndims < 1 || s.ndims > 2) return dnnl_unimplemented;
-    if (dt_nbits(s.data_type) == 4 || dt_nbits(d.data_type) == 4) return dnnl_unimplemented;
+    const bool s4 = dt_nbits(s.data_type) == 4, d4 = dt_nbits(d.data_type) == 4;
+    if (s4 || d4) {
+        // decompressing a 4-bit tensor into f32 / bf16 / f16 with source-side scales and zero-points;
+        // nothing else (src/cpu/reorder/cpu_reorder_regular_s4.cpp, _u4.cpp list what the reference has)
+        if (!s4 || d4) return dnnl_unimplemented;
+        if (!(d.data_type == dnnl_f32 || d.data_type == dnnl_bf16 || d.data_type == dnnl_f16)) return dnnl_unimplemented;
+        if (attr.scale(DNNL_ARG_DST).set || attr.zp(DNNL_ARG_DST).set || !attr.post_ops.entries.empty()) return dnnl_unimplemented;
+        // a 4-bit source takes no scale common to the whole tensor (src/common/reorder.cpp:117-120)
+        if (attr.scale(DNNL_ARG_SRC).set && attr.scale(DNNL_ARG_SRC).mask == 0) return dnnl_invalid_arguments;
+    }
     const int full = (1 << s.ndims) - 1;
     for (const auto &kv : attr.scales) {
         if (!kv.second.set) continue;
@@ -42,7 +51,7 @@ static dnnl_status_t reorder_quant_validate(const dnnl_memory_desc &s, const dnn
         if (kv.second.mask & ~full) return dnnl_invalid_arguments;
     }
     // zero-points go with integer tensors only
-    auto is_int = [](int dt) { return dt == dnnl_s32 || dt == dnnl_s8 || dt == dnnl_u8; };
+    auto is_int = [](int dt) { return dt == dnnl_s32 || dt == dnnl_s8 || dt == dnnl_u8 || dt == dnnl_s4 || dt == dnnl_u4; };
     if (attr.zp(DNNL_ARG_SRC).set && !is_int(s.data_type)) return dnnl_invalid_arguments;
     if (attr.zp(DNNL_ARG_DST).set && !is_int(d.data_type)) return dnnl_invalid_arguments;
     if (attr.zp(DNNL_ARG_DST).set && (attr.zp(DNNL_ARG_DST).mask != 0 || attr.zp(DNNL_ARG_DST).dt != dnnl_s32))
@@ -75,8 +84,25 @@ dnnl_status_t dnnl_reorder_primitive_desc_create(dnnl_primitive_desc_t *reorder_
         if (s.dims[i] != d.dims[i]) return dnnl_invalid_arguments;
     if (s.has_runtime_dims()) return dnnl_unimplemented;
     if (with_host) return host_reorder_pd_create(reorder_primitive_desc, s, src_engine, d, dst_engine, attr);
-    const bool quantising = attr && (!attr->scales.empty() || !attr->zero_points.empty() || !attr->post_ops.entries.empty());
-    if (quantising) {
+    bool quantising = attr && (!attr->scales.empty() || !attr->zero_points.empty() || !attr->post_ops.entries.empty());
+    // a 4-bit tensor and a float one: the conversion runs on the quantising reorder's kernel, attributes or not
+    // (4-bit -> f32 / bf16 / f16, and f32 -> 4-bit without attributes)
+    const bool conv4 = s.is_plain() && d.is_plain() && s.ndims <= 2 && dt_nbits(s.data_type) != dt_nbits(d.data_type)
+            && (dt_nbits(s.data_type) == 4 || dt_nbits(d.data_type) == 4);
+    if (conv4) {
+        static const dnnl_primitive_attr no_attr;
+        if (dt_nbits(d.data_type) == 4) {
+            if (quantising || s.data_type != dnnl_f32) return dnnl_unimplemented;
+        } else {
+            const dnnl_status_t st = reorder_quant_validate(s, d, attr ? *attr : no_attr);
+            if (st != dnnl_success) return st;
+        }
+        // dense rows that start on a byte
+        const dnnl_memory_desc &q = dt_nbits(s.data_type) == 4 ? s : d;
+        if (q.strides[q.ndims - 1] != 1 || (q.dims[q.ndims - 1] & 1) || (q.offset0 & 1) || (q.ndims == 2 && q.dims[0] > 1 && (q.strides[0] & 1)))
+            return dnnl_unimplemented;
+        quantising = true;
+    } else if (quantising) {
         const dnnl_status_t st = reorder_quant_validate(s, d, *attr);
         if (st != dnnl_success) return st;
     }
@@ -95,8 +121,8 @@ dnnl_status_t dnnl_reorder_primitive_desc_create(dnnl_primitive_desc_t *reorder_
     } else {
         if (s.ndims > 6) return dnnl_unimplemented;
         const int sb = dt_nbits(s.data_type), db = dt_nbits(d.data_type);
-        // 4-bit tensors: dense copies of the same type only
-        if ((sb == 4 || db == 4) && !(s.data_type == d.data_type && s.equal(d) && s.is_dense_row_major()))
+        // 4-bit tensors: dense copies of the same type (conversions to and from float types went above)
+        if (!conv4 && (sb == 4 || db == 4) && !(s.data_type == d.data_type && s.equal(d) && s.is_dense_row_major()))
             return dnnl_unimplemented;
     }
     auto pd = std::unique_ptr<dnnl_primitive_desc>(new dnnl_primitive_desc());

@@ -206,6 +206,42 @@ __global__ void __launch_bounds__(256) reorder_quant_elem_kernel(const __grid_co
     }
 }
 
+// 4-bit tensors on either side (two values per byte, even index in the low nibble; dense rows
+// that start on a byte): one thread per pair of neighbouring columns, so that a destination
+// byte has one writer.  s4 / u4 -> f32 / bf16 / f16 with source scales and zero-points of any
+// mask and grouping (decompressing weights), f32 -> s4 / u4 saturating, round to nearest even
+// (src/common/int4.hpp, src/cpu/ref_io_helper.hpp:84-97; the reference's own f32 -> 4-bit
+// reorder accepts a common destination scale and does not apply it: not mirrored, the launcher
+// takes no attributes on that side).
+__global__ void __launch_bounds__(256) reorder_quant_int4_kernel(const __grid_constant__ b200_reorder_quant_params_t p) {
+    const int64_t pairs = p.cols / 2, total = p.rows * pairs;
+    const bool dst4 = p.dst_dt == B200_DT_S4 || p.dst_dt == B200_DT_U4;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = i / pairs, c0 = 2 * (i - r * pairs);
+        float d[2];
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            const int64_t c = c0 + e;
+            const float ss = p.src_scale.ptr ? load_f32(p.src_scale.dt, p.src_scale.ptr, quant_off(p.src_scale, r, c)) : 1.f;
+            const int zp = p.src_zp.ptr ? (int)load_f32(p.src_zp.dt, p.src_zp.ptr, quant_off(p.src_zp, r, c)) : 0;
+            const int64_t so = r * p.src_s0 + c * p.src_s1;
+            const float v = dt_is_int(p.src_dt) || p.src_dt == B200_DT_S4 || p.src_dt == B200_DT_U4
+                    ? (float)(load_int(p.src_dt, p.src, so) - zp)
+                    : __fsub_rn(load_f32(p.src_dt, p.src, so), (float)zp);
+            d[e] = __fmul_rn(ss, v);
+        }
+        if (dst4) {
+            const float lo = p.dst_dt == B200_DT_S4 ? -8.f : 0.f, hi = p.dst_dt == B200_DT_S4 ? 7.f : 15.f;
+            const uint32_t q0 = (uint32_t)__float2int_rn(fminf(fmaxf(d[0], lo), hi)) & 0xfu;
+            const uint32_t q1 = (uint32_t)__float2int_rn(fminf(fmaxf(d[1], lo), hi)) & 0xfu;
+            ((uint8_t *)p.dst)[(r * p.dst_s0 + c0) >> 1] = (uint8_t)(q0 | (q1 << 4));
+        } else {
+            store_f32(p.dst_dt, d[0], p.dst, r * p.dst_s0 + c0 * p.dst_s1);
+            store_f32(p.dst_dt, d[1], p.dst, r * p.dst_s0 + (c0 + 1) * p.dst_s1);
+        }
+    }
+}
+
 bool dt_ok(int dt) {
     switch (dt) {
         case B200_DT_F32: case B200_DT_BF16: case B200_DT_F16: case B200_DT_F8_E4M3: case B200_DT_F8_E5M2:
@@ -268,6 +304,21 @@ extern "C" int b200_reorder_quant_launch(const b200_reorder_quant_params_t *p, b
     if (!p || p->rows < 0 || p->cols < 0) return B200_ERR_BAD_ARG;
     if (p->rows == 0 || p->cols == 0) return 0;
     if (!p->src || !p->dst) return B200_ERR_BAD_ARG;
+    const bool s4 = p->src_dt == B200_DT_S4 || p->src_dt == B200_DT_U4, d4 = p->dst_dt == B200_DT_S4 || p->dst_dt == B200_DT_U4;
+    if (s4 || d4) {
+        // one side 4-bit, the other a float type; dense rows that start on a byte; no sum, nothing on the dst side
+        if (s4 == d4 || p->beta != 0.f || p->dst_scale.ptr || p->dst_zp.ptr) return B200_ERR_UNSUPPORTED;
+        if (s4 && !(p->dst_dt == B200_DT_F32 || p->dst_dt == B200_DT_BF16 || p->dst_dt == B200_DT_F16)) return B200_ERR_UNSUPPORTED;
+        if (d4 && (p->src_dt != B200_DT_F32 || p->src_scale.ptr || p->src_zp.ptr)) return B200_ERR_UNSUPPORTED;
+        const int64_t s0_4 = s4 ? p->src_s0 : p->dst_s0, s1_4 = s4 ? p->src_s1 : p->dst_s1;
+        if ((p->cols & 1) || s1_4 != 1 || (p->rows > 1 && (s0_4 & 1))) return B200_ERR_UNSUPPORTED;
+        for (const b200_quant_t *q : {&p->src_scale, &p->src_zp})
+            if (q->ptr && (q->g0 <= 0 || q->g1 <= 0 || !dt_ok(q->dt))) return B200_ERR_BAD_ARG;
+        int64_t blocks = (p->rows * (p->cols / 2) + 255) / 256;
+        if (blocks > 148 * 32) blocks = 148 * 32;
+        reorder_quant_int4_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(*p);
+        return after_launch();
+    }
     if (!dt_ok(p->src_dt) || !dt_ok(p->dst_dt)) return B200_ERR_UNSUPPORTED;
     const b200_quant_t *qs[4] = {&p->src_scale, &p->dst_scale, &p->src_zp, &p->dst_zp};
     for (const b200_quant_t *q : qs)

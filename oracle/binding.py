@@ -240,6 +240,8 @@ def new_reorder_dst(case):
     shape = (case.rows, case.cols) if case.dst_tag == "ab" else (case.cols, case.rows)
     if case.dst_init is not None:
         return np.ascontiguousarray(case.dst_init).copy()
+    if case.dst_dt in (dt.S4, dt.U4):  # two values per byte along the contiguous dim
+        return np.zeros((shape[0], shape[1] // 2), dtype=np.uint8)
     return np.zeros(shape, dtype=dt.RAW[case.dst_dt])
 
 

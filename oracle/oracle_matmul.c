@@ -196,6 +196,17 @@ void orc_store_float(int32_t dt, float v, void *ptr, int64_t idx) {
             if (v > 255.f) v = 255.f;
             ((uint8_t *)ptr)[idx] = (uint8_t)(int32_t)nearbyintf(v);
         } break;
+        /* 4-bit types (src/common/int4.hpp, src/common/nstl.hpp numeric_limits of int4_t / uint4_t,
+         * src/cpu/ref_io_helper.hpp:84-97): saturate to [-8, 7] / [0, 15], round to nearest even,
+         * keep the low four bits; two values per byte, even index in the low nibble */
+        case ORC_S4: case ORC_U4: {
+            const float lo = dt == ORC_S4 ? -8.f : 0.f, hi = dt == ORC_S4 ? 7.f : 15.f;
+            if (v < lo) v = lo;
+            if (v > hi) v = hi;
+            const uint8_t q = (uint8_t)((int32_t)nearbyintf(v) & 0xf);
+            uint8_t *b = (uint8_t *)ptr + (idx >> 1);
+            *b = (idx & 1) ? (uint8_t)((*b & 0x0f) | (q << 4)) : (uint8_t)((*b & 0xf0) | q);
+        } break;
         default: break;
     }
 }
@@ -528,7 +539,7 @@ int orc_matmul(const orc_problem_t *p) {
 int orc_reorder(const orc_reorder_t *r) {
     if (!r || !r->src || !r->dst) return 1;
     if (r->rows <= 0 || r->cols <= 0) return 0;
-    const int int_src = r->src_dt == ORC_S32 || r->src_dt == ORC_S8 || r->src_dt == ORC_U8;
+    const int int_src = r->src_dt == ORC_S32 || r->src_dt == ORC_S8 || r->src_dt == ORC_U8 || r->src_dt == ORC_S4 || r->src_dt == ORC_U4;
     const int32_t dst_zp = r->dst_zp.ptr ? orc_load_int(r->dst_zp.dt, r->dst_zp.ptr, 0) : 0;
 #ifdef _OPENMP
     int saved = omp_get_max_threads();

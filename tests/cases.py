@@ -354,6 +354,8 @@ def tame_names():
 # per column), its s32 / s8 results dequantised or requantised behind it.
 
 def _rsrc(r, rows, cols, src_dt, spread=40.0):
+    if src_dt in (dt.S4, dt.U4):
+        return dt.pack_int4(r.integers(0, 16, (rows, cols)))
     x = (r.standard_normal((rows, cols)) * spread).astype(np.float32)
     if src_dt == dt.S8:
         return np.clip(np.rint(x), -128, 127).astype(np.int8)
@@ -419,6 +421,18 @@ REORDER_CASES = {
                                                dst_scale=lambda r: _rq(r, 32, 64, 2, 0.2, 0.5), dst_zp=_zp(-5)),
     "rq_s8_s32_transposed_dst": lambda: _reorder(116, 24, 40, dt.S8, dt.S32, dst_tag="ba",
                                                  src_scale=lambda r: _rq(r, 24, 40, 0, 3.0, 4.0)),
+    # 4-bit tensors: compressed weights back to a float type (scales / zero-points per column or
+    # per K group, as the decompression matmul takes them), and the plain conversions
+    "dq_u4_f32_per_col_zp": lambda: _reorder(117, 64, 96, dt.U4, dt.F32, src_scale=lambda r: _rq(r, 64, 96, 2, 0.01, 0.1),
+                                             src_zp=_zp(7)),
+    "dq_s4_bf16_grouped": lambda: _reorder(118, 128, 48, dt.S4, dt.BF16,
+                                           src_scale=lambda r: _rq(r, 128, 48, 3, 0.01, 0.1, dt.F32, (32, 1))),
+    "dq_u4_f16_grouped_zp": lambda: _reorder(
+        119, 64, 32, dt.U4, dt.F16, src_scale=lambda r: _rq(r, 64, 32, 3, 0.01, 0.1, dt.F32, (16, 2)),
+        src_zp=lambda r: Quant(r.integers(0, 16, (64 // 16) * (32 // 2)).astype(np.int32), dt.S32, 3, (16, 2))),
+    "dq_s4_f32_plain": lambda: _reorder(120, 9, 14, dt.S4, dt.F32),
+    "q_f32_s4_plain": lambda: _reorder(121, 33, 20, dt.F32, dt.S4, spread=5.0),
+    "q_f32_u4_plain": lambda: _reorder(122, 16, 64, dt.F32, dt.U4, spread=9.0),
 }
 
 

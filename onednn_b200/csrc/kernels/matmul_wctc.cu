@@ -12,18 +12,21 @@
 // this one only converts: per stage of 64 k, a group of four warps (one thread per output
 // column) turns the packed weights of 128 columns into a 128-column x 64-k bf16 tile in
 // shared memory, laid out as the 128-byte-swizzled K-major operand tile a TMA load would
-// have produced; the activations of the same 64 k arrive by TMA; one thread issues
-// tcgen05.mma (kind::f16, 128 x NB x 16) with the weights as the A operand (128 output
-// columns = the TMEM lanes) and the activations as B (NB = activation rows rounded up to
-// 16), accumulating in TMEM over the whole K.  The epilogue reads TMEM with one output
-// column per lane, so that stores of a dst row are coalesced.
+// have produced; the activations of the same 64 k arrive by TMA into a ring of their own; two
+// threads issue tcgen05.mma (kind::f16, 128 x NB x 16) for alternate k-blocks, each into its
+// own accumulator, with the weights as the A operand (128 output columns = the TMEM lanes)
+// and the activations as B (NB = activation rows rounded up to 16), accumulating in TMEM over
+// the whole K.  The epilogue adds the two accumulators and reads TMEM with one output column
+// per lane, so that stores of a dst row are coalesced.  Block i uses barrier pair i mod SA
+// (SA = stages of converted weights: 4, 6 or 8; SB <= SA stages of activations).
 //
-//   warp 0        TMA producer (activations)           waits empty[s]   -> full_a[s] (tx bytes)
-//   warps 1, 2    MMA issuers (warp 1 owns TMEM):      wait full_a[i]   -> empty[i], acc_full
+//   warp 0        TMA producer (activations)           waits empty[i - SB] -> full_a[i] (tx bytes)
+//   warps 1, 2    MMA issuers (warp 1 owns TMEM):      wait full_a[i]      -> empty[i], acc_full
 //                 issuer j takes the tile's k-blocks
 //                 j, j + 2, ... into accumulator j
-//   warps 3..18   four dequantising groups (group g    wait empty[i - 4] -> full_a[i]; acc_full -> acc_empty
-//                 owns stage g), then the epilogue
+//   warps 3..18   four dequantising groups (group g    wait empty[i - SA]  -> full_a[i]; acc_full -> acc_empty
+//                 converts blocks g, g + 4, ...), then
+//                 the epilogue
 //
 // Weights are read in the layouts written by the pack kernels below.  B200_WEI_WC4_TC:
 // blocks of 128 output columns x 64 k = 4 KiB, block (nt, kb) at ((nt * K/64) + kb) * 4096,
@@ -239,8 +242,6 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     const b200_matmul_params_t &p = args.p;
     const int nb = args.nb;
     const uint32_t b_bytes = (uint32_t)nb * (TK * 2); // a multiple of 2 KiB: every stage of either ring starts on a 1 KiB boundary
-    // both ring depths are powers of two: block index -> stage and use count by mask and shift (the
-    // loops of the two issuing threads set the pace; a division there costs more than the MMAs' issue)
     // block index -> stage and use count; the depths are 4, 6 or 8 so that this is a mask and a shift or
     // a division by a constant (the loops of the issuing threads set the pace: a division by a
     // run-time value there costs more than the MMAs' issue)

@@ -87,6 +87,9 @@ struct dnnl_memory_desc {
     bool is_any() const { return format_kind == dnnl_format_kind_any; }
     bool is_zero() const { return ndims == 0; }
     size_t size_bytes() const;
+    // opaque (packed weights) descriptors with batch dims: every 2-D slice is packed on its own and
+    // slices follow one another at this distance (a multiple of 256 bytes), batch index row-major
+    size_t packed_slice_stride() const;
     bool equal(const dnnl_memory_desc &o) const;
     bool is_dense_row_major() const; // strides of tag a / ab / abc ...
     std::string layout_str() const;  // "ab", "ba", "a:strided", "packed:kmajor", "any"

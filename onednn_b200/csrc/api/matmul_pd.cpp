@@ -498,9 +498,8 @@ static bool collapsible(const dnnl_primitive_desc *pd, int nb, dnnl_memory_desc 
 
 static dnnl_status_t select_batched(dnnl_primitive_desc *pd, int first) {
     const int nd = pd->user_dst.ndims, nb = nd - 2;
-    if (pd->user_src.format_kind == dnnl_format_kind_opaque || pd->user_wei.format_kind == dnnl_format_kind_opaque
-            || pd->user_dst.format_kind == dnnl_format_kind_opaque)
-        return first == 0 ? dnnl_unimplemented : dnnl_last_impl_reached; // packed layouts are 2-D
+    if (pd->user_src.format_kind == dnnl_format_kind_opaque || pd->user_dst.format_kind == dnnl_format_kind_opaque)
+        return first == 0 ? dnnl_unimplemented : dnnl_last_impl_reached; // packed layouts are for weights
     auto in = std::make_shared<dnnl_primitive_desc>();
     in->kind = dnnl_matmul;
     in->engine = pd->engine; // not counted: the slice descriptor lives and dies with this one
@@ -527,7 +526,18 @@ static dnnl_status_t select_batched(dnnl_primitive_desc *pd, int first) {
         }
     }
     in->user_src = collapse ? src2 : slice_2d(pd->user_src);
-    in->user_wei = slice_2d(pd->user_wei); // weights given as `any` stay plain: packing is per 2-D matrix
+    // weights given as `any` take the implementation's packed layout slice by slice: every batch
+    // index's (K, N) matrix packed on its own, the slices one after the other (packed_slice_stride)
+    if (pd->user_wei.is_any()) {
+        in->user_wei = dnnl_memory_desc();
+        in->user_wei.ndims = 2;
+        in->user_wei.data_type = pd->user_wei.data_type;
+        in->user_wei.format_kind = dnnl_format_kind_any;
+        in->user_wei.dims[0] = pd->user_wei.dims[nd - 2];
+        in->user_wei.dims[1] = pd->user_wei.dims[nd - 1];
+    } else {
+        in->user_wei = slice_2d(pd->user_wei);
+    }
     in->user_dst = collapse ? dst2 : slice_2d(pd->user_dst);
     if (pd->user_bias.ndims) in->user_bias = slice_2d(pd->user_bias);
     // every batch index must start a 4-bit tensor on a byte: the 2-D slices are addressed by pointer
@@ -541,7 +551,14 @@ static dnnl_status_t select_batched(dnnl_primitive_desc *pd, int first) {
     pd->src = pd->user_src;
     if (pd->src.is_any()) make_plain(pd->src);
     pd->wei = pd->user_wei;
-    if (pd->wei.is_any()) make_plain(pd->wei);
+    if (pd->wei.is_any()) {
+        if (in->wei.format_kind == dnnl_format_kind_opaque) {
+            pd->wei.format_kind = dnnl_format_kind_opaque;
+            pd->wei.packed_layout = in->wei.packed_layout;
+        } else {
+            make_plain(pd->wei);
+        }
+    }
     pd->dst = pd->user_dst;
     if (pd->dst.is_any()) make_plain(pd->dst);
     pd->bias = pd->user_bias;
@@ -620,6 +637,13 @@ static dnnl_status_t batched_execute(const dnnl_primitive *prim, dnnl_stream *st
             rem /= pd->dst.dims[d];
         }
         for (size_t i = 0; i < mv.size(); ++i) {
+            if (mv[i].full->format_kind == dnnl_format_kind_opaque) {
+                // packed weights: slices in row-major order of the weights' own batch dims
+                int64_t flat = 0;
+                for (int d = 0; d < nb; ++d) flat = flat * mv[i].full->dims[d] + (mv[i].full->dims[d] != 1 ? idx[d] : 0);
+                mv[i].mem.handle = (char *)base[i] + (size_t)flat * mv[i].full->packed_slice_stride();
+                continue;
+            }
             const int64_t off = batch_offset(*mv[i].full, idx, nb);
             const int bits = dt_nbits(mv[i].full->data_type);
             if ((off * bits) % 8 != 0) { st = dnnl_unimplemented; break; } // a 4-bit slice starting inside a byte

@@ -44,12 +44,21 @@ size_t dnnl_memory_desc::size_bytes() const {
         for (int i = 0; i < ndims; ++i) n *= (dims[i] + 63) / 64 * 64;
         return (size_t)((n * dt_nbits(data_type) + 7) / 8);
     }
-    if (format_kind == dnnl_format_kind_opaque)
-        return b200_packed_weights_bytes(dims[ndims - 2], dims[ndims - 1], data_type, packed_layout);
+    if (format_kind == dnnl_format_kind_opaque) {
+        if (ndims <= 2) return b200_packed_weights_bytes(dims[ndims - 2], dims[ndims - 1], data_type, packed_layout);
+        size_t batch = 1;
+        for (int i = 0; i < ndims - 2; ++i) batch *= (size_t)dims[i];
+        return batch * packed_slice_stride();
+    }
     int64_t span = 1;
     for (int i = 0; i < ndims; ++i) span += (dims[i] - 1) * strides[i];
     const int bits = dt_nbits(data_type);
     return (size_t)((span * bits + 7) / 8);
+}
+
+size_t dnnl_memory_desc::packed_slice_stride() const {
+    const size_t b = b200_packed_weights_bytes(dims[ndims - 2], dims[ndims - 1], data_type, packed_layout);
+    return (b + 255) / 256 * 256;
 }
 
 bool dnnl_memory_desc::equal(const dnnl_memory_desc &o) const {

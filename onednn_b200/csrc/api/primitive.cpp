@@ -108,16 +108,21 @@ dnnl_status_t dnnl_reorder_primitive_desc_create(dnnl_primitive_desc_t *reorder_
     }
     if (!s.is_plain()) return dnnl_unimplemented; // unpacking is not needed by the matmul path
     if (d.format_kind == dnnl_format_kind_opaque) {
-        if (s.ndims != 2 || s.data_type != d.data_type) return dnnl_unimplemented;
+        // packed weights: a (K, N) matrix, or batch dims in front of one (every slice packed on its own)
+        if (s.ndims < 2 || s.data_type != d.data_type) return dnnl_unimplemented;
+        const int64_t K = s.dims[s.ndims - 2], N = s.dims[s.ndims - 1];
+        const bool slice_dense = s.strides[s.ndims - 1] == 1 && s.strides[s.ndims - 2] == N;
         if (d.packed_layout == B200_WEI_KMAJOR && !(dt_is_int8(s.data_type) || dt_is_fp8(s.data_type)))
             return dnnl_unimplemented;
-        if (d.packed_layout == B200_WEI_WC4_TILED
-                && !(dt_is_int4(s.data_type) && s.is_dense_row_major() && s.dims[0] % 64 == 0 && s.dims[1] % 16 == 0))
+        if (d.packed_layout == B200_WEI_WC4_TILED && !(dt_is_int4(s.data_type) && slice_dense && K % 64 == 0 && N % 16 == 0))
             return dnnl_unimplemented;
-        if (d.packed_layout == B200_WEI_WC4_TC
-                && !(dt_is_int4(s.data_type) && s.is_dense_row_major() && s.dims[0] % 64 == 0 && s.dims[1] % 2 == 0))
+        if (d.packed_layout == B200_WEI_WC4_TC && !(dt_is_int4(s.data_type) && slice_dense && K % 64 == 0 && N % 2 == 0))
             return dnnl_unimplemented;
-        if (d.packed_layout == B200_WEI_WC8_TC && !(dt_is_int8(s.data_type) && s.dims[0] % 64 == 0)) return dnnl_unimplemented;
+        if (d.packed_layout == B200_WEI_WC8_TC && !(dt_is_int8(s.data_type) && K % 64 == 0)) return dnnl_unimplemented;
+        // a 4-bit slice must start on a byte
+        if (dt_is_int4(s.data_type))
+            for (int i = 0; i < s.ndims - 2; ++i)
+                if (s.dims[i] > 1 && (s.strides[i] & 1)) return dnnl_unimplemented;
     } else {
         if (s.ndims > 6) return dnnl_unimplemented;
         const int sb = dt_nbits(s.data_type), db = dt_nbits(d.data_type);
@@ -207,7 +212,31 @@ dnnl_status_t reorder_execute(const dnnl_primitive *prim, dnnl_stream *stream, c
     r.src_dt = s.data_type;
     r.dst_dt = d.data_type;
     int rc;
-    if (s.ndims == 2 || d.format_kind == dnnl_format_kind_opaque) {
+    if (d.format_kind == dnnl_format_kind_opaque && s.ndims > 2) {
+        // batched weights into the packed layout: one pack per batch index, slices at packed_slice_stride
+        const int nd = s.ndims;
+        int64_t outer = 1;
+        for (int i = 0; i < nd - 2; ++i) outer *= s.dims[i];
+        const size_t stride = d.packed_slice_stride();
+        rc = 0;
+        for (int64_t o = 0; o < outer && rc == 0; ++o) {
+            int64_t rem = o, so = 0;
+            for (int i = nd - 3; i >= 0; --i) {
+                so += (rem % s.dims[i]) * s.strides[i];
+                rem /= s.dims[i];
+            }
+            b200_reorder_params_t q = r;
+            q.src = (const char *)r.src + so * dt_nbits(s.data_type) / 8;
+            q.dst = (char *)r.dst + (size_t)o * stride;
+            q.K = s.dims[nd - 2];
+            q.N = s.dims[nd - 1];
+            q.src_sk = s.strides[nd - 2];
+            q.src_sn = s.strides[nd - 1];
+            q.src_layout = B200_WEI_PLAIN;
+            q.dst_layout = d.packed_layout;
+            rc = b200_reorder_launch(&q, stream->cuda_stream);
+        }
+    } else if (s.ndims == 2 || d.format_kind == dnnl_format_kind_opaque) {
         r.K = s.dims[0];
         r.N = s.dims[1];
         r.src_sk = s.strides[0];

@@ -25,10 +25,19 @@ def test_batched_descriptor_host():
     assert pd.impl_info_str() == "cuda:sm100:tcgen05_i8"
     assert pd.query_md(api.QUERY_EXEC_ARG_MD, api.ARG_ATTR_SCALES | api.ARG_WEIGHTS).dims == [48]
     assert pd.weights_desc().dims == [3, 64, 48]
-    # `any` weights of a batched problem stay plain
+    # `any` weights of a batched problem take the packed layout slice by slice: an opaque descriptor with the
+    # batch dims, three times the size of a slice (each rounded up to 256 bytes)
     any_w = api.MemoryDesc((3, 64, 48), dt.S8, api.TAG_ANY)
     pd = api.matmul_primitive_desc(eng, _md((3, 70, 64), dt.S8), any_w, _md((3, 70, 48), dt.F32))
-    assert pd.weights_desc() == _md((3, 64, 48), dt.S8)
+    wq = pd.weights_desc()
+    assert wq.format_kind == 3 and wq.dims == [3, 64, 48]
+    one = api.matmul_primitive_desc(eng, _md((70, 64), dt.S8), api.MemoryDesc((64, 48), dt.S8, api.TAG_ANY), _md((70, 48), dt.F32))
+    slice_bytes = one.weights_desc().get_size()
+    assert wq.get_size() == 3 * ((slice_bytes + 255) // 256 * 256)
+    # and that descriptor is accepted back as the weights of the same problem
+    pd2 = api.matmul_primitive_desc(eng, _md((3, 70, 64), dt.S8), wq, _md((3, 70, 48), dt.F32))
+    assert pd2.impl_info_str() == pd.impl_info_str() and pd2.weights_desc() == wq
+    api.reorder_primitive_desc(eng, _md((3, 64, 48), dt.S8), eng, wq)
     # broadcast weights are fine, mismatched batch dims are not, scales over a batch dim are not implemented
     api.matmul_primitive_desc(eng, _md((3, 70, 64), dt.S8), _md((1, 64, 48), dt.S8), _md((3, 70, 48), dt.F32))
     with pytest.raises(api.Error):
@@ -39,8 +48,10 @@ def test_batched_descriptor_host():
         api.matmul_primitive_desc(eng, _md((3, 70, 64), dt.S8), _md((3, 64, 48), dt.S8), _md((3, 70, 48), dt.F32), attr=a)
 
 
-def _run_batched(eng, strm, batch, wbatch, base: MatmulCase, binary=None):
-    """``base`` holds the tensors with leading batch dims; returns (result, impl)."""
+def _run_batched(eng, strm, batch, wbatch, base: MatmulCase, binary=None, weights_any=False):
+    """``base`` holds the tensors with leading batch dims; returns (result, impl).  With
+    ``weights_any`` the weights go through the implementation's packed layout: queried from the
+    primitive descriptor, filled by a reorder from the plain tensor."""
     nd = len(batch)
     M, N, K = base.M, base.N, base.K
     attr = api.PrimitiveAttr()
@@ -60,6 +71,9 @@ def _run_batched(eng, strm, batch, wbatch, base: MatmulCase, binary=None):
     src_md, wei_md = _md(batch + (M, K), base.src_dt), _md(wbatch + (K, N), base.wei_dt)
     dst_md = _md(batch + (M, N), base.dst_dt)
     bias_md = _md((1,) * nd + (1, N), base.bias_dt) if base.bias is not None else None
+    plain_wei_md = wei_md
+    if weights_any:
+        wei_md = api.MemoryDesc(wbatch + (K, N), base.wei_dt, api.TAG_ANY)
     pd = api.matmul_primitive_desc(eng, src_md, wei_md, dst_md, bias_md, attr)
     prim = api.Primitive(pd)
     mems = []
@@ -69,8 +83,16 @@ def _run_batched(eng, strm, batch, wbatch, base: MatmulCase, binary=None):
         m.write(np.ascontiguousarray(arr))
         mems.append(m)
         return m
-    args = {api.ARG_SRC: mem(src_md, base.src), api.ARG_WEIGHTS: mem(wei_md, base.wei),
+    args = {api.ARG_SRC: mem(src_md, base.src), api.ARG_WEIGHTS: mem(plain_wei_md, base.wei),
             api.ARG_DST: mem(dst_md, np.zeros(batch + (M, N), dt.RAW[base.dst_dt]))}
+    if weights_any:
+        wq = pd.weights_desc()
+        assert wq.format_kind == 3, "expected a packed layout for `any` weights"
+        packed = api.Memory(wq, eng)
+        mems.append(packed)
+        api.Primitive(api.reorder_primitive_desc(eng, plain_wei_md, eng, wq)).execute(
+            strm, {api.ARG_FROM: args[api.ARG_WEIGHTS], api.ARG_TO: packed})
+        args[api.ARG_WEIGHTS] = packed
     if base.bias is not None:
         args[api.ARG_BIAS] = mem(bias_md, base.bias)
     for q, arg in ((base.src_scale, api.ARG_ATTR_SCALES | api.ARG_SRC), (base.wei_scale, api.ARG_ATTR_SCALES | api.ARG_WEIGHTS),
@@ -97,11 +119,16 @@ def _slice_case(base, b, wb, binary=None):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("kind", ["int8_3d", "int8_bcast_weights_binary", "fp8_4d"])
+@pytest.mark.parametrize("kind", ["int8_3d", "int8_bcast_weights_binary", "fp8_4d", "int8_3d_packed", "fp8_4d_packed",
+                                  "int8_bcast_weights_packed"])
 def test_batched_matches_oracle_per_slice(kind):
     eng = api.Engine()
     strm = api.Stream(eng)
     r = np.random.default_rng(91)
+    packed = kind.endswith("_packed")  # weights as format_tag::any: packed once, slice by slice
+    kind = kind[:-len("_packed")] if packed else kind
+    if kind == "int8_bcast_weights":
+        kind = "int8_bcast_weights_binary"
     if kind == "fp8_4d":
         batch, wbatch, (M, N, K) = (2, 2), (2, 2), (40, 64, 96)
         base = W.config3(M, N, K, seed=92)
@@ -117,7 +144,7 @@ def test_batched_matches_oracle_per_slice(kind):
                           bias=r.uniform(-1, 1, (1, N)).astype(np.float32), bias_dt=dt.F32,
                           post_ops=[W.eltwise("relu", 0.0)], exact=False, rtol=1e-5, atol=1e-5)
     binary = r.uniform(-1, 1, batch + (M, 1)).astype(np.float32) if kind == "int8_bcast_weights_binary" else None
-    got, impl = _run_batched(eng, strm, batch, wbatch, base, binary)
+    got, impl = _run_batched(eng, strm, batch, wbatch, base, binary, weights_any=packed)
     assert "tcgen05" in impl
     for b in np.ndindex(*batch):
         wb = tuple(0 if wbatch[d] == 1 else b[d] for d in range(len(b)))

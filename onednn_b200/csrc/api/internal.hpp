@@ -195,6 +195,15 @@ struct dnnl_primitive_desc {
     // selected implementation runs once per batch index
     std::shared_ptr<dnnl_primitive_desc> inner;
     bool collapsed = false; // batched with broadcast weights and dense rows: `inner` is the whole problem as one 2-D matmul
+    // batched: scales / zero-points whose mask reaches into the batch dims -- the argument's memory then holds one
+    // set of values per index of those dims, and every batch index is executed with its own part of it
+    struct batch_quant_t {
+        int exec_arg;   // DNNL_ARG_ATTR_SCALES | arg or DNNL_ARG_ATTR_ZERO_POINTS | arg
+        int tensor_arg; // DNNL_ARG_SRC / WEIGHTS / DST: whose dims the mask is over
+        int batch_mask; // the mask's bits over the batch dims
+        bool is_zp;
+    };
+    std::vector<batch_quant_t> batch_quant;
     // some dims are DNNL_RUNTIME_DIM_VAL: the implementation is chosen at execution, from the
     // descriptors of the memory arguments
     bool runtime = false;

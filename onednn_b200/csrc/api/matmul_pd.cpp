@@ -504,18 +504,29 @@ static dnnl_status_t select_batched(dnnl_primitive_desc *pd, int first) {
     in->kind = dnnl_matmul;
     in->engine = pd->engine; // not counted: the slice descriptor lives and dies with this one
     in->attr = pd->attr;
-    // scales / zero-points may vary over the last two dims only; their masks move down with them
+    // scales / zero-points: the mask's bits over the last two dims move down with them; bits over batch
+    // dims mean one set of values per index of those dims, handed to the slice's execution part by part
+    pd->batch_quant.clear();
     for (auto *m : {&in->attr.scales, &in->attr.zero_points})
         for (auto &kv : *m) {
             if (!kv.second.set) continue;
-            if (kv.second.mask & ((1 << nb) - 1)) return first == 0 ? dnnl_unimplemented : dnnl_last_impl_reached;
+            const int bmask = kv.second.mask & ((1 << nb) - 1);
+            if (bmask) {
+                if (kv.second.group_ndims) return first == 0 ? dnnl_unimplemented : dnnl_last_impl_reached; // groups are over the last two dims
+                dnnl_primitive_desc::batch_quant_t q;
+                q.exec_arg = (m == &in->attr.scales ? DNNL_ARG_ATTR_SCALES : DNNL_ARG_ATTR_ZERO_POINTS) | kv.first;
+                q.tensor_arg = kv.first;
+                q.batch_mask = bmask;
+                q.is_zp = m != &in->attr.scales;
+                pd->batch_quant.push_back(q);
+            }
             kv.second.mask >>= nb;
         }
     for (auto &e : in->attr.post_ops.entries)
         if (e.kind == dnnl_binary && e.src1.ndims != nd) return dnnl_invalid_arguments;
     dnnl_memory_desc src2, dst2;
     std::vector<dnnl_memory_desc> src1_2d;
-    const bool collapse = collapsible(pd, nb, src2, dst2, src1_2d);
+    const bool collapse = pd->batch_quant.empty() && collapsible(pd, nb, src2, dst2, src1_2d);
     for (size_t i = 0; i < in->attr.post_ops.entries.size(); ++i) {
         auto &e = in->attr.post_ops.entries[i];
         if (e.kind == dnnl_binary) {
@@ -613,6 +624,38 @@ static dnnl_status_t batched_execute(const dnnl_primitive *prim, dnnl_stream *st
             if (!add(DNNL_ARG_ATTR_MULTIPLE_POST_OP((int)i) | DNNL_ARG_SRC_1, po_full[i], in->attr.post_ops.entries[i].src1))
                 return dnnl_invalid_arguments;
         }
+    // quantisation arguments that vary over batch dims: the part of batch index idx starts
+    // (row-major index of idx over the masked batch dims of the argument's tensor) x (values per slice) in
+    struct moving_quant_t { dnnl_memory mem; const dnnl_memory_desc *tensor; int batch_mask; int64_t per_slice; void *base0; int bits; };
+    std::vector<moving_quant_t> mq;
+    for (const auto &bq : pd->batch_quant) {
+        auto it = args.find(bq.exec_arg);
+        if (it == args.end() || !it->second->handle) return dnnl_invalid_arguments;
+        const dnnl_memory_desc *t = bq.tensor_arg == DNNL_ARG_SRC ? &pd->src : bq.tensor_arg == DNNL_ARG_WEIGHTS ? &pd->wei : &pd->dst;
+        const quant_entry_t &qe = bq.is_zp ? in->attr.zp(bq.tensor_arg) : in->attr.scale(bq.tensor_arg);
+        moving_quant_t q;
+        q.mem = *it->second;
+        q.tensor = t;
+        q.batch_mask = bq.batch_mask;
+        q.per_slice = ((qe.mask & 1) ? t->dims[nb] : 1) * ((qe.mask & 2) ? t->dims[nb + 1] : 1);
+        q.bits = dt_nbits(q.mem.md.data_type);
+        q.base0 = (char *)q.mem.handle + q.mem.md.offset0 * q.bits / 8;
+        int64_t sets = 1;
+        for (int d = 0; d < nb; ++d)
+            if (bq.batch_mask & (1 << d)) sets *= t->dims[d];
+        if (q.mem.md.nelems() < sets * q.per_slice) return dnnl_invalid_arguments;
+        // the slice's own descriptor: a 1-D run of per_slice values
+        dnnl_memory_desc one;
+        one.ndims = 1;
+        one.data_type = q.mem.md.data_type;
+        one.format_kind = dnnl_blocked;
+        one.dims[0] = q.per_slice;
+        one.strides[0] = 1;
+        q.mem.md = one;
+        q.mem.owned = false;
+        q.mem.mapped = nullptr;
+        mq.push_back(q);
+    }
     std::vector<void *> base(mv.size());
     for (size_t i = 0; i < mv.size(); ++i) {
         base[i] = (char *)mv[i].mem.handle + mv[i].full->offset0 * dt_nbits(mv[i].full->data_type) / 8;
@@ -628,6 +671,7 @@ static dnnl_status_t batched_execute(const dnnl_primitive *prim, dnnl_stream *st
     tmp.scratch_owner = prim->scratch_owner ? prim->scratch_owner : prim;
     std::map<int, dnnl_memory *> a2 = args;
     for (size_t i = 0; i < mv.size(); ++i) a2[mv[i].arg] = &mv[i].mem;
+    for (size_t i = 0; i < mq.size(); ++i) a2[pd->batch_quant[i].exec_arg] = &mq[i].mem;
     dnnl_status_t st = dnnl_success;
     int64_t idx[DNNL_MAX_NDIMS] = {0};
     for (int64_t b = 0; b < total && st == dnnl_success; ++b) {
@@ -648,6 +692,14 @@ static dnnl_status_t batched_execute(const dnnl_primitive *prim, dnnl_stream *st
             const int bits = dt_nbits(mv[i].full->data_type);
             if ((off * bits) % 8 != 0) { st = dnnl_unimplemented; break; } // a 4-bit slice starting inside a byte
             mv[i].mem.handle = (char *)base[i] + off * bits / 8;
+        }
+        for (auto &q : mq) {
+            int64_t flat = 0;
+            for (int d = 0; d < nb; ++d)
+                if (q.batch_mask & (1 << d)) flat = flat * q.tensor->dims[d] + (q.tensor->dims[d] != 1 ? idx[d] : 0);
+            const int64_t off_bits = flat * q.per_slice * q.bits;
+            if (off_bits % 8 != 0) { st = dnnl_unimplemented; break; } // a 4-bit part starting inside a byte
+            q.mem.handle = (char *)q.base0 + off_bits / 8;
         }
         if (st == dnnl_success) st = matmul_execute(&tmp, stream, a2);
     }

@@ -38,14 +38,15 @@ def test_batched_descriptor_host():
     pd2 = api.matmul_primitive_desc(eng, _md((3, 70, 64), dt.S8), wq, _md((3, 70, 48), dt.F32))
     assert pd2.impl_info_str() == pd.impl_info_str() and pd2.weights_desc() == wq
     api.reorder_primitive_desc(eng, _md((3, 64, 48), dt.S8), eng, wq)
-    # broadcast weights are fine, mismatched batch dims are not, scales over a batch dim are not implemented
+    # broadcast weights are fine, mismatched batch dims are not
     api.matmul_primitive_desc(eng, _md((3, 70, 64), dt.S8), _md((1, 64, 48), dt.S8), _md((3, 70, 48), dt.F32))
     with pytest.raises(api.Error):
         api.matmul_primitive_desc(eng, _md((3, 70, 64), dt.S8), _md((2, 64, 48), dt.S8), _md((3, 70, 48), dt.F32))
+    # weights scales over the batch dim (one set of per-N values per batch index): taken, on the fast kernel
     a = api.PrimitiveAttr()
-    a.set_scales(api.ARG_WEIGHTS, 1, (), dt.F32)
-    with pytest.raises(api.Error):
-        api.matmul_primitive_desc(eng, _md((3, 70, 64), dt.S8), _md((3, 64, 48), dt.S8), _md((3, 70, 48), dt.F32), attr=a)
+    a.set_scales(api.ARG_WEIGHTS, 1 | 4, (), dt.F32)
+    pd = api.matmul_primitive_desc(eng, _md((3, 70, 64), dt.S8), _md((3, 64, 48), dt.S8), _md((3, 70, 48), dt.F32), attr=a)
+    assert pd.impl_info_str() == "cuda:sm100:tcgen05_i8"
 
 
 def _run_batched(eng, strm, batch, wbatch, base: MatmulCase, binary=None, weights_any=False):
@@ -159,6 +160,48 @@ def _launches():
     v = C.c_uint64()
     assert api.lib().dnnl_b200_debug_counter(3, C.byref(v)) == 0
     return v.value
+
+
+@pytest.mark.gpu
+def test_weights_scales_and_zero_points_per_batch_index():
+    """Weights scales with mask batch + N (one set of per-column values per batch index) and a weights
+    zero-point per batch index: every batch index equals the oracle's 2-D problem with its own values."""
+    eng = api.Engine()
+    strm = api.Stream(eng)
+    r = np.random.default_rng(97)
+    B_, M, N, K = 3, 40, 48, 64
+    src = r.integers(-128, 128, (B_, M, K), dtype=np.int8)
+    wei = r.integers(-127, 128, (B_, K, N), dtype=np.int8)
+    wscale = r.uniform(1e-3, 4e-3, (B_, N)).astype(np.float32)
+    wzp = r.integers(-5, 6, (B_,)).astype(np.int32)
+    attr = api.PrimitiveAttr()
+    attr.set_scales(api.ARG_SRC, 0, (), dt.F32)
+    attr.set_scales(api.ARG_WEIGHTS, 1 | 4, (), dt.F32)
+    attr.set_zero_points(api.ARG_WEIGHTS, 1, (), dt.S32)
+    src_md, wei_md, dst_md = _md((B_, M, K), dt.S8), _md((B_, K, N), dt.S8), _md((B_, M, N), dt.F32)
+    pd = api.matmul_primitive_desc(eng, src_md, wei_md, dst_md, None, attr)
+    assert "tcgen05_i8" in pd.impl_info_str()
+    prim = api.Primitive(pd)
+    keep = []
+
+    def mem(md, arr):
+        m = api.Memory(md, eng)
+        m.write(np.ascontiguousarray(arr))
+        keep.append(m)
+        return m
+    args = {api.ARG_SRC: mem(src_md, src), api.ARG_WEIGHTS: mem(wei_md, wei), api.ARG_DST: mem(dst_md, np.zeros((B_, M, N), np.float32)),
+            api.ARG_ATTR_SCALES | api.ARG_SRC: mem(api.MemoryDesc((1,), dt.F32, api.TAG_A), np.float32([0.02])),
+            api.ARG_ATTR_SCALES | api.ARG_WEIGHTS: mem(api.MemoryDesc((B_ * N,), dt.F32, api.TAG_A), wscale),
+            api.ARG_ATTR_ZERO_POINTS | api.ARG_WEIGHTS: mem(api.MemoryDesc((B_,), dt.S32, api.TAG_A), wzp)}
+    prim.execute(strm, args)
+    strm.wait()
+    got = args[api.ARG_DST].read(np.float32, (B_, M, N))
+    for b in range(B_):
+        c = MatmulCase("slice", M, N, K, src=src[b], src_dt=dt.S8, wei=wei[b], wei_dt=dt.S8, dst_dt=dt.F32,
+                       src_scale=Quant(np.float32([0.02]), dt.F32, 0), wei_scale=Quant(wscale[b], dt.F32, 2),
+                       wei_zp=Quant(wzp[b:b + 1], dt.S32, 0), exact=False, rtol=1e-5, atol=1e-5)
+        want = B.run_oracle(c, exact_acc=1)
+        assert np.all(np.abs(got[b] - want) <= 1e-5 + 1e-5 * np.abs(want)), "batch %d" % b
 
 
 @pytest.mark.gpu

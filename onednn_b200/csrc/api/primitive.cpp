@@ -28,7 +28,30 @@ dnnl_primitive::~dnnl_primitive() {
 static dnnl_status_t reorder_quant_validate(const dnnl_memory_desc &s, const dnnl_memory_desc &d,
         const dnnl_primitive_attr &attr) {
     if (!s.is_plain() || !d.is_plain()) return dnnl_unimplemented;
-    if (s.ndims < 1 || s.ndims > 2) return dnnl_unimplemented;
+    if (s.ndims < 1) return dnnl_unimplemented;
+    if (s.ndims > 2) {
+        // more dims: dense row-major tensors whose scales / zero-points are per tensor or per element of
+        // the last dim fold into (prod(leading dims), last dim) -- activations of any rank quantised per
+        // tensor or per channel; anything else is not taken
+        if (!s.is_dense_row_major() || !d.is_dense_row_major()) return dnnl_unimplemented;
+        if (dt_nbits(s.data_type) == 4 || dt_nbits(d.data_type) == 4) return dnnl_unimplemented;
+        const int last = 1 << (s.ndims - 1);
+        for (auto *m : {&attr.scales, &attr.zero_points})
+            for (const auto &kv : *m) {
+                if (!kv.second.set) continue;
+                if (kv.first != DNNL_ARG_SRC && kv.first != DNNL_ARG_DST) return dnnl_unimplemented;
+                if (kv.second.mask & ~((1 << s.ndims) - 1)) return dnnl_invalid_arguments;
+                if ((kv.second.mask != 0 && kv.second.mask != last) || kv.second.group_ndims) return dnnl_unimplemented;
+            }
+        auto is_int_nd = [](int dt) { return dt == dnnl_s32 || dt == dnnl_s8 || dt == dnnl_u8; };
+        if (attr.zp(DNNL_ARG_SRC).set && !is_int_nd(s.data_type)) return dnnl_invalid_arguments;
+        if (attr.zp(DNNL_ARG_DST).set && !is_int_nd(d.data_type)) return dnnl_invalid_arguments;
+        if (attr.zp(DNNL_ARG_DST).set && (attr.zp(DNNL_ARG_DST).mask != 0 || attr.zp(DNNL_ARG_DST).dt != dnnl_s32)) return dnnl_unimplemented;
+        if (attr.scale(DNNL_ARG_DST).set && attr.scale(DNNL_ARG_DST).dt != dnnl_f32) return dnnl_unimplemented;
+        const auto &po_nd = attr.post_ops.entries;
+        if (po_nd.size() > 1 || (po_nd.size() == 1 && !(po_nd[0].kind == dnnl_sum && po_nd[0].zero_point == 0))) return dnnl_unimplemented;
+        return dnnl_success;
+    }
     const bool s4 = dt_nbits(s.data_type) == 4, d4 = dt_nbits(d.data_type) == 4;
     if (s4 || d4) {
         // decompressing a 4-bit tensor into f32 / bf16 / f16 with source-side scales and zero-points;
@@ -155,12 +178,20 @@ static dnnl_status_t reorder_quant_execute(const dnnl_primitive_desc *pd, dnnl_s
     r.dst = (char *)to->handle + d.offset0 * dt_nbits(d.data_type) / 8;
     r.src_dt = s.data_type;
     r.dst_dt = d.data_type;
-    // a 1-D tensor is one row; its only dim then is mask bit 1 below
-    const int sh = s.ndims == 1 ? 1 : 0;
-    r.rows = sh ? 1 : s.dims[0];
+    // a 1-D tensor is one row; its only dim then is mask bit 1 below.  More than two dims (dense
+    // row-major, validated at creation): the leading dims fold into the rows, and the only mask
+    // bit that can be set, the last dim's, becomes bit 1 as well.
+    const int sh = s.ndims == 1 ? 1 : s.ndims > 2 ? s.ndims - 2 : 0;
     r.cols = s.dims[s.ndims - 1];
-    r.src_s0 = sh ? 0 : s.strides[0];
-    r.dst_s0 = sh ? 0 : d.strides[0];
+    if (s.ndims > 2) {
+        r.rows = 1;
+        for (int i = 0; i < s.ndims - 1; ++i) r.rows *= s.dims[i];
+        r.src_s0 = r.dst_s0 = r.cols;
+    } else {
+        r.rows = sh ? 1 : s.dims[0];
+        r.src_s0 = sh ? 0 : s.strides[0];
+        r.dst_s0 = sh ? 0 : d.strides[0];
+    }
     r.src_s1 = s.strides[s.ndims - 1];
     r.dst_s1 = d.strides[s.ndims - 1];
     const dnnl_primitive_attr &a = pd->attr;
@@ -176,7 +207,7 @@ static dnnl_status_t reorder_quant_execute(const dnnl_primitive_desc *pd, dnnl_s
         auto it = args.find(e.arg);
         if (it == args.end() || !it->second->handle) return dnnl_invalid_arguments; // runtime argument missing
         const dnnl_memory *m = it->second;
-        const int mask = e.q->mask << sh;
+        const int mask = s.ndims > 2 ? (e.q->mask >> sh) : (e.q->mask << sh);
         o.ptr = (const char *)m->handle + m->md.offset0 * dt_nbits(m->md.data_type) / 8;
         o.dt = m->md.data_type;
         if (o.dt != e.q->dt) return dnnl_invalid_arguments;

@@ -138,3 +138,60 @@ def test_dynamic_quantisation_pipeline(ctx):
     ref = x @ (wei.astype(np.float32) * c.wei_scale.data)
     err = np.abs(got - ref).max() / np.abs(ref).max()
     assert err < 0.02, err
+
+
+# ---- tensors with more than two dims -------------------------------------------------------------
+
+def _nd_md(shape, dtype):
+    from onednn_b200 import api
+    return api.MemoryDesc(tuple(shape), dtype, strides=tuple(int(np.prod(shape[i + 1:])) for i in range(len(shape))))
+
+
+def test_more_than_two_dims_descriptor_host():
+    """Dense row-major tensors of any rank quantised per tensor or per element of the last dim are taken;
+    a mask over a middle dim is not."""
+    import os
+    os.environ["ONEDNN_B200_ALLOW_NO_DEVICE"] = "1"
+    from onednn_b200 import api
+    eng = api.Engine()
+    for mask in (0, 1 << 2):
+        a = api.PrimitiveAttr()
+        a.set_scales(api.ARG_DST, mask, (), dt.F32)
+        pd = api.reorder_primitive_desc(eng, _nd_md((4, 50, 96), dt.F32), eng, _nd_md((4, 50, 96), dt.S8), a)
+        assert pd.impl_info_str() == "cuda:reorder_quant"
+    a = api.PrimitiveAttr()
+    a.set_scales(api.ARG_DST, 1 << 1, (), dt.F32)
+    with pytest.raises(api.Error) as e:
+        api.reorder_primitive_desc(eng, _nd_md((4, 50, 96), dt.F32), eng, _nd_md((4, 50, 96), dt.S8), a)
+    assert e.value.name == "unimplemented"
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("shape,per_channel", [((4, 50, 96), True), ((2, 3, 20, 64), False)])
+def test_cuda_more_than_two_dims(shape, per_channel, ctx):
+    """The same bytes as the 2-D reorder of the tensor folded into (prod(leading dims), last dim)."""
+    from onednn_b200 import api
+    from onednn_b200.workloads import ReorderCase
+    eng, strm = ctx
+    r = np.random.default_rng(131)
+    rows, cols = int(np.prod(shape[:-1])), shape[-1]
+    x = (r.standard_normal((rows, cols)) * 30).astype(np.float32)
+    scale = r.uniform(0.2, 0.9, cols if per_channel else 1).astype(np.float32)
+    folded = ReorderCase("nd", rows, cols, x, dt.F32, dt.U8, dst_scale=Quant(scale, dt.F32, 2 if per_channel else 0),
+                         dst_zp=Quant(np.int32([100]), dt.S32, 0))
+    want = B.run_oracle_reorder(folded)
+    a = api.PrimitiveAttr()
+    a.set_scales(api.ARG_DST, (1 << (len(shape) - 1)) if per_channel else 0, (), dt.F32)
+    a.set_zero_points(api.ARG_DST, 0, (), dt.S32)
+    src_md, dst_md = _nd_md(shape, dt.F32), _nd_md(shape, dt.U8)
+    prim = api.Primitive(api.reorder_primitive_desc(eng, src_md, eng, dst_md, a))
+    src, dst = api.Memory(src_md, eng), api.Memory(dst_md, eng)
+    src.write(x)
+    sc, zp = api.Memory(api.MemoryDesc((scale.size,), dt.F32, api.TAG_A), eng), api.Memory(api.MemoryDesc((1,), dt.S32, api.TAG_A), eng)
+    sc.write(scale)
+    zp.write(np.int32([100]))
+    prim.execute(strm, {api.ARG_FROM: src, api.ARG_TO: dst, api.ARG_ATTR_SCALES | api.ARG_DST: sc,
+                        api.ARG_ATTR_ZERO_POINTS | api.ARG_DST: zp})
+    strm.wait()
+    got = dst.read(np.uint8, (rows, cols))
+    assert np.array_equal(got, want), "%d of %d bytes differ" % (int((got != want).sum()), want.size)
